@@ -1,0 +1,536 @@
+// Host side of b200attn: the extern "C" layer declared in include/b200attn.h, argument validation,
+// kernel selection, per-device workspace and the (batch, head) sharded launcher.
+//
+// The drop-in symbols mirror the reference launchers (final/attention.cu:195-221 and siblings):
+// legacy default stream, blocking, exit(EXIT_FAILURE) on error.  Everything else goes through
+// b200attn_forward_ex, which returns a status code instead.
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/b200attn.h"
+#include "splitd.cuh"
+#include "synth.cuh"
+#include "tc_bf16.cuh"
+
+namespace b200attn {
+
+static thread_local std::string t_last_error;
+static thread_local const char *t_last_path = "";
+static std::atomic<unsigned long long> g_launches{0};
+
+static int fail(int status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    t_last_error = buf;
+    return status;
+}
+#define CU_TRY(expr)                                                                                  \
+    do {                                                                                              \
+        cudaError_t e_ = (expr);                                                                      \
+        if (e_ != cudaSuccess)                                                                        \
+            return fail(B200ATTN_ERR_CUDA, "CUDA error %d (%s) at %s:%d: %s", (int)e_,                \
+                        cudaGetErrorString(e_), __FILE__, __LINE__, #expr);                           \
+    } while (0)
+
+constexpr int kMaxDevices = 64;
+constexpr int kSplitDMaxDs = 272;                      // widest slice whose Q,K,V tiles fit 227 KB
+constexpr size_t kDefaultScratchCap = 1ull << 30;      // two-pass scores scratch per launch chunk
+
+// Per-device state.  Guarded by `mu`: calls for one device are serialised on the host.
+struct DeviceCtx {
+    std::mutex mu;
+    bool ready = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    size_t max_smem_optin = 0;
+    float *S = nullptr;            // scores scratch
+    size_t S_bytes = 0;
+    unsigned *counters = nullptr;  // 2 per head
+    size_t counters_n = 0;
+    unsigned *err_dev = nullptr;
+    unsigned *err_host = nullptr;  // pinned mirror
+    bool scratch_dirty = false;    // a failed fused launch may have left S / counters non-zero
+    bool attr_set[8] = {false, false, false, false, false, false, false, false};
+    void *stage[4] = {nullptr, nullptr, nullptr, nullptr};   // host-buffer entry point: Q,K,V,O staging
+    size_t stage_bytes[4] = {0, 0, 0, 0};
+    cudaStream_t shard_stream = nullptr;
+    TcTables tc_tables;            // positional-encoding tables of the tensor-core path
+};
+static DeviceCtx g_ctx[kMaxDevices];
+
+static int get_ctx(DeviceCtx **out, int *dev_out = nullptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(B200ATTN_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(B200ATTN_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+    DeviceCtx &c = g_ctx[dev];
+    if (!c.ready) {
+        std::lock_guard<std::mutex> lk(c.mu);
+        if (!c.ready) {
+            cudaDeviceProp prop;
+            CU_TRY(cudaGetDeviceProperties(&prop, dev));
+            if (prop.major != 10)
+                return fail(B200ATTN_ERR_NO_DEVICE, "device %d is sm_%d%d; this library runs on sm_100 only", dev,
+                            prop.major, prop.minor);
+            c.sm_count = prop.multiProcessorCount;
+            c.cc_major = prop.major;
+            c.max_smem_optin = prop.sharedMemPerBlockOptin;
+            CU_TRY(cudaMalloc(&c.err_dev, sizeof(unsigned)));
+            CU_TRY(cudaMemset(c.err_dev, 0, sizeof(unsigned)));
+            CU_TRY(cudaHostAlloc(&c.err_host, sizeof(unsigned), cudaHostAllocDefault));
+            *c.err_host = 0;
+            c.ready = true;
+        }
+    }
+    *out = &c;
+    if (dev_out) *dev_out = dev;
+    return B200ATTN_OK;
+}
+
+static int ensure_scratch(DeviceCtx &c, size_t s_bytes, size_t n_counters, cudaStream_t st) {
+    if (s_bytes > c.S_bytes) {
+        if (c.S) CU_TRY(cudaFree(c.S));
+        c.S = nullptr; c.S_bytes = 0;
+        size_t want = s_bytes < (1u << 20) ? (1u << 20) : s_bytes;
+        CU_TRY(cudaMalloc(&c.S, want));
+        CU_TRY(cudaMemsetAsync(c.S, 0, want, st));
+        c.S_bytes = want;
+    }
+    if (n_counters > c.counters_n) {
+        if (c.counters) CU_TRY(cudaFree(c.counters));
+        c.counters = nullptr; c.counters_n = 0;
+        size_t want = n_counters < 4096 ? 4096 : n_counters;
+        CU_TRY(cudaMalloc(&c.counters, want * sizeof(unsigned)));
+        CU_TRY(cudaMemsetAsync(c.counters, 0, want * sizeof(unsigned), st));
+        c.counters_n = want;
+    }
+    if (c.scratch_dirty) {
+        CU_TRY(cudaMemsetAsync(c.S, 0, c.S_bytes, st));
+        CU_TRY(cudaMemsetAsync(c.counters, 0, c.counters_n * sizeof(unsigned), st));
+        CU_TRY(cudaMemsetAsync(c.err_dev, 0, sizeof(unsigned), st));
+        c.scratch_dirty = false;
+    }
+    return B200ATTN_OK;
+}
+
+static size_t fused_smem_bytes(int ds) {
+    return ((size_t)3 * SD_TILE * (ds + 4) + (size_t)SD_TILE * SD_PT_PITCH + ds / 2 + 4) * sizeof(float);
+}
+
+template <typename Kern>
+static int set_smem_attr(DeviceCtx &c, int slot, Kern kern) {
+    if (!c.attr_set[slot]) {
+        CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.max_smem_optin));
+        c.attr_set[slot] = true;
+    }
+    return B200ATTN_OK;
+}
+
+static unsigned spin_limit_from_env() {
+    static unsigned v = [] {
+        const char *s = getenv("B200ATTN_SPIN_LIMIT");
+        long x = s ? atol(s) : 0;
+        return (unsigned)(x > 0 ? x : (1 << 21));
+    }();
+    return v;
+}
+static int ctas_per_sm_from_env() {
+    static int v = [] {
+        const char *s = getenv("B200ATTN_SPLITD_CTAS_PER_SM");
+        int x = s ? atoi(s) : 0;
+        return x > 0 ? x : 1;
+    }();
+    return v;
+}
+
+// ---- split-head_d path --------------------------------------------------------------------------
+template <typename T>
+static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, cudaStream_t st) {
+    const long long BH = (long long)a.batch_sz * a.num_heads;
+    const int Lq = a.len_q, Lk = a.len_k, D = a.head_d;
+    SplitDParams p{};
+    p.Q = a.Q; p.K = a.K; p.V = a.V; p.O = a.out;
+    p.BH = BH; p.Lq = Lq; p.Lk = Lk; p.D = D;
+    p.pe = a.pe; p.rotary_dim = rd; p.rope_base = base;
+    p.scale = 1.0f / sqrtf((float)D);
+    p.cos_cache = a.cos_cache; p.sin_cache = a.sin_cache;
+    p.err = c.err_dev;
+    p.spin_limit = spin_limit_from_env();
+    const bool aligned16 = ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V) & 15) == 0);
+    p.use_tma = (sizeof(T) == 4 && a.pe == B200ATTN_PE_NONE && D % 4 == 0 && aligned16) ? 1 : 0;
+    if (getenv("B200ATTN_NO_TMA")) p.use_tma = 0;
+
+    // -- fused cooperative launch: whole heads co-resident, one CTA per slice --
+    bool fused = !(a.flags & B200ATTN_FLAG_FORCE_TWO_PASS) && Lq <= SD_TILE && Lk <= SD_TILE;
+    int ds = 0, nsplit = 0;
+    size_t smem = 0;
+    if (fused) {
+        const long long target = (long long)c.sm_count * ctas_per_sm_from_env();
+        long long nsplit_max = target / BH;
+        if (nsplit_max < 1) fused = false;
+        else {
+            ds = (int)((D + nsplit_max - 1) / nsplit_max);
+            ds = (ds + 7) & ~7;
+            if (ds < 8) ds = 8;
+            if (ds > kSplitDMaxDs) fused = false;
+            nsplit = (D + ds - 1) / ds;
+            smem = fused_smem_bytes(ds);
+            if (smem > c.max_smem_optin) fused = false;
+        }
+    }
+    if (fused) {
+        int rc = set_smem_attr(c, sizeof(T) == 4 ? 0 : 1, splitd_fused_kernel<T>);
+        if (rc) return rc;
+        int per_sm = 0;
+        CU_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, splitd_fused_kernel<T>, SD_THREADS, smem));
+        if ((long long)per_sm * c.sm_count < (long long)nsplit * BH || BH > 65535) fused = false;
+    }
+    if (fused) {
+        int rc = ensure_scratch(c, (size_t)BH * Lq * Lk * sizeof(float), (size_t)2 * BH, st);
+        if (rc) return rc;
+        p.S = c.S; p.counters = c.counters; p.ds = ds; p.nsplit = nsplit;
+        dim3 grid(nsplit, (unsigned)BH);
+        void *kargs[] = {&p};
+        CU_TRY(cudaLaunchCooperativeKernel((const void *)splitd_fused_kernel<T>, grid, dim3(SD_THREADS), kargs, smem, st));
+        g_launches.fetch_add(1);
+        t_last_path = "splitd_fused";
+        return B200ATTN_OK;
+    }
+
+    // -- two launches per chunk of heads: scores, then softmax + PV --
+    ds = D <= 128 ? ((D + 7) & ~7) : 128;
+    nsplit = (D + ds - 1) / ds;
+    const int dv = D < 64 ? ((D + 7) & ~7) : 64;
+    const int nqt = (Lq + SD_TILE - 1) / SD_TILE, nkt = (Lk + SD_TILE - 1) / SD_TILE;
+    if ((long long)nqt * nkt > 65535) return fail(B200ATTN_ERR_TOO_LARGE, "len_q x len_k = %d x %d exceeds the split-head_d path's tiling limit", Lq, Lk);
+    const size_t per_head = (size_t)Lq * Lk * sizeof(float);
+    size_t cap = kDefaultScratchCap;
+    if (per_head > cap) cap = per_head;
+    long long chunk = (long long)(cap / per_head);
+    if (chunk > BH) chunk = BH;
+    if (chunk > 65535) chunk = 65535;
+    int rc = ensure_scratch(c, (size_t)chunk * per_head, 0, st);
+    if (rc) return rc;
+    rc = set_smem_attr(c, sizeof(T) == 4 ? 2 : 3, splitd_scores_kernel<T>);
+    if (rc) return rc;
+    rc = set_smem_attr(c, sizeof(T) == 4 ? 4 : 5, splitd_softmax_pv_kernel<T>);
+    if (rc) return rc;
+    const size_t smem1 = ((size_t)2 * SD_TILE * (ds + 4) + ds / 2 + 4) * sizeof(float);
+    const size_t smem2 = ((size_t)SD_TILE * (dv + 4) + (size_t)SD_TILE * SD_PT_PITCH + 2 * SD_TILE) * sizeof(float);
+    const size_t esz = sizeof(T);
+    for (long long bh0 = 0; bh0 < BH; bh0 += chunk) {
+        const long long n = (BH - bh0 < chunk) ? (BH - bh0) : chunk;
+        SplitDParams q = p;
+        q.Q = (const char *)a.Q + (size_t)bh0 * Lq * D * esz;
+        q.K = (const char *)a.K + (size_t)bh0 * Lk * D * esz;
+        q.V = (const char *)a.V + (size_t)bh0 * Lk * D * esz;
+        q.O = (char *)a.out + (size_t)bh0 * Lq * D * esz;
+        q.BH = n; q.S = c.S; q.ds = ds; q.nsplit = nsplit; q.dv = dv; q.use_tma = 0;
+        splitd_scores_kernel<T><<<dim3(nsplit, nqt * nkt, (unsigned)n), SD_THREADS, smem1, st>>>(q);
+        CU_TRY(cudaGetLastError());
+        splitd_softmax_pv_kernel<T><<<dim3((D + dv - 1) / dv, nqt, (unsigned)n), SD_THREADS, smem2, st>>>(q);
+        CU_TRY(cudaGetLastError());
+        g_launches.fetch_add(2);
+        // the scratch must be all-zero again for the fused kernel
+        CU_TRY(cudaMemsetAsync(c.S, 0, (size_t)n * per_head, st));
+    }
+    t_last_path = "splitd_two_pass";
+    return B200ATTN_OK;
+}
+
+// ---- validation + dispatch ----------------------------------------------------------------------
+static int validate(const b200attn_args *a, int *rd_out, float *base_out) {
+    if (a == nullptr) return fail(B200ATTN_ERR_INVALID_ARG, "args is NULL");
+    if (a->struct_size != sizeof(b200attn_args))
+        return fail(B200ATTN_ERR_INVALID_ARG, "args->struct_size is %zu, expected %zu", a->struct_size, sizeof(b200attn_args));
+    if (!a->Q || !a->K || !a->V || !a->out) return fail(B200ATTN_ERR_INVALID_ARG, "Q, K, V and out must be non-NULL");
+    if (a->batch_sz <= 0 || a->num_heads <= 0 || a->len_q <= 0 || a->len_k <= 0 || a->head_d <= 0)
+        return fail(B200ATTN_ERR_INVALID_ARG, "batch_sz, num_heads, len_q, len_k, head_d must be positive (got %d,%d,%d,%d,%d)",
+                    a->batch_sz, a->num_heads, a->len_q, a->len_k, a->head_d);
+    if (a->dtype != B200ATTN_F32 && a->dtype != B200ATTN_BF16) return fail(B200ATTN_ERR_INVALID_ARG, "unknown dtype %d", a->dtype);
+    if (a->pe < B200ATTN_PE_NONE || a->pe > B200ATTN_PE_ROPE_Q_ONLY) return fail(B200ATTN_ERR_INVALID_ARG, "unknown pe kind %d", a->pe);
+    const size_t esz = a->dtype == B200ATTN_F32 ? 4 : 2;
+    if (((uintptr_t)a->Q | (uintptr_t)a->K | (uintptr_t)a->V | (uintptr_t)a->out) & (esz - 1))
+        return fail(B200ATTN_ERR_INVALID_ARG, "tensor pointers must be aligned to the element size");
+    if (a->out == a->Q || a->out == a->K || a->out == a->V) return fail(B200ATTN_ERR_INVALID_ARG, "out must not alias an input");
+    int rd = a->rotary_dim == 0 ? a->head_d : a->rotary_dim;
+    const bool rope = a->pe == B200ATTN_PE_ROPE_INTERLEAVED || a->pe == B200ATTN_PE_ROPE_HALF || a->pe == B200ATTN_PE_ROPE_Q_ONLY;
+    if (rope) {
+        if (rd < 0 || rd > a->head_d || (rd & 1))
+            return fail(B200ATTN_ERR_INVALID_ARG, "rotary_dim must be even and within [0, head_d] (got %d, head_d %d)", rd, a->head_d);
+        if ((a->cos_cache == nullptr) != (a->sin_cache == nullptr))
+            return fail(B200ATTN_ERR_INVALID_ARG, "cos_cache and sin_cache must be given together");
+    } else {
+        rd = a->head_d;
+    }
+    float base = a->rope_base == 0.0f ? 10000.0f : a->rope_base;
+    if (!(base > 0.0f)) return fail(B200ATTN_ERR_INVALID_ARG, "rope_base must be positive");
+    *rd_out = rd; *base_out = base;
+    return B200ATTN_OK;
+}
+
+static int check_kernel_errors(DeviceCtx &c, cudaStream_t st, bool sync) {
+    // asynchronous calls do not read the error word back (it would put a copy between launches);
+    // it is sticky on the device and is reported by the next synchronous call
+    if (!sync) return B200ATTN_OK;
+    CU_TRY(cudaMemcpyAsync(c.err_host, c.err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    if (*c.err_host != 0) {
+        unsigned bits = *c.err_host;
+        c.scratch_dirty = true;
+        *c.err_host = 0;
+        return fail(B200ATTN_ERR_KERNEL, "kernel reported error bits 0x%x (1: head barrier wait expired, 2: mbarrier wait expired, 4: tensor memory)", bits);
+    }
+    return B200ATTN_OK;
+}
+
+static int forward_device(const b200attn_args *a) {
+    int rd; float base;
+    int rc = validate(a, &rd, &base);
+    if (rc) return rc;
+    DeviceCtx *c;
+    rc = get_ctx(&c);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lk(c->mu);
+    cudaStream_t st = (cudaStream_t)a->stream;
+    // an error left by an earlier asynchronous call is reported now
+    if (*c->err_host != 0) {
+        unsigned bits = *c->err_host;
+        *c->err_host = 0;
+        c->scratch_dirty = true;
+        return fail(B200ATTN_ERR_KERNEL, "an earlier asynchronous call reported kernel error bits 0x%x", bits);
+    }
+    bool done = false;
+    if (a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC) && tc_bf16_supported(*a, rd)) {
+        rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
+        else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
+    }
+    if (!done) {
+        rc = (a->dtype == B200ATTN_F32) ? run_splitd<float>(*c, *a, rd, base, st) : run_splitd<__nv_bfloat16>(*c, *a, rd, base, st);
+        if (rc) return rc;
+    }
+    return check_kernel_errors(*c, st, !(a->flags & B200ATTN_FLAG_ASYNC));
+}
+
+static int ensure_stage(DeviceCtx &c, int i, size_t bytes) {
+    if (bytes > c.stage_bytes[i]) {
+        if (c.stage[i]) CU_TRY(cudaFree(c.stage[i]));
+        c.stage[i] = nullptr; c.stage_bytes[i] = 0;
+        CU_TRY(cudaMalloc(&c.stage[i], bytes));
+        c.stage_bytes[i] = bytes;
+    }
+    return B200ATTN_OK;
+}
+
+static void legacy(const void *Q, const void *K, const void *V, void *out, int B, int H, int Lq, int Lk, int D, int dtype,
+                   int pe, int rd, const float *cc, const float *sc) {
+    b200attn_args a{};
+    a.struct_size = sizeof a;
+    a.Q = Q; a.K = K; a.V = V; a.out = out;
+    a.batch_sz = B; a.num_heads = H; a.len_q = Lq; a.len_k = Lk; a.head_d = D;
+    a.dtype = dtype; a.pe = pe; a.rotary_dim = rd; a.cos_cache = cc; a.sin_cache = sc;
+    int rc = forward_device(&a);
+    if (rc == B200ATTN_OK) {
+        // the reference launchers end with cudaDeviceSynchronize (final/attention.cu:220)
+        cudaError_t e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) rc = fail(B200ATTN_ERR_CUDA, "CUDA error %d (%s) at %s:%d", (int)e, cudaGetErrorString(e), __FILE__, __LINE__);
+    }
+    if (rc != B200ATTN_OK) {
+        fprintf(stderr, "b200attn: %s\n", t_last_error.c_str());
+        exit(EXIT_FAILURE);
+    }
+}
+
+}  // namespace b200attn
+
+using namespace b200attn;
+
+extern "C" {
+
+void attention_forward_optimized(const float *Q, const float *K, const float *V, float *out, int B, int H, int Lq, int Lk, int D) {
+    legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_F32, B200ATTN_PE_NONE, 0, nullptr, nullptr);
+}
+void attention_forward_bf16(const void *Q, const void *K, const void *V, void *out, int B, int H, int Lq, int Lk, int D) {
+    legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_BF16, B200ATTN_PE_NONE, 0, nullptr, nullptr);
+}
+void attention_forward_rope_fused_v2(const float *Q, const float *K, const float *V, float *out, int B, int H, int Lq, int Lk, int D) {
+    legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_F32, B200ATTN_PE_ROPE_INTERLEAVED, D, nullptr, nullptr);
+}
+void attention_forward_rope_fused(const float *Q, const float *K, const float *V, float *out, const float *cos_cache,
+                                  const float *sin_cache, int B, int H, int Lq, int Lk, int D) {
+    if (!cos_cache || !sin_cache) {
+        fprintf(stderr, "b200attn: attention_forward_rope_fused needs cos_cache and sin_cache\n");
+        exit(EXIT_FAILURE);
+    }
+    legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_F32, B200ATTN_PE_ROPE_INTERLEAVED, D, cos_cache, sin_cache);
+}
+void attention_forward_rope_fused_v7_hybrid(const float *Q, const float *Kr, const float *V, float *out, int B, int H, int Lq,
+                                            int Lk, int D, int rotary_dim) {
+    legacy(Q, Kr, V, out, B, H, Lq, Lk, D, B200ATTN_F32, B200ATTN_PE_ROPE_Q_ONLY, rotary_dim, nullptr, nullptr);
+}
+void attention_forward_rope_bf16(const void *Q, const void *K, const void *V, void *out, int B, int H, int Lq, int Lk, int D) {
+    legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_BF16, B200ATTN_PE_ROPE_INTERLEAVED, D, nullptr, nullptr);
+}
+void attention_forward_rope_bf16_v7(const void *Q, const void *Kr, const void *V, void *out, int B, int H, int Lq, int Lk, int D,
+                                    int rotary_dim) {
+    legacy(Q, Kr, V, out, B, H, Lq, Lk, D, B200ATTN_BF16, B200ATTN_PE_ROPE_Q_ONLY, rotary_dim, nullptr, nullptr);
+}
+void attention_forward_sinusoidal_fused(const float *Q, const float *K, const float *V, float *out, int B, int H, int Lq, int Lk, int D) {
+    legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_F32, B200ATTN_PE_SINUSOIDAL, 0, nullptr, nullptr);
+}
+void attention_forward_sinusoidal_bf16(const void *Q, const void *K, const void *V, void *out, int B, int H, int Lq, int Lk, int D) {
+    legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_BF16, B200ATTN_PE_SINUSOIDAL, 0, nullptr, nullptr);
+}
+
+int b200attn_forward_ex(const b200attn_args *args) { return forward_device(args); }
+
+int b200attn_forward_many(const b200attn_args *args, int n) {
+    if (args == nullptr || n < 0) return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_many: NULL args or negative n");
+    for (int i = 0; i < n; ++i) {
+        int rc = forward_device(&args[i]);
+        if (rc) return rc;
+    }
+    return B200ATTN_OK;
+}
+
+int b200attn_forward_host(const b200attn_args *h) {
+    int rd; float base;
+    int rc = validate(h, &rd, &base);
+    if (rc) return rc;
+    if (h->cos_cache || h->sin_cache) return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_host takes no cos/sin caches");
+    DeviceCtx *c;
+    rc = get_ctx(&c);
+    if (rc) return rc;
+    const size_t esz = h->dtype == B200ATTN_F32 ? 4 : 2;
+    const size_t bh = (size_t)h->batch_sz * h->num_heads;
+    const size_t nq = bh * h->len_q * h->head_d * esz, nk = bh * h->len_k * h->head_d * esz;
+    b200attn_args d = *h;
+    {
+        std::lock_guard<std::mutex> lk(c->mu);
+        if ((rc = ensure_stage(*c, 0, nq)) || (rc = ensure_stage(*c, 1, nk)) || (rc = ensure_stage(*c, 2, nk)) || (rc = ensure_stage(*c, 3, nq))) return rc;
+        d.Q = c->stage[0]; d.K = c->stage[1]; d.V = c->stage[2]; d.out = c->stage[3];
+    }
+    d.stream = nullptr;
+    d.flags = (h->flags | B200ATTN_FLAG_ASYNC);
+    CU_TRY(cudaMemcpyAsync((void *)d.Q, h->Q, nq, cudaMemcpyHostToDevice, 0));
+    CU_TRY(cudaMemcpyAsync((void *)d.K, h->K, nk, cudaMemcpyHostToDevice, 0));
+    CU_TRY(cudaMemcpyAsync((void *)d.V, h->V, nk, cudaMemcpyHostToDevice, 0));
+    rc = forward_device(&d);
+    if (rc) return rc;
+    CU_TRY(cudaMemcpyAsync(h->out, d.out, nq, cudaMemcpyDeviceToHost, 0));
+    CU_TRY(cudaMemcpyAsync(c->err_host, c->err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, 0));
+    CU_TRY(cudaStreamSynchronize(0));
+    if (*c->err_host != 0) {
+        unsigned bits = *c->err_host;
+        *c->err_host = 0;
+        c->scratch_dirty = true;
+        return fail(B200ATTN_ERR_KERNEL, "kernel reported error bits 0x%x", bits);
+    }
+    return B200ATTN_OK;
+}
+
+void b200attn_shard_ranges(long long total, int n, long long *begin, long long *count) {
+    if (n <= 0) return;
+    const long long q = total / n, r = total % n;
+    long long at = 0;
+    for (int g = 0; g < n; ++g) {
+        count[g] = q + (g < r ? 1 : 0);
+        begin[g] = at;
+        at += count[g];
+    }
+}
+
+int b200attn_forward_sharded(const b200attn_args *proto, int n, const int *devices, const void *const *Q, const void *const *K,
+                             const void *const *V, void *const *out, const int *bh_count) {
+    if (!proto || n <= 0 || !devices || !Q || !K || !V || !out || !bh_count)
+        return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_sharded: NULL argument or n_devices <= 0");
+    int prev = 0;
+    CU_TRY(cudaGetDevice(&prev));
+    int status = B200ATTN_OK;
+    std::vector<cudaStream_t> streams(n, nullptr);
+    // launch everywhere first, wait afterwards
+    for (int g = 0; g < n && status == B200ATTN_OK; ++g) {
+        if (bh_count[g] <= 0) continue;
+        cudaError_t e = cudaSetDevice(devices[g]);
+        if (e != cudaSuccess) { status = fail(B200ATTN_ERR_CUDA, "cudaSetDevice(%d): %s", devices[g], cudaGetErrorString(e)); break; }
+        DeviceCtx *c;
+        if ((status = get_ctx(&c))) break;
+        if (!c->shard_stream) {
+            e = cudaStreamCreateWithFlags(&c->shard_stream, cudaStreamNonBlocking);
+            if (e != cudaSuccess) { status = fail(B200ATTN_ERR_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); break; }
+        }
+        streams[g] = c->shard_stream;
+        b200attn_args a = *proto;
+        a.Q = Q[g]; a.K = K[g]; a.V = V[g]; a.out = out[g];
+        a.batch_sz = 1; a.num_heads = bh_count[g];
+        a.stream = c->shard_stream;
+        a.flags |= B200ATTN_FLAG_ASYNC;
+        status = forward_device(&a);
+    }
+    for (int g = 0; g < n; ++g) {
+        if (!streams[g]) continue;
+        cudaSetDevice(devices[g]);
+        DeviceCtx &c = g_ctx[devices[g]];
+        cudaMemcpyAsync(c.err_host, c.err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, streams[g]);
+        cudaError_t e = cudaStreamSynchronize(streams[g]);
+        if (e != cudaSuccess && status == B200ATTN_OK) status = fail(B200ATTN_ERR_CUDA, "device %d: %s", devices[g], cudaGetErrorString(e));
+        if (c.ready && *c.err_host != 0 && status == B200ATTN_OK) {
+            status = fail(B200ATTN_ERR_KERNEL, "device %d: kernel reported error bits 0x%x", devices[g], *c.err_host);
+            *c.err_host = 0;
+            c.scratch_dirty = true;
+        }
+    }
+    cudaSetDevice(prev);
+    return status;
+}
+
+const char *b200attn_last_error(void) { return t_last_error.c_str(); }
+const char *b200attn_last_path(void) { return t_last_path; }
+unsigned long long b200attn_launch_count(void) { return g_launches.load(); }
+const char *b200attn_version(void) { return "b200attn 0.1 (sm_100a)"; }
+
+void b200attn_release_workspace(void) {
+    int prev = 0;
+    if (cudaGetDevice(&prev) != cudaSuccess) return;
+    for (int dev = 0; dev < kMaxDevices; ++dev) {
+        DeviceCtx &c = g_ctx[dev];
+        if (!c.ready) continue;
+        std::lock_guard<std::mutex> lk(c.mu);
+        cudaSetDevice(dev);
+        cudaDeviceSynchronize();
+        if (c.S) cudaFree(c.S);
+        c.S = nullptr; c.S_bytes = 0;
+        if (c.counters) cudaFree(c.counters);
+        c.counters = nullptr; c.counters_n = 0;
+        for (int i = 0; i < 4; ++i) { if (c.stage[i]) cudaFree(c.stage[i]); c.stage[i] = nullptr; c.stage_bytes[i] = 0; }
+        c.tc_tables.release();
+    }
+    cudaSetDevice(prev);
+}
+
+int b200attn_synth_fill(void *dst, long long n, unsigned long long seed, unsigned long long tensor_id, long long index0,
+                        int dist, int dtype, void *stream) {
+    if (!dst || n < 0 || (dist != 0 && dist != 1) || (dtype != B200ATTN_F32 && dtype != B200ATTN_BF16))
+        return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_synth_fill: bad argument");
+    if (n == 0) return B200ATTN_OK;
+    DeviceCtx *c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    launch_synth_fill(dst, n, seed, tensor_id, index0, dist, dtype, c->sm_count, (cudaStream_t)stream);
+    CU_TRY(cudaGetLastError());
+    g_launches.fetch_add(1);
+    return B200ATTN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,390 @@
+#!/usr/bin/env python3
+"""Benchmark of the attention-forward hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config cfg5] [--impl reference]
+
+One step = one forward pass of the workload, through the library's C ABI.  The default workload is
+the sharded benchmark configuration: bf16 SDPA with the additive sinusoidal encoding fused into
+the Q/K load, B=16 H=32 L=4096 head_d=512, one such problem per GPU (weak scaling; the (batch,
+head) slices are independent, so there is no collective on the data path).  Prints ONE JSON line.
+
+  value      whole-job TFLOP/s (4*B*H*Lq*Lk*D flops per problem) with inputs resident in HBM
+  e2e        the same through b200attn_forward_host with pinned HOST buffers, copies in the timed region
+  roofline   the dominant kernel against the measured peak of MEASURED_PEAKS.json
+  cpu_baseline  the reference project's own CPU attention (oracle/_ref) on a bounded sample, on
+             this box's host cores (rank 0, N=1 only)
+
+`--impl reference` times only that CPU implementation, with all host threads, on bounded samples.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PE = {"none": 0, "rope_half": 2, "sinusoidal": 3}
+CONFIGS = {
+    # name: (dtype, pe, B, H, Lq, Lk, D, dist, bound)
+    "cfg1": ("f32", "none", 1, 4, 64, 64, 2048, "uniform", "hbm"),
+    "cfg2a": ("f32", "none", 1, 4, 64, 64, 512, "uniform", "hbm"),
+    "cfg2b": ("f32", "none", 1, 4, 64, 64, 4096, "uniform", "hbm"),
+    "cfg2c": ("f32", "none", 1, 4, 64, 64, 8192, "uniform", "hbm"),
+    "cfg2d": ("f32", "none", 1, 4, 32, 64, 4096, "uniform", "hbm"),
+    "cfg3": ("bf16", "none", 8, 16, 1024, 1024, 512, "normal", "tensor"),
+    "cfg4": ("bf16", "rope_half", 4, 32, 2048, 2048, 1024, "normal", "tensor"),
+    "cfg5": ("bf16", "sinusoidal", 16, 32, 4096, 4096, 512, "normal", "tensor"),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (null until a capture exists for the kernel in use)
+NCU_TRAFFIC_BYTES = {}
+
+
+def flops_of(cfg):
+    _, _, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
+    return 4.0 * B * H * Lq * Lk * D
+
+
+def bytes_of(cfg):
+    dt, _, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
+    return (4 if dt == "f32" else 2) * B * H * D * (2 * Lq + 2 * Lk)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {k: float(d[k]) for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained")}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.split(", ") for r in open(self.f.name).read().strip().splitlines() if r.strip()]
+        os.unlink(self.f.name)
+        sm = sorted(float(r[1]) for r in rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
+        mx = [float(r[2]) for r in rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.strip().lower() == "active":
+                        reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def torch_dtype(torch, dt):
+    return torch.float32 if dt == "f32" else torch.bfloat16
+
+
+def make_inputs(pkg, torch, cfg, dev, seed):
+    dt, _, B, H, Lq, Lk, D, dist, _ = CONFIGS[cfg]
+    td = torch_dtype(torch, dt)
+    Q = torch.empty((B, H, Lq, D), dtype=td, device=dev)
+    K = torch.empty((B, H, Lk, D), dtype=td, device=dev)
+    V = torch.empty((B, H, Lk, D), dtype=td, device=dev)
+    for t, tid in ((Q, 0), (K, 1), (V, 2)):
+        pkg.synth_fill(t, seed, tid, dist)
+    return Q, K, V, torch.empty_like(Q)
+
+
+def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None):
+    """Times `steps` forwards (cycling through `sets` of (Q,K,V,out)) with CUDA events on the
+    stream the kernels are launched on; returns ms per step.  The steps are enqueued by one
+    b200attn_forward_many call so that no interpreter time sits between launches."""
+    n = len(sets)
+    mk = lambda i: pkg.args_for(*sets[i % n][:3], sets[i % n][3], pe=pe, flags=pkg.FLAG_ASYNC)
+    if warmup:
+        pkg.forward_many([mk(i) for i in range(warmup)])
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    batch = [mk(i) for i in range(steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = pkg.launch_count()
+    e0.record()
+    pkg.forward_many(batch)
+    e1.record()
+    torch.cuda.synchronize()
+    time_steps.launches = pkg.launch_count() - n0
+    if barrier:
+        barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def fp32_sweep(pkg, torch, dev, pk):
+    """The fp32 small-sequence configurations: L2-cold (rotation through >= 512 MiB of distinct
+    inputs), L2-warm (one set re-used) and single blocking-call latency, each vs the HBM peak."""
+    out = []
+    for cfg in ("cfg1", "cfg2a", "cfg2b", "cfg2c", "cfg2d"):
+        nbytes = bytes_of(cfg)
+        nsets = max(2, min(256, (512 << 20) // nbytes))
+        sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(nsets)]
+        cold = min(time_steps(pkg, torch, sets, 0, nsets, nsets if r == 0 else 0) for r in range(3))
+        warm = time_steps(pkg, torch, sets[:1], 0, 200, 20)
+        Q, K, V, O = sets[0]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(50):
+            pkg.forward(Q, K, V, out=O)
+        lat = (time.perf_counter() - t0) / 50 * 1e3
+        _, _, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
+        out.append({"config": cfg, "shape": [B, H, Lq, Lk, D], "path": pkg.last_path(), "cold_ms": round(cold, 5),
+                    "warm_ms": round(warm, 5), "blocking_call_ms": round(lat, 5),
+                    "cold_gbs": round(nbytes / cold / 1e6, 1), "cold_tflops": round(flops_of(cfg) / cold / 1e9, 2),
+                    "cold_frac_of_hbm_peak": round(nbytes / cold / 1e6 / pk["hbm_gbs"], 4), "rotation_sets": nsets})
+        del sets
+        torch.cuda.empty_cache()
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the reference project's own CPU attention (oracle/_ref), all host threads
+# ------------------------------------------------------------------------------------------------
+class CpuRef:
+    def __init__(self, cfg):
+        import numpy as np
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        self.np, self.ol = np, ol
+        self.cfg = cfg
+        self.kind = "reference" if ol.ref() is not None else "port"
+        self.cores = os.cpu_count() or 1
+        dt, pe, B, H, Lq, Lk, D, dist, _ = CONFIGS[cfg]
+        self.pe, self.Lk, self.D, self.Lq = pe, Lk, D, Lq
+        gen = ol.synth_uniform if dist == "uniform" else ol.synth_normal
+        n = min(self.cores, B * H)
+        self.nslices = n
+        self.K = [gen((1, 1, Lk, D), 42, 1 + 3 * i) for i in range(n)]
+        self.V = [gen((1, 1, Lk, D), 42, 2 + 3 * i) for i in range(n)]
+        self.Qfull = [gen((1, 1, Lq, D), 42, 3 * i) for i in range(n)]
+        if dt == "bf16":
+            rnd = lambda x: ol.from_bf16_bits(ol.to_bf16_bits(x))
+            self.K, self.V, self.Qfull = [rnd(x) for x in self.K], [rnd(x) for x in self.V], [rnd(x) for x in self.Qfull]
+        L = max(Lq, Lk)
+        if pe == "sinusoidal":
+            self.t0, self.t1 = ol.sinusoidal_tables(L, D)
+        elif pe == "rope_half":
+            self.t0, self.t1 = ol.rope_cache(L, D)
+            perm = np.empty(D, dtype=np.int64)   # rotate-half == interleaved under this column order
+            perm[0::2] = np.arange(D // 2)
+            perm[1::2] = np.arange(D // 2) + D // 2
+            self.K = [np.ascontiguousarray(x[..., perm]) for x in self.K]
+            self.Qfull = [np.ascontiguousarray(x[..., perm]) for x in self.Qfull]
+
+    def _one(self, i, rows):
+        np, ol = self.np, self.ol
+        q = np.ascontiguousarray(self.Qfull[i][:, :, :rows])
+        out = np.empty_like(q)
+        f = ol._f
+        ref = ol.ref()
+        if ref is not None:
+            if self.pe == "sinusoidal":
+                ref.ref_attention_sinusoidal_cpu(f(q), f(self.K[i]), f(self.V[i]), f(self.t0), f(self.t1), f(out), 1, 1, rows, self.Lk, self.D)
+            elif self.pe == "rope_half":
+                ref.ref_attention_rope_cpu(f(q), f(self.K[i]), f(self.V[i]), f(out), f(self.t0), f(self.t1), 1, 1, rows, self.Lk, self.D)
+            else:
+                ref.ref_attention_cpu(f(q), f(self.K[i]), f(self.V[i]), f(out), 1, 1, rows, self.Lk, self.D)
+        else:
+            pe = {"none": ol.PE_NONE, "sinusoidal": ol.PE_SINUSOIDAL, "rope_half": ol.PE_ROPE_INTERLEAVED}[self.pe]
+            ol.oracle().oracle_attention_pe_f32(f(q), f(self.K[i]), f(self.V[i]), f(out), 1, 1, rows, self.Lk, self.D, pe, self.D, 10000.0, 0, 1)
+
+    def run(self, rows):
+        """One sample: every host thread evaluates `rows` query rows of its own (b,h) slice.
+        Returns (seconds, flops)."""
+        th = [threading.Thread(target=self._one, args=(i, rows)) for i in range(self.nslices)]
+        t0 = time.perf_counter()
+        for t in th:
+            t.start()
+        for t in th:
+            t.join()
+        return time.perf_counter() - t0, 4.0 * self.nslices * rows * self.Lk * self.D
+
+    def calibrate(self, target_s):
+        rows = min(self.Lq, 4)
+        sec, _ = self.run(rows)
+        rows = int(max(1, min(self.Lq, rows * target_s / max(sec, 1e-4))))
+        return rows
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = args.config
+    cpu = CpuRef(cfg)
+    total = args.steps + args.warmup
+    rows = cpu.calibrate(min(6.0, 150.0 / max(total, 1)))
+    for _ in range(args.warmup):
+        cpu.run(rows)
+    secs, fl = 0.0, 0.0
+    for _ in range(args.steps):
+        s, f = cpu.run(rows)
+        secs += s
+        fl += f
+    v = fl / secs / 1e12
+    dt, pe, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
+    sample = f"{cpu.nslices} (b,h) slices x {rows} of {Lq} query rows x all {Lk} keys per step, one slice per host thread"
+    line = {"impl": "reference", "metric": "attn_fwd_tflops", "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / max(args.steps, 1) * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(cfg),
+            "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cpu.nslices, "kind": cpu.kind, "sample": sample},
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(cfg):
+    dt, pe, B, H, Lq, Lk, D, dist, bound = CONFIGS[cfg]
+    return {"workload": f"{cfg}: {dt} SDPA forward, pe={pe}, B={B} H={H} Lq={Lq} Lk={Lk} head_d={D} per GPU, non-causal",
+            "inputs": f"iid {dist} from a counter-based generator", "l2": "inputs larger than L2 (126 MB)" if bytes_of(cfg) > (200 << 20)
+            else "rotation through >= 512 MiB of distinct input sets", "parallelism": "one problem per GPU, sharded by (batch, head), no collective"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="cfg5", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the fp32 sweep, e2e and CPU baseline legs")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    pkg.lib()   # fails loudly when the CUDA library is missing: there is no fallback
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    cfg = args.config
+    dt, pe_name, B, H, Lq, Lk, D, _, bound = CONFIGS[cfg]
+    pe = PE[pe_name]
+    pk, pk_src = peaks()
+    nbytes, fl = bytes_of(cfg), flops_of(cfg)
+    nsets = 1 if nbytes > (200 << 20) else max(2, min(256, (512 << 20) // nbytes))
+    sets = [make_inputs(pkg, torch, cfg, dev, 42 + 1000 * rank + i) for i in range(nsets)]
+    warm = max(args.warmup, 3)
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = time_steps(pkg, torch, sets, pe, args.steps, warm, barrier)
+    launches = time_steps.launches
+    clocks = sampler.stop() if sampler else None
+    path = pkg.last_path()
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = fl * world / (ms_max * 1e-3) / 1e12
+
+    line = {"metric": "attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
+            "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": workload_config(cfg), "kernel_path": path, "hbm_gbs_algorithmic": nbytes * world / (ms_max * 1e-3) / 1e9,
+            "gpu_launches": int(launches)}
+    launches_per_step = max(1, round(launches / max(args.steps, 1)))
+    if bound == "tensor":
+        peak = pk["bf16_tflops_sustained"]
+        ach = fl / (ms * 1e-3) / 1e12
+        line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                            "traffic": NCU_TRAFFIC_BYTES.get((cfg, path)), "peak_source": pk_src + " (sustained cuBLAS bf16)",
+                            "kernel": path, "launches_per_step": launches_per_step}
+    else:
+        peak = pk["hbm_gbs"]
+        ach = nbytes / (ms * 1e-3) / 1e9
+        line["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                            "traffic": NCU_TRAFFIC_BYTES.get((cfg, path)), "peak_source": pk_src + " (device copy)",
+                            "kernel": path, "launches_per_step": launches_per_step}
+    if clocks:
+        line["clocks"] = clocks
+
+    # ---- end to end through the host-buffer entry point (pinned host memory, copies timed) ----
+    if not args.no_extras:
+        Q, K, V, O = sets[0]
+        hq, hk, hv = (torch.empty(x.shape, dtype=x.dtype).pin_memory() for x in (Q, K, V))
+        ho = torch.empty(O.shape, dtype=O.dtype).pin_memory()
+        hq.copy_(Q); hk.copy_(K); hv.copy_(V)
+        del sets, Q, K, V, O
+        torch.cuda.empty_cache()
+        e2e_steps = max(1, min(args.steps, 3 if nbytes > (1 << 30) else 20))
+        pkg.forward_host(hq, hk, hv, ho, pe=pe)
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            pkg.forward_host(hq, hk, hv, ho, pe=pe)
+            _ = float(ho.view(-1)[0])   # the result is read on the host every step
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        esz = 4 if dt == "f32" else 2
+        line["e2e"] = {"value": fl * world / (float(t.item()) * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": float(t.item()),
+                       "steps": e2e_steps, "h2d_bytes_per_step": esz * B * H * D * (Lq + 2 * Lk), "d2h_bytes_per_step": esz * B * H * D * Lq,
+                       "api": "b200attn_forward_host (pinned host buffers)"}
+        del hq, hk, hv, ho
+        pkg.lib().b200attn_release_workspace()
+        torch.cuda.empty_cache()
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        line["fp32_configs"] = fp32_sweep(pkg, torch, dev, pk)
+        cpu = CpuRef(cfg)
+        rows = cpu.calibrate(15.0)
+        sec, cfl = cpu.run(rows)
+        line["cpu_baseline"] = {"value": cfl / sec / 1e12, "unit": "TFLOP/s", "cores": cpu.nslices, "kind": cpu.kind, "seconds": round(sec, 2),
+                                "sample": f"{cpu.nslices} (b,h) slices x {rows} of {Lq} query rows x all {Lk} keys, one slice per host thread"}
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

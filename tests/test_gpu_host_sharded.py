@@ -1,0 +1,77 @@
+"""GPU tests of the host-buffer entry point, the (batch, head) sharded launcher and the device
+input generator, all through the C ABI."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+from gpu_util import to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def test_forward_host_pageable_and_pinned(pkg, cuda):
+    import torch
+    B, H, L, D = 1, 4, 64, 2048
+    Q, K, V = ol.make_qkv(B, H, L, L, D, 71, "uniform")
+    want = ol.attention(Q, K, V, pe=ol.PE_SINUSOIDAL)
+    out = np.empty_like(Q)
+    pkg.forward_host(torch.from_numpy(Q), torch.from_numpy(K), torch.from_numpy(V), torch.from_numpy(out), pe=pkg.PE_SINUSOIDAL)
+    assert ol.compare(out, want)["ok"]
+    qp, kp, vp = (torch.from_numpy(x).pin_memory() for x in (Q, K, V))
+    op = torch.empty_like(qp).pin_memory()
+    pkg.forward_host(qp, kp, vp, op, pe=pkg.PE_SINUSOIDAL)
+    assert ol.compare(op.numpy(), want)["ok"]
+
+
+def test_sharded_launcher_equals_single_call(pkg, cuda):
+    """Two shards placed on the devices that exist (both on device 0 when there is one GPU): the
+    launcher needs no collective because (b,h) slices are contiguous slabs."""
+    import torch
+    B, H, L, D = 2, 3, 48, 256
+    Q, K, V = ol.make_qkv(B, H, L, L, D, 72, "uniform")
+    want = ol.attention(Q, K, V, pe=ol.PE_ROPE_HALF)
+    ndev = min(2, torch.cuda.device_count())
+    devices = [g % ndev for g in range(2)]
+    begin, count = pkg.shard_ranges(B * H, 2)
+    flat = lambda x: x.reshape(B * H, L, D)
+    parts = []
+    for g in range(2):
+        d = torch.device(f"cuda:{devices[g]}")
+        sl = slice(begin[g], begin[g] + count[g])
+        parts.append(tuple(to_dev(flat(x)[sl], d) for x in (Q, K, V)) + (torch.empty(count[g], L, D, device=d),))
+    arr = lambda i: (C.c_void_p * 2)(*[parts[g][i].data_ptr() for g in range(2)])
+    proto = pkg.make_args(None, None, None, None, 0, 0, L, L, D, pkg.F32, pe=pkg.PE_ROPE_HALF)
+    rc = pkg.lib().b200attn_forward_sharded(C.byref(proto), 2, (C.c_int * 2)(*devices), arr(0), arr(1), arr(2), arr(3),
+                                            (C.c_int * 2)(*count))
+    pkg.check(rc)
+    got = np.concatenate([parts[g][3].cpu().numpy() for g in range(2)]).reshape(B, H, L, D)
+    assert ol.compare(got, want)["ok"]
+    # a failing device ordinal is reported as a status, not a crash
+    rc = pkg.lib().b200attn_forward_sharded(C.byref(proto), 1, (C.c_int * 1)(63), arr(0), arr(1), arr(2), arr(3), (C.c_int * 1)(1))
+    assert rc != 0 and len(pkg.lib().b200attn_last_error()) > 0
+    torch.cuda.set_device(0)
+
+
+def test_device_generator_matches_host_generator(pkg, cuda):
+    import torch
+    n = 1 << 16
+    t = pkg.synth_fill(torch.empty(n, device=cuda), 43, 1, "uniform")
+    assert np.array_equal(t.cpu().numpy(), ol.synth_uniform((n,), 43, 1))
+    g = pkg.synth_fill(torch.empty(n, device=cuda), 44, 2, "normal").cpu().numpy()
+    h = ol.synth_normal((n,), 44, 2)
+    # libm and the device math library may differ in the last place of logf/cosf
+    assert np.abs(g - h).max() < 1e-5
+    b = pkg.synth_fill(torch.empty(n, device=cuda, dtype=torch.bfloat16), 44, 2, "normal")
+    hb = ol.from_bf16_bits(ol.to_bf16_bits(h))
+    gb = b.float().cpu().numpy()
+    assert np.mean(gb != hb) < 1e-3
+
+
+def test_launch_counter_moves(pkg, cuda):
+    import torch
+    q = torch.rand(1, 2, 16, 64, device=cuda)
+    n0 = pkg.launch_count()
+    pkg.forward(q, q.clone(), q.clone())
+    assert pkg.launch_count() > n0
