@@ -61,6 +61,7 @@ struct DeviceCtx {
     unsigned *err_host = nullptr;  // pinned mirror
     bool scratch_dirty = false;    // a failed fused launch may have left S / counters non-zero
     bool attr_set[8] = {false, false, false, false, false, false, false, false};
+    size_t dyn_smem_max[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     void *stage[4] = {nullptr, nullptr, nullptr, nullptr};   // host-buffer entry point: Q,K,V,O staging
     size_t stage_bytes[4] = {0, 0, 0, 0};
     cudaStream_t shard_stream = nullptr;
@@ -130,7 +131,11 @@ static size_t fused_smem_bytes(int ds) {
 template <typename Kern>
 static int set_smem_attr(DeviceCtx &c, int slot, Kern kern) {
     if (!c.attr_set[slot]) {
-        CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.max_smem_optin));
+        // the opt-in limit covers static + dynamic shared memory
+        cudaFuncAttributes fa;
+        CU_TRY(cudaFuncGetAttributes(&fa, kern));
+        c.dyn_smem_max[slot] = c.max_smem_optin - fa.sharedSizeBytes;
+        CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.dyn_smem_max[slot]));
         c.attr_set[slot] = true;
     }
     return B200ATTN_OK;
@@ -189,8 +194,12 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
         }
     }
     if (fused) {
-        int rc = set_smem_attr(c, sizeof(T) == 4 ? 0 : 1, splitd_fused_kernel<T>);
+        const int slot = sizeof(T) == 4 ? 0 : 1;
+        int rc = set_smem_attr(c, slot, splitd_fused_kernel<T>);
         if (rc) return rc;
+        if (smem > c.dyn_smem_max[slot]) fused = false;
+    }
+    if (fused) {
         int per_sm = 0;
         CU_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, splitd_fused_kernel<T>, SD_THREADS, smem));
         if ((long long)per_sm * c.sm_count < (long long)nsplit * BH || BH > 65535) fused = false;
@@ -208,8 +217,17 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
     }
 
     // -- two launches per chunk of heads: scores, then softmax + PV --
+    // column chunks of <= 128; split a tile's chunks over several CTAs only when the grid would
+    // otherwise leave SMs idle (few heads, short sequences, wide heads)
     ds = D <= 128 ? ((D + 7) & ~7) : 128;
-    nsplit = (D + ds - 1) / ds;
+    {
+        const int nchunks = (D + ds - 1) / ds;
+        const long long tiles = (long long)((Lq + SD_TILE - 1) / SD_TILE) * ((Lk + SD_TILE - 1) / SD_TILE) * BH;
+        long long want = (2LL * c.sm_count + tiles - 1) / tiles;
+        nsplit = (int)(want < 1 ? 1 : (want > nchunks ? nchunks : want));
+        const int per = (nchunks + nsplit - 1) / nsplit;
+        nsplit = (nchunks + per - 1) / per;   // no empty CTA
+    }
     const int dv = D < 64 ? ((D + 7) & ~7) : 64;
     const int nqt = (Lq + SD_TILE - 1) / SD_TILE, nkt = (Lk + SD_TILE - 1) / SD_TILE;
     if ((long long)nqt * nkt > 65535) return fail(B200ATTN_ERR_TOO_LARGE, "len_q x len_k = %d x %d exceeds the split-head_d path's tiling limit", Lq, Lk);
@@ -463,7 +481,11 @@ int b200attn_forward_sharded(const b200attn_args *proto, int n, const int *devic
     for (int g = 0; g < n && status == B200ATTN_OK; ++g) {
         if (bh_count[g] <= 0) continue;
         cudaError_t e = cudaSetDevice(devices[g]);
-        if (e != cudaSuccess) { status = fail(B200ATTN_ERR_CUDA, "cudaSetDevice(%d): %s", devices[g], cudaGetErrorString(e)); break; }
+        if (e != cudaSuccess) {
+            status = fail(B200ATTN_ERR_CUDA, "cudaSetDevice(%d): %s", devices[g], cudaGetErrorString(e));
+            (void)cudaGetLastError();   // the failure is reported through the status; do not leave it pending
+            break;
+        }
         DeviceCtx *c;
         if ((status = get_ctx(&c))) break;
         if (!c->shard_stream) {

@@ -397,17 +397,17 @@ __global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const Split
 }
 
 // ------------------------------------------------------------------------------------------------
-// Two-pass path, pass 1: S[bh][i][j] (+)= sum over the slice.  grid (nsplit, nqt*nkt, BH).
+// Two-pass path, pass 1: S[bh][i][j] (+)= sum over this CTA's column chunks.  grid (nsplit, nqt*nkt, BH);
+// a CTA loops over ceil(nchunks/nsplit) chunks of ds columns, so nsplit = 1 needs no atomics.
 // Dynamic shared memory: Qs[64][ds+4] | Ks[64][ds+4] | freq[ds/2].
 // ------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(SD_THREADS) splitd_scores_kernel(const SplitDParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int slice = blockIdx.x;
     const int nkt = (p.Lk + SD_TILE - 1) / SD_TILE;
     const int qt = blockIdx.y / nkt, kt = blockIdx.y % nkt;
     const long long bh = blockIdx.z;
-    const int v0 = slice * p.ds, w = min(p.ds, p.D - v0), pitch = p.ds + 4;
+    const int pitch = p.ds + 4;
     const int i0 = qt * SD_TILE, j0 = kt * SD_TILE;
     const int nq = min(SD_TILE, p.Lq - i0), nk = min(SD_TILE, p.Lk - j0);
     const int rq_pad = nq <= 16 ? 16 : (nq <= 32 ? 32 : 64), rk_pad = nk <= 16 ? 16 : (nk <= 32 ? 32 : 64);
@@ -416,23 +416,32 @@ __global__ void __launch_bounds__(SD_THREADS) splitd_scores_kernel(const SplitDP
     float *freq_s = Ks + SD_TILE * pitch;
     const T *Qg = reinterpret_cast<const T *>(p.Q) + (bh * p.Lq + i0) * p.D;
     const T *Kg = reinterpret_cast<const T *>(p.K) + (bh * p.Lk + j0) * p.D;
-
     const bool need_freq = (p.pe != PE_NONE) && !(p.cos_cache != nullptr && p.pe != PE_SINUSOIDAL);
-    if (need_freq) {
-        fill_freqs(freq_s, v0, w, p.pe == PE_SINUSOIDAL ? 10000.0f : p.rope_base, p.pe == PE_SINUSOIDAL ? p.D : p.rotary_dim);
-        __syncthreads();
-    }
-    load_slice<T>(Qs, pitch, Qg, nq, rq_pad, i0, p.D, v0, w, p.pe, p.rotary_dim, true, freq_s, p.cos_cache, p.sin_cache);
-    load_slice<T>(Ks, pitch, Kg, nk, rk_pad, j0, p.D, v0, w, p.pe, p.rotary_dim, p.pe != PE_ROPE_Q_ONLY, freq_s,
-                  p.cos_cache, p.sin_cache);
-    __syncthreads();
+
     float acc[4][4];
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[r][c] = 0.0f;
-    qk_dispatch(Qs, Ks, pitch, (w + 3) & ~3, nq, nk, acc);
-    emit_scores(p.S + bh * p.Lq * p.Lk, p.Lk, i0, j0, nq, nk, acc, p.nsplit > 1);
+
+    // this CTA sums the column chunks [c0, c1) of width ds; the nsplit CTAs of a tile add up in S
+    const int nchunks = (p.D + p.ds - 1) / p.ds;
+    const int per = (nchunks + p.nsplit - 1) / p.nsplit;
+    const int c0 = blockIdx.x * per, c1 = min(nchunks, c0 + per);
+    for (int ch = c0; ch < c1; ++ch) {
+        const int v0 = ch * p.ds, w = min(p.ds, p.D - v0);
+        if (need_freq) {
+            fill_freqs(freq_s, v0, w, p.pe == PE_SINUSOIDAL ? 10000.0f : p.rope_base, p.pe == PE_SINUSOIDAL ? p.D : p.rotary_dim);
+            __syncthreads();
+        }
+        load_slice<T>(Qs, pitch, Qg, nq, rq_pad, i0, p.D, v0, w, p.pe, p.rotary_dim, true, freq_s, p.cos_cache, p.sin_cache);
+        load_slice<T>(Ks, pitch, Kg, nk, rk_pad, j0, p.D, v0, w, p.pe, p.rotary_dim, p.pe != PE_ROPE_Q_ONLY, freq_s,
+                      p.cos_cache, p.sin_cache);
+        __syncthreads();
+        qk_dispatch(Qs, Ks, pitch, (w + 3) & ~3, nq, nk, acc);
+        __syncthreads();
+    }
+    if (c0 < c1) emit_scores(p.S + bh * p.Lq * p.Lk, p.Lk, i0, j0, nq, nk, acc, p.nsplit > 1);
 }
 
 // ------------------------------------------------------------------------------------------------
