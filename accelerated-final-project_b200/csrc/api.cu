@@ -413,6 +413,22 @@ void attention_forward_sinusoidal_bf16(const void *Q, const void *K, const void 
 
 int b200attn_forward_ex(const b200attn_args *args) { return forward_device(args); }
 
+// Bring-up aid (not part of the public header): runs the tensor-core kernel and also returns the
+// raw scores Q K^T of key block 0, [B*H*(Lq/128)][128][128] fp32, for checking the first MMA stage.
+int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
+    int rd; float base;
+    int rc = validate(a, &rd, &base);
+    if (rc) return rc;
+    DeviceCtx *c;
+    rc = get_ctx(&c);
+    if (rc) return rc;
+    if (!tc_bf16_supported(*a, rd)) return fail(B200ATTN_ERR_INVALID_ARG, "shape not taken by the tensor-core kernel");
+    std::lock_guard<std::mutex> lk(c->mu);
+    rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->sm_count, spin_limit_from_env(), (cudaStream_t)a->stream, &g_launches, scores_dev);
+    if (rc) return fail(rc, "%s", tc_bf16_error());
+    return check_kernel_errors(*c, (cudaStream_t)a->stream, true);
+}
+
 int b200attn_forward_many(const b200attn_args *args, int n) {
     if (args == nullptr || n < 0) return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_many: NULL args or negative n");
     for (int i = 0; i < n; ++i) {

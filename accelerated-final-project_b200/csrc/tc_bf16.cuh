@@ -1,22 +1,589 @@
-// Tensor-core (tcgen05) bf16 forward: placeholder interface while the kernel is brought up.
+// bf16 attention forward on the 5th-generation tensor cores (tcgen05 + tensor memory + TMA).
+//
+// Why a CTA PAIR per query tile.  With head_d = 512 an fp32 output accumulator of 128 query rows
+// fills all 512 columns of an SM's tensor memory, so the score tile S = Q K^T has nowhere to live
+// on the same SM.  The work of one (batch-head, 128-query tile) is therefore split over a cluster
+// of two CTAs that run different programs and execute the same number of tensor-core flops:
+//
+//   rank 0, "score CTA":  Q tile resident in shared memory (K-major, 128-byte swizzle), K streamed
+//       by TMA in [128 keys x 64 columns] chunks, S = Q K^T into tensor memory (4 buffers of 128
+//       columns), softmax warps read S with tcgen05.ld, keep the running max / sum per row in
+//       registers and write P = exp2(scale*log2e*(S - m)) as bf16 straight into the OTHER CTA's
+//       shared memory (distributed shared memory stores), in the swizzled K-major layout the PV
+//       MMA wants.  The positional encoding is applied by transform warps to the Q tile once and
+//       to every K chunk between its TMA arrival and its MMA (no separate pass over global memory).
+//   rank 1, "output CTA": V streamed by TMA in [32 keys x head_d] stages (MN-major operand), the
+//       accumulator O[128 x head_d] fp32 resident in tensor memory, O += P V; correction warps
+//       rescale O only when the score CTA raised a row's reference max (lazy rescaling), and at
+//       the end divide by the row sums and store bf16.
+//
+// All cross-role hand-offs are mbarriers; arrivals that cross the CTA boundary use cluster scope.
+// Every wait is bounded: on expiry the role records KERR_MBAR_TIMEOUT and leaves its loop; all
+// threads of both CTAs always reach the final cluster barrier, so neither CTA exits while its peer
+// may still address its shared memory.
+//
+// Shapes taken here: bf16, head_d % 64 == 0, 64 <= head_d <= 512, len_q % 128 == 0,
+// len_k % 128 == 0, encodings none / sinusoidal / interleaved RoPE (with or without K rotation).
+// Everything else runs on the split-head_d kernels.
 #pragma once
 
 #include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
 
 #include "../../include/b200attn.h"
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace b200attn {
 
-struct TcTables {
-    void release() {}
+constexpr int TC_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 softmax / correction, warps 6-9 transform / relay
+constexpr int TC_BM = 128;        // query rows per tile
+constexpr int TC_BN = 128;        // keys per block
+constexpr int TC_VS = 32;         // keys per V stage
+constexpr int TC_NK = 5;          // K chunk ring depth (score CTA)
+constexpr int TC_NS = 4;          // S buffers in tensor memory (4 x 128 columns)
+constexpr int TC_NP = 2;          // P buffers (output CTA shared memory)
+constexpr int TC_NV = 4;          // V stage ring depth (output CTA)
+constexpr int TC_CHUNK_BYTES = TC_BM * 128;          // [128 rows x 64 bf16]
+constexpr int TC_P_BYTES = TC_BM * TC_BN * 2;        // one P buffer
+constexpr float TC_RESCALE_LOG2 = 8.0f;              // rescale O only when the max grew by > 2^8
+
+struct TcParams {
+    int Lq, Lk, D;
+    int n_qtiles, n_blocks, n_chunks;   // Lq/128, Lk/128, D/64
+    float scale_log2;                   // log2(e) / sqrt(D)
+    int pe, rd;                         // PeKind; rotary_dim
+    int rotate_k;                       // 0 for PE_ROPE_Q_ONLY
+    const float *pe_table;              // sinusoidal: [L][D] fp32; RoPE: [L][rd/2] (cos, sin) pairs
+    __nv_bfloat16 *O;
+    unsigned *err;
+    unsigned spin_limit;
+    float *debug_scores;                // optional: raw S of key block 0, [units][128][128]
 };
 
-inline bool tc_bf16_supported(const b200attn_args &, int) { return false; }
-inline const char *tc_bf16_error() { return ""; }
-inline int tc_bf16_run(const b200attn_args &, int, float, TcTables &, unsigned *, int, unsigned, cudaStream_t,
-                       std::atomic<unsigned long long> *) {
-    return -1;
+struct TcBarriers {
+    uint64_t q_full, q_ready;
+    uint64_t k_full[TC_NK], k_ready[TC_NK], k_empty[TC_NK];
+    uint64_t s_full[TC_NS], s_empty[TC_NS];
+    uint64_t p_empty[TC_NP];    // in the score CTA; arrived by the output CTA's relay warp
+    uint64_t v_full[TC_NV], v_empty[TC_NV];
+    uint64_t p_full[TC_NP];     // in the output CTA; arrived by the score CTA's softmax threads
+    uint64_t pv_done[TC_NP];
+    uint64_t corr_done[TC_NP];
+    uint64_t l_full;
+};
+
+// In-place positional encoding of one [128 rows x 64 columns] bf16 chunk in swizzled shared memory.
+// 128 threads: thread -> 16-byte chunk q = tid % 8 of rows tid/8 + 16*it, so that a warp reads 4
+// full rows of the fp32 table (coalesced) and hits every shared-memory bank group once.
+__device__ __forceinline__ void tc_pe_chunk(unsigned char *tile, int pos0, int d0, const TcParams &p, int tid) {
+    const int q = tid & 7, r0 = tid >> 3;
+    const int d = d0 + q * 8;
+#pragma unroll 2
+    for (int it = 0; it < 8; ++it) {
+        const int r = r0 + 16 * it;
+        const long long pos = pos0 + r;
+        uint4 *ptr = reinterpret_cast<uint4 *>(tile + r * 128 + ((q ^ (r & 7)) << 4));
+        uint4 v = *ptr;
+        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&v);
+        if (p.pe == PE_SINUSOIDAL) {
+            const float4 *tp = reinterpret_cast<const float4 *>(p.pe_table + pos * p.D + d);
+            const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+            float2 x0 = __bfloat1622float2(h[0]), x1 = __bfloat1622float2(h[1]), x2 = __bfloat1622float2(h[2]), x3 = __bfloat1622float2(h[3]);
+            h[0] = __floats2bfloat162_rn(x0.x + t0.x, x0.y + t0.y);
+            h[1] = __floats2bfloat162_rn(x1.x + t0.z, x1.y + t0.w);
+            h[2] = __floats2bfloat162_rn(x2.x + t1.x, x2.y + t1.y);
+            h[3] = __floats2bfloat162_rn(x3.x + t1.z, x3.y + t1.w);
+        } else if (d < p.rd) {   // interleaved RoPE: pairs (2i, 2i+1); rd % 8 == 0 so a chunk is all-in or all-out
+            const float4 *tp = reinterpret_cast<const float4 *>(p.pe_table + (pos * (p.rd >> 1) + (d >> 1)) * 2);
+            const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);   // (c0,s0,c1,s1), (c2,s2,c3,s3)
+            float2 x0 = __bfloat1622float2(h[0]), x1 = __bfloat1622float2(h[1]), x2 = __bfloat1622float2(h[2]), x3 = __bfloat1622float2(h[3]);
+            h[0] = __floats2bfloat162_rn(x0.x * t0.x - x0.y * t0.y, x0.x * t0.y + x0.y * t0.x);
+            h[1] = __floats2bfloat162_rn(x1.x * t0.z - x1.y * t0.w, x1.x * t0.w + x1.y * t0.z);
+            h[2] = __floats2bfloat162_rn(x2.x * t1.x - x2.y * t1.y, x2.x * t1.y + x2.y * t1.x);
+            h[3] = __floats2bfloat162_rn(x3.x * t1.z - x3.y * t1.w, x3.x * t1.w + x3.y * t1.z);
+        }
+        *ptr = v;
+    }
+}
+
+#define TC_FAIL_IF(cond)                                         \
+    if (cond) {                                                  \
+        atomicOr(p.err, (unsigned)KERR_MBAR_TIMEOUT);            \
+        failed = true;                                           \
+        break;                                                   \
+    }
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const TcParams p) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ TcBarriers bars;
+    __shared__ uint32_t tmem_slot;
+    __shared__ unsigned skip_flag;
+
+    // 1024-byte aligned base; identical offset in both CTAs of the cluster (same kernel, same layout)
+    const uint32_t raw_addr = smem_u32(tc_smem_raw);
+    unsigned char *smem = tc_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+
+    const uint32_t rank = cluster_ctarank();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int unit = blockIdx.x >> 1;
+    const int qt = unit % p.n_qtiles;
+    const long long bh = unit / p.n_qtiles;
+    const int D = p.D, nch = p.n_chunks, T = p.n_blocks;
+    const uint32_t lim = p.spin_limit;
+    const bool has_pe = (p.pe != PE_NONE);
+
+    // ---- shared-memory carve-up ----
+    // score CTA : [Q: nch chunks of 16 KB][K ring: TC_NK chunks of 16 KB]
+    // output CTA: [P: TC_NP x 32 KB][V ring: TC_NV stages of TC_VS*D*2 B][alpha: TC_NP x 128 f32][lsum: 128 f32]
+    unsigned char *q_smem = smem;
+    unsigned char *k_smem = smem + (size_t)nch * TC_CHUNK_BYTES;
+    unsigned char *p_smem = smem;
+    unsigned char *v_smem = smem + (size_t)TC_NP * TC_P_BYTES;
+    const int v_stage_bytes = TC_VS * D * 2;
+    float *alpha_smem = reinterpret_cast<float *>(v_smem + (size_t)TC_NV * v_stage_bytes);
+    float *lsum_smem = alpha_smem + TC_NP * TC_BM;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars.q_full, 1);
+        mbar_init(&bars.q_ready, 128);
+        for (int i = 0; i < TC_NK; ++i) { mbar_init(&bars.k_full[i], 1); mbar_init(&bars.k_ready[i], 128); mbar_init(&bars.k_empty[i], 1); }
+        for (int i = 0; i < TC_NS; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 128); }
+        for (int i = 0; i < TC_NV; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
+        for (int i = 0; i < TC_NP; ++i) {
+            mbar_init(&bars.p_empty[i], 1);
+            mbar_init(&bars.p_full[i], 128);
+            mbar_init(&bars.pv_done[i], 1);
+            mbar_init(&bars.corr_done[i], 128);
+        }
+        mbar_init(&bars.l_full, 128);
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    // Once any cluster has reported an error the remaining clusters skip their work.  The score
+    // CTA samples the error word and tells its peer, so that both CTAs take the same decision.
+    cluster_arrive();   // both CTAs are running and have initialised their barriers
+    cluster_wait();
+    if (rank == 0 && threadIdx.x == 0) {
+        const unsigned seen = *reinterpret_cast<volatile unsigned *>(p.err);
+        skip_flag = seen;
+        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_rank(smem_u32(&skip_flag), 1)), "r"(seen) : "memory");
+    }
+    cluster_arrive();
+    cluster_wait();
+
+    bool failed = false;
+    const bool skip = (skip_flag != 0);
+
+    if (skip) {
+        // nothing: fall through to the common exit
+    } else if (rank == 0) {
+        // =============================== score CTA ===============================
+        if (warp == 0) {
+            if (lane == 0) {
+                mbar_expect_tx(&bars.q_full, (uint32_t)nch * TC_CHUNK_BYTES);
+                for (int c = 0; c < nch; ++c)
+                    tma_load_2d(q_smem + (size_t)c * TC_CHUNK_BYTES, &tmQ, c * 64, (int)(bh * p.Lq + qt * TC_BM), &bars.q_full);
+                int it = 0;
+                for (int t = 0; t < T && !failed; ++t)
+                    for (int c = 0; c < nch; ++c, ++it) {
+                        const int s = it % TC_NK;
+                        TC_FAIL_IF(!mbar_wait(&bars.k_empty[s], ((it / TC_NK) & 1) ^ 1, lim));
+                        mbar_expect_tx(&bars.k_full[s], TC_CHUNK_BYTES);
+                        tma_load_2d(k_smem + (size_t)s * TC_CHUNK_BYTES, &tmK, c * 64, (int)(bh * p.Lk + t * TC_BN), &bars.k_full[s]);
+                    }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                const uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN, 0, 0);
+                do {
+                    TC_FAIL_IF(!mbar_wait(has_pe ? &bars.q_ready : &bars.q_full, 0, lim));
+                } while (0);
+                tc_fence_after();
+                int it = 0;
+                for (int t = 0; t < T && !failed; ++t) {
+                    const int sb = t % TC_NS;
+                    TC_FAIL_IF(!mbar_wait(&bars.s_empty[sb], ((t / TC_NS) & 1) ^ 1, lim));
+                    tc_fence_after();
+                    for (int c = 0; c < nch; ++c, ++it) {
+                        const int s = it % TC_NK;
+                        uint64_t *kb = (has_pe && p.rotate_k) ? &bars.k_ready[s] : &bars.k_full[s];
+                        TC_FAIL_IF(!mbar_wait(kb, (it / TC_NK) & 1, lim));
+                        tc_fence_after();
+                        const uint64_t da = umma_desc_k_sw128(smem_u32(q_smem + (size_t)c * TC_CHUNK_BYTES));
+                        const uint64_t db = umma_desc_k_sw128(smem_u32(k_smem + (size_t)s * TC_CHUNK_BYTES));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma_bf16(tmem + sb * TC_BN, da + 2 * k, db + 2 * k, idesc, (c | k) != 0);
+                        umma_commit(&bars.k_empty[s]);
+                    }
+                    if (failed) break;
+                    umma_commit(&bars.s_full[sb]);
+                }
+            }
+        } else if (warp < 6) {
+            // ---- softmax: one thread per query row ----
+            const int row = 32 * (warp & 3) + lane;
+            const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+            const uint32_t p_remote = map_to_rank(smem_u32(p_smem), 1);
+            const uint32_t alpha_remote = map_to_rank(smem_u32(alpha_smem), 1);
+            float m_used = -INFINITY, l = 0.0f;
+            uint32_t r[32];
+            for (int t = 0; t < T; ++t) {
+                const int sb = t % TC_NS, pb = t % TC_NP;
+                TC_FAIL_IF(!mbar_wait(&bars.s_full[sb], (t / TC_NS) & 1, lim));
+                tc_fence_after();
+                const uint32_t ta = lane_addr + sb * TC_BN;
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld32(ta + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+                    if (p.debug_scores != nullptr && t == 0) {
+                        float *dbg = p.debug_scores + ((long long)unit * TC_BM + row) * TC_BN + c * 32;
+                        for (int j = 0; j < 32; ++j) dbg[j] = __uint_as_float(r[j]);
+                    }
+                }
+                float alpha = 1.0f;
+                if (t == 0) {
+                    m_used = mx;
+                } else if ((mx - m_used) * p.scale_log2 > TC_RESCALE_LOG2) {
+                    alpha = fast_exp2((m_used - mx) * p.scale_log2);
+                    l *= alpha;
+                    m_used = mx;
+                }
+                TC_FAIL_IF(!mbar_wait_cluster(&bars.p_empty[pb], ((t / TC_NP) & 1) ^ 1, lim));
+                const float msl = m_used * p.scale_log2;
+                const uint32_t prow = p_remote + pb * TC_P_BYTES + row * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld32(ta + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        float e[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            e[j] = fast_exp2(fmaf(__uint_as_float(r[8 * g + j]), p.scale_log2, -msl));
+                            l += e[j];
+                        }
+                        const int q16 = c * 4 + g;   // 16-byte chunk index within the 128-key row
+                        const uint32_t addr = prow + (q16 >> 3) * (TC_BM * 128) + (((q16 & 7) ^ (row & 7)) << 4);
+                        st_cluster_v4(addr, pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&bars.s_empty[sb]);
+                st_cluster_f32(alpha_remote + (pb * TC_BM + row) * 4, alpha);
+                fence_proxy_async();
+                mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[pb]), 1));
+            }
+            // row sums for the epilogue (sent even after a failure so that the peer is not left waiting)
+            st_cluster_f32(map_to_rank(smem_u32(lsum_smem), 1) + row * 4, l);
+            mbar_arrive_cluster(map_to_rank(smem_u32(&bars.l_full), 1));
+        } else if (has_pe) {
+            // ---- transform warps: positional encoding of Q once and of every K chunk ----
+            const int tid = threadIdx.x - 6 * 32;
+            do {
+                TC_FAIL_IF(!mbar_wait(&bars.q_full, 0, lim));
+                for (int c = 0; c < nch; ++c) tc_pe_chunk(q_smem + (size_t)c * TC_CHUNK_BYTES, qt * TC_BM, c * 64, p, tid);
+                fence_proxy_async();
+                mbar_arrive(&bars.q_ready);
+            } while (0);
+            if (p.rotate_k) {
+                int it = 0;
+                for (int t = 0; t < T && !failed; ++t)
+                    for (int c = 0; c < nch; ++c, ++it) {
+                        const int s = it % TC_NK;
+                        TC_FAIL_IF(!mbar_wait(&bars.k_full[s], (it / TC_NK) & 1, lim));
+                        tc_pe_chunk(k_smem + (size_t)s * TC_CHUNK_BYTES, t * TC_BN, c * 64, p, tid);
+                        fence_proxy_async();
+                        mbar_arrive(&bars.k_ready[s]);
+                    }
+            }
+        }
+    } else {
+        // =============================== output CTA ===============================
+        if (warp == 0) {
+            if (lane == 0) {
+                int it = 0;
+                for (int t = 0; t < T && !failed; ++t)
+                    for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
+                        const int s = it % TC_NV;
+                        TC_FAIL_IF(!mbar_wait(&bars.v_empty[s], ((it / TC_NV) & 1) ^ 1, lim));
+                        mbar_expect_tx(&bars.v_full[s], (uint32_t)v_stage_bytes);
+                        for (int g = 0; g < nch; ++g)
+                            tma_load_2d(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TC_VS * 128), &tmV, g * 64,
+                                        (int)(bh * p.Lk + t * TC_BN + vs * TC_VS), &bars.v_full[s]);
+                    }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                int it = 0;
+                for (int t = 0; t < T && !failed; ++t) {
+                    const int pb = t % TC_NP;
+                    TC_FAIL_IF(!mbar_wait_cluster(&bars.p_full[pb], (t / TC_NP) & 1, lim));
+                    TC_FAIL_IF(!mbar_wait(&bars.corr_done[pb], (t / TC_NP) & 1, lim));
+                    tc_fence_after();
+                    for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
+                        const int s = it % TC_NV;
+                        TC_FAIL_IF(!mbar_wait(&bars.v_full[s], (it / TC_NV) & 1, lim));
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 0; kk < TC_VS / 16; ++kk) {
+                            const int kg = vs * (TC_VS / 16) + kk;   // 16-key step within the block, 0..7
+                            const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TC_BM * 128))) + 2 * (kg & 3);
+                            for (int n0 = 0; n0 < D; n0 += 256) {
+                                const int N = min(256, D - n0);
+                                const uint64_t db = umma_desc_mn_sw128(
+                                    smem_u32(v_smem + (size_t)s * v_stage_bytes + (size_t)(n0 >> 6) * (TC_VS * 128) + kk * 2048), TC_VS * 128);
+                                umma_bf16(tmem + n0, da, db, umma_idesc_bf16(TC_BM, N, 0, 1), (t | kg) != 0);
+                            }
+                        }
+                        umma_commit(&bars.v_empty[s]);
+                    }
+                    if (failed) break;
+                    umma_commit(&bars.pv_done[pb]);
+                }
+            }
+        } else if (warp < 6) {
+            // ---- correction + epilogue: one thread per query row ----
+            const int row = 32 * (warp & 3) + lane;
+            const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+            uint32_t r[32];
+            for (int t = 0; t < T; ++t) {
+                const int pb = t % TC_NP;
+                TC_FAIL_IF(!mbar_wait_cluster(&bars.p_full[pb], (t / TC_NP) & 1, lim));
+                const float a = alpha_smem[pb * TC_BM + row];
+                if (t > 0 && __any_sync(0xffffffffu, a != 1.0f)) {
+                    TC_FAIL_IF(!mbar_wait(&bars.pv_done[(t - 1) % TC_NP], ((t - 1) / TC_NP) & 1, lim));
+                    tc_fence_after();
+                    for (int c = 0; c < D / 32; ++c) {
+                        tmem_ld32(lane_addr + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * a);
+                        tmem_st32(lane_addr + c * 32, r);
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                }
+                mbar_arrive(&bars.corr_done[pb]);
+            }
+            do {
+                if (failed) break;
+                TC_FAIL_IF(!mbar_wait(&bars.pv_done[(T - 1) % TC_NP], ((T - 1) / TC_NP) & 1, lim));
+                tc_fence_after();
+                TC_FAIL_IF(!mbar_wait_cluster(&bars.l_full, 0, lim));
+                const float inv = 1.0f / lsum_smem[row];
+                __nv_bfloat16 *orow = p.O + ((bh * p.Lq + qt * TC_BM + row) * (long long)D);
+                for (int c = 0; c < D / 32; ++c) {
+                    tmem_ld32(lane_addr + c * 32, r);
+                    tmem_ld_wait();
+                    uint4 *dst = reinterpret_cast<uint4 *>(orow + c * 32);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 o;
+                        o.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
+                        o.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
+                        o.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
+                        o.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
+                        dst[g] = o;
+                    }
+                }
+            } while (0);
+        } else if (warp == 6) {
+            // ---- relay: "PV of block t finished" -> the score CTA may overwrite that P buffer ----
+            if (lane == 0) {
+                for (int t = 0; t < T; ++t) {
+                    const int pb = t % TC_NP;
+                    TC_FAIL_IF(!mbar_wait(&bars.pv_done[pb], (t / TC_NP) & 1, lim));
+                    mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_empty[pb]), 0));
+                }
+            }
+        }
+    }
+
+    // a role that gave up lets copies and MMAs it may still have in flight drain before the CTA ends
+    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+#undef TC_FAIL_IF
+
+// ---- positional-encoding tables (built on the device with the arithmetic of the reference CPU tables) ----
+__global__ void tc_build_pe_table(float *table, int L, int D, int pe, int rd, float base) {
+    const long long n = (pe == PE_SINUSOIDAL) ? (long long)L * D : (long long)L * (rd >> 1);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        if (pe == PE_SINUSOIDAL) {
+            const int pos = (int)(i / D), d = (int)(i % D);
+            const float freq = 1.0f / powf(10000.0f, (2.0f * (float)(d / 2)) / (float)D);   // final/sinusoidal.cu:848
+            const float ang = (float)pos * freq;
+            table[i] = (d & 1) ? cosf(ang) : sinf(ang);
+        } else {
+            const int pos = (int)(i / (rd >> 1)), pr = (int)(i % (rd >> 1));
+            const float freq = 1.0f / powf(base, (2.0f * (float)pr) / (float)rd);           // final/rope.cu:29
+            const float th = (float)pos * freq;
+            table[2 * i] = cosf(th);
+            table[2 * i + 1] = sinf(th);
+        }
+    }
+}
+
+struct TcTables {
+    struct Entry { int pe, L, D, rd; float base; float *ptr; };
+    static constexpr int kMax = 8;
+    Entry e[kMax];
+    int n = 0;
+    void release() {
+        for (int i = 0; i < n; ++i) cudaFree(e[i].ptr);
+        n = 0;
+    }
+    // Returns a device table for the key, building it on `st` when it is new.
+    float *get(int pe, int L, int D, int rd, float base, cudaStream_t st, std::atomic<unsigned long long> *launches) {
+        const int kind = (pe == PE_SINUSOIDAL) ? PE_SINUSOIDAL : PE_ROPE_INTERLEAVED;
+        for (int i = 0; i < n; ++i)
+            if (e[i].pe == kind && e[i].L >= L && e[i].D == D && e[i].rd == rd && e[i].base == base) return e[i].ptr;
+        if (n == kMax) {   // evict everything once no kernel can still be reading a table
+            cudaDeviceSynchronize();
+            release();
+        }
+        const size_t bytes = (kind == PE_SINUSOIDAL ? (size_t)L * D : (size_t)L * rd) * sizeof(float);
+        float *ptr = nullptr;
+        if (cudaMalloc(&ptr, bytes) != cudaSuccess) return nullptr;
+        tc_build_pe_table<<<296, 256, 0, st>>>(ptr, L, D, kind, rd, base);
+        launches->fetch_add(1);
+        e[n++] = Entry{kind, L, D, rd, base, ptr};
+        return ptr;
+    }
+};
+
+static thread_local char t_tc_error[256] = "";
+inline const char *tc_bf16_error() { return t_tc_error; }
+
+inline bool tc_bf16_supported(const b200attn_args &a, int rd) {
+    if (getenv("B200ATTN_NO_TC")) return false;
+    if (a.dtype != B200ATTN_BF16) return false;
+    if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 512) return false;
+    if (a.len_q % TC_BM != 0 || a.len_k % TC_BN != 0) return false;
+    if (a.pe == B200ATTN_PE_ROPE_HALF) return false;
+    if (a.pe != B200ATTN_PE_NONE && a.pe != B200ATTN_PE_SINUSOIDAL && (rd % 8 != 0)) return false;
+    if (a.cos_cache != nullptr) return false;
+    if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return false;
+    const long long BH = (long long)a.batch_sz * a.num_heads;
+    if (BH * a.len_q >= (1ll << 31) || BH * a.len_k >= (1ll << 31)) return false;
+    if (BH * (a.len_q / TC_BM) * 2 >= (1ll << 31)) return false;
+    return true;
+}
+
+typedef CUresult (*PFN_tmapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                         const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                         CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline PFN_tmapEncodeTiled tc_encode_fn() {
+    static PFN_tmapEncodeTiled fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (PFN_tmapEncodeTiled)f;
+    }();
+    return fn;
+}
+
+// 2-D bf16 tensor map over a [rows][D] row-major matrix with a [box_rows][64] box, 128-byte swizzle.
+inline bool tc_make_map(CUtensorMap *m, const void *base, long long rows, int D, int box_rows) {
+    PFN_tmapEncodeTiled enc = tc_encode_fn();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline size_t tc_smem_bytes(int D) {
+    const size_t score = (size_t)(D / 64) * TC_CHUNK_BYTES + (size_t)TC_NK * TC_CHUNK_BYTES;
+    const size_t outp = (size_t)TC_NP * TC_P_BYTES + (size_t)TC_NV * TC_VS * D * 2 + (size_t)(TC_NP + 1) * TC_BM * sizeof(float);
+    return (score > outp ? score : outp) + 1024;
+}
+
+// Returns B200ATTN_OK, -1 when the shape should run on the other path, or a status with tc_bf16_error() set.
+inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tables, unsigned *err_dev, int sm_count,
+                       unsigned spin_limit, cudaStream_t st, std::atomic<unsigned long long> *launches, float *debug_scores = nullptr) {
+    (void)sm_count;
+    const long long BH = (long long)a.batch_sz * a.num_heads;
+    const int D = a.head_d;
+    static std::mutex attr_mu;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const size_t smem = tc_smem_bytes(D);
+    {
+        std::lock_guard<std::mutex> lk(attr_mu);
+        if (!attr_done[dev & 63]) {
+            cudaFuncAttributes fa;
+            if (cudaFuncGetAttributes(&fa, tc_bf16_pair_kernel) != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncGetAttributes failed"); return B200ATTN_ERR_CUDA; }
+            cudaDeviceProp prop;
+            cudaGetDeviceProperties(&prop, dev);
+            const size_t dyn_max = prop.sharedMemPerBlockOptin - fa.sharedSizeBytes;
+            if (cudaFuncSetAttribute(tc_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_max) != cudaSuccess) {
+                snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncSetAttribute(max dynamic shared memory) failed");
+                return B200ATTN_ERR_CUDA;
+            }
+            attr_done[dev & 63] = true;
+        }
+    }
+    TcParams p{};
+    p.Lq = a.len_q; p.Lk = a.len_k; p.D = D;
+    p.n_qtiles = a.len_q / TC_BM; p.n_blocks = a.len_k / TC_BN; p.n_chunks = D / 64;
+    p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+    p.pe = a.pe == B200ATTN_PE_ROPE_Q_ONLY ? (int)PE_ROPE_INTERLEAVED : a.pe;
+    p.rd = rd;
+    p.rotate_k = (a.pe == B200ATTN_PE_ROPE_Q_ONLY) ? 0 : 1;
+    p.O = (__nv_bfloat16 *)a.out;
+    p.err = err_dev;
+    p.spin_limit = spin_limit;
+    p.debug_scores = debug_scores;
+    if (a.pe != B200ATTN_PE_NONE) {
+        const int L = a.len_q > a.len_k ? a.len_q : a.len_k;
+        p.pe_table = tables.get(a.pe, L, D, rd, a.pe == B200ATTN_PE_SINUSOIDAL ? 10000.0f : base, st, launches);
+        if (!p.pe_table) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the positional-encoding table"); return B200ATTN_ERR_CUDA; }
+    }
+    CUtensorMap tmQ, tmK, tmV;
+    if (!tc_make_map(&tmQ, a.Q, BH * a.len_q, D, TC_BM) || !tc_make_map(&tmK, a.K, BH * a.len_k, D, TC_BN) ||
+        !tc_make_map(&tmV, a.V, BH * a.len_k, D, TC_VS)) {
+        snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
+        return B200ATTN_ERR_CUDA;
+    }
+    const long long units = BH * p.n_qtiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * units));
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, tc_bf16_pair_kernel, tmQ, tmK, tmV, p);
+    if (e != cudaSuccess) {
+        snprintf(t_tc_error, sizeof t_tc_error, "tc_bf16_pair_kernel launch failed: %s", cudaGetErrorString(e));
+        return B200ATTN_ERR_CUDA;
+    }
+    launches->fetch_add(1);
+    return B200ATTN_OK;
 }
 
 }  // namespace b200attn
