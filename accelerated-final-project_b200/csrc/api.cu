@@ -429,6 +429,13 @@ int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
     return check_kernel_errors(*c, (cudaStream_t)a->stream, true);
 }
 
+#ifdef B200ATTN_TC_PROFILE
+int b200attn_debug_tc_prof(unsigned long long *out32, int reset) {
+    if (reset) { unsigned long long z[32] = {}; return (int)cudaMemcpyToSymbol(tc_prof, z, sizeof z); }
+    return (int)cudaMemcpyFromSymbol(out32, tc_prof, 32 * sizeof(unsigned long long));
+}
+#endif
+
 int b200attn_forward_many(const b200attn_args *args, int n) {
     if (args == nullptr || n < 0) return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_many: NULL args or negative n");
     for (int i = 0; i < n; ++i) {

@@ -55,7 +55,7 @@ struct TcParams {
     float scale_log2;                   // log2(e) / sqrt(D)
     int pe, rd;                         // PeKind; rotary_dim
     int rotate_k;                       // 0 for PE_ROPE_Q_ONLY
-    const float *pe_table;              // sinusoidal: [L][D] fp32; RoPE: [L][rd/2] (cos, sin) pairs
+    int k_stages, k_stage_bytes;        // K ring: 5 x 16 KB, or 3 x (16 KB K chunk + 16 KB encoding chunk)
     __nv_bfloat16 *O;
     unsigned *err;
     unsigned spin_limit;
@@ -74,39 +74,54 @@ struct TcBarriers {
     uint64_t l_full;
 };
 
-// In-place positional encoding of one [128 rows x 64 columns] bf16 chunk in swizzled shared memory.
-// 128 threads: thread -> 16-byte chunk q = tid % 8 of rows tid/8 + 16*it, so that a warp reads 4
-// full rows of the fp32 table (coalesced) and hits every shared-memory bank group once.
-__device__ __forceinline__ void tc_pe_chunk(unsigned char *tile, int pos0, int d0, const TcParams &p, int tid) {
-    const int q = tid & 7, r0 = tid >> 3;
-    const int d = d0 + q * 8;
-#pragma unroll 2
-    for (int it = 0; it < 8; ++it) {
-        const int r = r0 + 16 * it;
-        const long long pos = pos0 + r;
-        uint4 *ptr = reinterpret_cast<uint4 *>(tile + r * 128 + ((q ^ (r & 7)) << 4));
-        uint4 v = *ptr;
-        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&v);
-        if (p.pe == PE_SINUSOIDAL) {
-            const float4 *tp = reinterpret_cast<const float4 *>(p.pe_table + pos * p.D + d);
-            const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
-            float2 x0 = __bfloat1622float2(h[0]), x1 = __bfloat1622float2(h[1]), x2 = __bfloat1622float2(h[2]), x3 = __bfloat1622float2(h[3]);
-            h[0] = __floats2bfloat162_rn(x0.x + t0.x, x0.y + t0.y);
-            h[1] = __floats2bfloat162_rn(x1.x + t0.z, x1.y + t0.w);
-            h[2] = __floats2bfloat162_rn(x2.x + t1.x, x2.y + t1.y);
-            h[3] = __floats2bfloat162_rn(x3.x + t1.z, x3.y + t1.w);
-        } else if (d < p.rd) {   // interleaved RoPE: pairs (2i, 2i+1); rd % 8 == 0 so a chunk is all-in or all-out
-            const float4 *tp = reinterpret_cast<const float4 *>(p.pe_table + (pos * (p.rd >> 1) + (d >> 1)) * 2);
-            const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);   // (c0,s0,c1,s1), (c2,s2,c3,s3)
-            float2 x0 = __bfloat1622float2(h[0]), x1 = __bfloat1622float2(h[1]), x2 = __bfloat1622float2(h[2]), x3 = __bfloat1622float2(h[3]);
-            h[0] = __floats2bfloat162_rn(x0.x * t0.x - x0.y * t0.y, x0.x * t0.y + x0.y * t0.x);
-            h[1] = __floats2bfloat162_rn(x1.x * t0.z - x1.y * t0.w, x1.x * t0.w + x1.y * t0.z);
-            h[2] = __floats2bfloat162_rn(x2.x * t1.x - x2.y * t1.y, x2.x * t1.y + x2.y * t1.x);
-            h[3] = __floats2bfloat162_rn(x3.x * t1.z - x3.y * t1.w, x3.x * t1.w + x3.y * t1.z);
-        }
-        *ptr = v;
+// Positional encoding of one [128 rows x 64 columns] bf16 chunk in shared memory.  The encoding
+// values arrive by TMA from a bf16 table in global memory as a tile of the SAME shape and swizzle,
+// so element (row, col) of both tiles sits at the same byte offset and the transform is a plain
+// element-wise pass over 1024 16-byte vectors (128 threads x 8), done with packed bf16x2 math:
+//   sinusoidal: x += pe                                  (table: sin at even, cos at odd columns)
+//   RoPE pairs: (xe, xo) -> (xe*c - xo*s, xe*s + xo*c)    (table: c at even, s at odd columns; c=1,
+//                                                         s=0 beyond rotary_dim)
+__device__ __forceinline__ uint32_t tc_pe_pair(uint32_t x, uint32_t t, bool sinus) {
+    __nv_bfloat162 xv = *reinterpret_cast<__nv_bfloat162 *>(&x);
+    __nv_bfloat162 r;
+    if (sinus) {
+        r = __hadd2(xv, *reinterpret_cast<__nv_bfloat162 *>(&t));
+    } else {
+        uint32_t cc = __byte_perm(t, 0, 0x1010);                  // (c, c)
+        uint32_t ss = __byte_perm(t, 0, 0x3232) ^ 0x00008000u;    // (-s, s)
+        uint32_t xs = __byte_perm(x, 0, 0x1032);                  // (xo, xe)
+        r = __hfma2(*reinterpret_cast<__nv_bfloat162 *>(&xs), *reinterpret_cast<__nv_bfloat162 *>(&ss),
+                    __hmul2(xv, *reinterpret_cast<__nv_bfloat162 *>(&cc)));
+    }
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+__device__ __forceinline__ void tc_pe_chunk(unsigned char *tile, const unsigned char *pe_tile, bool sinus, int tid) {
+    uint4 *x = reinterpret_cast<uint4 *>(tile);
+    const uint4 *t = reinterpret_cast<const uint4 *>(pe_tile);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int o = tid + 128 * i;
+        uint4 v = x[o];
+        const uint4 w = t[o];
+        v.x = tc_pe_pair(v.x, w.x, sinus);
+        v.y = tc_pe_pair(v.y, w.y, sinus);
+        v.z = tc_pe_pair(v.z, w.z, sinus);
+        v.w = tc_pe_pair(v.w, w.w, sinus);
+        x[o] = v;
     }
 }
+
+// Optional cycle accounting of the roles of cluster 0 (build with -DB200ATTN_TC_PROFILE).
+#ifdef B200ATTN_TC_PROFILE
+__device__ unsigned long long tc_prof[32];
+#define TC_PROF_DECL long long pc_ = clock64(); unsigned long long pa_[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define TC_PROF(slot) do { const long long n_ = clock64(); pa_[(slot) & 7] += (unsigned long long)(n_ - pc_); pc_ = n_; } while (0)
+#define TC_PROF_FLUSH(base, on) do { if ((on) && blockIdx.x < 2) for (int i_ = 0; i_ < 8; ++i_) tc_prof[(base) + i_] = pa_[i_]; } while (0)
+#else
+#define TC_PROF_DECL
+#define TC_PROF(slot)
+#define TC_PROF_FLUSH(base, on)
+#endif
 
 #define TC_FAIL_IF(cond)                                         \
     if (cond) {                                                  \
@@ -117,7 +132,7 @@ __device__ __forceinline__ void tc_pe_chunk(unsigned char *tile, int pos0, int d
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
 tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const TcParams p) {
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmPE, const TcParams p) {
     extern __shared__ unsigned char tc_smem_raw[];
     __shared__ TcBarriers bars;
     __shared__ uint32_t tmem_slot;
@@ -135,9 +150,11 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int D = p.D, nch = p.n_chunks, T = p.n_blocks;
     const uint32_t lim = p.spin_limit;
     const bool has_pe = (p.pe != PE_NONE);
+    const bool pe_k = has_pe && p.rotate_k;          // K chunks are encoded too (not for pre-rotated K)
+    const int NKS = p.k_stages, KSB = p.k_stage_bytes;
 
     // ---- shared-memory carve-up ----
-    // score CTA : [Q: nch chunks of 16 KB][K ring: TC_NK chunks of 16 KB]
+    // score CTA : [Q: nch chunks of 16 KB][K ring: k_stages stages of (K chunk [+ encoding chunk])]
     // output CTA: [P: TC_NP x 32 KB][V ring: TC_NV stages of TC_VS*D*2 B][alpha: TC_NP x 128 f32][lsum: 128 f32]
     unsigned char *q_smem = smem;
     unsigned char *k_smem = smem + (size_t)nch * TC_CHUNK_BYTES;
@@ -149,19 +166,20 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (threadIdx.x == 0) {
         mbar_init(&bars.q_full, 1);
-        mbar_init(&bars.q_ready, 128);
-        for (int i = 0; i < TC_NK; ++i) { mbar_init(&bars.k_full[i], 1); mbar_init(&bars.k_ready[i], 128); mbar_init(&bars.k_empty[i], 1); }
-        for (int i = 0; i < TC_NS; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 128); }
+        mbar_init(&bars.q_ready, 4);
+        for (int i = 0; i < TC_NK; ++i) { mbar_init(&bars.k_full[i], 1); mbar_init(&bars.k_ready[i], 4); mbar_init(&bars.k_empty[i], 1); }
+        for (int i = 0; i < TC_NS; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 4); }
         for (int i = 0; i < TC_NV; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
         for (int i = 0; i < TC_NP; ++i) {
             mbar_init(&bars.p_empty[i], 1);
-            mbar_init(&bars.p_full[i], 128);
+            mbar_init(&bars.p_full[i], 4);
             mbar_init(&bars.pv_done[i], 1);
-            mbar_init(&bars.corr_done[i], 128);
+            mbar_init(&bars.corr_done[i], 4);
         }
-        mbar_init(&bars.l_full, 128);
+        mbar_init(&bars.l_full, 4);
         mbar_fence_init();
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+        if (p.pe != PE_NONE) tma_prefetch_desc(&tmPE);
     }
     if (warp == 0) tmem_alloc(&tmem_slot, 512);
     tc_fence_before();
@@ -192,34 +210,52 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 mbar_expect_tx(&bars.q_full, (uint32_t)nch * TC_CHUNK_BYTES);
                 for (int c = 0; c < nch; ++c)
                     tma_load_2d(q_smem + (size_t)c * TC_CHUNK_BYTES, &tmQ, c * 64, (int)(bh * p.Lq + qt * TC_BM), &bars.q_full);
+                // With an encoding, the first nch ring slots carry the encoding rows of the QUERY
+                // tile (added to / rotated into the resident Q tile by the transform warps); after
+                // that every slot carries a K chunk and, if K is encoded too, its encoding chunk.
                 int it = 0;
+                if (has_pe)
+                    for (int c = 0; c < nch; ++c, ++it) {
+                        const int s = it % NKS;
+                        TC_FAIL_IF(!mbar_wait(&bars.k_empty[s], ((it / NKS) & 1) ^ 1, lim));
+                        mbar_expect_tx(&bars.k_full[s], TC_CHUNK_BYTES);
+                        tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, qt * TC_BM, &bars.k_full[s]);
+                    }
                 for (int t = 0; t < T && !failed; ++t)
                     for (int c = 0; c < nch; ++c, ++it) {
-                        const int s = it % TC_NK;
-                        TC_FAIL_IF(!mbar_wait(&bars.k_empty[s], ((it / TC_NK) & 1) ^ 1, lim));
-                        mbar_expect_tx(&bars.k_full[s], TC_CHUNK_BYTES);
-                        tma_load_2d(k_smem + (size_t)s * TC_CHUNK_BYTES, &tmK, c * 64, (int)(bh * p.Lk + t * TC_BN), &bars.k_full[s]);
+                        const int s = it % NKS;
+                        TC_FAIL_IF(!mbar_wait(&bars.k_empty[s], ((it / NKS) & 1) ^ 1, lim));
+                        mbar_expect_tx(&bars.k_full[s], pe_k ? 2 * TC_CHUNK_BYTES : TC_CHUNK_BYTES);
+                        tma_load_2d(k_smem + (size_t)s * KSB, &tmK, c * 64, (int)(bh * p.Lk + t * TC_BN), &bars.k_full[s]);
+                        if (pe_k) tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, t * TC_BN, &bars.k_full[s]);
                     }
             }
         } else if (warp == 1) {
             if (lane == 0) {
                 const uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN, 0, 0);
                 do {
-                    TC_FAIL_IF(!mbar_wait(has_pe ? &bars.q_ready : &bars.q_full, 0, lim));
+                    TC_FAIL_IF(!mbar_wait(&bars.q_full, 0, lim));
                 } while (0);
-                tc_fence_after();
                 int it = 0;
+                if (has_pe)   // hand the ring slots of the query-encoding phase back once the transform warps are done with them
+                    for (int c = 0; c < nch && !failed; ++c, ++it) {
+                        const int s = it % NKS;
+                        TC_FAIL_IF(!mbar_wait(&bars.k_ready[s], (it / NKS) & 1, lim));
+                        mbar_arrive(&bars.k_empty[s]);
+                    }
+                tc_fence_after();
+                TC_PROF_DECL;
                 for (int t = 0; t < T && !failed; ++t) {
                     const int sb = t % TC_NS;
                     TC_FAIL_IF(!mbar_wait(&bars.s_empty[sb], ((t / TC_NS) & 1) ^ 1, lim));
                     tc_fence_after();
+                    TC_PROF(4);
                     for (int c = 0; c < nch; ++c, ++it) {
-                        const int s = it % TC_NK;
-                        uint64_t *kb = (has_pe && p.rotate_k) ? &bars.k_ready[s] : &bars.k_full[s];
-                        TC_FAIL_IF(!mbar_wait(kb, (it / TC_NK) & 1, lim));
+                        const int s = it % NKS;
+                        TC_FAIL_IF(!mbar_wait(pe_k ? &bars.k_ready[s] : &bars.k_full[s], (it / NKS) & 1, lim));
                         tc_fence_after();
                         const uint64_t da = umma_desc_k_sw128(smem_u32(q_smem + (size_t)c * TC_CHUNK_BYTES));
-                        const uint64_t db = umma_desc_k_sw128(smem_u32(k_smem + (size_t)s * TC_CHUNK_BYTES));
+                        const uint64_t db = umma_desc_k_sw128(smem_u32(k_smem + (size_t)s * KSB));
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             umma_bf16(tmem + sb * TC_BN, da + 2 * k, db + 2 * k, idesc, (c | k) != 0);
@@ -227,7 +263,9 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                     if (failed) break;
                     umma_commit(&bars.s_full[sb]);
+                    TC_PROF(5);
                 }
+                TC_PROF_FLUSH(8, true);
             }
         } else if (warp < 6) {
             // ---- softmax: one thread per query row ----
@@ -237,23 +275,41 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const uint32_t alpha_remote = map_to_rank(smem_u32(alpha_smem), 1);
             float m_used = -INFINITY, l = 0.0f;
             uint32_t r[32];
+            TC_PROF_DECL;
+            // Block t's probabilities are written to the peer with plain distributed-shared-memory
+            // stores; making them visible to the peer's tensor core (proxy fence) waits for those
+            // stores, so the hand-over of block t is issued after the max pass of block t+1.
             for (int t = 0; t < T; ++t) {
                 const int sb = t % TC_NS, pb = t % TC_NP;
                 TC_FAIL_IF(!mbar_wait(&bars.s_full[sb], (t / TC_NS) & 1, lim));
                 tc_fence_after();
+                TC_PROF(0);
                 const uint32_t ta = lane_addr + sb * TC_BN;
-                float mx = -INFINITY;
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     tmem_ld32(ta + c * 32, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+                    for (int j = 0; j < 32; j += 4) {
+                        mx0 = fmaxf(mx0, __uint_as_float(r[j]));
+                        mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
+                        mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
+                        mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
+                    }
                     if (p.debug_scores != nullptr && t == 0) {
                         float *dbg = p.debug_scores + ((long long)unit * TC_BM + row) * TC_BN + c * 32;
                         for (int j = 0; j < 32; ++j) dbg[j] = __uint_as_float(r[j]);
                     }
                 }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                TC_PROF(1);
+                if (t > 0) {   // hand block t-1 over: every lane fences its own stores, one lane arrives for the warp
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[(t - 1) % TC_NP]), 1));
+                }
+                TC_PROF(4);
                 float alpha = 1.0f;
                 if (t == 0) {
                     m_used = mx;
@@ -263,8 +319,10 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     m_used = mx;
                 }
                 TC_FAIL_IF(!mbar_wait_cluster(&bars.p_empty[pb], ((t / TC_NP) & 1) ^ 1, lim));
+                TC_PROF(2);
                 const float msl = m_used * p.scale_log2;
                 const uint32_t prow = p_remote + pb * TC_P_BYTES + row * 128;
+                float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     tmem_ld32(ta + c * 32, r);
@@ -273,44 +331,57 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     for (int g = 0; g < 4; ++g) {
                         float e[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            e[j] = fast_exp2(fmaf(__uint_as_float(r[8 * g + j]), p.scale_log2, -msl));
-                            l += e[j];
-                        }
+                        for (int j = 0; j < 8; ++j) e[j] = fast_exp2(fmaf(__uint_as_float(r[8 * g + j]), p.scale_log2, -msl));
+                        l0 += e[0] + e[4]; l1 += e[1] + e[5]; l2 += e[2] + e[6]; l3 += e[3] + e[7];
                         const int q16 = c * 4 + g;   // 16-byte chunk index within the 128-key row
                         const uint32_t addr = prow + (q16 >> 3) * (TC_BM * 128) + (((q16 & 7) ^ (row & 7)) << 4);
                         st_cluster_v4(addr, pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
                     }
                 }
+                l += (l0 + l1) + (l2 + l3);
                 tc_fence_before();
-                mbar_arrive(&bars.s_empty[sb]);
                 st_cluster_f32(alpha_remote + (pb * TC_BM + row) * 4, alpha);
-                fence_proxy_async();
-                mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[pb]), 1));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
+                TC_PROF(3);
             }
+            if (!failed && T > 0) {   // hand the last block over
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[(T - 1) % TC_NP]), 1));
+            }
+            TC_PROF_FLUSH(0, threadIdx.x == 64);
             // row sums for the epilogue (sent even after a failure so that the peer is not left waiting)
             st_cluster_f32(map_to_rank(smem_u32(lsum_smem), 1) + row * 4, l);
-            mbar_arrive_cluster(map_to_rank(smem_u32(&bars.l_full), 1));
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.l_full), 1));
         } else if (has_pe) {
-            // ---- transform warps: positional encoding of Q once and of every K chunk ----
+            // ---- transform warps: encoding of the Q tile once, then of every K chunk ----
             const int tid = threadIdx.x - 6 * 32;
+            const bool sinus = (p.pe == PE_SINUSOIDAL);
+            int it = 0;
             do {
                 TC_FAIL_IF(!mbar_wait(&bars.q_full, 0, lim));
-                for (int c = 0; c < nch; ++c) tc_pe_chunk(q_smem + (size_t)c * TC_CHUNK_BYTES, qt * TC_BM, c * 64, p, tid);
-                fence_proxy_async();
-                mbar_arrive(&bars.q_ready);
+                for (int c = 0; c < nch; ++c, ++it) {
+                    const int s = it % NKS;
+                    TC_FAIL_IF(!mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
+                    tc_pe_chunk(q_smem + (size_t)c * TC_CHUNK_BYTES, k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, sinus, tid);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.k_ready[s]);
+                }
             } while (0);
-            if (p.rotate_k) {
-                int it = 0;
+            if (pe_k)
                 for (int t = 0; t < T && !failed; ++t)
                     for (int c = 0; c < nch; ++c, ++it) {
-                        const int s = it % TC_NK;
-                        TC_FAIL_IF(!mbar_wait(&bars.k_full[s], (it / TC_NK) & 1, lim));
-                        tc_pe_chunk(k_smem + (size_t)s * TC_CHUNK_BYTES, t * TC_BN, c * 64, p, tid);
+                        const int s = it % NKS;
+                        TC_FAIL_IF(!mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
+                        unsigned char *kt = k_smem + (size_t)s * KSB;
+                        tc_pe_chunk(kt, kt + TC_CHUNK_BYTES, sinus, tid);
                         fence_proxy_async();
-                        mbar_arrive(&bars.k_ready[s]);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bars.k_ready[s]);
                     }
-            }
         }
     } else {
         // =============================== output CTA ===============================
@@ -330,11 +401,14 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         } else if (warp == 1) {
             if (lane == 0) {
                 int it = 0;
+                TC_PROF_DECL;
                 for (int t = 0; t < T && !failed; ++t) {
                     const int pb = t % TC_NP;
                     TC_FAIL_IF(!mbar_wait_cluster(&bars.p_full[pb], (t / TC_NP) & 1, lim));
+                    TC_PROF(0);
                     TC_FAIL_IF(!mbar_wait(&bars.corr_done[pb], (t / TC_NP) & 1, lim));
                     tc_fence_after();
+                    TC_PROF(1);
                     for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
                         const int s = it % TC_NV;
                         TC_FAIL_IF(!mbar_wait(&bars.v_full[s], (it / TC_NV) & 1, lim));
@@ -354,7 +428,9 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                     if (failed) break;
                     umma_commit(&bars.pv_done[pb]);
+                    TC_PROF(2);
                 }
+                TC_PROF_FLUSH(16, true);
             }
         } else if (warp < 6) {
             // ---- correction + epilogue: one thread per query row ----
@@ -378,7 +454,8 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     tmem_st_wait();
                     tc_fence_before();
                 }
-                mbar_arrive(&bars.corr_done[pb]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.corr_done[pb]);
             }
             do {
                 if (failed) break;
@@ -425,27 +502,30 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }
 #undef TC_FAIL_IF
 
-// ---- positional-encoding tables (built on the device with the arithmetic of the reference CPU tables) ----
-__global__ void tc_build_pe_table(float *table, int L, int D, int pe, int rd, float base) {
-    const long long n = (pe == PE_SINUSOIDAL) ? (long long)L * D : (long long)L * (rd >> 1);
+// ---- positional-encoding tables: [L][D] bf16, built on the device with the fp32 arithmetic of the
+// reference CPU tables (final/sinusoidal.cu:838-855, final/rope.cu:20-40) and rounded once ----
+__global__ void tc_build_pe_table(__nv_bfloat16 *table, int L, int D, int pe, int rd, float base) {
+    const long long n = (long long)L * D;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int pos = (int)(i / D), d = (int)(i % D);
+        float v;
         if (pe == PE_SINUSOIDAL) {
-            const int pos = (int)(i / D), d = (int)(i % D);
-            const float freq = 1.0f / powf(10000.0f, (2.0f * (float)(d / 2)) / (float)D);   // final/sinusoidal.cu:848
+            const float freq = 1.0f / powf(10000.0f, (2.0f * (float)(d / 2)) / (float)D);
             const float ang = (float)pos * freq;
-            table[i] = (d & 1) ? cosf(ang) : sinf(ang);
-        } else {
-            const int pos = (int)(i / (rd >> 1)), pr = (int)(i % (rd >> 1));
-            const float freq = 1.0f / powf(base, (2.0f * (float)pr) / (float)rd);           // final/rope.cu:29
+            v = (d & 1) ? cosf(ang) : sinf(ang);
+        } else if (d < rd) {
+            const float freq = 1.0f / powf(base, (2.0f * (float)(d / 2)) / (float)rd);
             const float th = (float)pos * freq;
-            table[2 * i] = cosf(th);
-            table[2 * i + 1] = sinf(th);
+            v = (d & 1) ? sinf(th) : cosf(th);
+        } else {
+            v = (d & 1) ? 0.0f : 1.0f;   // columns beyond rotary_dim: identity rotation
         }
+        table[i] = __float2bfloat16_rn(v);
     }
 }
 
 struct TcTables {
-    struct Entry { int pe, L, D, rd; float base; float *ptr; };
+    struct Entry { int pe, L, D, rd; float base; __nv_bfloat16 *ptr; };
     static constexpr int kMax = 8;
     Entry e[kMax];
     int n = 0;
@@ -453,21 +533,21 @@ struct TcTables {
         for (int i = 0; i < n; ++i) cudaFree(e[i].ptr);
         n = 0;
     }
-    // Returns a device table for the key, building it on `st` when it is new.
-    float *get(int pe, int L, int D, int rd, float base, cudaStream_t st, std::atomic<unsigned long long> *launches) {
+    // Returns a device table with at least L rows for the key, building it on `st` when it is new.
+    __nv_bfloat16 *get(int pe, int L, int D, int rd, float base, cudaStream_t st, std::atomic<unsigned long long> *launches, int *rows) {
         const int kind = (pe == PE_SINUSOIDAL) ? PE_SINUSOIDAL : PE_ROPE_INTERLEAVED;
         for (int i = 0; i < n; ++i)
-            if (e[i].pe == kind && e[i].L >= L && e[i].D == D && e[i].rd == rd && e[i].base == base) return e[i].ptr;
+            if (e[i].pe == kind && e[i].L >= L && e[i].D == D && e[i].rd == rd && e[i].base == base) { *rows = e[i].L; return e[i].ptr; }
         if (n == kMax) {   // evict everything once no kernel can still be reading a table
             cudaDeviceSynchronize();
             release();
         }
-        const size_t bytes = (kind == PE_SINUSOIDAL ? (size_t)L * D : (size_t)L * rd) * sizeof(float);
-        float *ptr = nullptr;
-        if (cudaMalloc(&ptr, bytes) != cudaSuccess) return nullptr;
+        __nv_bfloat16 *ptr = nullptr;
+        if (cudaMalloc(&ptr, (size_t)L * D * sizeof(__nv_bfloat16)) != cudaSuccess) return nullptr;
         tc_build_pe_table<<<296, 256, 0, st>>>(ptr, L, D, kind, rd, base);
         launches->fetch_add(1);
         e[n++] = Entry{kind, L, D, rd, base, ptr};
+        *rows = L;
         return ptr;
     }
 };
@@ -517,8 +597,9 @@ inline bool tc_make_map(CUtensorMap *m, const void *base, long long rows, int D,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-inline size_t tc_smem_bytes(int D) {
-    const size_t score = (size_t)(D / 64) * TC_CHUNK_BYTES + (size_t)TC_NK * TC_CHUNK_BYTES;
+inline size_t tc_smem_bytes(int D, bool has_pe) {
+    const size_t ring = has_pe ? (size_t)3 * 2 * TC_CHUNK_BYTES : (size_t)TC_NK * TC_CHUNK_BYTES;
+    const size_t score = (size_t)(D / 64) * TC_CHUNK_BYTES + ring;
     const size_t outp = (size_t)TC_NP * TC_P_BYTES + (size_t)TC_NV * TC_VS * D * 2 + (size_t)(TC_NP + 1) * TC_BM * sizeof(float);
     return (score > outp ? score : outp) + 1024;
 }
@@ -533,7 +614,7 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    const size_t smem = tc_smem_bytes(D);
+    const size_t smem = tc_smem_bytes(D, a.pe != B200ATTN_PE_NONE);
     {
         std::lock_guard<std::mutex> lk(attr_mu);
         if (!attr_done[dev & 63]) {
@@ -560,16 +641,23 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     p.err = err_dev;
     p.spin_limit = spin_limit;
     p.debug_scores = debug_scores;
-    if (a.pe != B200ATTN_PE_NONE) {
-        const int L = a.len_q > a.len_k ? a.len_q : a.len_k;
-        p.pe_table = tables.get(a.pe, L, D, rd, a.pe == B200ATTN_PE_SINUSOIDAL ? 10000.0f : base, st, launches);
-        if (!p.pe_table) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the positional-encoding table"); return B200ATTN_ERR_CUDA; }
-    }
-    CUtensorMap tmQ, tmK, tmV;
+    CUtensorMap tmQ, tmK, tmV, tmPE;
     if (!tc_make_map(&tmQ, a.Q, BH * a.len_q, D, TC_BM) || !tc_make_map(&tmK, a.K, BH * a.len_k, D, TC_BN) ||
         !tc_make_map(&tmV, a.V, BH * a.len_k, D, TC_VS)) {
         snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
         return B200ATTN_ERR_CUDA;
+    }
+    tmPE = tmK;
+    p.k_stages = TC_NK;
+    p.k_stage_bytes = TC_CHUNK_BYTES;
+    if (a.pe != B200ATTN_PE_NONE) {
+        const int L = a.len_q > a.len_k ? a.len_q : a.len_k;
+        int rows = 0;
+        const __nv_bfloat16 *tab = tables.get(a.pe, L, D, rd, a.pe == B200ATTN_PE_SINUSOIDAL ? 10000.0f : base, st, launches, &rows);
+        if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the positional-encoding table"); return B200ATTN_ERR_CUDA; }
+        if (!tc_make_map(&tmPE, tab, rows, D, TC_BN)) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
+        p.k_stages = 3;
+        p.k_stage_bytes = 2 * TC_CHUNK_BYTES;
     }
     const long long units = BH * p.n_qtiles;
     cudaLaunchConfig_t cfg = {};
@@ -577,7 +665,7 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     cfg.blockDim = dim3(TC_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, tc_bf16_pair_kernel, tmQ, tmK, tmV, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, tc_bf16_pair_kernel, tmQ, tmK, tmV, tmPE, p);
     if (e != cudaSuccess) {
         snprintf(t_tc_error, sizeof t_tc_error, "tc_bf16_pair_kernel launch failed: %s", cudaGetErrorString(e));
         return B200ATTN_ERR_CUDA;
