@@ -37,14 +37,14 @@
 
 namespace b200attn {
 
-constexpr int TC_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 softmax / correction, warps 6-9 transform / relay
+constexpr int TC_THREADS = 448;   // warp 0 TMA, warp 1 MMA, warps 2-9 softmax (output CTA: 2-5 correction, 6 relay), warps 10-13 transform
 constexpr int TC_BM = 128;        // query rows per tile
 constexpr int TC_BN = 128;        // keys per block
 constexpr int TC_VS = 32;         // keys per V stage
 constexpr int TC_NK = 5;          // K chunk ring depth (score CTA)
 constexpr int TC_NS = 4;          // S buffers in tensor memory (4 x 128 columns)
-constexpr int TC_NP = 2;          // P buffers (output CTA shared memory)
-constexpr int TC_NV = 4;          // V stage ring depth (output CTA)
+constexpr int TC_NP = 3;          // P buffers (output CTA shared memory)
+constexpr int TC_NV = 3;          // V stage ring depth (output CTA)
 constexpr int TC_CHUNK_BYTES = TC_BM * 128;          // [128 rows x 64 bf16]
 constexpr int TC_P_BYTES = TC_BM * TC_BN * 2;        // one P buffer
 constexpr float TC_RESCALE_LOG2 = 8.0f;              // rescale O only when the max grew by > 2^8
@@ -55,6 +55,7 @@ struct TcParams {
     float scale_log2;                   // log2(e) / sqrt(D)
     int pe, rd;                         // PeKind; rotary_dim
     int rotate_k;                       // 0 for PE_ROPE_Q_ONLY
+    int sb_keys;                        // keys per score MMA tile: 256 (no encoding) or 128
     int k_stages, k_stage_bytes;        // K ring: 5 x 16 KB, or 3 x (16 KB K chunk + 16 KB encoding chunk)
     __nv_bfloat16 *O;
     unsigned *err;
@@ -72,6 +73,7 @@ struct TcBarriers {
     uint64_t pv_done[TC_NP];
     uint64_t corr_done[TC_NP];
     uint64_t l_full;
+    uint64_t decided[2];        // score CTA: reference max of block t settled (t & 1)
 };
 
 // Positional encoding of one [128 rows x 64 columns] bf16 chunk in shared memory.  The encoding
@@ -137,6 +139,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     __shared__ TcBarriers bars;
     __shared__ uint32_t tmem_slot;
     __shared__ unsigned skip_flag;
+    __shared__ float m_state[TC_BM];
 
     // 1024-byte aligned base; identical offset in both CTAs of the cluster (same kernel, same layout)
     const uint32_t raw_addr = smem_u32(tc_smem_raw);
@@ -152,6 +155,10 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool has_pe = (p.pe != PE_NONE);
     const bool pe_k = has_pe && p.rotate_k;          // K chunks are encoded too (not for pre-rotated K)
     const int NKS = p.k_stages, KSB = p.k_stage_bytes;
+    const int SB = p.sb_keys;                        // keys per score tile (one S buffer in tensor memory)
+    const int HPS = SB / TC_BN;                      // 128-key blocks per score tile
+    const int NSB = 512 / SB;                        // score tiles resident in tensor memory
+    const int U = (T + HPS - 1) / HPS;               // score tiles per unit
 
     // ---- shared-memory carve-up ----
     // score CTA : [Q: nch chunks of 16 KB][K ring: k_stages stages of (K chunk [+ encoding chunk])]
@@ -168,7 +175,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         mbar_init(&bars.q_full, 1);
         mbar_init(&bars.q_ready, 4);
         for (int i = 0; i < TC_NK; ++i) { mbar_init(&bars.k_full[i], 1); mbar_init(&bars.k_ready[i], 4); mbar_init(&bars.k_empty[i], 1); }
-        for (int i = 0; i < TC_NS; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 4); }
+        for (int i = 0; i < TC_NS; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 4 * (p.sb_keys / TC_BN)); }
         for (int i = 0; i < TC_NV; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
         for (int i = 0; i < TC_NP; ++i) {
             mbar_init(&bars.p_empty[i], 1);
@@ -176,7 +183,9 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_init(&bars.pv_done[i], 1);
             mbar_init(&bars.corr_done[i], 4);
         }
-        mbar_init(&bars.l_full, 4);
+        mbar_init(&bars.l_full, 8);
+        mbar_init(&bars.decided[0], 4);
+        mbar_init(&bars.decided[1], 4);
         mbar_fence_init();
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
         if (p.pe != PE_NONE) tma_prefetch_desc(&tmPE);
@@ -221,18 +230,18 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         mbar_expect_tx(&bars.k_full[s], TC_CHUNK_BYTES);
                         tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, qt * TC_BM, &bars.k_full[s]);
                     }
-                for (int t = 0; t < T && !failed; ++t)
+                for (int u = 0; u < U && !failed; ++u)
                     for (int c = 0; c < nch; ++c, ++it) {
                         const int s = it % NKS;
                         TC_FAIL_IF(!mbar_wait(&bars.k_empty[s], ((it / NKS) & 1) ^ 1, lim));
-                        mbar_expect_tx(&bars.k_full[s], pe_k ? 2 * TC_CHUNK_BYTES : TC_CHUNK_BYTES);
-                        tma_load_2d(k_smem + (size_t)s * KSB, &tmK, c * 64, (int)(bh * p.Lk + t * TC_BN), &bars.k_full[s]);
-                        if (pe_k) tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, t * TC_BN, &bars.k_full[s]);
+                        mbar_expect_tx(&bars.k_full[s], (uint32_t)SB * 128u + (pe_k ? TC_CHUNK_BYTES : 0));
+                        tma_load_2d(k_smem + (size_t)s * KSB, &tmK, c * 64, (int)(bh * p.Lk + u * SB), &bars.k_full[s]);
+                        if (pe_k) tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, u * SB, &bars.k_full[s]);
                     }
             }
         } else if (warp == 1) {
             if (lane == 0) {
-                const uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN, 0, 0);
+                const uint32_t idesc = umma_idesc_bf16(TC_BM, SB, 0, 0);
                 do {
                     TC_FAIL_IF(!mbar_wait(&bars.q_full, 0, lim));
                 } while (0);
@@ -245,20 +254,22 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                 tc_fence_after();
                 TC_PROF_DECL;
-                for (int t = 0; t < T && !failed; ++t) {
-                    const int sb = t % TC_NS;
-                    TC_FAIL_IF(!mbar_wait(&bars.s_empty[sb], ((t / TC_NS) & 1) ^ 1, lim));
+                for (int u = 0; u < U && !failed; ++u) {
+                    const int sb = u % NSB;
+                    TC_FAIL_IF(!mbar_wait(&bars.s_empty[sb], ((u / NSB) & 1) ^ 1, lim));
                     tc_fence_after();
                     TC_PROF(4);
                     for (int c = 0; c < nch; ++c, ++it) {
                         const int s = it % NKS;
+                        TC_PROF(5);
                         TC_FAIL_IF(!mbar_wait(pe_k ? &bars.k_ready[s] : &bars.k_full[s], (it / NKS) & 1, lim));
                         tc_fence_after();
+                        TC_PROF(6);
                         const uint64_t da = umma_desc_k_sw128(smem_u32(q_smem + (size_t)c * TC_CHUNK_BYTES));
                         const uint64_t db = umma_desc_k_sw128(smem_u32(k_smem + (size_t)s * KSB));
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            umma_bf16(tmem + sb * TC_BN, da + 2 * k, db + 2 * k, idesc, (c | k) != 0);
+                            umma_bf16(tmem + sb * SB, da + 2 * k, db + 2 * k, idesc, (c | k) != 0);
                         umma_commit(&bars.k_empty[s]);
                     }
                     if (failed) break;
@@ -267,24 +278,36 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
                 TC_PROF_FLUSH(8, true);
             }
-        } else if (warp < 6) {
-            // ---- softmax: one thread per query row ----
+        } else if (warp < 10) {
+            // ---- softmax: two warpgroups (warps 2-5 and 6-9) take alternate key blocks; in each a
+            // thread owns one query row.  The rows' reference maxima live in shared memory (m_state)
+            // and are advanced strictly in block order: the group of block t waits for the decision
+            // of block t-1, which the other group publishes through the `decided` barriers, right
+            // after its (short) max pass, so the long exp/store passes of the two groups overlap.
+            const int wg = (warp - 2) >> 2;
             const int row = 32 * (warp & 3) + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
             const uint32_t p_remote = map_to_rank(smem_u32(p_smem), 1);
             const uint32_t alpha_remote = map_to_rank(smem_u32(alpha_smem), 1);
-            float m_used = -INFINITY, l = 0.0f;
+            float m_seen = -INFINITY, l = 0.0f;   // l is relative to m_seen
             uint32_t r[32];
+            int last = -1;
             TC_PROF_DECL;
-            // Block t's probabilities are written to the peer with plain distributed-shared-memory
-            // stores; making them visible to the peer's tensor core (proxy fence) waits for those
-            // stores, so the hand-over of block t is issued after the max pass of block t+1.
-            for (int t = 0; t < T; ++t) {
-                const int sb = t % TC_NS, pb = t % TC_NP;
-                TC_FAIL_IF(!mbar_wait(&bars.s_full[sb], (t / TC_NS) & 1, lim));
+            // a score tile holds HPS blocks of 128 keys; with 256-key tiles the two groups work on the
+            // two halves of the same tile, with 128-key tiles on alternate tiles
+            const int t_end = U * HPS;
+            for (int t = wg; t < t_end; t += 2) {
+                const int u = t / HPS;
+                const int sb = u % NSB, pb = t % TC_NP;
+                TC_FAIL_IF(!mbar_wait(&bars.s_full[sb], (u / NSB) & 1, lim));
+                if (t >= T) {   // padding half of the last tile: nothing to do but release it
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
+                    continue;
+                }
                 tc_fence_after();
                 TC_PROF(0);
-                const uint32_t ta = lane_addr + sb * TC_BN;
+                const uint32_t ta = lane_addr + sb * SB + (t % HPS) * TC_BN;
                 float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -304,23 +327,23 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
                 const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
                 TC_PROF(1);
-                if (t > 0) {   // hand block t-1 over: every lane fences its own stores, one lane arrives for the warp
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[(t - 1) % TC_NP]), 1));
+                // decision for block t (needs the decision of block t-1)
+                float m_new = mx, alpha = 1.0f;
+                if (t > 0) {
+                    TC_FAIL_IF(!mbar_wait(&bars.decided[(t - 1) & 1], ((t - 1) >> 1) & 1, lim));
+                    const float m_prev = m_state[row];
+                    if ((mx - m_prev) * p.scale_log2 > TC_RESCALE_LOG2) alpha = fast_exp2((m_prev - mx) * p.scale_log2);
+                    else m_new = m_prev;
                 }
+                m_state[row] = m_new;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.decided[t & 1]);
+                if (last >= 0 && m_new != m_seen) l *= fast_exp2((m_seen - m_new) * p.scale_log2);
+                m_seen = m_new;
                 TC_PROF(4);
-                float alpha = 1.0f;
-                if (t == 0) {
-                    m_used = mx;
-                } else if ((mx - m_used) * p.scale_log2 > TC_RESCALE_LOG2) {
-                    alpha = fast_exp2((m_used - mx) * p.scale_log2);
-                    l *= alpha;
-                    m_used = mx;
-                }
                 TC_FAIL_IF(!mbar_wait_cluster(&bars.p_empty[pb], ((t / TC_NP) & 1) ^ 1, lim));
                 TC_PROF(2);
-                const float msl = m_used * p.scale_log2;
+                const float msl = m_new * p.scale_log2;
                 const uint32_t prow = p_remote + pb * TC_P_BYTES + row * 128;
                 float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
 #pragma unroll
@@ -343,21 +366,32 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 st_cluster_f32(alpha_remote + (pb * TC_BM + row) * 4, alpha);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
+                last = t;
                 TC_PROF(3);
-            }
-            if (!failed && T > 0) {   // hand the last block over
+                // hand the block over: every lane makes its stores visible to the peer's tensor core,
+                // one lane arrives for the warp (the other group computes meanwhile)
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[(T - 1) % TC_NP]), 1));
+                if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[pb]), 1));
+                TC_PROF(5);
             }
             TC_PROF_FLUSH(0, threadIdx.x == 64);
-            // row sums for the epilogue (sent even after a failure so that the peer is not left waiting)
-            st_cluster_f32(map_to_rank(smem_u32(lsum_smem), 1) + row * 4, l);
+            // this group's part of the row sums, brought to the final reference max (sent even after
+            // a failure so that the peer is not left waiting)
+            if (!failed && last >= 0 && last != T - 1) {
+                if (mbar_wait(&bars.decided[(T - 1) & 1], ((T - 1) >> 1) & 1, lim)) {
+                    const float m_fin = m_state[row];
+                    if (m_fin != m_seen) l *= fast_exp2((m_seen - m_fin) * p.scale_log2);
+                } else {
+                    atomicOr(p.err, (unsigned)KERR_MBAR_TIMEOUT);
+                }
+            }
+            st_cluster_f32(map_to_rank(smem_u32(lsum_smem), 1) + (wg * TC_BM + row) * 4, l);
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.l_full), 1));
         } else if (has_pe) {
             // ---- transform warps: encoding of the Q tile once, then of every K chunk ----
-            const int tid = threadIdx.x - 6 * 32;
+            const int tid = threadIdx.x - 10 * 32;
             const bool sinus = (p.pe == PE_SINUSOIDAL);
             int it = 0;
             do {
@@ -411,8 +445,10 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     TC_PROF(1);
                     for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
                         const int s = it % TC_NV;
+                        TC_PROF(2);
                         TC_FAIL_IF(!mbar_wait(&bars.v_full[s], (it / TC_NV) & 1, lim));
                         tc_fence_after();
+                        TC_PROF(3);
 #pragma unroll
                         for (int kk = 0; kk < TC_VS / 16; ++kk) {
                             const int kg = vs * (TC_VS / 16) + kk;   // 16-key step within the block, 0..7
@@ -462,7 +498,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 TC_FAIL_IF(!mbar_wait(&bars.pv_done[(T - 1) % TC_NP], ((T - 1) / TC_NP) & 1, lim));
                 tc_fence_after();
                 TC_FAIL_IF(!mbar_wait_cluster(&bars.l_full, 0, lim));
-                const float inv = 1.0f / lsum_smem[row];
+                const float inv = 1.0f / (lsum_smem[row] + lsum_smem[TC_BM + row]);
                 __nv_bfloat16 *orow = p.O + ((bh * p.Lq + qt * TC_BM + row) * (long long)D);
                 for (int c = 0; c < D / 32; ++c) {
                     tmem_ld32(lane_addr + c * 32, r);
@@ -598,9 +634,10 @@ inline bool tc_make_map(CUtensorMap *m, const void *base, long long rows, int D,
 }
 
 inline size_t tc_smem_bytes(int D, bool has_pe) {
-    const size_t ring = has_pe ? (size_t)3 * 2 * TC_CHUNK_BYTES : (size_t)TC_NK * TC_CHUNK_BYTES;
+    (void)has_pe;
+    const size_t ring = (size_t)3 * 2 * TC_CHUNK_BYTES;   // 3 stages of 32 KB: a 256-key K chunk, or a 128-key chunk + its encoding chunk
     const size_t score = (size_t)(D / 64) * TC_CHUNK_BYTES + ring;
-    const size_t outp = (size_t)TC_NP * TC_P_BYTES + (size_t)TC_NV * TC_VS * D * 2 + (size_t)(TC_NP + 1) * TC_BM * sizeof(float);
+    const size_t outp = (size_t)TC_NP * TC_P_BYTES + (size_t)TC_NV * TC_VS * D * 2 + (size_t)(TC_NP + 2) * TC_BM * sizeof(float);
     return (score > outp ? score : outp) + 1024;
 }
 
@@ -642,22 +679,25 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     p.spin_limit = spin_limit;
     p.debug_scores = debug_scores;
     CUtensorMap tmQ, tmK, tmV, tmPE;
-    if (!tc_make_map(&tmQ, a.Q, BH * a.len_q, D, TC_BM) || !tc_make_map(&tmK, a.K, BH * a.len_k, D, TC_BN) ||
+    if (!tc_make_map(&tmQ, a.Q, BH * a.len_q, D, TC_BM) || !tc_make_map(&tmK, a.K, BH * a.len_k, D, 256) ||
         !tc_make_map(&tmV, a.V, BH * a.len_k, D, TC_VS)) {
         snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
         return B200ATTN_ERR_CUDA;
     }
     tmPE = tmK;
-    p.k_stages = TC_NK;
-    p.k_stage_bytes = TC_CHUNK_BYTES;
+    p.sb_keys = 256;
+    p.k_stages = 3;
+    p.k_stage_bytes = 2 * TC_CHUNK_BYTES;
     if (a.pe != B200ATTN_PE_NONE) {
         const int L = a.len_q > a.len_k ? a.len_q : a.len_k;
         int rows = 0;
         const __nv_bfloat16 *tab = tables.get(a.pe, L, D, rd, a.pe == B200ATTN_PE_SINUSOIDAL ? 10000.0f : base, st, launches, &rows);
         if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the positional-encoding table"); return B200ATTN_ERR_CUDA; }
         if (!tc_make_map(&tmPE, tab, rows, D, TC_BN)) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
+        p.sb_keys = 128;
         p.k_stages = 3;
         p.k_stage_bytes = 2 * TC_CHUNK_BYTES;
+        if (!tc_make_map(&tmK, a.K, BH * a.len_k, D, 128)) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
     }
     const long long units = BH * p.n_qtiles;
     cudaLaunchConfig_t cfg = {};
