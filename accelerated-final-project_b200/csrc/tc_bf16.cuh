@@ -54,7 +54,9 @@ struct TcParams {
     int n_qtiles, n_blocks, n_chunks;   // Lq/128, Lk/128, D/64
     float scale_log2;                   // log2(e) / sqrt(D)
     int pe, rd;                         // PeKind; rotary_dim
-    int rotate_k;                       // 0 for PE_ROPE_Q_ONLY
+    int rotate_k;                       // 0: K is taken as given (pre-rotated by the caller, or the encoded-K cache)
+    int qt0, n_qt;                      // this launch covers query tiles [qt0, qt0 + n_qt) of every head
+    __nv_bfloat16 *k_store;             // optional: encoded K chunks are also written here ([BH*Lk][D])
     int sb_keys;                        // keys per score MMA tile: 256 (no encoding) or 128
     int k_stages, k_stage_bytes;        // K ring: 5 x 16 KB, or 3 x (16 KB K chunk + 16 KB encoding chunk)
     __nv_bfloat16 *O;
@@ -97,7 +99,8 @@ __device__ __forceinline__ uint32_t tc_pe_pair(uint32_t x, uint32_t t, bool sinu
     }
     return *reinterpret_cast<uint32_t *>(&r);
 }
-__device__ __forceinline__ void tc_pe_chunk(unsigned char *tile, const unsigned char *pe_tile, bool sinus, int tid) {
+__device__ __forceinline__ void tc_pe_chunk(unsigned char *tile, const unsigned char *pe_tile, bool sinus, int tid,
+                                            __nv_bfloat16 *gdst = nullptr, int D = 0) {
     uint4 *x = reinterpret_cast<uint4 *>(tile);
     const uint4 *t = reinterpret_cast<const uint4 *>(pe_tile);
 #pragma unroll
@@ -110,6 +113,10 @@ __device__ __forceinline__ void tc_pe_chunk(unsigned char *tile, const unsigned 
         v.z = tc_pe_pair(v.z, w.z, sinus);
         v.w = tc_pe_pair(v.w, w.w, sinus);
         x[o] = v;
+        if (gdst != nullptr) {   // un-swizzle: piece o is row o/8, logical 16-byte column (o%8) ^ (row%8)
+            const int r = o >> 3, q = (o & 7) ^ (r & 7);
+            *reinterpret_cast<uint4 *>(gdst + (long long)r * D + q * 8) = v;
+        }
     }
 }
 
@@ -148,8 +155,8 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t rank = cluster_ctarank();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = blockIdx.x >> 1;
-    const int qt = unit % p.n_qtiles;
-    const long long bh = unit / p.n_qtiles;
+    const int qt = p.qt0 + unit % p.n_qt;
+    const long long bh = unit / p.n_qt;
     const int D = p.D, nch = p.n_chunks, T = p.n_blocks;
     const uint32_t lim = p.spin_limit;
     const bool has_pe = (p.pe != PE_NONE);
@@ -411,7 +418,8 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         const int s = it % NKS;
                         TC_FAIL_IF(!mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
                         unsigned char *kt = k_smem + (size_t)s * KSB;
-                        tc_pe_chunk(kt, kt + TC_CHUNK_BYTES, sinus, tid);
+                        __nv_bfloat16 *gd = p.k_store ? p.k_store + ((bh * p.Lk + (long long)t * TC_BN) * D + c * 64) : nullptr;
+                        tc_pe_chunk(kt, kt + TC_CHUNK_BYTES, sinus, tid, gd, D);
                         fence_proxy_async();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&bars.k_ready[s]);
@@ -565,9 +573,24 @@ struct TcTables {
     static constexpr int kMax = 8;
     Entry e[kMax];
     int n = 0;
+    __nv_bfloat16 *kcache = nullptr;   // encoded K of the current call (see tc_bf16_run)
+    size_t kcache_bytes = 0;
     void release() {
         for (int i = 0; i < n; ++i) cudaFree(e[i].ptr);
         n = 0;
+        if (kcache) cudaFree(kcache);
+        kcache = nullptr;
+        kcache_bytes = 0;
+    }
+    __nv_bfloat16 *get_kcache(size_t bytes) {
+        if (bytes > kcache_bytes) {
+            if (kcache) { cudaDeviceSynchronize(); cudaFree(kcache); }
+            kcache = nullptr;
+            kcache_bytes = 0;
+            if (cudaMalloc(&kcache, bytes) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+            kcache_bytes = bytes;
+        }
+        return kcache;
     }
     // Returns a device table with at least L rows for the key, building it on `st` when it is new.
     __nv_bfloat16 *get(int pe, int L, int D, int rd, float base, cudaStream_t st, std::atomic<unsigned long long> *launches, int *rows) {
@@ -678,40 +701,61 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     p.err = err_dev;
     p.spin_limit = spin_limit;
     p.debug_scores = debug_scores;
-    CUtensorMap tmQ, tmK, tmV, tmPE;
-    if (!tc_make_map(&tmQ, a.Q, BH * a.len_q, D, TC_BM) || !tc_make_map(&tmK, a.K, BH * a.len_k, D, 256) ||
-        !tc_make_map(&tmV, a.V, BH * a.len_k, D, TC_VS)) {
+    p.k_stages = 3;
+    p.k_stage_bytes = 2 * TC_CHUNK_BYTES;
+    const bool has_pe = (a.pe != B200ATTN_PE_NONE);
+    CUtensorMap tmQ, tmK128, tmK256, tmV, tmPE;
+    if (!tc_make_map(&tmQ, a.Q, BH * a.len_q, D, TC_BM) || !tc_make_map(&tmK128, a.K, BH * a.len_k, D, 128) ||
+        !tc_make_map(&tmK256, a.K, BH * a.len_k, D, 256) || !tc_make_map(&tmV, a.V, BH * a.len_k, D, TC_VS)) {
         snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
         return B200ATTN_ERR_CUDA;
     }
-    tmPE = tmK;
-    p.sb_keys = 256;
-    p.k_stages = 3;
-    p.k_stage_bytes = 2 * TC_CHUNK_BYTES;
-    if (a.pe != B200ATTN_PE_NONE) {
+    tmPE = tmK128;
+    if (has_pe) {
         const int L = a.len_q > a.len_k ? a.len_q : a.len_k;
         int rows = 0;
         const __nv_bfloat16 *tab = tables.get(a.pe, L, D, rd, a.pe == B200ATTN_PE_SINUSOIDAL ? 10000.0f : base, st, launches, &rows);
         if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the positional-encoding table"); return B200ATTN_ERR_CUDA; }
         if (!tc_make_map(&tmPE, tab, rows, D, TC_BN)) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
-        p.sb_keys = 128;
-        p.k_stages = 3;
-        p.k_stage_bytes = 2 * TC_CHUNK_BYTES;
-        if (!tc_make_map(&tmK, a.K, BH * a.len_k, D, 128)) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
     }
-    const long long units = BH * p.n_qtiles;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(2 * units));
-    cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, tc_bf16_pair_kernel, tmQ, tmK, tmV, tmPE, p);
-    if (e != cudaSuccess) {
-        snprintf(t_tc_error, sizeof t_tc_error, "tc_bf16_pair_kernel launch failed: %s", cudaGetErrorString(e));
-        return B200ATTN_ERR_CUDA;
+    auto launch = [&](const CUtensorMap &mK, int qt0, int n_qt) -> int {
+        p.qt0 = qt0; p.n_qt = n_qt;
+        const long long units = BH * n_qt;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(2 * units));
+        cfg.blockDim = dim3(TC_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, tc_bf16_pair_kernel, tmQ, mK, tmV, tmPE, p);
+        if (e != cudaSuccess) {
+            snprintf(t_tc_error, sizeof t_tc_error, "tc_bf16_pair_kernel launch failed: %s", cudaGetErrorString(e));
+            return B200ATTN_ERR_CUDA;
+        }
+        launches->fetch_add(1);
+        return B200ATTN_OK;
+    };
+    const bool pe_k = has_pe && p.rotate_k;
+    // Encoded-K cache.  When K carries an encoding and a head has several query tiles, the unit of
+    // the head's FIRST query tile encodes K inside its K load (as every unit would) and, while the
+    // encoded chunk is in registers, also writes it to a scratch copy; the units of the other query
+    // tiles of that head then load the encoded K and run without the transform (second launch,
+    // stream-ordered after the first).  The encoding is still applied once, inside a K load, by
+    // the attention kernel itself; the scratch is as large as K.
+    if (pe_k && p.n_qtiles >= 3 && !getenv("B200ATTN_NO_KCACHE")) {
+        const size_t kbytes = (size_t)BH * a.len_k * D * sizeof(__nv_bfloat16);
+        __nv_bfloat16 *kc = tables.get_kcache(kbytes);
+        CUtensorMap tmKc;
+        if (kc != nullptr && tc_make_map(&tmKc, kc, BH * a.len_k, D, 256)) {
+            p.sb_keys = 128; p.k_store = kc;
+            int rc = launch(tmK128, 0, 1);
+            if (rc) return rc;
+            p.sb_keys = 256; p.k_store = nullptr; p.rotate_k = 0;
+            return launch(tmKc, 1, p.n_qtiles - 1);
+        }
     }
-    launches->fetch_add(1);
-    return B200ATTN_OK;
+    p.k_store = nullptr;
+    p.sb_keys = pe_k ? 128 : 256;
+    return launch(pe_k ? tmK128 : tmK256, 0, p.n_qtiles);
 }
 
 }  // namespace b200attn
