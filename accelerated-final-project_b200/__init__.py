@@ -76,6 +76,9 @@ def lib():
         L.b200attn_launch_count.restype = C.c_ulonglong
         L.b200attn_version.restype = C.c_char_p
         L.b200attn_release_workspace.restype = None
+        L.b200attn_forward_static.argtypes = [C.c_void_p] * 4 + [C.c_int] * 5 + [C.c_void_p]
+        L.b200attn_forward_static.restype = C.c_int
+        L.b200attn_static_last_error.restype = C.c_char_p
         L.b200attn_synth_fill.argtypes = [C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong,
                                           C.c_int, C.c_int, C.c_void_p]
         L.b200attn_synth_fill.restype = C.c_int

@@ -177,6 +177,24 @@ void b200attn_release_workspace(void);
 /* Library version string. */
 const char *b200attn_version(void);
 
+/* fp32 forward without positional encoding that never allocates device memory: its scratch is a
+ * fixed array inside the library image (B200ATTN_STATIC_SCRATCH_BYTES per GPU, held from library
+ * load to process exit).  For callers that cannot call cudaMalloc when they need attention: code
+ * recording a CUDA graph, or code living under a framework allocator that owns the device.
+ * No counterpart in the reference (its launcher needs no scratch).  Device pointers as for
+ * attention_forward_optimized; the work is enqueued on `stream` and NOT waited for.  Limits:
+ * len_q, len_k <= 64, batch_sz*num_heads <= SM count, and
+ * 256 + round_up(8*batch_sz*num_heads, 256) + 4*batch_sz*num_heads*len_q*len_k bytes within the
+ * static scratch; beyond them the call returns B200ATTN_ERR_TOO_LARGE and does nothing.  The first
+ * call on a device does host-side set-up (symbol address, shared-memory limit): make it before any
+ * stream capture.  All calls share the one array, so calls that overlap on the GPU race; the kernel's
+ * error word is not read back (check the output, or use b200attn_forward_ex).  Message of the last
+ * failure on this thread: b200attn_static_last_error(). */
+#define B200ATTN_STATIC_SCRATCH_BYTES 1048576u
+int b200attn_forward_static(const float *Q, const float *K, const float *V, float *out, int batch_sz, int num_heads,
+                            int len_q, int len_k, int head_d, void *stream);
+const char *b200attn_static_last_error(void);
+
 /* Fills a device buffer with the synthetic inputs the tests and the benchmark use: element i gets
  * a value drawn from splitmix64(seed*2^40 + tensor_id*2^36 + index0 + i); dist 0 = uniform[-1,1),
  * 1 = normal(0,1) by Box-Muller; stored as fp32 or rounded to bf16. */
