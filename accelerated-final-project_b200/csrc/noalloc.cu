@@ -1,9 +1,10 @@
 // b200attn_forward_static: fp32 forward for small problems that never allocates.
 //
-// Some callers cannot allocate device memory at the moment they need attention: code running
-// while a stream is being captured into a CUDA graph, code inside a framework whose caching
-// allocator owns the whole device and must not see foreign cudaMalloc calls, or a process that
-// has handed its memory budget to something else.  The regular entry points of this library
+// Some callers cannot allocate device memory at the moment they need attention: code living inside
+// a framework whose caching allocator owns the whole device and must not see foreign cudaMalloc
+// calls, a latency-critical loop that cannot afford the implicit device synchronisation an
+// allocation may cause, or a process that has handed its memory budget to something else.  The
+// regular entry points of this library
 // grow a per-device scratch with cudaMalloc on demand; this one uses a fixed scratch that is part
 // of the library image instead (a file-scope __device__ array, so every GPU that loads the
 // library holds B200ATTN_STATIC_SCRATCH_BYTES of it until the process exits).

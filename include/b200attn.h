@@ -180,7 +180,8 @@ const char *b200attn_version(void);
 /* fp32 forward without positional encoding that never allocates device memory: its scratch is a
  * fixed array inside the library image (B200ATTN_STATIC_SCRATCH_BYTES per GPU, held from library
  * load to process exit).  For callers that cannot call cudaMalloc when they need attention: code
- * recording a CUDA graph, or code living under a framework allocator that owns the device.
+ * living under a framework allocator that owns the device, or a latency-critical loop that cannot
+ * afford the implicit synchronisation of an allocation.
  * No counterpart in the reference (its launcher needs no scratch).  Device pointers as for
  * attention_forward_optimized; the work is enqueued on `stream` and NOT waited for.  Limits:
  * len_q, len_k <= 64, batch_sz*num_heads <= SM count, and

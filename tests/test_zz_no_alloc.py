@@ -1,6 +1,6 @@
 """GPU test of b200attn_forward_static, the entry point for callers that cannot allocate device
-memory when they need attention (code recording a CUDA graph, or code living under a framework
-allocator that owns the device): its scratch is a fixed array inside the library image.  Called
+memory when they need attention (code living under a framework allocator that owns the device, or a
+latency-critical loop that cannot afford the implicit synchronisation of an allocation): its scratch is a fixed array inside the library image.  Called
 through the C ABI twice in a row (the array is shared by all calls and keeps the previous call's
 contents, so the second call must not be disturbed by the first) and compared with the regular
 entry point under the fp32 tolerance of the other tests (max-abs 1e-4 / rel 1e-3).
