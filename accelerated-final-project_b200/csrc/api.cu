@@ -185,8 +185,17 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
         if (nsplit_max < 1) fused = false;
         else {
             ds = (int)((D + nsplit_max - 1) / nsplit_max);
-            ds = (ds + 7) & ~7;
-            if (ds < 8) ds = 8;
+            if (p.use_tma) {
+                // packed TMA tiles: slice width a multiple of 4 with ds/4 odd (16 rows then cover all
+                // shared-memory banks) and within the 256-element box limit
+                ds = (ds + 3) & ~3;
+                if (((ds >> 2) & 1) == 0) ds += 4;
+                if (ds > 252) p.use_tma = 0;
+            }
+            if (!p.use_tma) {
+                ds = (ds + 7) & ~7;
+                if (ds < 8) ds = 8;
+            }
             if (ds > kSplitDMaxDs) fused = false;
             nsplit = (D + ds - 1) / ds;
             smem = fused_smem_bytes(ds);
@@ -208,8 +217,16 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
         int rc = ensure_scratch(c, (size_t)BH * Lq * Lk * sizeof(float), (size_t)2 * BH, st);
         if (rc) return rc;
         p.S = c.S; p.counters = c.counters; p.ds = ds; p.nsplit = nsplit;
+        CUtensorMap tmQ, tmK, tmV;
+        memset(&tmQ, 0, sizeof tmQ); memset(&tmK, 0, sizeof tmK); memset(&tmV, 0, sizeof tmV);
+        if (p.use_tma) {
+            if (!make_tmap_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.Q, BH * Lq, D, ds, Lq, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                !make_tmap_2d(&tmK, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.K, BH * Lk, D, ds, Lk, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                !make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.V, BH * Lk, D, ds, Lk, CU_TENSOR_MAP_SWIZZLE_NONE))
+                return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the split-head_d slices");
+        }
         dim3 grid(nsplit, (unsigned)BH);
-        void *kargs[] = {&p};
+        void *kargs[] = {&tmQ, &tmK, &tmV, &p};
         CU_TRY(cudaLaunchCooperativeKernel((const void *)splitd_fused_kernel<T>, grid, dim3(SD_THREADS), kargs, smem, st));
         g_launches.fetch_add(1);
         t_last_path = "splitd_fused";
@@ -428,6 +445,12 @@ int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
     if (rc) return fail(rc, "%s", tc_bf16_error());
     return check_kernel_errors(*c, (cudaStream_t)a->stream, true);
 }
+
+#ifdef B200ATTN_SD_PROFILE
+int b200attn_debug_sd_stamps(unsigned long long *out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, sd_stamps, (size_t)n * sizeof(unsigned long long));
+}
+#endif
 
 #ifdef B200ATTN_TC_PROFILE
 int b200attn_debug_tc_prof(unsigned long long *out32, int reset) {

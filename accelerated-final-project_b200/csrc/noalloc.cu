@@ -22,6 +22,7 @@
 // calls that overlap on the GPU (different streams, no dependency) would race on it.
 #include <cmath>
 #include <cstdio>
+#include <cstring>
 #include <mutex>
 
 #include "../../include/b200attn.h"
@@ -93,13 +94,29 @@ extern "C" int b200attn_forward_static(const float *Q, const float *K, const flo
     const size_t need = 256 + counters_bytes + scores_bytes;
     if (need > kStaticScratchBytes) return static_fail(B200ATTN_ERR_TOO_LARGE, "b200attn_forward_static: batch*heads*len_q*len_k exceeds the static scratch");
 
+    // slice width as in the regular entry point: packed TMA tiles want ds a multiple of 4 with ds/4 odd
+    const bool tma_ok = (D % 4 == 0) && ((((uintptr_t)Q | (uintptr_t)K | (uintptr_t)V) & 15) == 0);
     long long nsplit_max = sd.sm_count / BH;
     int ds = (int)((D + nsplit_max - 1) / nsplit_max);
-    ds = (ds + 7) & ~7;
-    if (ds < 8) ds = 8;
+    bool use_tma = tma_ok;
+    if (use_tma) {
+        ds = (ds + 3) & ~3;
+        if (((ds >> 2) & 1) == 0) ds += 4;
+        if (ds > 252) use_tma = false;
+    }
+    if (!use_tma) {
+        ds = (ds + 7) & ~7;
+        if (ds < 8) ds = 8;
+    }
     const int nsplit = (D + ds - 1) / ds;
     const size_t smem = ((size_t)3 * SD_TILE * (ds + 4) + (size_t)SD_TILE * SD_PT_PITCH + ds / 2 + 4) * sizeof(float);
     if (smem > sd.dyn_smem_max) return static_fail(B200ATTN_ERR_TOO_LARGE, "b200attn_forward_static: head_d too large for one slice per SM");
+    CUtensorMap tmQ, tmK, tmV;   // encoded on the host; no device allocation involved
+    memset(&tmQ, 0, sizeof tmQ); memset(&tmK, 0, sizeof tmK); memset(&tmV, 0, sizeof tmV);
+    if (use_tma && (!make_tmap_2d(&tmQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, Q, BH * Lq, D, ds, Lq, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                    !make_tmap_2d(&tmK, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, K, BH * Lk, D, ds, Lk, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+                    !make_tmap_2d(&tmV, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, V, BH * Lk, D, ds, Lk, CU_TENSOR_MAP_SWIZZLE_NONE)))
+        return static_fail(B200ATTN_ERR_CUDA, "b200attn_forward_static: cuTensorMapEncodeTiled failed");
 
     cudaStream_t st = (cudaStream_t)stream;
     // the array keeps whatever the last call left: clear the part this call reads before writing
@@ -115,9 +132,9 @@ extern "C" int b200attn_forward_static(const float *Q, const float *K, const flo
     p.counters = reinterpret_cast<unsigned *>(sd.scratch + 256);
     p.S = reinterpret_cast<float *>(sd.scratch + 256 + counters_bytes);
     p.spin_limit = 1u << 21;
-    p.use_tma = (D % 4 == 0 && ((((uintptr_t)Q | (uintptr_t)K | (uintptr_t)V) & 15) == 0)) ? 1 : 0;
+    p.use_tma = use_tma ? 1 : 0;
     dim3 grid(nsplit, (unsigned)BH);
-    void *kargs[] = {&p};
+    void *kargs[] = {&tmQ, &tmK, &tmV, &p};
     e = cudaLaunchCooperativeKernel((const void *)splitd_fused_kernel<float>, grid, dim3(SD_THREADS), kargs, smem, st);
     if (e != cudaSuccess) return static_fail(B200ATTN_ERR_CUDA, cudaGetErrorString(e));
     return B200ATTN_OK;

@@ -19,7 +19,7 @@
 // launches (scores, then softmax+PV) tiled 64 x 64 over queries and keys.
 #pragma once
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace b200attn {
 
@@ -41,7 +41,7 @@ struct SplitDParams {
     unsigned *counters;      // fused kernel: [2*BH] arrive / done counters, zero on entry and on exit
     unsigned *err;           // error word (KernelErr bits)
     unsigned spin_limit;     // polls before a wait gives up
-    int use_tma;             // fp32, no PE, D % 4 == 0: stage slices with cp.async.bulk
+    int use_tma;             // fp32, no PE, D % 4 == 0: stage slices with three tiled TMA loads (tensor maps)
     int dv;                  // two-pass PV kernel: width of an output column slice
 };
 
@@ -145,12 +145,6 @@ __device__ __forceinline__ void fill_freqs(float *freq_s, int v0, int w, float b
         freq_s[i] = 1.0f / powf(base, (2.0f * (float)(p0 + i)) / (float)rd);
 }
 
-// TMA staging of a slice: one bulk copy per row (fp32, columns [v0, v0+w), w % 4 == 0).
-__device__ __forceinline__ void tma_rows(float *dst, int pitch, const float *src, int rows, int D, int v0, int w,
-                                         uint64_t *bar) {
-    for (int r = threadIdx.x; r < rows; r += blockDim.x)
-        bulk_g2s(dst + (long long)r * pitch, src + (long long)r * D + v0, (uint32_t)w * 4u, bar);
-}
 __device__ __forceinline__ void zero_rows(float *dst, int pitch, int row_begin, int row_end, int ncols) {
     const int n = (row_end - row_begin) * ncols;
     for (int i = threadIdx.x; i < n; i += blockDim.x) dst[(long long)(row_begin + i / ncols) * pitch + (i % ncols)] = 0.0f;
@@ -247,17 +241,33 @@ __device__ __forceinline__ void store_unit(T *O, int D, int nq, int w, int v0, i
 // Fused kernel: grid (nsplit, BH), cooperative launch, Lq <= 64 and Lk <= 64.
 // Dynamic shared memory: Qs[64][ds+4] | Ks[64][ds+4] | Vs[64][ds+4] | Pt[64][68] | freq[ds/2].
 // ------------------------------------------------------------------------------------------------
+// Optional phase timestamps (build with -DB200ATTN_SD_PROFILE): CTA b writes globaltimer at stage k to sd_stamps[b*8+k].
+#ifdef B200ATTN_SD_PROFILE
+__device__ unsigned long long sd_stamps[8 * 1024];
+#define SD_STAMP(k) do { if (threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+    sd_stamps[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (k)] = t_; } } while (0)
+#else
+#define SD_STAMP(k)
+#endif
+
 template <typename T>
-__global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const SplitDParams p) {
+__global__ void __launch_bounds__(SD_THREADS, 1)
+splitd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const SplitDParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_qk, bar_v;
     __shared__ unsigned s_flag;
 
+    SD_STAMP(0);
     const int slice = blockIdx.x;
     const long long bh = blockIdx.y;
     const int v0 = slice * p.ds;
     const int w = min(p.ds, p.D - v0);
-    const int pitch = p.ds + 4;
+    bool tma = false;
+    if constexpr (sizeof(T) == 4) tma = (p.use_tma != 0);
+    // TMA tiles are packed (row pitch = ds, chosen with ds/4 odd so that 16 rows spread over all
+    // banks); the register-staged path pads the pitch instead
+    const int pitch = tma ? p.ds : p.ds + 4;
     const int Lq = p.Lq, Lk = p.Lk, D = p.D;
     const int rq_pad = Lq <= 16 ? 16 : (Lq <= 32 ? 32 : 64), rk_pad = Lk <= 16 ? 16 : (Lk <= 32 ? 32 : 64);
 
@@ -273,8 +283,6 @@ __global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const Split
     T *Og = reinterpret_cast<T *>(p.O) + bh * Lq * D;
     float *Sg = p.S + bh * Lq * Lk;
 
-    bool tma = false;
-    if constexpr (sizeof(T) == 4) tma = (p.use_tma != 0);
     const int wq = (w + 3) & ~3;
 
     // ---- stage the slice ----
@@ -283,17 +291,15 @@ __global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const Split
             mbar_init(&bar_qk, 1);
             mbar_init(&bar_v, 1);
             mbar_fence_init();
+            // one tiled load per tensor: box = [L rows x ds columns] at (column v0, row bh*L); columns
+            // beyond head_d read as zero and still count as transferred bytes
+            mbar_expect_tx(&bar_qk, (uint32_t)(Lq + Lk) * (uint32_t)p.ds * 4u);
+            tma_load_2d(Qs, &tmQ, v0, (int)(bh * Lq), &bar_qk);
+            tma_load_2d(Ks, &tmK, v0, (int)(bh * Lk), &bar_qk);
+            mbar_expect_tx(&bar_v, (uint32_t)Lk * (uint32_t)p.ds * 4u);
+            tma_load_2d(Vs, &tmV, v0, (int)(bh * Lk), &bar_v);
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            mbar_expect_tx(&bar_qk, (uint32_t)(Lq + Lk) * (uint32_t)w * 4u);
-            mbar_expect_tx(&bar_v, (uint32_t)Lk * (uint32_t)w * 4u);
-        }
-        if constexpr (sizeof(T) == 4) {
-            tma_rows(Qs, pitch, Qg, Lq, D, v0, w, &bar_qk);
-            tma_rows(Ks, pitch, Kg, Lk, D, v0, w, &bar_qk);
-            tma_rows(Vs, pitch, Vg, Lk, D, v0, w, &bar_v);
-        }
         zero_rows(Qs, pitch, Lq, rq_pad, wq);
         zero_rows(Ks, pitch, Lk, rk_pad, wq);
     } else {
@@ -311,6 +317,7 @@ __global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const Split
     bool ok = true;
     if (tma) ok = mbar_wait(&bar_qk, 0, p.spin_limit);
     __syncthreads();
+    SD_STAMP(1);
 
     // ---- phase 1: partial scores of this slice ----
     float acc[4][4];
@@ -323,8 +330,10 @@ __global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const Split
     emit_scores(Sg, Lk, 0, 0, Lq, Lk, acc, !single);
 
     // ---- per-head barrier: all slices of this head have added their partial scores ----
+    SD_STAMP(2);
     __threadfence();
     __syncthreads();
+    SD_STAMP(3);
     if (threadIdx.x == 0) {
         unsigned flag = ok ? 0u : KERR_MBAR_TIMEOUT;
         if (!single) {
@@ -341,21 +350,34 @@ __global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const Split
         s_flag = flag;
     }
     __syncthreads();
+    SD_STAMP(4);
     const bool failed = (s_flag != 0);
 
     // ---- phase 2a: softmax of the full score matrix into the transposed tile Pt[j][i] ----
     if (!failed) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
         const int lq4 = (Lq + 3) & ~3;
-        for (int i = warp; i < lq4; i += SD_THREADS / 32) {
-            float s0 = -INFINITY, s1 = -INFINITY;
+        // all score loads of the warp's (up to 8) rows are issued before any of them is used: the
+        // matrix lives in L2 and one dependent round trip per row would cost more than the softmax
+        constexpr int RPW = SD_TILE / (SD_THREADS / 32);
+        float s0[RPW], s1[RPW];
+#pragma unroll
+        for (int k = 0; k < RPW; ++k) {
+            const int i = warp + k * (SD_THREADS / 32);
+            s0[k] = -INFINITY; s1[k] = -INFINITY;
             if (i < Lq) {
-                if (lane < Lk) s0 = __ldcg(Sg + (long long)i * Lk + lane) * p.scale;
-                if (lane + 32 < Lk) s1 = __ldcg(Sg + (long long)i * Lk + lane + 32) * p.scale;
+                if (lane < Lk) s0[k] = __ldcg(Sg + (long long)i * Lk + lane);
+                if (lane + 32 < Lk) s1[k] = __ldcg(Sg + (long long)i * Lk + lane + 32);
             }
-            const float m = warp_max(fmaxf(s0, s1));
-            const float e0 = (i < Lq && lane < Lk) ? expf(s0 - m) : 0.0f;
-            const float e1 = (i < Lq && lane + 32 < Lk) ? expf(s1 - m) : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < RPW; ++k) {
+            const int i = warp + k * (SD_THREADS / 32);
+            if (i >= lq4) break;
+            const float a0 = s0[k] * p.scale, a1 = s1[k] * p.scale;
+            const float m = warp_max(fmaxf(a0, a1));
+            const float e0 = (i < Lq && lane < Lk) ? expf(a0 - m) : 0.0f;
+            const float e1 = (i < Lq && lane + 32 < Lk) ? expf(a1 - m) : 0.0f;
             const float tot = warp_sum(e0 + e1);
             if (lane < Lk) Pt[lane * SD_PT_PITCH + i] = (i < Lq) ? e0 / tot : 0.0f;
             if (lane + 32 < Lk) Pt[(lane + 32) * SD_PT_PITCH + i] = (i < Lq) ? e1 / tot : 0.0f;
@@ -374,6 +396,7 @@ __global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const Split
     }
 
     // ---- phase 2b: O[:, slice] = P * V[:, slice] ----
+    SD_STAMP(5);
     bool okv = true;
     if (tma) okv = mbar_wait(&bar_v, 0, p.spin_limit);
     if (!okv && threadIdx.x == 0) atomicOr(p.err, (unsigned)KERR_MBAR_TIMEOUT);
@@ -394,6 +417,7 @@ __global__ void __launch_bounds__(SD_THREADS, 1) splitd_fused_kernel(const Split
         pv_unit(Pt, Vs, pitch, Lk, r0, c4, o);
         store_unit<T>(Og, D, Lq, w, v0, r0, c4, o);
     }
+    SD_STAMP(6);
 }
 
 // ------------------------------------------------------------------------------------------------

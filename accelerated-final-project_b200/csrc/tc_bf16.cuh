@@ -629,31 +629,9 @@ inline bool tc_bf16_supported(const b200attn_args &a, int rd) {
     return true;
 }
 
-typedef CUresult (*PFN_tmapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                         const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                         CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-inline PFN_tmapEncodeTiled tc_encode_fn() {
-    static PFN_tmapEncodeTiled fn = [] {
-        void *f = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess)
-            f = nullptr;
-        return (PFN_tmapEncodeTiled)f;
-    }();
-    return fn;
-}
-
 // 2-D bf16 tensor map over a [rows][D] row-major matrix with a [box_rows][64] box, 128-byte swizzle.
 inline bool tc_make_map(CUtensorMap *m, const void *base, long long rows, int D, int box_rows) {
-    PFN_tmapEncodeTiled enc = tc_encode_fn();
-    if (!enc) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return make_tmap_2d(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, rows, D, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 inline size_t tc_smem_bytes(int D, bool has_pe) {
