@@ -227,7 +227,12 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
         }
         dim3 grid(nsplit, (unsigned)BH);
         void *kargs[] = {&tmQ, &tmK, &tmV, &p};
-        CU_TRY(cudaLaunchCooperativeKernel((const void *)splitd_fused_kernel<T>, grid, dim3(SD_THREADS), kargs, smem, st));
+        if (getenv("B200ATTN_SPLITD_PLAIN_LAUNCH")) {   // experiment: no co-residency guarantee, waits are bounded
+            splitd_fused_kernel<T><<<grid, SD_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
+            CU_TRY(cudaGetLastError());
+        } else {
+            CU_TRY(cudaLaunchCooperativeKernel((const void *)splitd_fused_kernel<T>, grid, dim3(SD_THREADS), kargs, smem, st));
+        }
         g_launches.fetch_add(1);
         t_last_path = "splitd_fused";
         return B200ATTN_OK;

@@ -384,17 +384,9 @@ splitd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
     }
     __syncthreads();
-    // ---- scratch hygiene: the last slice of the head to have read S zeroes it for the next call ----
-    if (!failed) {
-        if (threadIdx.x == 0)
-            s_flag = (single || atomicAdd(&p.counters[2 * bh + 1], 1u) == (unsigned)p.nsplit - 1u) ? 1u : 0u;
-        __syncthreads();
-        if (s_flag) {
-            for (int i = threadIdx.x; i < Lq * Lk; i += SD_THREADS) Sg[i] = 0.0f;
-            if (threadIdx.x == 0 && !single) { p.counters[2 * bh] = 0u; p.counters[2 * bh + 1] = 0u; }
-        }
-    }
-
+    // every thread has read its scores (they are in Pt now); the count of readers is taken here,
+    // without waiting for the answer: the clean-up itself is at the very end of the kernel
+    __syncthreads();
     // ---- phase 2b: O[:, slice] = P * V[:, slice] ----
     SD_STAMP(5);
     bool okv = true;
@@ -418,6 +410,15 @@ splitd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         store_unit<T>(Og, D, Lq, w, v0, r0, c4, o);
     }
     SD_STAMP(6);
+    // ---- scratch hygiene, off the critical path: the last slice of the head to get here (all of them
+    // read S before their PV phase) zeroes the head's scores and counters for the next call ----
+    if (threadIdx.x == 0)
+        s_flag = (single || atomicAdd(&p.counters[2 * bh + 1], 1u) == (unsigned)p.nsplit - 1u) ? 1u : 0u;
+    __syncthreads();
+    if (s_flag) {
+        for (int i = threadIdx.x; i < Lq * Lk; i += SD_THREADS) Sg[i] = 0.0f;
+        if (threadIdx.x == 0 && !single) { p.counters[2 * bh] = 0u; p.counters[2 * bh + 1] = 0u; }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
