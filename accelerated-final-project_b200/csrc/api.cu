@@ -329,7 +329,8 @@ static int check_kernel_errors(DeviceCtx &c, cudaStream_t st, bool sync) {
         unsigned bits = *c.err_host;
         c.scratch_dirty = true;
         *c.err_host = 0;
-        return fail(B200ATTN_ERR_KERNEL, "kernel reported error bits 0x%x (1: head barrier wait expired, 2: mbarrier wait expired, 4: tensor memory)", bits);
+        cudaMemsetAsync(c.err_dev, 0, sizeof(unsigned), st);   // the error is reported once; later launches start clean
+        return fail(B200ATTN_ERR_KERNEL, "kernel reported error bits 0x%x (bit 0: head barrier wait expired, bit 1: mbarrier wait expired, bits 8..31: which wait of the tensor-core kernel)", bits);
     }
     return B200ATTN_OK;
 }

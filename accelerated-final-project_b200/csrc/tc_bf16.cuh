@@ -45,6 +45,7 @@ constexpr int TC_NK = 5;          // K chunk ring depth (score CTA)
 constexpr int TC_NS = 4;          // S buffers in tensor memory (4 x 128 columns)
 constexpr int TC_NP = 3;          // P buffers (output CTA shared memory)
 constexpr int TC_NV = 3;          // V stage ring depth (output CTA)
+constexpr int TC_NL = 8;          // row-sum slots in flight (the score CTA may run a few units ahead)
 constexpr int TC_CHUNK_BYTES = TC_BM * 128;          // [128 rows x 64 bf16]
 constexpr int TC_P_BYTES = TC_BM * TC_BN * 2;        // one P buffer
 constexpr float TC_RESCALE_LOG2 = 8.0f;              // rescale O only when the max grew by > 2^8
@@ -56,6 +57,7 @@ struct TcParams {
     int pe, rd;                         // PeKind; rotary_dim
     int rotate_k;                       // 0: K is taken as given (pre-rotated by the caller, or the encoded-K cache)
     int qt0, n_qt;                      // this launch covers query tiles [qt0, qt0 + n_qt) of every head
+    long long n_units;                  // BH * n_qt units, dealt round-robin to the persistent clusters
     __nv_bfloat16 *k_store;             // optional: encoded K chunks are also written here ([BH*Lk][D])
     int sb_keys;                        // keys per score MMA tile: 256 (no encoding) or 128
     int k_stages, k_stage_bytes;        // K ring: 5 x 16 KB, or 3 x (16 KB K chunk + 16 KB encoding chunk)
@@ -66,7 +68,7 @@ struct TcParams {
 };
 
 struct TcBarriers {
-    uint64_t q_full, q_ready;
+    uint64_t q_full, q_empty;   // Q tile of the unit landed / was read by the unit's last score MMA
     uint64_t k_full[TC_NK], k_ready[TC_NK], k_empty[TC_NK];
     uint64_t s_full[TC_NS], s_empty[TC_NS];
     uint64_t p_empty[TC_NP];    // in the score CTA; arrived by the output CTA's relay warp
@@ -74,7 +76,7 @@ struct TcBarriers {
     uint64_t p_full[TC_NP];     // in the output CTA; arrived by the score CTA's softmax threads
     uint64_t pv_done[TC_NP];
     uint64_t corr_done[TC_NP];
-    uint64_t l_full;
+    uint64_t l_full[TC_NL];     // row sums of unit (ui % TC_NL) have been sent
     uint64_t decided[2];        // score CTA: reference max of block t settled (t & 1)
 };
 
@@ -132,11 +134,13 @@ __device__ unsigned long long tc_prof[32];
 #define TC_PROF_FLUSH(base, on)
 #endif
 
-#define TC_FAIL_IF(cond)                                         \
-    if (cond) {                                                  \
-        atomicOr(p.err, (unsigned)KERR_MBAR_TIMEOUT);            \
-        failed = true;                                           \
-        break;                                                   \
+// A bounded wait that expired: record the error bit and, in bits 8.., which wait it was (the
+// sites are numbered in source order), then leave the enclosing loop.
+#define TC_FAIL_AT(site, cond)                                                     \
+    if (cond) {                                                                    \
+        atomicOr(p.err, (unsigned)KERR_MBAR_TIMEOUT | (1u << (7 + (site))));       \
+        failed = true;                                                             \
+        break;                                                                     \
     }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
@@ -146,7 +150,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     __shared__ TcBarriers bars;
     __shared__ uint32_t tmem_slot;
     __shared__ unsigned skip_flag;
-    __shared__ float m_state[TC_BM];
+    __shared__ float m_state[2][TC_BM];   // reference maxima of the rows, by unit parity
 
     // 1024-byte aligned base; identical offset in both CTAs of the cluster (same kernel, same layout)
     const uint32_t raw_addr = smem_u32(tc_smem_raw);
@@ -154,9 +158,10 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     const uint32_t rank = cluster_ctarank();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int unit = blockIdx.x >> 1;
-    const int qt = p.qt0 + unit % p.n_qt;
-    const long long bh = unit / p.n_qt;
+    // Persistent clusters: cluster k runs the units k, k + n_clusters, ...  Ring and barrier phases
+    // run on through the units, so the score CTA starts the next unit (Q load, first score tiles,
+    // softmax) while the output CTA is still finishing and storing the previous one.
+    const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
     const int D = p.D, nch = p.n_chunks, T = p.n_blocks;
     const uint32_t lim = p.spin_limit;
     const bool has_pe = (p.pe != PE_NONE);
@@ -169,7 +174,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     // ---- shared-memory carve-up ----
     // score CTA : [Q: nch chunks of 16 KB][K ring: k_stages stages of (K chunk [+ encoding chunk])]
-    // output CTA: [P: TC_NP x 32 KB][V ring: TC_NV stages of TC_VS*D*2 B][alpha: TC_NP x 128 f32][lsum: 128 f32]
+    // output CTA: [P: TC_NP x 32 KB][V ring: TC_NV stages of TC_VS*D*2 B][alpha: TC_NP x 128 f32][lsum: TC_NL x 2 x 128 f32]
     unsigned char *q_smem = smem;
     unsigned char *k_smem = smem + (size_t)nch * TC_CHUNK_BYTES;
     unsigned char *p_smem = smem;
@@ -180,7 +185,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (threadIdx.x == 0) {
         mbar_init(&bars.q_full, 1);
-        mbar_init(&bars.q_ready, 4);
+        mbar_init(&bars.q_empty, 1);
         for (int i = 0; i < TC_NK; ++i) { mbar_init(&bars.k_full[i], 1); mbar_init(&bars.k_ready[i], 4); mbar_init(&bars.k_empty[i], 1); }
         for (int i = 0; i < TC_NS; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.s_empty[i], 4 * (p.sb_keys / TC_BN)); }
         for (int i = 0; i < TC_NV; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
@@ -190,7 +195,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_init(&bars.pv_done[i], 1);
             mbar_init(&bars.corr_done[i], 4);
         }
-        mbar_init(&bars.l_full, 8);
+        for (int i = 0; i < TC_NL; ++i) mbar_init(&bars.l_full[i], p.n_blocks >= 2 ? 8 : 4);
         mbar_init(&bars.decided[0], 4);
         mbar_init(&bars.decided[1], 4);
         mbar_fence_init();
@@ -216,6 +221,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     bool failed = false;
     const bool skip = (skip_flag != 0);
+    const long long n_units = p.n_units;
 
     if (skip) {
         // nothing: fall through to the common exit
@@ -223,65 +229,76 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // =============================== score CTA ===============================
         if (warp == 0) {
             if (lane == 0) {
-                mbar_expect_tx(&bars.q_full, (uint32_t)nch * TC_CHUNK_BYTES);
-                for (int c = 0; c < nch; ++c)
-                    tma_load_2d(q_smem + (size_t)c * TC_CHUNK_BYTES, &tmQ, c * 64, (int)(bh * p.Lq + qt * TC_BM), &bars.q_full);
-                // With an encoding, the first nch ring slots carry the encoding rows of the QUERY
-                // tile (added to / rotated into the resident Q tile by the transform warps); after
-                // that every slot carries a K chunk and, if K is encoded too, its encoding chunk.
-                int it = 0;
-                if (has_pe)
-                    for (int c = 0; c < nch; ++c, ++it) {
-                        const int s = it % NKS;
-                        TC_FAIL_IF(!mbar_wait(&bars.k_empty[s], ((it / NKS) & 1) ^ 1, lim));
-                        mbar_expect_tx(&bars.k_full[s], TC_CHUNK_BYTES);
-                        tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, qt * TC_BM, &bars.k_full[s]);
-                    }
-                for (int u = 0; u < U && !failed; ++u)
-                    for (int c = 0; c < nch; ++c, ++it) {
-                        const int s = it % NKS;
-                        TC_FAIL_IF(!mbar_wait(&bars.k_empty[s], ((it / NKS) & 1) ^ 1, lim));
-                        mbar_expect_tx(&bars.k_full[s], (uint32_t)SB * 128u + (pe_k ? TC_CHUNK_BYTES : 0));
-                        tma_load_2d(k_smem + (size_t)s * KSB, &tmK, c * 64, (int)(bh * p.Lk + u * SB), &bars.k_full[s]);
-                        if (pe_k) tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, u * SB, &bars.k_full[s]);
-                    }
+                int it = 0, ui = 0;
+                for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters, ++ui) {
+                    const int qt = p.qt0 + (int)(unit % p.n_qt);
+                    const long long bh = unit / p.n_qt;
+                    // the Q tile of the previous unit must have been read by its last score MMA
+                    TC_FAIL_AT(1, !mbar_wait(&bars.q_empty, (ui & 1) ^ 1, lim));
+                    mbar_expect_tx(&bars.q_full, (uint32_t)nch * TC_CHUNK_BYTES);
+                    for (int c = 0; c < nch; ++c)
+                        tma_load_2d(q_smem + (size_t)c * TC_CHUNK_BYTES, &tmQ, c * 64, (int)(bh * p.Lq + qt * TC_BM), &bars.q_full);
+                    // With an encoding, the first nch ring slots of a unit carry the encoding rows of the
+                    // QUERY tile (applied to the resident Q tile by the transform warps); after that every
+                    // slot carries a K chunk and, if K is encoded too, its encoding chunk.
+                    if (has_pe)
+                        for (int c = 0; c < nch; ++c, ++it) {
+                            const int s = it % NKS;
+                            TC_FAIL_AT(2, !mbar_wait(&bars.k_empty[s], ((it / NKS) & 1) ^ 1, lim));
+                            mbar_expect_tx(&bars.k_full[s], TC_CHUNK_BYTES);
+                            tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, qt * TC_BM, &bars.k_full[s]);
+                        }
+                    for (int u = 0; u < U && !failed; ++u)
+                        for (int c = 0; c < nch; ++c, ++it) {
+                            const int s = it % NKS;
+                            TC_FAIL_AT(3, !mbar_wait(&bars.k_empty[s], ((it / NKS) & 1) ^ 1, lim));
+                            mbar_expect_tx(&bars.k_full[s], (uint32_t)SB * 128u + (pe_k ? TC_CHUNK_BYTES : 0));
+                            tma_load_2d(k_smem + (size_t)s * KSB, &tmK, c * 64, (int)(bh * p.Lk + u * SB), &bars.k_full[s]);
+                            if (pe_k) tma_load_2d(k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, &tmPE, c * 64, u * SB, &bars.k_full[s]);
+                        }
+                }
             }
         } else if (warp == 1) {
             if (lane == 0) {
                 const uint32_t idesc = umma_idesc_bf16(TC_BM, SB, 0, 0);
-                do {
-                    TC_FAIL_IF(!mbar_wait(&bars.q_full, 0, lim));
-                } while (0);
-                int it = 0;
-                if (has_pe)   // hand the ring slots of the query-encoding phase back once the transform warps are done with them
-                    for (int c = 0; c < nch && !failed; ++c, ++it) {
-                        const int s = it % NKS;
-                        TC_FAIL_IF(!mbar_wait(&bars.k_ready[s], (it / NKS) & 1, lim));
-                        mbar_arrive(&bars.k_empty[s]);
-                    }
-                tc_fence_after();
+                int it = 0, ui = 0;
+                long long ug = 0;   // running score-tile counter
                 TC_PROF_DECL;
-                for (int u = 0; u < U && !failed; ++u) {
-                    const int sb = u % NSB;
-                    TC_FAIL_IF(!mbar_wait(&bars.s_empty[sb], ((u / NSB) & 1) ^ 1, lim));
+                for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters, ++ui) {
+                    TC_FAIL_AT(4, !mbar_wait(&bars.q_full, ui & 1, lim));
+                    if (has_pe)   // hand the ring slots of the query-encoding phase back once the transform warps are done with them
+                        for (int c = 0; c < nch && !failed; ++c, ++it) {
+                            const int s = it % NKS;
+                            TC_FAIL_AT(5, !mbar_wait(&bars.k_ready[s], (it / NKS) & 1, lim));
+                            mbar_arrive(&bars.k_empty[s]);
+                        }
                     tc_fence_after();
-                    TC_PROF(4);
-                    for (int c = 0; c < nch; ++c, ++it) {
-                        const int s = it % NKS;
-                        TC_PROF(5);
-                        TC_FAIL_IF(!mbar_wait(pe_k ? &bars.k_ready[s] : &bars.k_full[s], (it / NKS) & 1, lim));
+                    for (int u = 0; u < U && !failed; ++u, ++ug) {
+                        const int sb = (int)(ug % NSB);
+                        TC_FAIL_AT(6, !mbar_wait(&bars.s_empty[sb], ((ug / NSB) & 1) ^ 1, lim));
                         tc_fence_after();
-                        TC_PROF(6);
-                        const uint64_t da = umma_desc_k_sw128(smem_u32(q_smem + (size_t)c * TC_CHUNK_BYTES));
-                        const uint64_t db = umma_desc_k_sw128(smem_u32(k_smem + (size_t)s * KSB));
+                        TC_PROF(4);
+                        for (int c = 0; c < nch; ++c, ++it) {
+                            const int s = it % NKS;
+                            TC_PROF(5);
+                            // with an encoding every ring slot passes through the transform warps (k_ready), so
+                            // that the phases of k_ready stay in step with the ring across units
+                            TC_FAIL_AT(7, !mbar_wait(has_pe ? &bars.k_ready[s] : &bars.k_full[s], (it / NKS) & 1, lim));
+                            tc_fence_after();
+                            TC_PROF(6);
+                            const uint64_t da = umma_desc_k_sw128(smem_u32(q_smem + (size_t)c * TC_CHUNK_BYTES));
+                            const uint64_t db = umma_desc_k_sw128(smem_u32(k_smem + (size_t)s * KSB));
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            umma_bf16(tmem + sb * SB, da + 2 * k, db + 2 * k, idesc, (c | k) != 0);
-                        umma_commit(&bars.k_empty[s]);
+                            for (int k = 0; k < 4; ++k)
+                                umma_bf16(tmem + sb * SB, da + 2 * k, db + 2 * k, idesc, (c | k) != 0);
+                            umma_commit(&bars.k_empty[s]);
+                        }
+                        if (failed) break;
+                        umma_commit(&bars.s_full[sb]);
+                        TC_PROF(5);
                     }
                     if (failed) break;
-                    umma_commit(&bars.s_full[sb]);
-                    TC_PROF(5);
+                    umma_commit(&bars.q_empty);   // the Q tile may be replaced once these MMAs have run
                 }
                 TC_PROF_FLUSH(8, true);
             }
@@ -292,187 +309,215 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // of block t-1, which the other group publishes through the `decided` barriers, right
             // after its (short) max pass, so the long exp/store passes of the two groups overlap.
             const int wg = (warp - 2) >> 2;
+            const int n_groups = (T >= 2) ? 2 : 1;   // with a single key block per unit the second group has nothing to do
             const int row = 32 * (warp & 3) + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
             const uint32_t p_remote = map_to_rank(smem_u32(p_smem), 1);
             const uint32_t alpha_remote = map_to_rank(smem_u32(alpha_smem), 1);
-            float m_seen = -INFINITY, l = 0.0f;   // l is relative to m_seen
+            const uint32_t lsum_remote = map_to_rank(smem_u32(lsum_smem), 1);
             uint32_t r[32];
-            int last = -1;
+            int ui = 0;
             TC_PROF_DECL;
-            // a score tile holds HPS blocks of 128 keys; with 256-key tiles the two groups work on the
-            // two halves of the same tile, with 128-key tiles on alternate tiles
-            const int t_end = U * HPS;
-            for (int t = wg; t < t_end; t += 2) {
-                const int u = t / HPS;
-                const int sb = u % NSB, pb = t % TC_NP;
-                TC_FAIL_IF(!mbar_wait(&bars.s_full[sb], (u / NSB) & 1, lim));
-                if (t >= T) {   // padding half of the last tile: nothing to do but release it
+            for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters, ++ui) {
+                const long long tbase = (long long)ui * T, ubase = (long long)ui * U;   // running block / tile counters
+                float *mst = m_state[ui & 1];
+                float m_seen = -INFINITY, l = 0.0f;   // l is relative to m_seen
+                int last = -1;
+                // a score tile holds HPS blocks of 128 keys; with 256-key tiles the two groups work on the
+                // two halves of the same tile, with 128-key tiles on alternate tiles
+                const int t_end = U * HPS;
+                for (int t = wg; t < t_end; t += 2) {
+                    const long long tg = tbase + t, ug = ubase + t / HPS;
+                    const int sb = (int)(ug % NSB), pb = (int)(tg % TC_NP);
+                    TC_FAIL_AT(8, !mbar_wait(&bars.s_full[sb], (ug / NSB) & 1, lim));
+                    if (t >= T) {   // padding half of the last tile: nothing to do but release it
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
+                        continue;
+                    }
+                    tc_fence_after();
+                    TC_PROF(0);
+                    const uint32_t ta = lane_addr + sb * SB + (t % HPS) * TC_BN;
+                    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld32(ta + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            mx0 = fmaxf(mx0, __uint_as_float(r[j]));
+                            mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
+                            mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
+                            mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
+                        }
+                        if (p.debug_scores != nullptr && t == 0) {
+                            float *dbg = p.debug_scores + ((long long)unit * TC_BM + row) * TC_BN + c * 32;
+                            for (int j = 0; j < 32; ++j) dbg[j] = __uint_as_float(r[j]);
+                        }
+                    }
+                    const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                    TC_PROF(1);
+                    // decision for block t (needs the decision of block t-1 of this unit)
+                    float m_new = mx, alpha = 1.0f;
+                    if (t > 0) {
+                        TC_FAIL_AT(9, !mbar_wait(&bars.decided[(tg - 1) & 1], ((tg - 1) >> 1) & 1, lim));
+                        const float m_prev = mst[row];
+                        if ((mx - m_prev) * p.scale_log2 > TC_RESCALE_LOG2) alpha = fast_exp2((m_prev - mx) * p.scale_log2);
+                        else m_new = m_prev;
+                    }
+                    mst[row] = m_new;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.decided[tg & 1]);
+                    if (last >= 0 && m_new != m_seen) l *= fast_exp2((m_seen - m_new) * p.scale_log2);
+                    m_seen = m_new;
+                    TC_PROF(4);
+                    TC_FAIL_AT(10, !mbar_wait_cluster(&bars.p_empty[pb], ((tg / TC_NP) & 1) ^ 1, lim));
+                    TC_PROF(2);
+                    const float msl = m_new * p.scale_log2;
+                    const uint32_t prow = p_remote + pb * TC_P_BYTES + row * 128;
+                    float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld32(ta + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            float e[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) e[j] = fast_exp2(fmaf(__uint_as_float(r[8 * g + j]), p.scale_log2, -msl));
+                            l0 += e[0] + e[4]; l1 += e[1] + e[5]; l2 += e[2] + e[6]; l3 += e[3] + e[7];
+                            const int q16 = c * 4 + g;   // 16-byte chunk index within the 128-key row
+                            const uint32_t addr = prow + (q16 >> 3) * (TC_BM * 128) + (((q16 & 7) ^ (row & 7)) << 4);
+                            st_cluster_v4(addr, pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
+                        }
+                    }
+                    l += (l0 + l1) + (l2 + l3);
+                    tc_fence_before();
+                    st_cluster_f32(alpha_remote + (pb * TC_BM + row) * 4, alpha);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
-                    continue;
+                    last = t;
+                    TC_PROF(3);
+                    // hand the block over: every lane makes its stores visible to the peer's tensor core,
+                    // one lane arrives for the warp (the other group computes meanwhile)
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[pb]), 1));
+                    TC_PROF(5);
                 }
-                tc_fence_after();
-                TC_PROF(0);
-                const uint32_t ta = lane_addr + sb * SB + (t % HPS) * TC_BN;
-                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld32(ta + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        mx0 = fmaxf(mx0, __uint_as_float(r[j]));
-                        mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
-                        mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
-                        mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
+                if (failed) break;
+                // this group's part of the row sums, brought to the unit's final reference max.  A group
+                // that did not take the last block waits for its decision first.  With a single key
+                // block per unit the second group only releases the padding halves of the score tiles
+                // and sends nothing.
+                if (wg < n_groups) {
+                    if (last != T - 1) {
+                        const long long tl = tbase + T - 1;
+                        TC_FAIL_AT(11, !mbar_wait(&bars.decided[tl & 1], (tl >> 1) & 1, lim));
+                        const float m_fin = mst[row];
+                        if (last >= 0 && m_fin != m_seen) l *= fast_exp2((m_seen - m_fin) * p.scale_log2);
                     }
-                    if (p.debug_scores != nullptr && t == 0) {
-                        float *dbg = p.debug_scores + ((long long)unit * TC_BM + row) * TC_BN + c * 32;
-                        for (int j = 0; j < 32; ++j) dbg[j] = __uint_as_float(r[j]);
-                    }
+                    const int ls = ui % TC_NL;
+                    st_cluster_f32(lsum_remote + ((ls * 2 + wg) * TC_BM + row) * 4, l);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.l_full[ls]), 1));
                 }
-                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-                TC_PROF(1);
-                // decision for block t (needs the decision of block t-1)
-                float m_new = mx, alpha = 1.0f;
-                if (t > 0) {
-                    TC_FAIL_IF(!mbar_wait(&bars.decided[(t - 1) & 1], ((t - 1) >> 1) & 1, lim));
-                    const float m_prev = m_state[row];
-                    if ((mx - m_prev) * p.scale_log2 > TC_RESCALE_LOG2) alpha = fast_exp2((m_prev - mx) * p.scale_log2);
-                    else m_new = m_prev;
-                }
-                m_state[row] = m_new;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.decided[t & 1]);
-                if (last >= 0 && m_new != m_seen) l *= fast_exp2((m_seen - m_new) * p.scale_log2);
-                m_seen = m_new;
-                TC_PROF(4);
-                TC_FAIL_IF(!mbar_wait_cluster(&bars.p_empty[pb], ((t / TC_NP) & 1) ^ 1, lim));
-                TC_PROF(2);
-                const float msl = m_new * p.scale_log2;
-                const uint32_t prow = p_remote + pb * TC_P_BYTES + row * 128;
-                float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld32(ta + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        float e[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) e[j] = fast_exp2(fmaf(__uint_as_float(r[8 * g + j]), p.scale_log2, -msl));
-                        l0 += e[0] + e[4]; l1 += e[1] + e[5]; l2 += e[2] + e[6]; l3 += e[3] + e[7];
-                        const int q16 = c * 4 + g;   // 16-byte chunk index within the 128-key row
-                        const uint32_t addr = prow + (q16 >> 3) * (TC_BM * 128) + (((q16 & 7) ^ (row & 7)) << 4);
-                        st_cluster_v4(addr, pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
-                    }
-                }
-                l += (l0 + l1) + (l2 + l3);
-                tc_fence_before();
-                st_cluster_f32(alpha_remote + (pb * TC_BM + row) * 4, alpha);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.s_empty[sb]);
-                last = t;
-                TC_PROF(3);
-                // hand the block over: every lane makes its stores visible to the peer's tensor core,
-                // one lane arrives for the warp (the other group computes meanwhile)
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[pb]), 1));
-                TC_PROF(5);
             }
             TC_PROF_FLUSH(0, threadIdx.x == 64);
-            // this group's part of the row sums, brought to the final reference max (sent even after
-            // a failure so that the peer is not left waiting)
-            if (!failed && last >= 0 && last != T - 1) {
-                if (mbar_wait(&bars.decided[(T - 1) & 1], ((T - 1) >> 1) & 1, lim)) {
-                    const float m_fin = m_state[row];
-                    if (m_fin != m_seen) l *= fast_exp2((m_seen - m_fin) * p.scale_log2);
-                } else {
-                    atomicOr(p.err, (unsigned)KERR_MBAR_TIMEOUT);
-                }
-            }
-            st_cluster_f32(map_to_rank(smem_u32(lsum_smem), 1) + (wg * TC_BM + row) * 4, l);
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.l_full), 1));
         } else if (has_pe) {
-            // ---- transform warps: encoding of the Q tile once, then of every K chunk ----
+            // ---- transform warps: encoding of the Q tile once per unit, then of every K chunk ----
             const int tid = threadIdx.x - 10 * 32;
             const bool sinus = (p.pe == PE_SINUSOIDAL);
-            int it = 0;
-            do {
-                TC_FAIL_IF(!mbar_wait(&bars.q_full, 0, lim));
+            int it = 0, ui = 0;
+            for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters, ++ui) {
+                const long long bh = unit / p.n_qt;
+                TC_FAIL_AT(12, !mbar_wait(&bars.q_full, ui & 1, lim));
                 for (int c = 0; c < nch; ++c, ++it) {
                     const int s = it % NKS;
-                    TC_FAIL_IF(!mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
+                    TC_FAIL_AT(13, !mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
                     tc_pe_chunk(q_smem + (size_t)c * TC_CHUNK_BYTES, k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, sinus, tid);
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.k_ready[s]);
                 }
-            } while (0);
-            if (pe_k)
-                for (int t = 0; t < T && !failed; ++t)
-                    for (int c = 0; c < nch; ++c, ++it) {
-                        const int s = it % NKS;
-                        TC_FAIL_IF(!mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
-                        unsigned char *kt = k_smem + (size_t)s * KSB;
-                        __nv_bfloat16 *gd = p.k_store ? p.k_store + ((bh * p.Lk + (long long)t * TC_BN) * D + c * 64) : nullptr;
-                        tc_pe_chunk(kt, kt + TC_CHUNK_BYTES, sinus, tid, gd, D);
-                        fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars.k_ready[s]);
-                    }
+                if (failed) break;
+                if (pe_k) {
+                    for (int t = 0; t < T && !failed; ++t)
+                        for (int c = 0; c < nch; ++c, ++it) {
+                            const int s = it % NKS;
+                            TC_FAIL_AT(14, !mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
+                            unsigned char *kt = k_smem + (size_t)s * KSB;
+                            __nv_bfloat16 *gd = p.k_store ? p.k_store + ((bh * p.Lk + (long long)t * TC_BN) * D + c * 64) : nullptr;
+                            tc_pe_chunk(kt, kt + TC_CHUNK_BYTES, sinus, tid, gd, D);
+                            fence_proxy_async();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&bars.k_ready[s]);
+                        }
+                } else {   // K comes encoded already: just pass the slots on
+                    for (int u = 0; u < U && !failed; ++u)
+                        for (int c = 0; c < nch; ++c, ++it) {
+                            const int s = it % NKS;
+                            TC_FAIL_AT(15, !mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&bars.k_ready[s]);
+                        }
+                }
+            }
         }
     } else {
         // =============================== output CTA ===============================
         if (warp == 0) {
             if (lane == 0) {
                 int it = 0;
-                for (int t = 0; t < T && !failed; ++t)
-                    for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
-                        const int s = it % TC_NV;
-                        TC_FAIL_IF(!mbar_wait(&bars.v_empty[s], ((it / TC_NV) & 1) ^ 1, lim));
-                        mbar_expect_tx(&bars.v_full[s], (uint32_t)v_stage_bytes);
-                        for (int g = 0; g < nch; ++g)
-                            tma_load_2d(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TC_VS * 128), &tmV, g * 64,
-                                        (int)(bh * p.Lk + t * TC_BN + vs * TC_VS), &bars.v_full[s]);
-                    }
+                for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters) {
+                    const long long bh = unit / p.n_qt;
+                    for (int t = 0; t < T && !failed; ++t)
+                        for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
+                            const int s = it % TC_NV;
+                            TC_FAIL_AT(16, !mbar_wait(&bars.v_empty[s], ((it / TC_NV) & 1) ^ 1, lim));
+                            mbar_expect_tx(&bars.v_full[s], (uint32_t)v_stage_bytes);
+                            for (int g = 0; g < nch; ++g)
+                                tma_load_2d(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TC_VS * 128), &tmV, g * 64,
+                                            (int)(bh * p.Lk + t * TC_BN + vs * TC_VS), &bars.v_full[s]);
+                        }
+                }
             }
         } else if (warp == 1) {
             if (lane == 0) {
                 int it = 0;
+                long long tg = 0;   // running block counter
                 TC_PROF_DECL;
-                for (int t = 0; t < T && !failed; ++t) {
-                    const int pb = t % TC_NP;
-                    TC_FAIL_IF(!mbar_wait_cluster(&bars.p_full[pb], (t / TC_NP) & 1, lim));
-                    TC_PROF(0);
-                    TC_FAIL_IF(!mbar_wait(&bars.corr_done[pb], (t / TC_NP) & 1, lim));
-                    tc_fence_after();
-                    TC_PROF(1);
-                    for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
-                        const int s = it % TC_NV;
-                        TC_PROF(2);
-                        TC_FAIL_IF(!mbar_wait(&bars.v_full[s], (it / TC_NV) & 1, lim));
+                for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters) {
+                    for (int t = 0; t < T && !failed; ++t, ++tg) {
+                        const int pb = (int)(tg % TC_NP);
+                        TC_FAIL_AT(17, !mbar_wait_cluster(&bars.p_full[pb], (tg / TC_NP) & 1, lim));
+                        TC_PROF(0);
+                        TC_FAIL_AT(18, !mbar_wait(&bars.corr_done[pb], (tg / TC_NP) & 1, lim));
                         tc_fence_after();
-                        TC_PROF(3);
+                        TC_PROF(1);
+                        for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
+                            const int s = it % TC_NV;
+                            TC_PROF(2);
+                            TC_FAIL_AT(19, !mbar_wait(&bars.v_full[s], (it / TC_NV) & 1, lim));
+                            tc_fence_after();
+                            TC_PROF(3);
 #pragma unroll
-                        for (int kk = 0; kk < TC_VS / 16; ++kk) {
-                            const int kg = vs * (TC_VS / 16) + kk;   // 16-key step within the block, 0..7
-                            const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TC_BM * 128))) + 2 * (kg & 3);
-                            for (int n0 = 0; n0 < D; n0 += 256) {
-                                const int N = min(256, D - n0);
-                                const uint64_t db = umma_desc_mn_sw128(
-                                    smem_u32(v_smem + (size_t)s * v_stage_bytes + (size_t)(n0 >> 6) * (TC_VS * 128) + kk * 2048), TC_VS * 128);
-                                umma_bf16(tmem + n0, da, db, umma_idesc_bf16(TC_BM, N, 0, 1), (t | kg) != 0);
+                            for (int kk = 0; kk < TC_VS / 16; ++kk) {
+                                const int kg = vs * (TC_VS / 16) + kk;   // 16-key step within the block, 0..7
+                                const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TC_BM * 128))) + 2 * (kg & 3);
+                                for (int n0 = 0; n0 < D; n0 += 256) {
+                                    const int N = min(256, D - n0);
+                                    const uint64_t db = umma_desc_mn_sw128(
+                                        smem_u32(v_smem + (size_t)s * v_stage_bytes + (size_t)(n0 >> 6) * (TC_VS * 128) + kk * 2048), TC_VS * 128);
+                                    umma_bf16(tmem + n0, da, db, umma_idesc_bf16(TC_BM, N, 0, 1), (t | kg) != 0);
+                                }
                             }
+                            umma_commit(&bars.v_empty[s]);
                         }
-                        umma_commit(&bars.v_empty[s]);
+                        if (failed) break;
+                        umma_commit(&bars.pv_done[pb]);
+                        TC_PROF(2);
                     }
-                    if (failed) break;
-                    umma_commit(&bars.pv_done[pb]);
-                    TC_PROF(2);
                 }
                 TC_PROF_FLUSH(16, true);
             }
@@ -480,33 +525,45 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // ---- correction + epilogue: one thread per query row ----
             const int row = 32 * (warp & 3) + lane;
             const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+            const int n_groups = (T >= 2) ? 2 : 1;
             uint32_t r[32];
-            for (int t = 0; t < T; ++t) {
-                const int pb = t % TC_NP;
-                TC_FAIL_IF(!mbar_wait_cluster(&bars.p_full[pb], (t / TC_NP) & 1, lim));
-                const float a = alpha_smem[pb * TC_BM + row];
-                if (t > 0 && __any_sync(0xffffffffu, a != 1.0f)) {
-                    TC_FAIL_IF(!mbar_wait(&bars.pv_done[(t - 1) % TC_NP], ((t - 1) / TC_NP) & 1, lim));
-                    tc_fence_after();
-                    for (int c = 0; c < D / 32; ++c) {
-                        tmem_ld32(lane_addr + c * 32, r);
-                        tmem_ld_wait();
+            int ui = 0;
+            long long tg = 0;
+            for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters, ++ui) {
+                const int qt = p.qt0 + (int)(unit % p.n_qt);
+                const long long bh = unit / p.n_qt;
+                for (int t = 0; t < T; ++t, ++tg) {
+                    const int pb = (int)(tg % TC_NP);
+                    TC_FAIL_AT(20, !mbar_wait_cluster(&bars.p_full[pb], (tg / TC_NP) & 1, lim));
+                    const float a = alpha_smem[pb * TC_BM + row];
+                    if (t > 0 && __any_sync(0xffffffffu, a != 1.0f)) {
+                        TC_FAIL_AT(21, !mbar_wait(&bars.pv_done[(tg - 1) % TC_NP], ((tg - 1) / TC_NP) & 1, lim));
+                        tc_fence_after();
+                        for (int c = 0; c < D / 32; ++c) {
+                            tmem_ld32(lane_addr + c * 32, r);
+                            tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * a);
-                        tmem_st32(lane_addr + c * 32, r);
+                            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * a);
+                            tmem_st32(lane_addr + c * 32, r);
+                        }
+                        tmem_st_wait();
+                        tc_fence_before();
                     }
-                    tmem_st_wait();
-                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.corr_done[pb]);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.corr_done[pb]);
-            }
-            do {
                 if (failed) break;
-                TC_FAIL_IF(!mbar_wait(&bars.pv_done[(T - 1) % TC_NP], ((T - 1) / TC_NP) & 1, lim));
+                // epilogue of the unit: O / row sum -> bf16 -> global.  The accumulator is free for the
+                // next unit (whose first block overwrites it) only after these reads: the arrival on
+                // corr_done for that block comes after this point in program order.
+                const long long tl = tg - 1;
+                TC_FAIL_AT(22, !mbar_wait(&bars.pv_done[tl % TC_NP], (tl / TC_NP) & 1, lim));
                 tc_fence_after();
-                TC_FAIL_IF(!mbar_wait_cluster(&bars.l_full, 0, lim));
-                const float inv = 1.0f / (lsum_smem[row] + lsum_smem[TC_BM + row]);
+                const int ls = ui % TC_NL;
+                TC_FAIL_AT(23, !mbar_wait_cluster(&bars.l_full[ls], (ui / TC_NL) & 1, lim));
+                float lsum = lsum_smem[(ls * 2) * TC_BM + row];
+                if (n_groups == 2) lsum += lsum_smem[(ls * 2 + 1) * TC_BM + row];
+                const float inv = 1.0f / lsum;
                 __nv_bfloat16 *orow = p.O + ((bh * p.Lq + qt * TC_BM + row) * (long long)D);
                 for (int c = 0; c < D / 32; ++c) {
                     tmem_ld32(lane_addr + c * 32, r);
@@ -522,15 +579,18 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         dst[g] = o;
                     }
                 }
-            } while (0);
+                tc_fence_before();   // the accumulator reads are ordered before the corr_done arrival of the next unit
+            }
         } else if (warp == 6) {
             // ---- relay: "PV of block t finished" -> the score CTA may overwrite that P buffer ----
             if (lane == 0) {
-                for (int t = 0; t < T; ++t) {
-                    const int pb = t % TC_NP;
-                    TC_FAIL_IF(!mbar_wait(&bars.pv_done[pb], (t / TC_NP) & 1, lim));
-                    mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_empty[pb]), 0));
-                }
+                long long tg = 0;
+                for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters)
+                    for (int t = 0; t < T; ++t, ++tg) {
+                        const int pb = (int)(tg % TC_NP);
+                        TC_FAIL_AT(24, !mbar_wait(&bars.pv_done[pb], (tg / TC_NP) & 1, lim));
+                        mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_empty[pb]), 0));
+                    }
             }
         }
     }
@@ -544,7 +604,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     cluster_wait();
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
-#undef TC_FAIL_IF
+#undef TC_FAIL_AT
 
 // ---- positional-encoding tables: [L][D] bf16, built on the device with the fp32 arithmetic of the
 // reference CPU tables (final/sinusoidal.cu:838-855, final/rope.cu:20-40) and rounded once ----
@@ -638,14 +698,13 @@ inline size_t tc_smem_bytes(int D, bool has_pe) {
     (void)has_pe;
     const size_t ring = (size_t)3 * 2 * TC_CHUNK_BYTES;   // 3 stages of 32 KB: a 256-key K chunk, or a 128-key chunk + its encoding chunk
     const size_t score = (size_t)(D / 64) * TC_CHUNK_BYTES + ring;
-    const size_t outp = (size_t)TC_NP * TC_P_BYTES + (size_t)TC_NV * TC_VS * D * 2 + (size_t)(TC_NP + 2) * TC_BM * sizeof(float);
+    const size_t outp = (size_t)TC_NP * TC_P_BYTES + (size_t)TC_NV * TC_VS * D * 2 + (size_t)(TC_NP + 2 * TC_NL) * TC_BM * sizeof(float);
     return (score > outp ? score : outp) + 1024;
 }
 
 // Returns B200ATTN_OK, -1 when the shape should run on the other path, or a status with tc_bf16_error() set.
 inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tables, unsigned *err_dev, int sm_count,
                        unsigned spin_limit, cudaStream_t st, std::atomic<unsigned long long> *launches, float *debug_scores = nullptr) {
-    (void)sm_count;
     const long long BH = (long long)a.batch_sz * a.num_heads;
     const int D = a.head_d;
     static std::mutex attr_mu;
@@ -699,8 +758,12 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     auto launch = [&](const CUtensorMap &mK, int qt0, int n_qt) -> int {
         p.qt0 = qt0; p.n_qt = n_qt;
         const long long units = BH * n_qt;
+        p.n_units = units;
+        long long clusters = sm_count / 2;   // persistent: one cluster per SM pair, units dealt round-robin
+        if (const char *e = getenv("B200ATTN_TC_CLUSTERS")) { long long v = atoll(e); if (v > 0) clusters = v; }
+        if (clusters > units) clusters = units;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(2 * units));
+        cfg.gridDim = dim3((unsigned)(2 * clusters));
         cfg.blockDim = dim3(TC_THREADS);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = st;

@@ -57,7 +57,12 @@ def test_bf16_both_paths_against_oracle(pkg, cuda, pe, shape):
 @pytest.mark.parametrize("cfg", [
     ("cfg3 bf16 plain", 8, 16, 1024, 512, ol.PE_NONE),
     ("cfg4 bf16 rope-half", 4, 32, 2048, 1024, ol.PE_ROPE_HALF),
-])
+    ("cfg5 bf16 sinusoidal", 16, 32, 4096, 512, ol.PE_SINUSOIDAL),
+    ("many units per cluster, sinusoidal", 2, 40, 1024, 512, ol.PE_SINUSOIDAL),
+    ("many units per cluster, interleaved rope", 3, 30, 768, 256, ol.PE_ROPE_INTERLEAVED),
+    ("single key block per unit", 1, 200, 128, 128, ol.PE_NONE),
+    ("odd number of key blocks", 1, 90, 256, 384, ol.PE_SINUSOIDAL),
+], ids=lambda c: c[0].replace(" ", "_").replace(",", ""))
 def test_benchmark_bf16_configs_sampled(pkg, cuda, cfg):
     """Full benchmark shapes, inputs generated in HBM by the library; the oracle evaluates a
     stratified sample of rows (first/last, tile boundaries) of a few heads from the very bytes the
@@ -71,7 +76,7 @@ def test_benchmark_bf16_configs_sampled(pkg, cuda, cfg):
     out = pkg.forward(Q, K, V, pe=pe)
     torch.cuda.synchronize()
     heads = [0, B * H // 2 + 1, B * H - 1]
-    rows = [0, 1, 63, 64, 127, 128, L // 2 + 5, L - 1]
+    rows = sorted({0, 1, 63, 64, 127, min(128, L - 1), L // 2 + 5, L - 1})
     o = out.view(B * H, L, D)
     q3, k3, v3 = (t.view(B * H, L, D) for t in (Q, K, V))
     for h in heads:
