@@ -173,10 +173,11 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int U = (T + HPS - 1) / HPS;               // score tiles per unit
 
     // ---- shared-memory carve-up ----
-    // score CTA : [Q: nch chunks of 16 KB][K ring: k_stages stages of (K chunk [+ encoding chunk])]
+    // score CTA : [Q: nch chunks of 16 KB][K ring: k_stages stages of (K chunk [+ encoding chunk])][P staging: 8 x 4 KB]
     // output CTA: [P: TC_NP x 32 KB][V ring: TC_NV stages of TC_VS*D*2 B][alpha: TC_NP x 128 f32][lsum: TC_NL x 2 x 128 f32]
     unsigned char *q_smem = smem;
     unsigned char *k_smem = smem + (size_t)nch * TC_CHUNK_BYTES;
+    unsigned char *stage_smem = k_smem + (size_t)p.k_stages * p.k_stage_bytes;   // 8 x 4 KB: P staging of the softmax warps
     unsigned char *p_smem = smem;
     unsigned char *v_smem = smem + (size_t)TC_NP * TC_P_BYTES;
     const int v_stage_bytes = TC_VS * D * 2;
@@ -315,6 +316,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const uint32_t p_remote = map_to_rank(smem_u32(p_smem), 1);
             const uint32_t alpha_remote = map_to_rank(smem_u32(alpha_smem), 1);
             const uint32_t lsum_remote = map_to_rank(smem_u32(lsum_smem), 1);
+            unsigned char *my_stage = stage_smem + (warp - 2) * 4096;   // 4 KB per softmax warp
             uint32_t r[32];
             int ui = 0;
             TC_PROF_DECL;
@@ -374,22 +376,36 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     TC_FAIL_AT(10, !mbar_wait_cluster(&bars.p_empty[pb], ((tg / TC_NP) & 1) ^ 1, lim));
                     TC_PROF(2);
                     const float msl = m_new * p.scale_log2;
-                    const uint32_t prow = p_remote + pb * TC_P_BYTES + row * 128;
+                    // The block's probabilities go to the peer in two column blocks of 64 keys.  A warp
+                    // first lays its 32 rows x 128 B out in its own 4 KB staging area (already in the
+                    // swizzled layout of the destination), then copies it with lane-contiguous 16-byte
+                    // remote stores, so that every remote store instruction covers 512 contiguous bytes.
+                    const uint32_t pblk = p_remote + pb * TC_P_BYTES + (32 * (warp & 3)) * 128;
                     float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        tmem_ld32(ta + c * 32, r);
-                        tmem_ld_wait();
+                    for (int cb = 0; cb < 2; ++cb) {
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            float e[8];
+                        for (int ch = 0; ch < 2; ++ch) {
+                            tmem_ld32(ta + (cb * 2 + ch) * 32, r);
+                            tmem_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) e[j] = fast_exp2(fmaf(__uint_as_float(r[8 * g + j]), p.scale_log2, -msl));
-                            l0 += e[0] + e[4]; l1 += e[1] + e[5]; l2 += e[2] + e[6]; l3 += e[3] + e[7];
-                            const int q16 = c * 4 + g;   // 16-byte chunk index within the 128-key row
-                            const uint32_t addr = prow + (q16 >> 3) * (TC_BM * 128) + (((q16 & 7) ^ (row & 7)) << 4);
-                            st_cluster_v4(addr, pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
+                            for (int g = 0; g < 4; ++g) {
+                                float e[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) e[j] = fast_exp2(fmaf(__uint_as_float(r[8 * g + j]), p.scale_log2, -msl));
+                                l0 += e[0] + e[4]; l1 += e[1] + e[5]; l2 += e[2] + e[6]; l3 += e[3] + e[7];
+                                const int q = ch * 4 + g;   // 16-byte chunk index within the 64-key row
+                                *reinterpret_cast<uint4 *>(my_stage + lane * 128 + ((q ^ (row & 7)) << 4)) =
+                                    make_uint4(pack_bf16x2(e[0], e[1]), pack_bf16x2(e[2], e[3]), pack_bf16x2(e[4], e[5]), pack_bf16x2(e[6], e[7]));
+                            }
                         }
+                        __syncwarp();
+#pragma unroll 4
+                        for (int i = 0; i < 8; ++i) {
+                            const uint4 v = *reinterpret_cast<const uint4 *>(my_stage + i * 512 + lane * 16);
+                            st_cluster_v4(pblk + cb * (TC_BM * 128) + i * 512 + lane * 16, v.x, v.y, v.z, v.w);
+                        }
+                        __syncwarp();
                     }
                     l += (l0 + l1) + (l2 + l3);
                     tc_fence_before();
@@ -696,7 +712,7 @@ inline bool tc_make_map(CUtensorMap *m, const void *base, long long rows, int D,
 
 inline size_t tc_smem_bytes(int D, bool has_pe) {
     (void)has_pe;
-    const size_t ring = (size_t)3 * 2 * TC_CHUNK_BYTES;   // 3 stages of 32 KB: a 256-key K chunk, or a 128-key chunk + its encoding chunk
+    const size_t ring = (size_t)2 * 2 * TC_CHUNK_BYTES + 8 * 4096;   // 2 stages of 32 KB (a 256-key K chunk, or a 128-key chunk + its encoding chunk) + P staging
     const size_t score = (size_t)(D / 64) * TC_CHUNK_BYTES + ring;
     const size_t outp = (size_t)TC_NP * TC_P_BYTES + (size_t)TC_NV * TC_VS * D * 2 + (size_t)(TC_NP + 2 * TC_NL) * TC_BM * sizeof(float);
     return (score > outp ? score : outp) + 1024;
@@ -738,7 +754,7 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     p.err = err_dev;
     p.spin_limit = spin_limit;
     p.debug_scores = debug_scores;
-    p.k_stages = 3;
+    p.k_stages = 2;   // two 32 KB stages measure the same as three; the third's 32 KB are the P staging
     p.k_stage_bytes = 2 * TC_CHUNK_BYTES;
     const bool has_pe = (a.pe != B200ATTN_PE_NONE);
     CUtensorMap tmQ, tmK128, tmK256, tmV, tmPE;
