@@ -263,6 +263,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (lane == 0) {
                 const uint32_t idesc = umma_idesc_bf16(TC_BM, SB, 0, 0);
                 int it = 0, ui = 0;
+                uint32_t qph = 0;   // per-slot phase parity of k_ready when only the query phase uses it
                 long long ug = 0;   // running score-tile counter
                 TC_PROF_DECL;
                 for (long long unit = cluster_id; unit < n_units && !failed; unit += n_clusters, ++ui) {
@@ -270,7 +271,11 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     if (has_pe)   // hand the ring slots of the query-encoding phase back once the transform warps are done with them
                         for (int c = 0; c < nch && !failed; ++c, ++it) {
                             const int s = it % NKS;
-                            TC_FAIL_AT(5, !mbar_wait(&bars.k_ready[s], (it / NKS) & 1, lim));
+                            // k_ready[s] completes one phase per use by the transform warps: every ring use
+                            // when K is encoded too, only these query-phase uses otherwise (tracked in qph)
+                            const uint32_t par = pe_k ? ((it / NKS) & 1) : ((qph >> s) & 1);
+                            qph ^= 1u << s;
+                            TC_FAIL_AT(5, !mbar_wait(&bars.k_ready[s], par, lim));
                             mbar_arrive(&bars.k_empty[s]);
                         }
                     tc_fence_after();
@@ -282,9 +287,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         for (int c = 0; c < nch; ++c, ++it) {
                             const int s = it % NKS;
                             TC_PROF(5);
-                            // with an encoding every ring slot passes through the transform warps (k_ready), so
-                            // that the phases of k_ready stay in step with the ring across units
-                            TC_FAIL_AT(7, !mbar_wait(has_pe ? &bars.k_ready[s] : &bars.k_full[s], (it / NKS) & 1, lim));
+                            TC_FAIL_AT(7, !mbar_wait(pe_k ? &bars.k_ready[s] : &bars.k_full[s], (it / NKS) & 1, lim));
                             tc_fence_after();
                             TC_PROF(6);
                             const uint64_t da = umma_desc_k_sw128(smem_u32(q_smem + (size_t)c * TC_CHUNK_BYTES));
@@ -469,14 +472,8 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&bars.k_ready[s]);
                         }
-                } else {   // K comes encoded already: just pass the slots on
-                    for (int u = 0; u < U && !failed; ++u)
-                        for (int c = 0; c < nch; ++c, ++it) {
-                            const int s = it % NKS;
-                            TC_FAIL_AT(15, !mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&bars.k_ready[s]);
-                        }
+                } else {   // K comes encoded already and goes straight to the MMA; only the ring counter moves on
+                    it += U * nch;
                 }
             }
         }
