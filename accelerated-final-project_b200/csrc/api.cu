@@ -62,8 +62,10 @@ struct DeviceCtx {
     bool scratch_dirty = false;    // a failed fused launch may have left S / counters non-zero
     bool attr_set[8] = {false, false, false, false, false, false, false, false};
     size_t dyn_smem_max[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    void *stage[4] = {nullptr, nullptr, nullptr, nullptr};   // host-buffer entry point: Q,K,V,O staging
-    size_t stage_bytes[4] = {0, 0, 0, 0};
+    void *stage[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // host-buffer entry point: two sets of Q,K,V,O chunk buffers
+    size_t stage_bytes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    cudaStream_t host_streams[3] = {nullptr, nullptr, nullptr};   // copy-in, compute, copy-out
+    cudaEvent_t host_events[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     cudaStream_t shard_stream = nullptr;
     TcTables tc_tables;            // positional-encoding tables of the tensor-core path
 };
@@ -483,28 +485,68 @@ int b200attn_forward_host(const b200attn_args *h) {
     rc = get_ctx(&c);
     if (rc) return rc;
     const size_t esz = h->dtype == B200ATTN_F32 ? 4 : 2;
-    const size_t bh = (size_t)h->batch_sz * h->num_heads;
-    const size_t nq = bh * h->len_q * h->head_d * esz, nk = bh * h->len_k * h->head_d * esz;
-    b200attn_args d = *h;
+    const long long BH = (long long)h->batch_sz * h->num_heads;
+    const size_t q1 = (size_t)h->len_q * h->head_d * esz, k1 = (size_t)h->len_k * h->head_d * esz;   // bytes per (b,h) slice
+    // (batch, head) slices are independent and contiguous, so the problem is cut into chunks of heads
+    // and copy-in, compute and copy-out of consecutive chunks overlap on three streams (two buffer
+    // sets).  Small problems go through in one chunk.
+    long long chunk = BH;
+    const size_t per_head = 2 * q1 + 2 * k1;
+    if ((size_t)BH * per_head > ((size_t)64 << 20)) {
+        chunk = (long long)((((size_t)256 << 20) + per_head - 1) / per_head);   // about 256 MiB of traffic per chunk
+        if (chunk < 1) chunk = 1;
+        if (chunk * 4 > BH) chunk = (BH + 3) / 4;                                // at least four chunks in flight
+        if (chunk < 1) chunk = 1;
+    }
+    const long long nchunks = (BH + chunk - 1) / chunk;
     {
         std::lock_guard<std::mutex> lk(c->mu);
-        if ((rc = ensure_stage(*c, 0, nq)) || (rc = ensure_stage(*c, 1, nk)) || (rc = ensure_stage(*c, 2, nk)) || (rc = ensure_stage(*c, 3, nq))) return rc;
-        d.Q = c->stage[0]; d.K = c->stage[1]; d.V = c->stage[2]; d.out = c->stage[3];
+        if (!c->host_streams[0]) {
+            for (int i = 0; i < 3; ++i) CU_TRY(cudaStreamCreateWithFlags(&c->host_streams[i], cudaStreamNonBlocking));
+            for (int i = 0; i < 6; ++i) CU_TRY(cudaEventCreateWithFlags(&c->host_events[i], cudaEventDisableTiming));
+        }
+        const int nbuf = nchunks > 1 ? 2 : 1;
+        for (int sset = 0; sset < nbuf; ++sset) {
+            if ((rc = ensure_stage(*c, 4 * sset + 0, (size_t)chunk * q1)) || (rc = ensure_stage(*c, 4 * sset + 1, (size_t)chunk * k1)) ||
+                (rc = ensure_stage(*c, 4 * sset + 2, (size_t)chunk * k1)) || (rc = ensure_stage(*c, 4 * sset + 3, (size_t)chunk * q1)))
+                return rc;
+        }
     }
-    d.stream = nullptr;
-    d.flags = (h->flags | B200ATTN_FLAG_ASYNC);
-    CU_TRY(cudaMemcpyAsync((void *)d.Q, h->Q, nq, cudaMemcpyHostToDevice, 0));
-    CU_TRY(cudaMemcpyAsync((void *)d.K, h->K, nk, cudaMemcpyHostToDevice, 0));
-    CU_TRY(cudaMemcpyAsync((void *)d.V, h->V, nk, cudaMemcpyHostToDevice, 0));
-    rc = forward_device(&d);
-    if (rc) return rc;
-    CU_TRY(cudaMemcpyAsync(h->out, d.out, nq, cudaMemcpyDeviceToHost, 0));
-    CU_TRY(cudaMemcpyAsync(c->err_host, c->err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, 0));
-    CU_TRY(cudaStreamSynchronize(0));
+    cudaStream_t s_in = c->host_streams[0], s_run = c->host_streams[1], s_out = c->host_streams[2];
+    cudaEvent_t *ev_in = &c->host_events[0], *ev_run = &c->host_events[2], *ev_out = &c->host_events[4];   // [2] each, by buffer set
+    for (long long ci = 0; ci < nchunks; ++ci) {
+        const int sset = (int)(ci & 1);
+        const long long h0 = ci * chunk, n = (BH - h0 < chunk) ? (BH - h0) : chunk;
+        void *dq = c->stage[4 * sset + 0], *dk = c->stage[4 * sset + 1], *dv = c->stage[4 * sset + 2], *dout = c->stage[4 * sset + 3];
+        // the inputs of this buffer set may be overwritten once the chunk two steps back has been computed
+        if (ci >= 2) CU_TRY(cudaStreamWaitEvent(s_in, ev_run[sset], 0));
+        CU_TRY(cudaMemcpyAsync(dq, (const char *)h->Q + (size_t)h0 * q1, (size_t)n * q1, cudaMemcpyHostToDevice, s_in));
+        CU_TRY(cudaMemcpyAsync(dk, (const char *)h->K + (size_t)h0 * k1, (size_t)n * k1, cudaMemcpyHostToDevice, s_in));
+        CU_TRY(cudaMemcpyAsync(dv, (const char *)h->V + (size_t)h0 * k1, (size_t)n * k1, cudaMemcpyHostToDevice, s_in));
+        CU_TRY(cudaEventRecord(ev_in[sset], s_in));
+        CU_TRY(cudaStreamWaitEvent(s_run, ev_in[sset], 0));
+        if (ci >= 2) CU_TRY(cudaStreamWaitEvent(s_run, ev_out[sset], 0));   // the output buffer has been copied out
+        b200attn_args d = *h;
+        d.Q = dq; d.K = dk; d.V = dv; d.out = dout;
+        d.batch_sz = 1; d.num_heads = (int)n;
+        d.stream = s_run;
+        d.flags = (h->flags | B200ATTN_FLAG_ASYNC);
+        rc = forward_device(&d);
+        if (rc) { cudaDeviceSynchronize(); return rc; }
+        CU_TRY(cudaEventRecord(ev_run[sset], s_run));
+        CU_TRY(cudaStreamWaitEvent(s_out, ev_run[sset], 0));
+        CU_TRY(cudaMemcpyAsync((char *)h->out + (size_t)h0 * q1, dout, (size_t)n * q1, cudaMemcpyDeviceToHost, s_out));
+        CU_TRY(cudaEventRecord(ev_out[sset], s_out));
+    }
+    CU_TRY(cudaStreamWaitEvent(s_out, ev_run[(nchunks - 1) & 1], 0));
+    CU_TRY(cudaMemcpyAsync(c->err_host, c->err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, s_out));
+    CU_TRY(cudaStreamSynchronize(s_out));
+    CU_TRY(cudaStreamSynchronize(s_in));
     if (*c->err_host != 0) {
         unsigned bits = *c->err_host;
         *c->err_host = 0;
         c->scratch_dirty = true;
+        cudaMemsetAsync(c->err_dev, 0, sizeof(unsigned), s_run);
         return fail(B200ATTN_ERR_KERNEL, "kernel reported error bits 0x%x", bits);
     }
     return B200ATTN_OK;
@@ -587,7 +629,7 @@ void b200attn_release_workspace(void) {
         c.S = nullptr; c.S_bytes = 0;
         if (c.counters) cudaFree(c.counters);
         c.counters = nullptr; c.counters_n = 0;
-        for (int i = 0; i < 4; ++i) { if (c.stage[i]) cudaFree(c.stage[i]); c.stage[i] = nullptr; c.stage_bytes[i] = 0; }
+        for (int i = 0; i < 8; ++i) { if (c.stage[i]) cudaFree(c.stage[i]); c.stage[i] = nullptr; c.stage_bytes[i] = 0; }
         c.tc_tables.release();
     }
     cudaSetDevice(prev);

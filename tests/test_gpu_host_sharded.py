@@ -25,6 +25,23 @@ def test_forward_host_pageable_and_pinned(pkg, cuda):
     assert ol.compare(op.numpy(), want)["ok"]
 
 
+def test_forward_host_pipelined_chunks_equal_device_call(pkg, cuda):
+    """A problem large enough to be cut into chunks of heads whose copy-in, compute and copy-out
+    overlap: the result must equal the single device call on the same bytes."""
+    import torch
+    B, H, L, D = 2, 40, 1024, 512
+    Q, K, V = (torch.empty(B, H, L, D, dtype=torch.bfloat16, device=cuda) for _ in range(3))
+    for t, tid in ((Q, 0), (K, 1), (V, 2)):
+        pkg.synth_fill(t, 73, tid, "normal")
+    want = pkg.forward(Q, K, V, pe=pkg.PE_SINUSOIDAL).cpu()
+    hq, hk, hv = (t.cpu().pin_memory() for t in (Q, K, V))
+    ho = torch.empty_like(hq).pin_memory()
+    for _ in range(2):   # twice: the second call reuses the staging buffers
+        ho.zero_()
+        pkg.forward_host(hq, hk, hv, ho, pe=pkg.PE_SINUSOIDAL)
+        assert torch.equal(ho.view(torch.int16), want.view(torch.int16))
+
+
 def test_sharded_launcher_equals_single_call(pkg, cuda):
     """Two shards placed on the devices that exist (both on device 0 when there is one GPU): the
     launcher needs no collective because (b,h) slices are contiguous slabs."""
