@@ -150,28 +150,53 @@ __device__ __forceinline__ void zero_rows(float *dst, int pitch, int row_begin, 
     for (int i = threadIdx.x; i < n; i += blockDim.x) dst[(long long)(row_begin + i / ncols) * pitch + (i % ncols)] = 0.0f;
 }
 
-// 64 x 64 score tile on a 16 x 16 thread grid: thread (ty,tx) owns rows ty+16r, keys tx+16c.
+// Packed fp32 FMA (two lanes per instruction, sm_100): acc.xy += a.xy * b.xy
+__device__ __forceinline__ void ffma2(float2 &acc, const float2 a, const float2 b) {
+    unsigned long long &c = reinterpret_cast<unsigned long long &>(acc);
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c) : "l"(reinterpret_cast<const unsigned long long &>(a)), "l"(reinterpret_cast<const unsigned long long &>(b)));
+}
+
+// 64 x 64 score tile on a 16 x 16 thread grid: thread (ty,tx) owns rows ty+16r, keys tx+16c.  The
+// (x,y) and (z,w) halves of the float4 operands feed packed FMAs; each score is kept as two partial
+// sums that are added at the end.
 template <int RQ, int RK>
 __device__ __forceinline__ void qk_tile(const float *Qs, const float *Ks, int pitch, int wq, float (&acc)[4][4]) {
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
     const float *qp = Qs + (long long)ty * pitch, *kp = Ks + (long long)tx * pitch;
+    float2 a2[RQ][RK];
+#pragma unroll
+    for (int r = 0; r < RQ; ++r)
+#pragma unroll
+        for (int c = 0; c < RK; ++c) a2[r][c] = make_float2(0.0f, 0.0f);
+    // software pipeline: the operands of step d+4 are loaded while the FMAs of step d issue
+    float4 q[RQ], k[RK], qn[RQ], kn[RK];
+#pragma unroll
+    for (int r = 0; r < RQ; ++r) q[r] = *reinterpret_cast<const float4 *>(qp + (long long)(16 * r) * pitch);
+#pragma unroll
+    for (int c = 0; c < RK; ++c) k[c] = *reinterpret_cast<const float4 *>(kp + (long long)(16 * c) * pitch);
 #pragma unroll 2
     for (int d = 0; d < wq; d += 4) {
-        float4 q[RQ], k[RK];
+        const int dn = (d + 4 < wq) ? d + 4 : d;
 #pragma unroll
-        for (int r = 0; r < RQ; ++r) q[r] = *reinterpret_cast<const float4 *>(qp + (long long)(16 * r) * pitch + d);
+        for (int r = 0; r < RQ; ++r) qn[r] = *reinterpret_cast<const float4 *>(qp + (long long)(16 * r) * pitch + dn);
 #pragma unroll
-        for (int c = 0; c < RK; ++c) k[c] = *reinterpret_cast<const float4 *>(kp + (long long)(16 * c) * pitch + d);
+        for (int c = 0; c < RK; ++c) kn[c] = *reinterpret_cast<const float4 *>(kp + (long long)(16 * c) * pitch + dn);
 #pragma unroll
         for (int r = 0; r < RQ; ++r)
 #pragma unroll
             for (int c = 0; c < RK; ++c) {
-                acc[r][c] = fmaf(q[r].x, k[c].x, acc[r][c]);
-                acc[r][c] = fmaf(q[r].y, k[c].y, acc[r][c]);
-                acc[r][c] = fmaf(q[r].z, k[c].z, acc[r][c]);
-                acc[r][c] = fmaf(q[r].w, k[c].w, acc[r][c]);
+                ffma2(a2[r][c], make_float2(q[r].x, q[r].y), make_float2(k[c].x, k[c].y));
+                ffma2(a2[r][c], make_float2(q[r].z, q[r].w), make_float2(k[c].z, k[c].w));
             }
+#pragma unroll
+        for (int r = 0; r < RQ; ++r) q[r] = qn[r];
+#pragma unroll
+        for (int c = 0; c < RK; ++c) k[c] = kn[c];
     }
+#pragma unroll
+    for (int r = 0; r < RQ; ++r)
+#pragma unroll
+        for (int c = 0; c < RK; ++c) acc[r][c] += a2[r][c].x + a2[r][c].y;
 }
 
 __device__ __forceinline__ void qk_dispatch(const float *Qs, const float *Ks, int pitch, int wq, int nq, int nk,
@@ -203,7 +228,7 @@ __device__ __forceinline__ void emit_scores(float *S, int Lk, int i0, int j0, in
 __device__ __forceinline__ void pv_unit(const float *Pt, const float *Vs, int vpitch, int nj, int r0, int c4,
                                         float (&o)[4][4]) {
     const float *pp = Pt + r0, *vp = Vs + 4 * c4;
-#pragma unroll 4
+#pragma unroll 8
     for (int j = 0; j < nj; ++j) {
         const float4 p = *reinterpret_cast<const float4 *>(pp + j * SD_PT_PITCH);
         const float4 v = *reinterpret_cast<const float4 *>(vp + (long long)j * vpitch);
@@ -370,20 +395,43 @@ splitd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 if (lane + 32 < Lk) s1[k] = __ldcg(Sg + (long long)i * Lk + lane + 32);
             }
         }
+#ifdef B200ATTN_SD_PROFILE
+        { float acc_ = 0.f; for (int k = 0; k < RPW; ++k) acc_ += s0[k] + s1[k]; if (acc_ == 123.456f) Pt[0] = acc_; }
+        SD_STAMP(7);
+#endif
+        // the warp's rows go through max / exp / sum in lock step, so that the shuffle and
+        // special-function latencies of the eight rows overlap instead of adding up
+        float mx[RPW], e0[RPW], e1[RPW], tot[RPW];
+#pragma unroll
+        for (int k = 0; k < RPW; ++k) {
+            s0[k] *= p.scale; s1[k] *= p.scale;
+            mx[k] = fmaxf(s0[k], s1[k]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int k = 0; k < RPW; ++k) mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
 #pragma unroll
         for (int k = 0; k < RPW; ++k) {
             const int i = warp + k * (SD_THREADS / 32);
-            if (i >= lq4) break;
-            const float a0 = s0[k] * p.scale, a1 = s1[k] * p.scale;
-            const float m = warp_max(fmaxf(a0, a1));
-            const float e0 = (i < Lq && lane < Lk) ? expf(a0 - m) : 0.0f;
-            const float e1 = (i < Lq && lane + 32 < Lk) ? expf(a1 - m) : 0.0f;
-            const float tot = warp_sum(e0 + e1);
-            if (lane < Lk) Pt[lane * SD_PT_PITCH + i] = (i < Lq) ? e0 / tot : 0.0f;
-            if (lane + 32 < Lk) Pt[(lane + 32) * SD_PT_PITCH + i] = (i < Lq) ? e1 / tot : 0.0f;
+            e0[k] = (i < Lq && lane < Lk) ? __expf(s0[k] - mx[k]) : 0.0f;   // arguments are <= 0: 2 ulp
+            e1[k] = (i < Lq && lane + 32 < Lk) ? __expf(s1[k] - mx[k]) : 0.0f;
+            tot[k] = e0[k] + e1[k];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int k = 0; k < RPW; ++k) tot[k] += __shfl_xor_sync(0xffffffffu, tot[k], o);
+#pragma unroll
+        for (int k = 0; k < RPW; ++k) {
+            const int i = warp + k * (SD_THREADS / 32);
+            if (i < lq4) {
+                const float inv = (i < Lq) ? __frcp_rn(tot[k]) : 0.0f;
+                if (lane < Lk) Pt[lane * SD_PT_PITCH + i] = e0[k] * inv;
+                if (lane + 32 < Lk) Pt[(lane + 32) * SD_PT_PITCH + i] = e1[k] * inv;
+            }
         }
     }
-    __syncthreads();
     // every thread has read its scores (they are in Pt now); the count of readers is taken here,
     // without waiting for the answer: the clean-up itself is at the very end of the kernel
     __syncthreads();
