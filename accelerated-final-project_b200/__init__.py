@@ -82,6 +82,8 @@ def lib():
         L.b200attn_synth_fill.argtypes = [C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong,
                                           C.c_int, C.c_int, C.c_void_p]
         L.b200attn_synth_fill.restype = C.c_int
+        L.b200attn_debug_lost_arrival.argtypes = [C.c_uint, C.c_uint]
+        L.b200attn_debug_lost_arrival.restype = None
         _lib = L
     return _lib
 

@@ -58,7 +58,9 @@ struct DeviceCtx {
     unsigned *counters = nullptr;  // 2 per head
     size_t counters_n = 0;
     unsigned *err_dev = nullptr;
-    unsigned *err_host = nullptr;  // pinned mirror
+    unsigned *err_host = nullptr;  // word of mapped pinned host memory: a kernel that reports an error also writes it here
+    unsigned *err_host_dev = nullptr;   // the same word as the device sees it
+    unsigned *err_bits = nullptr;  // pinned landing place for the device word when err_host says there is something to read
     bool scratch_dirty = false;    // a failed fused launch may have left S / counters non-zero
     bool attr_set[8] = {false, false, false, false, false, false, false, false};
     size_t dyn_smem_max[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -90,8 +92,10 @@ static int get_ctx(DeviceCtx **out, int *dev_out = nullptr) {
             c.max_smem_optin = prop.sharedMemPerBlockOptin;
             CU_TRY(cudaMalloc(&c.err_dev, sizeof(unsigned)));
             CU_TRY(cudaMemset(c.err_dev, 0, sizeof(unsigned)));
-            CU_TRY(cudaHostAlloc(&c.err_host, sizeof(unsigned), cudaHostAllocDefault));
-            *c.err_host = 0;
+            CU_TRY(cudaHostAlloc(&c.err_host, 2 * sizeof(unsigned), cudaHostAllocMapped | cudaHostAllocPortable));
+            c.err_host[0] = c.err_host[1] = 0;
+            c.err_bits = c.err_host + 1;
+            CU_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c.err_host_dev), c.err_host, 0));
             c.ready = true;
         }
     }
@@ -143,7 +147,12 @@ static int set_smem_attr(DeviceCtx &c, int slot, Kern kern) {
     return B200ATTN_OK;
 }
 
+// Test hook (b200attn_debug_lost_arrival): the per-head barrier of the fused kernel expects this many
+// arrivals more than there are slices, i.e. waits for a flag that nothing sets, with this poll limit.
+static std::atomic<unsigned> g_test_wait_extra{0}, g_test_spin_limit{0};
+
 static unsigned spin_limit_from_env() {
+    if (unsigned t = g_test_spin_limit.load()) return t;
     static unsigned v = [] {
         const char *s = getenv("B200ATTN_SPIN_LIMIT");
         long x = s ? atol(s) : 0;
@@ -172,7 +181,9 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
     p.scale = 1.0f / sqrtf((float)D);
     p.cos_cache = a.cos_cache; p.sin_cache = a.sin_cache;
     p.err = c.err_dev;
+    p.err_sys = c.err_host_dev;
     p.spin_limit = spin_limit_from_env();
+    p.wait_extra = g_test_wait_extra.load();
     const bool aligned16 = ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V) & 15) == 0);
     p.use_tma = (sizeof(T) == 4 && a.pe == B200ATTN_PE_NONE && D % 4 == 0 && aligned16) ? 1 : 0;
     if (getenv("B200ATTN_NO_TMA")) p.use_tma = 0;
@@ -321,20 +332,23 @@ static int validate(const b200attn_args *a, int *rd_out, float *base_out) {
     return B200ATTN_OK;
 }
 
+// To be called with the work of the call complete (its streams synchronised): kernels mirror an error
+// into mapped host memory, so the common case is one host load and no device-to-host copy.
+static int report_kernel_errors(DeviceCtx &c, const char *what) {
+    if (*reinterpret_cast<volatile unsigned *>(c.err_host) == 0) return B200ATTN_OK;
+    unsigned bits = *c.err_host;
+    if (cudaMemcpy(c.err_bits, c.err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost) == cudaSuccess) bits |= *c.err_bits;
+    *c.err_host = 0;
+    c.scratch_dirty = true;
+    cudaMemset(c.err_dev, 0, sizeof(unsigned));   // the error is reported once; later launches start clean
+    return fail(B200ATTN_ERR_KERNEL, "%s reported error bits 0x%x (bit 0: head barrier wait expired, bit 1: mbarrier wait expired, bits 8..31: which wait of the tensor-core kernel)", what, bits);
+}
+
 static int check_kernel_errors(DeviceCtx &c, cudaStream_t st, bool sync) {
-    // asynchronous calls do not read the error word back (it would put a copy between launches);
-    // it is sticky on the device and is reported by the next synchronous call
+    // asynchronous calls do not wait; an error of theirs is reported by the next call on this device
     if (!sync) return B200ATTN_OK;
-    CU_TRY(cudaMemcpyAsync(c.err_host, c.err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
-    if (*c.err_host != 0) {
-        unsigned bits = *c.err_host;
-        c.scratch_dirty = true;
-        *c.err_host = 0;
-        cudaMemsetAsync(c.err_dev, 0, sizeof(unsigned), st);   // the error is reported once; later launches start clean
-        return fail(B200ATTN_ERR_KERNEL, "kernel reported error bits 0x%x (bit 0: head barrier wait expired, bit 1: mbarrier wait expired, bits 8..31: which wait of the tensor-core kernel)", bits);
-    }
-    return B200ATTN_OK;
+    return report_kernel_errors(c, "kernel");
 }
 
 static int forward_device(const b200attn_args *a) {
@@ -347,15 +361,13 @@ static int forward_device(const b200attn_args *a) {
     std::lock_guard<std::mutex> lk(c->mu);
     cudaStream_t st = (cudaStream_t)a->stream;
     // an error left by an earlier asynchronous call is reported now
-    if (*c->err_host != 0) {
-        unsigned bits = *c->err_host;
-        *c->err_host = 0;
-        c->scratch_dirty = true;
-        return fail(B200ATTN_ERR_KERNEL, "an earlier asynchronous call reported kernel error bits 0x%x", bits);
+    if (*reinterpret_cast<volatile unsigned *>(c->err_host) != 0) {
+        cudaDeviceSynchronize();   // let the failed work drain before the scratch is cleaned
+        return report_kernel_errors(*c, "an earlier asynchronous call");
     }
     bool done = false;
     if (a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC) && tc_bf16_supported(*a, rd)) {
-        rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
@@ -383,11 +395,17 @@ static void legacy(const void *Q, const void *K, const void *V, void *out, int B
     a.Q = Q; a.K = K; a.V = V; a.out = out;
     a.batch_sz = B; a.num_heads = H; a.len_q = Lq; a.len_k = Lk; a.head_d = D;
     a.dtype = dtype; a.pe = pe; a.rotary_dim = rd; a.cos_cache = cc; a.sin_cache = sc;
+    a.flags = B200ATTN_FLAG_ASYNC;   // the one wait of the call is the device-wide one below
     int rc = forward_device(&a);
     if (rc == B200ATTN_OK) {
         // the reference launchers end with cudaDeviceSynchronize (final/attention.cu:220)
         cudaError_t e = cudaDeviceSynchronize();
         if (e != cudaSuccess) rc = fail(B200ATTN_ERR_CUDA, "CUDA error %d (%s) at %s:%d", (int)e, cudaGetErrorString(e), __FILE__, __LINE__);
+        DeviceCtx *c;
+        if (rc == B200ATTN_OK && get_ctx(&c) == B200ATTN_OK) {
+            std::lock_guard<std::mutex> lk(c->mu);
+            rc = report_kernel_errors(*c, "kernel");
+        }
     }
     if (rc != B200ATTN_OK) {
         fprintf(stderr, "b200attn: %s\n", t_last_error.c_str());
@@ -449,7 +467,7 @@ int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
     if (rc) return rc;
     if (!tc_bf16_supported(*a, rd)) return fail(B200ATTN_ERR_INVALID_ARG, "shape not taken by the tensor-core kernel");
     std::lock_guard<std::mutex> lk(c->mu);
-    rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->sm_count, spin_limit_from_env(), (cudaStream_t)a->stream, &g_launches, scores_dev);
+    rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), (cudaStream_t)a->stream, &g_launches, scores_dev);
     if (rc) return fail(rc, "%s", tc_bf16_error());
     return check_kernel_errors(*c, (cudaStream_t)a->stream, true);
 }
@@ -539,17 +557,10 @@ int b200attn_forward_host(const b200attn_args *h) {
         CU_TRY(cudaEventRecord(ev_out[sset], s_out));
     }
     CU_TRY(cudaStreamWaitEvent(s_out, ev_run[(nchunks - 1) & 1], 0));
-    CU_TRY(cudaMemcpyAsync(c->err_host, c->err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, s_out));
     CU_TRY(cudaStreamSynchronize(s_out));
     CU_TRY(cudaStreamSynchronize(s_in));
-    if (*c->err_host != 0) {
-        unsigned bits = *c->err_host;
-        *c->err_host = 0;
-        c->scratch_dirty = true;
-        cudaMemsetAsync(c->err_dev, 0, sizeof(unsigned), s_run);
-        return fail(B200ATTN_ERR_KERNEL, "kernel reported error bits 0x%x", bits);
-    }
-    return B200ATTN_OK;
+    CU_TRY(cudaStreamSynchronize(s_run));
+    return report_kernel_errors(*c, "kernel");
 }
 
 void b200attn_shard_ranges(long long total, int n, long long *begin, long long *count) {
@@ -598,17 +609,26 @@ int b200attn_forward_sharded(const b200attn_args *proto, int n, const int *devic
         if (!streams[g]) continue;
         cudaSetDevice(devices[g]);
         DeviceCtx &c = g_ctx[devices[g]];
-        cudaMemcpyAsync(c.err_host, c.err_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, streams[g]);
         cudaError_t e = cudaStreamSynchronize(streams[g]);
         if (e != cudaSuccess && status == B200ATTN_OK) status = fail(B200ATTN_ERR_CUDA, "device %d: %s", devices[g], cudaGetErrorString(e));
-        if (c.ready && *c.err_host != 0 && status == B200ATTN_OK) {
-            status = fail(B200ATTN_ERR_KERNEL, "device %d: kernel reported error bits 0x%x", devices[g], *c.err_host);
-            *c.err_host = 0;
-            c.scratch_dirty = true;
+        if (c.ready && *reinterpret_cast<volatile unsigned *>(c.err_host) != 0) {
+            char what[32];
+            snprintf(what, sizeof what, "device %d: kernel", devices[g]);
+            std::lock_guard<std::mutex> lk(c.mu);
+            const int rc = report_kernel_errors(c, what);
+            if (status == B200ATTN_OK) status = rc;
         }
     }
     cudaSetDevice(prev);
     return status;
+}
+
+// Failure detection can be exercised without faulting anything: with extra > 0 the next fused
+// split-head_d launches wait (at most spin_limit polls) for arrivals that never come, give up, and
+// report B200ATTN_ERR_KERNEL through the normal error path.  (0, 0) restores normal operation.
+void b200attn_debug_lost_arrival(unsigned extra, unsigned spin_limit) {
+    g_test_wait_extra.store(extra);
+    g_test_spin_limit.store(spin_limit);
 }
 
 const char *b200attn_last_error(void) { return t_last_error.c_str(); }

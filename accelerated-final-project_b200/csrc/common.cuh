@@ -21,6 +21,17 @@ enum KernelErr : unsigned {
     KERR_TMEM = 4u                   // tensor-memory allocation protocol failed
 };
 
+// Record kernel error bits: in the device error word (complete, OR-ed) and, when the host gave one,
+// in a word of mapped pinned host memory, which the host can look at after a synchronisation
+// without a device-to-host copy (any non-zero value there means "read the device word").
+__device__ __forceinline__ void report_kernel_error(unsigned *err, unsigned *err_sys, unsigned bits) {
+    atomicOr(err, bits);
+    if (err_sys != nullptr) {
+        *reinterpret_cast<volatile unsigned *>(err_sys) = bits;
+        __threadfence_system();
+    }
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

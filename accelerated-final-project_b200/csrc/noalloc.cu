@@ -129,6 +129,7 @@ extern "C" int b200attn_forward_static(const float *Q, const float *K, const flo
     p.pe = PE_NONE; p.rotary_dim = D; p.rope_base = 10000.0f;
     p.scale = 1.0f / sqrtf((float)D);
     p.err = reinterpret_cast<unsigned *>(sd.scratch);
+    p.err_sys = nullptr;
     p.counters = reinterpret_cast<unsigned *>(sd.scratch + 256);
     p.S = reinterpret_cast<float *>(sd.scratch + 256 + counters_bytes);
     p.spin_limit = 1u << 21;

@@ -40,7 +40,9 @@ struct SplitDParams {
     float *S;                // scratch scores [BH][Lq][Lk], all zero on entry when nsplit > 1
     unsigned *counters;      // fused kernel: [2*BH] arrive / done counters, zero on entry and on exit
     unsigned *err;           // error word (KernelErr bits)
+    unsigned *err_sys;       // optional mirror flag in mapped host memory (may be null)
     unsigned spin_limit;     // polls before a wait gives up
+    unsigned wait_extra;     // 0; a test sets it to make the head barrier wait for arrivals that never come
     int use_tma;             // fp32, no PE, D % 4 == 0: stage slices with three tiled TMA loads (tensor maps)
     int dv;                  // two-pass PV kernel: width of an output column slice
 };
@@ -366,12 +368,12 @@ splitd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             unsigned seen = 0;
             for (unsigned it = 0; it < p.spin_limit; ++it) {
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&p.counters[2 * bh]) : "memory");
-                if (seen >= (unsigned)p.nsplit) break;
+                if (seen >= (unsigned)p.nsplit + p.wait_extra) break;
                 __nanosleep(40);
             }
-            if (seen < (unsigned)p.nsplit) flag |= KERR_HEAD_BARRIER_TIMEOUT;
+            if (seen < (unsigned)p.nsplit + p.wait_extra) flag |= KERR_HEAD_BARRIER_TIMEOUT;
         }
-        if (flag) atomicOr(p.err, flag);
+        if (flag) report_kernel_error(p.err, p.err_sys, flag);
         s_flag = flag;
     }
     __syncthreads();
@@ -439,7 +441,7 @@ splitd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     SD_STAMP(5);
     bool okv = true;
     if (tma) okv = mbar_wait(&bar_v, 0, p.spin_limit);
-    if (!okv && threadIdx.x == 0) atomicOr(p.err, (unsigned)KERR_MBAR_TIMEOUT);
+    if (!okv && threadIdx.x == 0) report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT);
     if (failed || !okv) {
         // never leave the CTA while its own bulk copies may still be landing in shared memory
         if (tma) { mbar_wait(&bar_qk, 0, p.spin_limit); mbar_wait(&bar_v, 0, p.spin_limit); }

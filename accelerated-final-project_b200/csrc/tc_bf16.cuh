@@ -63,6 +63,7 @@ struct TcParams {
     int k_stages, k_stage_bytes;        // K ring: 5 x 16 KB, or 3 x (16 KB K chunk + 16 KB encoding chunk)
     __nv_bfloat16 *O;
     unsigned *err;
+    unsigned *err_sys;   // mirror flag in mapped host memory (may be null)
     unsigned spin_limit;
     float *debug_scores;                // optional: raw S of key block 0, [units][128][128]
 };
@@ -138,7 +139,7 @@ __device__ unsigned long long tc_prof[32];
 // sites are numbered in source order), then leave the enclosing loop.
 #define TC_FAIL_AT(site, cond)                                                     \
     if (cond) {                                                                    \
-        atomicOr(p.err, (unsigned)KERR_MBAR_TIMEOUT | (1u << (7 + (site))));       \
+        report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << (7 + (site)))); \
         failed = true;                                                             \
         break;                                                                     \
     }
@@ -716,7 +717,7 @@ inline size_t tc_smem_bytes(int D, bool has_pe) {
 }
 
 // Returns B200ATTN_OK, -1 when the shape should run on the other path, or a status with tc_bf16_error() set.
-inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tables, unsigned *err_dev, int sm_count,
+inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tables, unsigned *err_dev, unsigned *err_sys, int sm_count,
                        unsigned spin_limit, cudaStream_t st, std::atomic<unsigned long long> *launches, float *debug_scores = nullptr) {
     const long long BH = (long long)a.batch_sz * a.num_heads;
     const int D = a.head_d;
@@ -749,6 +750,7 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     p.rotate_k = (a.pe == B200ATTN_PE_ROPE_Q_ONLY) ? 0 : 1;
     p.O = (__nv_bfloat16 *)a.out;
     p.err = err_dev;
+    p.err_sys = err_sys;
     p.spin_limit = spin_limit;
     p.debug_scores = debug_scores;
     p.k_stages = 2;   // two 32 KB stages measure the same as three; the third's 32 KB are the P staging

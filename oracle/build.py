@@ -56,7 +56,28 @@ def build_ref(force=False):
     return REF_SO
 
 
+REF_DROPIN = os.path.join(HERE, "_ref", "ref_benchmark_dropin")
+
+
+def build_ref_dropin(force=False):
+    """The reference's only external caller (final/benchmark_pytorch_comparison.cu, compiled unmodified
+    from the reference tree) linked against THIS library instead of the reference's own definition."""
+    src = os.path.join(REF_ROOT, "final", "benchmark_pytorch_comparison.cu")
+    lib = os.path.join(HERE, "..", "accelerated-final-project_b200", "lib", "libb200attn.so")
+    if not os.path.isfile(src) or not os.path.exists(lib):
+        return REF_DROPIN if os.path.exists(REF_DROPIN) else None
+    if not force and _newer(REF_DROPIN, [src]):
+        return REF_DROPIN
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    os.makedirs(os.path.dirname(REF_DROPIN), exist_ok=True)
+    libdir = os.path.dirname(os.path.abspath(lib))
+    subprocess.check_call([nvcc, "-O3", "-w", "-gencode", "arch=compute_100a,code=sm_100a", src, "-o", REF_DROPIN,
+                           "-L", libdir, "-lb200attn", "-Xlinker", "-rpath=$ORIGIN/../../accelerated-final-project_b200/lib"])
+    return REF_DROPIN
+
+
 if __name__ == "__main__":
     force = "--force" in sys.argv
     print(build_oracle(force))
     print(build_ref(force))
+    print(build_ref_dropin(force))
