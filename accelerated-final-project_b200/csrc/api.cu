@@ -18,6 +18,7 @@
 #include "splitd.cuh"
 #include "synth.cuh"
 #include "tc_bf16.cuh"
+#include "tc_wide.cuh"
 
 namespace b200attn {
 
@@ -70,6 +71,7 @@ struct DeviceCtx {
     cudaEvent_t host_events[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     cudaStream_t shard_stream = nullptr;
     TcTables tc_tables;            // positional-encoding tables of the tensor-core path
+    TcwScratch tcw;                // scratch of the wide-head tensor-core path
 };
 static DeviceCtx g_ctx[kMaxDevices];
 
@@ -371,6 +373,11 @@ static int forward_device(const b200attn_args *a) {
         if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
+    if (!done && a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC) && tcw_supported(*a, rd)) {
+        rc = tcw_run(*a, base, c->tcw, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        if (rc == B200ATTN_OK) { t_last_path = "tc_wide"; done = true; }
+        else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
+    }
     if (!done) {
         rc = (a->dtype == B200ATTN_F32) ? run_splitd<float>(*c, *a, rd, base, st) : run_splitd<__nv_bfloat16>(*c, *a, rd, base, st);
         if (rc) return rc;
@@ -651,6 +658,7 @@ void b200attn_release_workspace(void) {
         c.counters = nullptr; c.counters_n = 0;
         for (int i = 0; i < 8; ++i) { if (c.stage[i]) cudaFree(c.stage[i]); c.stage[i] = nullptr; c.stage_bytes[i] = 0; }
         c.tc_tables.release();
+        c.tcw.release();
     }
     cudaSetDevice(prev);
 }

@@ -1,0 +1,630 @@
+// bf16 attention forward for wide heads (head_d > 512) and for the rotate-half RoPE pairing, on the
+// 5th-generation tensor cores.  A 128-row fp32 output accumulator of a 1024-wide head is twice the
+// tensor memory of an SM and the query tile is more shared memory than an SM has, so the one-kernel
+// pipeline of tc_bf16.cuh does not fit; this path runs two persistent kernels per call instead:
+//
+//   tcw_scores_kernel   S tiles [128 queries x 256 keys] = Q Kt, a K-loop over 64-wide chunks of
+//                       head_d with both operands streamed by TMA through a 4-stage ring, the
+//                       accumulator double-buffered in tensor memory (2 x 256 columns) so that the
+//                       epilogue of one tile runs under the MMAs of the next.  The epilogue takes the
+//                       row maximum of the tile and writes the scores in log2 units RELATIVE to that
+//                       maximum as bf16 (values near the maximum, the ones that carry weight, are
+//                       then small numbers and keep their precision) plus the maximum itself in fp32.
+//   tcw_pv_kernel       per (head, query tile, block of <= 512 output columns): the global row
+//                       maximum is the maximum of the tile maxima, so P = exp2(S - max) is final when
+//                       it is computed (no running rescale of the accumulator); eight warps turn the
+//                       stored scores into bf16 P tiles in shared memory, one thread issues
+//                       O += P V with V streamed by TMA, and the accumulator [128 x <=512] fp32 stays
+//                       in tensor memory until the unit's epilogue divides by the row sums.
+//
+// Rotate-half RoPE (pairs (i, i + head_d/2)) is applied inside the operand load of the score kernel:
+// the ring is filled with chunk pairs (c, c + n_chunks/2), eight transform warps rotate the pair in
+// shared memory between TMA arrival and MMA, and while the rotated pieces are in registers they are
+// also written to a scratch copy.  The tiles that do this are one "diagonal" set per head that
+// touches every query tile and every key tile once; a second launch computes all the other tiles
+// from the rotated copies without any transform.
+//
+// Shapes taken here: bf16, head_d % 64 == 0 (rotate-half: % 128 and rotary_dim == head_d),
+// len_q % 128 == 0, len_k % 128 == 0.  Every wait is bounded.
+#pragma once
+
+#include "tc_bf16.cuh"
+
+namespace b200attn {
+
+constexpr int TW_THREADS = 448;            // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-13 transform
+constexpr int TW_NST = 4;                  // operand ring depth
+constexpr int TW_BM = 128;                 // query rows per score tile
+constexpr int TW_BN = 256;                 // keys per score tile
+constexpr int TW_QCHUNK = TW_BM * 128;     // [128 rows x 64 bf16]
+constexpr int TW_KCHUNK = TW_BN * 128;     // [256 rows x 64 bf16]
+constexpr int TW_STAGE = TW_QCHUNK + TW_KCHUNK;
+
+struct TcwScoreParams {
+    int Lq, Lk, D, nch;        // nch = D / 64
+    int nqt, nkt;              // Lq / 128, ceil(Lk / 256)
+    int mode;                  // 0: every tile, operands as given; 1: the encoding tile set; 2: all other tiles
+    int tph;                   // tiles per head in this launch
+    long long n_tiles;         // heads * tph
+    float scale_log2;          // log2(e) / sqrt(D)
+    __nv_bfloat16 *S;          // [heads * Lq][Lk]  scores, log2 units, relative to the tile's row maximum
+    float *rowmax;             // [heads * Lq][nkt] row maxima of the tiles, log2 units
+    const __nv_bfloat16 *tab;  // mode 1: [>= max(Lq, 256 * nkt)][D], cos in columns [0, D/2), sin in [D/2, D)
+    __nv_bfloat16 *q_store, *k_store;   // mode 1: rotated copies, [heads * Lq][D] and [heads * Lk][D]
+    unsigned *err, *err_sys;
+    unsigned spin_limit;
+};
+
+struct TwBars {
+    uint64_t full[TW_NST], ready[TW_NST], empty[TW_NST];
+    uint64_t acc_full[2], acc_empty[2];
+};
+
+#define TW_FAIL_AT(site, cond)                                                                      \
+    if (cond) {                                                                                     \
+        report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << (7 + (site))));  \
+        failed = true;                                                                              \
+        break;                                                                                      \
+    }
+
+// Tile j of a head for the three launch modes.  Mode 1 is a set of max(nqt, nkt) tiles that contains
+// every query tile and every key tile; mode 2 is its complement.
+__device__ __forceinline__ void tcw_tile_of(int mode, int j, int nqt, int nkt, int *qt, int *kt) {
+    if (mode == 0) { *qt = j / nkt; *kt = j - *qt * nkt; }
+    else if (mode == 1) { *qt = j % nqt; *kt = j % nkt; }
+    else if (nkt <= nqt) { const int q = j / (nkt - 1), r = j - q * (nkt - 1); *qt = q; *kt = (q % nkt + 1 + r) % nkt; }
+    else { const int k = j / (nqt - 1), r = j - k * (nqt - 1); *kt = k; *qt = (k % nqt + 1 + r) % nqt; }
+}
+
+// (lo, hi) -> (lo*c - hi*s, hi*c + lo*s) on packed bf16 pairs
+__device__ __forceinline__ void tcw_rotate(uint32_t &lo, uint32_t &hi, uint32_t c, uint32_t s) {
+    const __nv_bfloat162 l = *reinterpret_cast<__nv_bfloat162 *>(&lo), h = *reinterpret_cast<__nv_bfloat162 *>(&hi);
+    const __nv_bfloat162 cc = *reinterpret_cast<__nv_bfloat162 *>(&c), ss = *reinterpret_cast<__nv_bfloat162 *>(&s);
+    uint32_t ns_bits = s ^ 0x80008000u;
+    const __nv_bfloat162 ns = *reinterpret_cast<__nv_bfloat162 *>(&ns_bits);
+    __nv_bfloat162 nl = __hfma2(h, ns, __hmul2(l, cc));
+    __nv_bfloat162 nh = __hfma2(l, ss, __hmul2(h, cc));
+    lo = *reinterpret_cast<uint32_t *>(&nl);
+    hi = *reinterpret_cast<uint32_t *>(&nh);
+}
+
+__global__ void __launch_bounds__(TW_THREADS, 1)
+tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const TcwScoreParams p) {
+    extern __shared__ unsigned char tw_smem_raw[];
+    __shared__ TwBars bars;
+    __shared__ uint32_t tmem_slot;
+    const uint32_t raw_addr = smem_u32(tw_smem_raw);
+    unsigned char *smem = tw_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nch = p.nch;
+    const uint32_t lim = p.spin_limit;
+    const bool encode = (p.mode == 1);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TW_NST; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.ready[i], 8); mbar_init(&bars.empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&bars.acc_full[i], 1); mbar_init(&bars.acc_empty[i], 4); }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    bool failed = false;
+    const bool skip = (*reinterpret_cast<volatile unsigned *>(p.err) != 0);   // an earlier kernel of the call failed
+
+    if (skip) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x) {
+                const long long bh = tile / p.tph;
+                int qt, kt;
+                tcw_tile_of(p.mode, (int)(tile - bh * p.tph), p.nqt, p.nkt, &qt, &kt);
+                for (int ci = 0; ci < nch; ++ci, ++it) {
+                    // encoding tiles take the chunks in pairs (c, c + nch/2) on neighbouring ring slots
+                    const int c = encode ? ((ci >> 1) + (ci & 1) * (nch >> 1)) : ci;
+                    const int s = it % TW_NST;
+                    TW_FAIL_AT(0, !mbar_wait(&bars.empty[s], ((it / TW_NST) & 1) ^ 1, lim));
+                    unsigned char *st = smem + (size_t)s * TW_STAGE;
+                    mbar_expect_tx(&bars.full[s], TW_STAGE);
+                    tma_load_2d(st, &tmQ, c * 64, (int)(bh * p.Lq + qt * TW_BM), &bars.full[s]);
+                    tma_load_2d(st + TW_QCHUNK, &tmK, c * 64, (int)(bh * p.Lk + kt * TW_BN), &bars.full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TW_BM, TW_BN, 0, 0);
+            int it = 0;
+            long long tc = 0;
+            for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x, ++tc) {
+                const int ab = (int)(tc & 1);
+                TW_FAIL_AT(1, !mbar_wait(&bars.acc_empty[ab], ((tc >> 1) & 1) ^ 1, lim));
+                tc_fence_after();
+                for (int ci = 0; ci < nch; ++ci, ++it) {
+                    const int s = it % TW_NST;
+                    TW_FAIL_AT(2, !mbar_wait(encode ? &bars.ready[s] : &bars.full[s], (it / TW_NST) & 1, lim));
+                    tc_fence_after();
+                    const uint64_t da = umma_desc_k_sw128(smem_u32(smem + (size_t)s * TW_STAGE));
+                    const uint64_t db = umma_desc_k_sw128(smem_u32(smem + (size_t)s * TW_STAGE + TW_QCHUNK));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma_bf16(tmem + ab * TW_BN, da + 2 * k, db + 2 * k, idesc, (ci | k) != 0);
+                    umma_commit(&bars.empty[s]);
+                }
+                if (failed) break;
+                umma_commit(&bars.acc_full[ab]);
+            }
+        }
+    } else if (warp < 6) {
+        // ---- epilogue: one thread per query row of the tile ----
+        const int row = 32 * (warp & 3) + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+        uint32_t r[32];
+        long long tc = 0;
+        for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x, ++tc) {
+            const long long bh = tile / p.tph;
+            int qt, kt;
+            tcw_tile_of(p.mode, (int)(tile - bh * p.tph), p.nqt, p.nkt, &qt, &kt);
+            const int ab = (int)(tc & 1);
+            TW_FAIL_AT(3, !mbar_wait(&bars.acc_full[ab], (tc >> 1) & 1, lim));
+            tc_fence_after();
+            const int ncc = min(TW_BN, p.Lk - kt * TW_BN) / 32;   // 32-column groups that hold real keys
+            const uint32_t ta = lane_addr + ab * TW_BN;
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            for (int c = 0; c < ncc; ++c) {
+                tmem_ld32(ta + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(r[j]));
+                    mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
+                }
+            }
+            const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+            const long long grow = bh * p.Lq + (long long)qt * TW_BM + row;
+            p.rowmax[grow * p.nkt + kt] = mt;
+            __nv_bfloat16 *srow = p.S + grow * p.Lk + (long long)kt * TW_BN;
+            for (int c = 0; c < ncc; ++c) {
+                tmem_ld32(ta + c * 32, r);
+                tmem_ld_wait();
+                uint4 *dst = reinterpret_cast<uint4 *>(srow + c * 32);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint4 o;
+                    o.x = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 0]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 1]), p.scale_log2, -mt));
+                    o.y = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 2]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 3]), p.scale_log2, -mt));
+                    o.z = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 4]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 5]), p.scale_log2, -mt));
+                    o.w = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 6]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 7]), p.scale_log2, -mt));
+                    dst[g] = o;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.acc_empty[ab]);
+        }
+    } else if (encode) {
+        // ---- transform warps: rotate-half of the chunk pair in ring slots (s, s+1) ----
+        const int tid = threadIdx.x - 6 * 32;   // 0..255
+        const int half = p.D >> 1;
+        int it = 0;
+        for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x) {
+            const long long bh = tile / p.tph;
+            int qt, kt;
+            tcw_tile_of(p.mode, (int)(tile - bh * p.tph), p.nqt, p.nkt, &qt, &kt);
+            for (int c = 0; c < (nch >> 1); ++c, it += 2) {
+                const int s = it % TW_NST;
+                TW_FAIL_AT(4, !mbar_wait(&bars.full[s], (it / TW_NST) & 1, lim));
+                TW_FAIL_AT(5, !mbar_wait(&bars.full[s + 1], (it / TW_NST) & 1, lim));
+                unsigned char *lo_st = smem + (size_t)s * TW_STAGE, *hi_st = lo_st + TW_STAGE;
+                for (int o = tid; o < (TW_BM + TW_BN) * 8; o += 256) {
+                    const bool is_k = (o >= TW_BM * 8);
+                    const int oo = is_k ? o - TW_BM * 8 : o;
+                    const int r = oo >> 3, q = (oo & 7) ^ (r & 7);     // row, logical 16-byte column
+                    const int pos = (is_k ? kt * TW_BN : qt * TW_BM) + r;
+                    const size_t off = (size_t)(is_k ? TW_QCHUNK : 0) + (size_t)oo * 16;
+                    uint4 lo = *reinterpret_cast<uint4 *>(lo_st + off), hi = *reinterpret_cast<uint4 *>(hi_st + off);
+                    const __nv_bfloat16 *tp = p.tab + (long long)pos * p.D + c * 64 + q * 8;
+                    const uint4 tc4 = __ldg(reinterpret_cast<const uint4 *>(tp));
+                    const uint4 ts4 = __ldg(reinterpret_cast<const uint4 *>(tp + half));
+                    tcw_rotate(lo.x, hi.x, tc4.x, ts4.x);
+                    tcw_rotate(lo.y, hi.y, tc4.y, ts4.y);
+                    tcw_rotate(lo.z, hi.z, tc4.z, ts4.z);
+                    tcw_rotate(lo.w, hi.w, tc4.w, ts4.w);
+                    *reinterpret_cast<uint4 *>(lo_st + off) = lo;
+                    *reinterpret_cast<uint4 *>(hi_st + off) = hi;
+                    if (!is_k || pos < p.Lk) {
+                        __nv_bfloat16 *g = (is_k ? p.k_store + (bh * p.Lk + pos) * (long long)p.D : p.q_store + (bh * p.Lq + pos) * (long long)p.D) + c * 64 + q * 8;
+                        *reinterpret_cast<uint4 *>(g) = lo;
+                        *reinterpret_cast<uint4 *>(g + half) = hi;
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(&bars.ready[s]); mbar_arrive(&bars.ready[s + 1]); }
+            }
+        }
+    }
+
+    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies and MMAs in flight drain
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------------
+constexpr int TP_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-9 softmax (2-5 also run the unit's epilogue)
+constexpr int TP_NV = 4;          // V stage ring depth (32 keys per stage)
+constexpr int TP_NP = 2;          // P buffers
+
+struct TcwPvParams {
+    int Lq, Lk, D;
+    int DW, ndp;               // output columns per unit (<= 512, a multiple of 64) and units per query tile
+    int nqt, nkt, nblk;        // Lq / 128, ceil(Lk / 256), Lk / 128
+    long long n_units;         // heads * nqt * ndp
+    const __nv_bfloat16 *S;    // as written by tcw_scores_kernel
+    const float *rowmax;
+    __nv_bfloat16 *O;          // [heads * Lq][D]
+    unsigned *err, *err_sys;
+    unsigned spin_limit;
+};
+
+struct TpBars {
+    uint64_t v_full[TP_NV], v_empty[TP_NV];
+    uint64_t p_full[TP_NP], p_empty[TP_NP];
+    uint64_t o_full, o_empty;
+    uint64_t l_full;   // the eight softmax warps have written the unit's row sums
+};
+
+__global__ void __launch_bounds__(TP_THREADS, 1)
+tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const TcwPvParams p) {
+    extern __shared__ unsigned char tw_smem_raw[];
+    __shared__ TpBars bars;
+    __shared__ uint32_t tmem_slot;
+    __shared__ float l_smem[2][TW_BM];
+    const uint32_t raw_addr = smem_u32(tw_smem_raw);
+    unsigned char *smem = tw_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    unsigned char *p_smem = smem;                                   // TP_NP x 32 KB
+    unsigned char *v_smem = smem + (size_t)TP_NP * TC_P_BYTES;      // TP_NV x (32 keys x DW x 2 B)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int DW = p.DW, nblk = p.nblk;
+    const int v_stage_bytes = TC_VS * DW * 2;
+    const uint32_t lim = p.spin_limit;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < TP_NV; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
+        for (int i = 0; i < TP_NP; ++i) { mbar_init(&bars.p_full[i], 8); mbar_init(&bars.p_empty[i], 1); }
+        mbar_init(&bars.o_full, 1);
+        mbar_init(&bars.o_empty, 4);
+        mbar_init(&bars.l_full, 8);
+        mbar_fence_init();
+        tma_prefetch_desc(&tmV);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    bool failed = false;
+    const bool skip = (*reinterpret_cast<volatile unsigned *>(p.err) != 0);
+
+    if (skip) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
+                const int dp = (int)(unit % p.ndp);
+                const long long bh = unit / p.ndp / p.nqt;
+                for (int t = 0; t < nblk && !failed; ++t)
+                    for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
+                        const int s = it % TP_NV;
+                        TW_FAIL_AT(8, !mbar_wait(&bars.v_empty[s], ((it / TP_NV) & 1) ^ 1, lim));
+                        mbar_expect_tx(&bars.v_full[s], (uint32_t)v_stage_bytes);
+                        for (int g = 0; g < DW / 64; ++g)
+                            tma_load_2d(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TC_VS * 128), &tmV, dp * DW + g * 64,
+                                        (int)(bh * p.Lk + t * TC_BN + vs * TC_VS), &bars.v_full[s]);
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, ui = 0;
+            long long tg = 0;
+            for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x, ++ui) {
+                // the epilogue of the previous unit has read the accumulator
+                TW_FAIL_AT(9, !mbar_wait(&bars.o_empty, (ui & 1) ^ 1, lim));
+                tc_fence_after();
+                for (int t = 0; t < nblk && !failed; ++t, ++tg) {
+                    const int pb = (int)(tg % TP_NP);
+                    TW_FAIL_AT(10, !mbar_wait(&bars.p_full[pb], (tg / TP_NP) & 1, lim));
+                    tc_fence_after();
+                    for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
+                        const int s = it % TP_NV;
+                        TW_FAIL_AT(11, !mbar_wait(&bars.v_full[s], (it / TP_NV) & 1, lim));
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 0; kk < TC_VS / 16; ++kk) {
+                            const int kg = vs * (TC_VS / 16) + kk;   // 16-key step within the block, 0..7
+                            const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TW_BM * 128))) + 2 * (kg & 3);
+                            for (int n0 = 0; n0 < DW; n0 += 256) {
+                                const int N = min(256, DW - n0);
+                                const uint64_t db = umma_desc_mn_sw128(
+                                    smem_u32(v_smem + (size_t)s * v_stage_bytes + (size_t)(n0 >> 6) * (TC_VS * 128) + kk * 2048), TC_VS * 128);
+                                umma_bf16(tmem + n0, da, db, umma_idesc_bf16(TW_BM, N, 0, 1), (t | kg) != 0);
+                            }
+                        }
+                        umma_commit(&bars.v_empty[s]);
+                    }
+                    if (failed) break;
+                    umma_commit(&bars.p_empty[pb]);
+                }
+                if (failed) break;
+                umma_commit(&bars.o_full);
+            }
+        }
+    } else {
+        // ---- softmax warps: warp w turns rows [16w, 16w+16) of every key block into P, lane = 4 keys ----
+        const int w = warp - 2;
+        int ui = 0;
+        long long tg = 0;
+        for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x, ++ui) {
+            const int dp = (int)(unit % p.ndp);
+            const long long rest = unit / p.ndp;
+            const int qt = (int)(rest % p.nqt);
+            const long long bh = rest / p.nqt;
+            const long long grow0 = bh * p.Lq + (long long)qt * TW_BM + 16 * w;
+            float M[16], l[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                float m = -INFINITY;
+                for (int j = lane; j < p.nkt; j += 32) m = fmaxf(m, __ldg(p.rowmax + (grow0 + k) * p.nkt + j));
+                M[k] = warp_max(m);
+                l[k] = 0.0f;
+            }
+            uint2 cur[16], nxt[16];
+            float off[16], noff[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                cur[k] = *reinterpret_cast<const uint2 *>(p.S + (grow0 + k) * p.Lk + 4 * lane);
+                off[k] = __ldg(p.rowmax + (grow0 + k) * p.nkt) - M[k];
+            }
+            for (int t = 0; t < nblk; ++t, ++tg) {
+                const int pb = (int)(tg % TP_NP);
+                if (t + 1 < nblk) {
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        nxt[k] = *reinterpret_cast<const uint2 *>(p.S + (grow0 + k) * p.Lk + (t + 1) * TC_BN + 4 * lane);
+                        noff[k] = __ldg(p.rowmax + (grow0 + k) * p.nkt + ((t + 1) >> 1)) - M[k];
+                    }
+                }
+                TW_FAIL_AT(12, !mbar_wait(&bars.p_empty[pb], ((tg / TP_NP) & 1) ^ 1, lim));
+                unsigned char *pbuf = p_smem + (size_t)pb * TC_P_BYTES + (lane >> 4) * (TW_BM * 128) + (lane & 1) * 8;
+                const int u16 = (lane & 15) >> 1;
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const int r = 16 * w + k;
+                    const float e0 = fast_exp2(__uint_as_float(cur[k].x << 16) + off[k]);
+                    const float e1 = fast_exp2(__uint_as_float(cur[k].x & 0xffff0000u) + off[k]);
+                    const float e2 = fast_exp2(__uint_as_float(cur[k].y << 16) + off[k]);
+                    const float e3 = fast_exp2(__uint_as_float(cur[k].y & 0xffff0000u) + off[k]);
+                    l[k] += (e0 + e1) + (e2 + e3);
+                    uint2 o;
+                    o.x = pack_bf16x2(e0, e1);
+                    o.y = pack_bf16x2(e2, e3);
+                    *reinterpret_cast<uint2 *>(pbuf + r * 128 + ((u16 ^ (r & 7)) << 4)) = o;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.p_full[pb]);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) { cur[k] = nxt[k]; off[k] = noff[k]; }
+            }
+            if (failed) break;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const float s = warp_sum(l[k]);
+                if (lane == k) l_smem[ui & 1][16 * w + k] = s;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.l_full);
+            if (w < 4) {
+                // ---- epilogue of the unit: O / row sum -> bf16 -> global, one thread per query row ----
+                const int row = 32 * (warp & 3) + lane;
+                const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+                TW_FAIL_AT(13, !mbar_wait(&bars.l_full, ui & 1, lim));
+                TW_FAIL_AT(14, !mbar_wait(&bars.o_full, ui & 1, lim));
+                tc_fence_after();
+                const float inv = 1.0f / l_smem[ui & 1][row];
+                __nv_bfloat16 *orow = p.O + (bh * p.Lq + (long long)qt * TW_BM + row) * (long long)p.D + dp * DW;
+                uint32_t r[32];
+                for (int c = 0; c < DW / 32; ++c) {
+                    tmem_ld32(lane_addr + c * 32, r);
+                    tmem_ld_wait();
+                    uint4 *dst = reinterpret_cast<uint4 *>(orow + c * 32);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 o;
+                        o.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
+                        o.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
+                        o.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
+                        o.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
+                        dst[g] = o;
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.o_empty);
+            }
+        }
+    }
+
+    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+#undef TW_FAIL_AT
+
+// ---- host side ------------------------------------------------------------------------------------
+// cos(pos * f_i) in columns [0, D/2) and sin(pos * f_i) in [D/2, D), f_i = base^(-2i/D): the fp32
+// arithmetic of the reference's cos/sin caches (final/rope.cu:20-40), rounded once to bf16.
+__global__ void tcw_build_half_table(__nv_bfloat16 *table, int L, int D, float base) {
+    const long long n = (long long)L * D;
+    const int half = D >> 1;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int pos = (int)(i / D), d = (int)(i % D);
+        const int f = d < half ? d : d - half;
+        const float freq = 1.0f / powf(base, (2.0f * (float)f) / (float)D);
+        const float th = (float)pos * freq;
+        table[i] = __float2bfloat16_rn(d < half ? cosf(th) : sinf(th));
+    }
+}
+
+// Scratch of the wide path, kept per device and grown on demand.
+struct TcwScratch {
+    void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};   // S, rowmax, rotated Q, rotated K, table
+    size_t bytes[5] = {0, 0, 0, 0, 0};
+    int tab_L = 0, tab_D = 0;
+    float tab_base = 0.0f;
+    void *get(int i, size_t want) {
+        if (want > bytes[i]) {
+            if (buf[i]) { cudaDeviceSynchronize(); cudaFree(buf[i]); }
+            buf[i] = nullptr; bytes[i] = 0;
+            if (i == 4) tab_L = 0;
+            if (cudaMalloc(&buf[i], want) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+            bytes[i] = want;
+        }
+        return buf[i];
+    }
+    void release() {
+        for (int i = 0; i < 5; ++i) { if (buf[i]) cudaFree(buf[i]); buf[i] = nullptr; bytes[i] = 0; }
+        tab_L = 0;
+    }
+};
+
+inline bool tcw_supported(const b200attn_args &a, int rd) {
+    if (getenv("B200ATTN_NO_TC") || getenv("B200ATTN_NO_TC_WIDE")) return false;
+    if (a.dtype != B200ATTN_BF16) return false;
+    if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 8192) return false;
+    if (a.len_q % TW_BM != 0 || a.len_k % TC_BN != 0) return false;
+    if (a.pe == B200ATTN_PE_ROPE_HALF) { if (a.head_d % 128 != 0 || rd != a.head_d) return false; }
+    else if (a.pe != B200ATTN_PE_NONE) return false;
+    if (a.cos_cache != nullptr) return false;
+    if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return false;
+    const long long BH = (long long)a.batch_sz * a.num_heads;
+    if (BH * a.len_q >= (1ll << 31) || BH * (a.len_k + 256) >= (1ll << 31)) return false;
+    return true;
+}
+
+// Returns B200ATTN_OK, -1 when the shape should run on another path, or a status with tc_bf16_error() set.
+inline int tcw_run(const b200attn_args &a, float base, TcwScratch &sc, unsigned *err_dev, unsigned *err_sys, int sm_count,
+                   unsigned spin_limit, cudaStream_t st, std::atomic<unsigned long long> *launches) {
+    const long long BH = (long long)a.batch_sz * a.num_heads;
+    const int D = a.head_d, Lq = a.len_q, Lk = a.len_k;
+    const bool rope = (a.pe == B200ATTN_PE_ROPE_HALF);
+    int ndp = 1;
+    while (D % (64 * ndp) != 0 || D / ndp > 512) ++ndp;
+    const int DW = D / ndp;
+    const int nqt = Lq / TW_BM, nkt = (Lk + TW_BN - 1) / TW_BN, nblk = Lk / TC_BN;
+    const size_t smem_s = (size_t)TW_NST * TW_STAGE + 1024;
+    const size_t smem_p = (size_t)TP_NP * TC_P_BYTES + (size_t)TP_NV * TC_VS * DW * 2 + 1024;
+    static std::mutex attr_mu;
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> lk(attr_mu);
+        if (!attr_done[dev & 63]) {
+            cudaFuncAttributes fa;
+            cudaDeviceProp prop;
+            cudaGetDeviceProperties(&prop, dev);
+            bool ok = cudaFuncGetAttributes(&fa, tcw_scores_kernel) == cudaSuccess &&
+                      cudaFuncSetAttribute(tcw_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
+            ok = ok && cudaFuncGetAttributes(&fa, tcw_pv_kernel) == cudaSuccess &&
+                 cudaFuncSetAttribute(tcw_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
+            if (!ok) { (void)cudaGetLastError(); snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncSetAttribute(max dynamic shared memory) failed"); return B200ATTN_ERR_CUDA; }
+            attr_done[dev & 63] = true;
+        }
+    }
+    // heads per pass: the score scratch of one pass stays below a cap (default 2 GiB)
+    size_t cap = (size_t)2 << 30;
+    if (const char *e = getenv("B200ATTN_TCW_SCRATCH_MB")) { long long v = atoll(e); if (v > 0) cap = (size_t)v << 20; }
+    const size_t s_head = (size_t)Lq * Lk * sizeof(__nv_bfloat16);
+    long long G = (long long)(cap / s_head);
+    if (G < 1) G = 1;
+    if (G > BH) G = BH;
+    __nv_bfloat16 *S = (__nv_bfloat16 *)sc.get(0, (size_t)G * s_head);
+    float *rowmax = (float *)sc.get(1, (size_t)G * Lq * nkt * sizeof(float));
+    __nv_bfloat16 *qs = nullptr, *ks = nullptr, *tab = nullptr;
+    if (!S || !rowmax) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the score scratch"); return B200ATTN_ERR_CUDA; }
+    if (rope) {
+        qs = (__nv_bfloat16 *)sc.get(2, (size_t)G * Lq * D * 2);
+        ks = (__nv_bfloat16 *)sc.get(3, (size_t)G * Lk * D * 2);
+        const int Lt = (Lq > nkt * TW_BN ? Lq : nkt * TW_BN);
+        const bool have = sc.buf[4] && sc.tab_L >= Lt && sc.tab_D == D && sc.tab_base == base;
+        tab = (__nv_bfloat16 *)(have ? sc.buf[4] : sc.get(4, (size_t)Lt * D * 2));
+        if (!qs || !ks || !tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the rotated-operand scratch"); return B200ATTN_ERR_CUDA; }
+        if (!have) {
+            if (sc.tab_L != 0) cudaDeviceSynchronize();   // no kernel may still be reading the table that is replaced
+            tcw_build_half_table<<<296, 256, 0, st>>>(tab, Lt, D, base);
+            launches->fetch_add(1);
+            sc.tab_L = Lt; sc.tab_D = D; sc.tab_base = base;
+        }
+    }
+    for (long long h0 = 0; h0 < BH; h0 += G) {
+        const long long nh = (BH - h0 < G) ? BH - h0 : G;
+        const __nv_bfloat16 *Qg = (const __nv_bfloat16 *)a.Q + h0 * Lq * D, *Kg = (const __nv_bfloat16 *)a.K + h0 * Lk * D;
+        const __nv_bfloat16 *Vg = (const __nv_bfloat16 *)a.V + h0 * Lk * D;
+        TcwScoreParams sp{};
+        sp.Lq = Lq; sp.Lk = Lk; sp.D = D; sp.nch = D / 64; sp.nqt = nqt; sp.nkt = nkt;
+        sp.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+        sp.S = S; sp.rowmax = rowmax; sp.tab = tab; sp.q_store = qs; sp.k_store = ks;
+        sp.err = err_dev; sp.err_sys = err_sys; sp.spin_limit = spin_limit;
+        auto launch_scores = [&](const void *Qp, const void *Kp, int mode, int tph) -> int {
+            if (tph <= 0) return B200ATTN_OK;
+            CUtensorMap tmQ, tmK;
+            if (!tc_make_map(&tmQ, Qp, nh * Lq, D, TW_BM) || !tc_make_map(&tmK, Kp, nh * Lk, D, TW_BN)) {
+                snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
+                return B200ATTN_ERR_CUDA;
+            }
+            sp.mode = mode; sp.tph = tph; sp.n_tiles = nh * tph;
+            const unsigned grid = (unsigned)(sp.n_tiles < sm_count ? sp.n_tiles : sm_count);
+            tcw_scores_kernel<<<grid, TW_THREADS, smem_s, st>>>(tmQ, tmK, sp);
+            cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "tcw_scores_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
+            launches->fetch_add(1);
+            return B200ATTN_OK;
+        };
+        int rc;
+        if (rope) {
+            const int nA = nqt > nkt ? nqt : nkt;
+            rc = launch_scores(Qg, Kg, 1, nA);
+            if (rc == B200ATTN_OK) rc = launch_scores(qs, ks, 2, nqt * nkt - nA);
+        } else {
+            rc = launch_scores(Qg, Kg, 0, nqt * nkt);
+        }
+        if (rc) return rc;
+        CUtensorMap tmV;
+        if (!tc_make_map(&tmV, Vg, nh * Lk, D, TC_VS)) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
+        TcwPvParams pp{};
+        pp.Lq = Lq; pp.Lk = Lk; pp.D = D; pp.DW = DW; pp.ndp = ndp; pp.nqt = nqt; pp.nkt = nkt; pp.nblk = nblk;
+        pp.n_units = nh * nqt * ndp;
+        pp.S = S; pp.rowmax = rowmax; pp.O = (__nv_bfloat16 *)a.out + h0 * Lq * D;
+        pp.err = err_dev; pp.err_sys = err_sys; pp.spin_limit = spin_limit;
+        const unsigned grid = (unsigned)(pp.n_units < sm_count ? pp.n_units : sm_count);
+        tcw_pv_kernel<<<grid, TP_THREADS, smem_p, st>>>(tmV, pp);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "tcw_pv_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
+        launches->fetch_add(1);
+    }
+    return B200ATTN_OK;
+}
+
+}  // namespace b200attn
