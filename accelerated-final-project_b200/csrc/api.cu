@@ -368,7 +368,8 @@ static int forward_device(const b200attn_args *a) {
         return report_kernel_errors(*c, "an earlier asynchronous call");
     }
     bool done = false;
-    if (a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC) && tc_bf16_supported(*a, rd)) {
+    const bool prefer_wide = getenv("B200ATTN_TC_PREFER_WIDE") != nullptr && tcw_supported(*a, rd);
+    if (!prefer_wide && a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC) && tc_bf16_supported(*a, rd)) {
         rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());

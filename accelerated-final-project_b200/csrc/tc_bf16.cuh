@@ -420,7 +420,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     TC_PROF(3);
                     // hand the block over: every lane makes its stores visible to the peer's tensor core,
                     // one lane arrives for the warp (the other group computes meanwhile)
-                    fence_proxy_async();
+                    fence_proxy_async_dsmem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[pb]), 1));
                     TC_PROF(5);
@@ -456,7 +456,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const int s = it % NKS;
                     TC_FAIL_AT(13, !mbar_wait(&bars.k_full[s], (it / NKS) & 1, lim));
                     tc_pe_chunk(q_smem + (size_t)c * TC_CHUNK_BYTES, k_smem + (size_t)s * KSB + TC_CHUNK_BYTES, sinus, tid);
-                    fence_proxy_async();
+                    fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.k_ready[s]);
                 }
@@ -469,7 +469,7 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                             unsigned char *kt = k_smem + (size_t)s * KSB;
                             __nv_bfloat16 *gd = p.k_store ? p.k_store + ((bh * p.Lk + (long long)t * TC_BN) * D + c * 64) : nullptr;
                             tc_pe_chunk(kt, kt + TC_CHUNK_BYTES, sinus, tid, gd, D);
-                            fence_proxy_async();
+                            fence_proxy_async_smem();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&bars.k_ready[s]);
                         }

@@ -54,6 +54,11 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity
 }
 // Generic-proxy writes (st.shared / st.shared::cluster) -> visible to the async proxy (UMMA, TMA).
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// The same restricted to this CTA's shared memory / to the cluster's shared memory.  The unrestricted
+// form also orders global memory between the proxies: it waits for the thread's global stores and for
+// bulk copies in flight, which costs thousands of cycles inside a pipelined loop.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_dsmem() { asm volatile("fence.proxy.async.shared::cluster;" ::: "memory"); }
 
 // ---- TMA tiled load (no multicast) ----------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *tmap, int x, int y, uint64_t *bar) {

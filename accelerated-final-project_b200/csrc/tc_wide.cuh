@@ -12,7 +12,7 @@
 //                       then small numbers and keep their precision) plus the maximum itself in fp32.
 //   tcw_pv_kernel       per (head, query tile, block of <= 512 output columns): the global row
 //                       maximum is the maximum of the tile maxima, so P = exp2(S - max) is final when
-//                       it is computed (no running rescale of the accumulator); eight warps turn the
+//                       it is computed (no running rescale of the accumulator); sixteen warps turn the
 //                       stored scores into bf16 P tiles in shared memory, one thread issues
 //                       O += P V with V streamed by TMA, and the accumulator [128 x <=512] fp32 stays
 //                       in tensor memory until the unit's epilogue divides by the row sums.
@@ -60,6 +60,25 @@ struct TwBars {
     uint64_t acc_full[2], acc_empty[2];
 };
 
+// Optional cycle accounting (profiling builds only): -DB200ATTN_TC_PROFILE plus -DB200ATTN_PROF_WIDE=1
+// (score kernel, launches of mode B200ATTN_PROF_MODE) or =2 (P V kernel).
+#if defined(B200ATTN_TC_PROFILE) && defined(B200ATTN_PROF_WIDE)
+#ifndef B200ATTN_PROF_MODE
+#define B200ATTN_PROF_MODE 1
+#endif
+#define TWS_DECL TC_PROF_DECL
+#define TWS(slot) do { if (B200ATTN_PROF_WIDE == 1) TC_PROF(slot); } while (0)
+#define TWS_FLUSH(base, on) do { if (B200ATTN_PROF_WIDE == 1 && p.mode == B200ATTN_PROF_MODE) TC_PROF_FLUSH(base, on); } while (0)
+#define TWP(slot) do { if (B200ATTN_PROF_WIDE == 2) TC_PROF(slot); } while (0)
+#define TWP_FLUSH(base, on) do { if (B200ATTN_PROF_WIDE == 2) TC_PROF_FLUSH(base, on); } while (0)
+#else
+#define TWS_DECL
+#define TWS(slot)
+#define TWS_FLUSH(base, on)
+#define TWP(slot)
+#define TWP_FLUSH(base, on)
+#endif
+
 #define TW_FAIL_AT(site, cond)                                                                      \
     if (cond) {                                                                                     \
         report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << (7 + (site))));  \
@@ -86,6 +105,14 @@ __device__ __forceinline__ void tcw_rotate(uint32_t &lo, uint32_t &hi, uint32_t 
     __nv_bfloat162 nh = __hfma2(l, ss, __hmul2(h, cc));
     lo = *reinterpret_cast<uint32_t *>(&nl);
     hi = *reinterpret_cast<uint32_t *>(&nh);
+}
+
+// A 16-byte read-only load that the compiler keeps where it is written (it would otherwise be free to
+// sink a plain load down to its first use, which defeats a software pipeline of loads).
+__device__ __forceinline__ uint4 tcw_ldg_here(const void *ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
 }
 
 __global__ void __launch_bounds__(TW_THREADS, 1)
@@ -119,6 +146,7 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     } else if (warp == 0) {
         if (lane == 0) {
             int it = 0;
+            TWS_DECL;
             for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x) {
                 const long long bh = tile / p.tph;
                 int qt, kt;
@@ -127,27 +155,35 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     // encoding tiles take the chunks in pairs (c, c + nch/2) on neighbouring ring slots
                     const int c = encode ? ((ci >> 1) + (ci & 1) * (nch >> 1)) : ci;
                     const int s = it % TW_NST;
+                    TWS(0);
                     TW_FAIL_AT(0, !mbar_wait(&bars.empty[s], ((it / TW_NST) & 1) ^ 1, lim));
+                    TWS(1);
                     unsigned char *st = smem + (size_t)s * TW_STAGE;
                     mbar_expect_tx(&bars.full[s], TW_STAGE);
                     tma_load_2d(st, &tmQ, c * 64, (int)(bh * p.Lq + qt * TW_BM), &bars.full[s]);
                     tma_load_2d(st + TW_QCHUNK, &tmK, c * 64, (int)(bh * p.Lk + kt * TW_BN), &bars.full[s]);
                 }
             }
+            TWS_FLUSH(0, true);
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(TW_BM, TW_BN, 0, 0);
             int it = 0;
             long long tc = 0;
+            TWS_DECL;
             for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x, ++tc) {
                 const int ab = (int)(tc & 1);
+                TWS(2);
                 TW_FAIL_AT(1, !mbar_wait(&bars.acc_empty[ab], ((tc >> 1) & 1) ^ 1, lim));
                 tc_fence_after();
+                TWS(0);
                 for (int ci = 0; ci < nch; ++ci, ++it) {
                     const int s = it % TW_NST;
+                    TWS(2);
                     TW_FAIL_AT(2, !mbar_wait(encode ? &bars.ready[s] : &bars.full[s], (it / TW_NST) & 1, lim));
                     tc_fence_after();
+                    TWS(1);
                     const uint64_t da = umma_desc_k_sw128(smem_u32(smem + (size_t)s * TW_STAGE));
                     const uint64_t db = umma_desc_k_sw128(smem_u32(smem + (size_t)s * TW_STAGE + TW_QCHUNK));
 #pragma unroll
@@ -157,6 +193,7 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (failed) break;
                 umma_commit(&bars.acc_full[ab]);
             }
+            TWS_FLUSH(8, true);
         }
     } else if (warp < 6) {
         // ---- epilogue: one thread per query row of the tile ----
@@ -209,45 +246,88 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
     } else if (encode) {
         // ---- transform warps: rotate-half of the chunk pair in ring slots (s, s+1) ----
+        // A thread owns 12 of the 3072 16-byte piece pairs of a step: pieces 0-3 in the Q chunks and
+        // 4-11 in the K chunks, each 32 rows below the last, all in the same logical column.  The
+        // cos/sin values come straight from the table in global memory through a 6-deep register
+        // pipeline: the slot of a piece is refilled, as soon as it has been used, with the values
+        // of the piece six further on (of the next step where needed), so the L2 latency of the
+        // table reads is covered by the work on the pieces in between.
         const int tid = threadIdx.x - 6 * 32;   // 0..255
-        const int half = p.D >> 1;
-        int it = 0;
-        for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x) {
-            const long long bh = tile / p.tph;
-            int qt, kt;
-            tcw_tile_of(p.mode, (int)(tile - bh * p.tph), p.nqt, p.nkt, &qt, &kt);
-            for (int c = 0; c < (nch >> 1); ++c, it += 2) {
-                const int s = it % TW_NST;
-                TW_FAIL_AT(4, !mbar_wait(&bars.full[s], (it / TW_NST) & 1, lim));
-                TW_FAIL_AT(5, !mbar_wait(&bars.full[s + 1], (it / TW_NST) & 1, lim));
-                unsigned char *lo_st = smem + (size_t)s * TW_STAGE, *hi_st = lo_st + TW_STAGE;
-                for (int o = tid; o < (TW_BM + TW_BN) * 8; o += 256) {
-                    const bool is_k = (o >= TW_BM * 8);
-                    const int oo = is_k ? o - TW_BM * 8 : o;
-                    const int r = oo >> 3, q = (oo & 7) ^ (r & 7);     // row, logical 16-byte column
-                    const int pos = (is_k ? kt * TW_BN : qt * TW_BM) + r;
-                    const size_t off = (size_t)(is_k ? TW_QCHUNK : 0) + (size_t)oo * 16;
-                    uint4 lo = *reinterpret_cast<uint4 *>(lo_st + off), hi = *reinterpret_cast<uint4 *>(hi_st + off);
-                    const __nv_bfloat16 *tp = p.tab + (long long)pos * p.D + c * 64 + q * 8;
-                    const uint4 tc4 = __ldg(reinterpret_cast<const uint4 *>(tp));
-                    const uint4 ts4 = __ldg(reinterpret_cast<const uint4 *>(tp + half));
-                    tcw_rotate(lo.x, hi.x, tc4.x, ts4.x);
-                    tcw_rotate(lo.y, hi.y, tc4.y, ts4.y);
-                    tcw_rotate(lo.z, hi.z, tc4.z, ts4.z);
-                    tcw_rotate(lo.w, hi.w, tc4.w, ts4.w);
-                    *reinterpret_cast<uint4 *>(lo_st + off) = lo;
-                    *reinterpret_cast<uint4 *>(hi_st + off) = hi;
-                    if (!is_k || pos < p.Lk) {
-                        __nv_bfloat16 *g = (is_k ? p.k_store + (bh * p.Lk + pos) * (long long)p.D : p.q_store + (bh * p.Lq + pos) * (long long)p.D) + c * 64 + q * 8;
-                        *reinterpret_cast<uint4 *>(g) = lo;
-                        *reinterpret_cast<uint4 *>(g + half) = hi;
-                    }
-                }
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) { mbar_arrive(&bars.ready[s]); mbar_arrive(&bars.ready[s + 1]); }
+        const int half = p.D >> 1, npairs = nch >> 1;
+        const int r0 = tid >> 3;
+        const int qcol = (tid & 7) ^ (r0 & 7);   // logical 16-byte column of all pieces of this thread
+        struct Step { long long tile, bh; int qt, kt, c; bool valid; };
+        auto decode = [&](Step &s) {
+            s.valid = s.tile < p.n_tiles;
+            if (s.valid) {
+                s.bh = s.tile / p.tph;
+                tcw_tile_of(p.mode, (int)(s.tile - s.bh * p.tph), p.nqt, p.nkt, &s.qt, &s.kt);
+            }
+        };
+        auto next_of = [&](const Step &s) {   // the step after s: next chunk pair, or the first of this CTA's next tile
+            Step n = s;
+            if (++n.c == npairs) { n.c = 0; n.tile += gridDim.x; decode(n); }
+            return n;
+        };
+        auto tab_ptr = [&](const Step &s, int i) {
+            const int pos = (i >= 4 ? s.kt * TW_BN + 32 * (i - 4) : s.qt * TW_BM + 32 * i) + r0;
+            return p.tab + (long long)pos * p.D + s.c * 64 + qcol * 8;
+        };
+        uint4 tcv[6], tsv[6];
+        Step cur;
+        cur.tile = blockIdx.x; cur.bh = 0; cur.qt = 0; cur.kt = 0; cur.c = 0;
+        decode(cur);
+        if (cur.valid) {
+#pragma unroll
+            for (int i = 0; i < 6; ++i) {
+                const __nv_bfloat16 *tp = tab_ptr(cur, i);
+                tcv[i] = tcw_ldg_here(tp);
+                tsv[i] = tcw_ldg_here(tp + half);
             }
         }
+        int it = 0;
+        TWS_DECL;
+        for (long long n = 0; cur.valid && !failed; ++n, it += 2) {
+            TWS(3);
+            const Step nx = next_of(cur);
+            const int s = it % TW_NST;
+            TWS(0);
+            TW_FAIL_AT(4, !mbar_wait(&bars.full[s], (it / TW_NST) & 1, lim));
+            TW_FAIL_AT(5, !mbar_wait(&bars.full[s + 1], (it / TW_NST) & 1, lim));
+            TWS(1);
+            unsigned char *lo_st = smem + (size_t)s * TW_STAGE, *hi_st = lo_st + TW_STAGE;
+#pragma unroll
+            for (int i = 0; i < 12; ++i) {
+                const int slot = i % 6;
+                const bool is_k = (i >= 4);
+                const int r = r0 + 32 * (is_k ? i - 4 : i);
+                const int pos = (is_k ? cur.kt * TW_BN : cur.qt * TW_BM) + r;
+                const size_t off = (size_t)(is_k ? TW_QCHUNK : 0) + (size_t)(tid + 256 * (is_k ? i - 4 : i)) * 16;
+                uint4 lo = *reinterpret_cast<uint4 *>(lo_st + off), hi = *reinterpret_cast<uint4 *>(hi_st + off);
+                tcw_rotate(lo.x, hi.x, tcv[slot].x, tsv[slot].x);
+                tcw_rotate(lo.y, hi.y, tcv[slot].y, tsv[slot].y);
+                tcw_rotate(lo.z, hi.z, tcv[slot].z, tsv[slot].z);
+                tcw_rotate(lo.w, hi.w, tcv[slot].w, tsv[slot].w);
+                if (i < 6 || nx.valid) {
+                    const __nv_bfloat16 *tp = (i < 6) ? tab_ptr(cur, i + 6) : tab_ptr(nx, i - 6);
+                    tcv[slot] = tcw_ldg_here(tp);
+                    tsv[slot] = tcw_ldg_here(tp + half);
+                }
+                *reinterpret_cast<uint4 *>(lo_st + off) = lo;
+                *reinterpret_cast<uint4 *>(hi_st + off) = hi;
+                if (!is_k || pos < p.Lk) {
+                    __nv_bfloat16 *g = (is_k ? p.k_store + (cur.bh * p.Lk + pos) * (long long)p.D : p.q_store + (cur.bh * p.Lq + pos) * (long long)p.D) + cur.c * 64 + qcol * 8;
+                    *reinterpret_cast<uint4 *>(g) = lo;
+                    *reinterpret_cast<uint4 *>(g + half) = hi;
+                }
+            }
+            TWS(2);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&bars.ready[s]); mbar_arrive(&bars.ready[s + 1]); }
+            cur = nx;
+        }
+        TWS_FLUSH(16, tid == 0);
     }
 
     if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies and MMAs in flight drain
@@ -258,17 +338,20 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------------------------------
-constexpr int TP_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-9 softmax (2-5 also run the unit's epilogue)
-constexpr int TP_NV = 4;          // V stage ring depth (32 keys per stage)
-constexpr int TP_NP = 2;          // P buffers
+constexpr int TP_THREADS = 608;   // warp 0 V loads, warp 1 MMA, warps 2-17 softmax and the unit's epilogue, warp 18 S loads
+#ifndef B200ATTN_TP_VS
+#define B200ATTN_TP_VS 64
+#endif
+constexpr int TP_VS = B200ATTN_TP_VS;           // keys per V stage
+constexpr int TP_NV = 128 / TP_VS;   // V stage ring depth: 128 keys in flight
+constexpr int TP_NP = 3;          // score / P buffers
 
 struct TcwPvParams {
     int Lq, Lk, D;
     int DW, ndp;               // output columns per unit (<= 512, a multiple of 64) and units per query tile
     int nqt, nkt, nblk;        // Lq / 128, ceil(Lk / 256), Lk / 128
     long long n_units;         // heads * nqt * ndp
-    const __nv_bfloat16 *S;    // as written by tcw_scores_kernel
-    const float *rowmax;
+    const float *rowmax;       // as written by tcw_scores_kernel (the scores themselves come through the tensor map)
     __nv_bfloat16 *O;          // [heads * Lq][D]
     unsigned *err, *err_sys;
     unsigned spin_limit;
@@ -276,13 +359,20 @@ struct TcwPvParams {
 
 struct TpBars {
     uint64_t v_full[TP_NV], v_empty[TP_NV];
-    uint64_t p_full[TP_NP], p_empty[TP_NP];
+    uint64_t s_full[TP_NP];    // the score block has landed in the buffer
+    uint64_t p_full[TP_NP];    // ... has been turned into P in place
+    uint64_t p_empty[TP_NP];   // ... has been read by the block's last MMA
     uint64_t o_full, o_empty;
-    uint64_t l_full;   // the eight softmax warps have written the unit's row sums
+    uint64_t l_full;           // the sixteen softmax warps have written the unit's row sums
 };
 
+// The stored scores of a key block [128 rows x 128 keys] bf16 are loaded by TMA as two
+// [128 x 64] boxes with the 128-byte swizzle, which is exactly the K-major operand layout the MMA
+// wants for P: the softmax warps turn the block into P IN PLACE (exp2 is element-wise, every
+// thread rewrites the 16-byte pieces it read), so no score ever passes through a register before
+// it is needed and the P tile needs no second buffer.
 __global__ void __launch_bounds__(TP_THREADS, 1)
-tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const TcwPvParams p) {
+tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmS, const TcwPvParams p) {
     extern __shared__ unsigned char tw_smem_raw[];
     __shared__ TpBars bars;
     __shared__ uint32_t tmem_slot;
@@ -293,17 +383,17 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const TcwPvParams p) {
     unsigned char *v_smem = smem + (size_t)TP_NP * TC_P_BYTES;      // TP_NV x (32 keys x DW x 2 B)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int DW = p.DW, nblk = p.nblk;
-    const int v_stage_bytes = TC_VS * DW * 2;
+    const int v_stage_bytes = TP_VS * DW * 2;
     const uint32_t lim = p.spin_limit;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < TP_NV; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
-        for (int i = 0; i < TP_NP; ++i) { mbar_init(&bars.p_full[i], 8); mbar_init(&bars.p_empty[i], 1); }
+        for (int i = 0; i < TP_NP; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.p_full[i], 16); mbar_init(&bars.p_empty[i], 1); }
         mbar_init(&bars.o_full, 1);
-        mbar_init(&bars.o_empty, 4);
-        mbar_init(&bars.l_full, 8);
+        mbar_init(&bars.o_empty, 16);
+        mbar_init(&bars.l_full, 16);
         mbar_fence_init();
-        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmS);
     }
     if (warp == 0) tmem_alloc(&tmem_slot, 512);
     tc_fence_before();
@@ -318,44 +408,73 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const TcwPvParams p) {
     } else if (warp == 0) {
         if (lane == 0) {
             int it = 0;
+            TWS_DECL;
             for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
                 const int dp = (int)(unit % p.ndp);
                 const long long bh = unit / p.ndp / p.nqt;
                 for (int t = 0; t < nblk && !failed; ++t)
-                    for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
+                    for (int vs = 0; vs < TC_BN / TP_VS; ++vs, ++it) {
                         const int s = it % TP_NV;
+                        TWP(1);
                         TW_FAIL_AT(8, !mbar_wait(&bars.v_empty[s], ((it / TP_NV) & 1) ^ 1, lim));
+                        TWP(0);
                         mbar_expect_tx(&bars.v_full[s], (uint32_t)v_stage_bytes);
                         for (int g = 0; g < DW / 64; ++g)
-                            tma_load_2d(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TC_VS * 128), &tmV, dp * DW + g * 64,
-                                        (int)(bh * p.Lk + t * TC_BN + vs * TC_VS), &bars.v_full[s]);
+                            tma_load_2d(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TP_VS * 128), &tmV, dp * DW + g * 64,
+                                        (int)(bh * p.Lk + t * TC_BN + vs * TP_VS), &bars.v_full[s]);
                     }
             }
+            TWP_FLUSH(0, true);
+        }
+    } else if (warp == 18) {
+        if (lane == 0) {
+            long long tg = 0;
+            TWS_DECL;
+            for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
+                const long long rest = unit / p.ndp;   // = bh * nqt + qt: the row tile of the score matrix
+                for (int t = 0; t < nblk; ++t, ++tg) {
+                    const int pb = (int)(tg % TP_NP);
+                    TWP(1);
+                    TW_FAIL_AT(15, !mbar_wait(&bars.p_empty[pb], ((tg / TP_NP) & 1) ^ 1, lim));
+                    TWP(0);
+                    mbar_expect_tx(&bars.s_full[pb], TC_P_BYTES);
+                    tma_load_2d(p_smem + (size_t)pb * TC_P_BYTES, &tmS, t * TC_BN, (int)(rest * TW_BM), &bars.s_full[pb]);
+                    tma_load_2d(p_smem + (size_t)pb * TC_P_BYTES + TW_BM * 128, &tmS, t * TC_BN + 64, (int)(rest * TW_BM), &bars.s_full[pb]);
+                }
+            }
+            TWP_FLUSH(4, true);
         }
     } else if (warp == 1) {
         if (lane == 0) {
             int it = 0, ui = 0;
             long long tg = 0;
+            TWS_DECL;
             for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x, ++ui) {
                 // the epilogue of the previous unit has read the accumulator
+                TWP(3);
                 TW_FAIL_AT(9, !mbar_wait(&bars.o_empty, (ui & 1) ^ 1, lim));
                 tc_fence_after();
+                TWP(0);
                 for (int t = 0; t < nblk && !failed; ++t, ++tg) {
                     const int pb = (int)(tg % TP_NP);
+                    TWP(3);
                     TW_FAIL_AT(10, !mbar_wait(&bars.p_full[pb], (tg / TP_NP) & 1, lim));
                     tc_fence_after();
-                    for (int vs = 0; vs < TC_BN / TC_VS; ++vs, ++it) {
+                    TWP(1);
+                    for (int vs = 0; vs < TC_BN / TP_VS; ++vs, ++it) {
                         const int s = it % TP_NV;
+                        TWP(3);
                         TW_FAIL_AT(11, !mbar_wait(&bars.v_full[s], (it / TP_NV) & 1, lim));
                         tc_fence_after();
+                        TWP(2);
 #pragma unroll
-                        for (int kk = 0; kk < TC_VS / 16; ++kk) {
-                            const int kg = vs * (TC_VS / 16) + kk;   // 16-key step within the block, 0..7
+                        for (int kk = 0; kk < TP_VS / 16; ++kk) {
+                            const int kg = vs * (TP_VS / 16) + kk;   // 16-key step within the block, 0..7
                             const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TW_BM * 128))) + 2 * (kg & 3);
                             for (int n0 = 0; n0 < DW; n0 += 256) {
                                 const int N = min(256, DW - n0);
                                 const uint64_t db = umma_desc_mn_sw128(
-                                    smem_u32(v_smem + (size_t)s * v_stage_bytes + (size_t)(n0 >> 6) * (TC_VS * 128) + kk * 2048), TC_VS * 128);
+                                    smem_u32(v_smem + (size_t)s * v_stage_bytes + (size_t)(n0 >> 6) * (TP_VS * 128) + kk * 2048), TP_VS * 128);
                                 umma_bf16(tmem + n0, da, db, umma_idesc_bf16(TW_BM, N, 0, 1), (t | kg) != 0);
                             }
                         }
@@ -367,74 +486,81 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const TcwPvParams p) {
                 if (failed) break;
                 umma_commit(&bars.o_full);
             }
+            TWP_FLUSH(8, true);
         }
     } else {
-        // ---- softmax warps: warp w turns rows [16w, 16w+16) of every key block into P, lane = 4 keys ----
-        const int w = warp - 2;
+        // ---- softmax warps: warp w owns rows [8w, 8w+8) of every key block.  Eight lanes cover one
+        // 128-byte row of a 64-key half (conflict-free 16-byte accesses), so a thread works on rows
+        // 8w + lane/8 and 8w + 4 + lane/8, in both halves: four 16-byte pieces per block.  The offset
+        // (tile maximum - row maximum) of row 8w + k for key tile j is kept in lane j of offs[k]. ----
+        const int w = warp - 2, rl = lane >> 3;
         int ui = 0;
         long long tg = 0;
+        TWS_DECL;
         for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x, ++ui) {
             const int dp = (int)(unit % p.ndp);
             const long long rest = unit / p.ndp;
             const int qt = (int)(rest % p.nqt);
             const long long bh = rest / p.nqt;
-            const long long grow0 = bh * p.Lq + (long long)qt * TW_BM + 16 * w;
-            float M[16], l[16];
+            const long long grow0 = bh * p.Lq + (long long)qt * TW_BM + 8 * w;
+            float offs[8];
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                float m = -INFINITY;
-                for (int j = lane; j < p.nkt; j += 32) m = fmaxf(m, __ldg(p.rowmax + (grow0 + k) * p.nkt + j));
-                M[k] = warp_max(m);
-                l[k] = 0.0f;
+            for (int k = 0; k < 8; ++k) {
+                const float m = lane < p.nkt ? __ldg(p.rowmax + (grow0 + k) * p.nkt + lane) : -INFINITY;
+                offs[k] = m - warp_max(m);
             }
-            uint2 cur[16], nxt[16];
-            float off[16], noff[16];
-#pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                cur[k] = *reinterpret_cast<const uint2 *>(p.S + (grow0 + k) * p.Lk + 4 * lane);
-                off[k] = __ldg(p.rowmax + (grow0 + k) * p.nkt) - M[k];
-            }
+            float lA = 0.0f, lB = 0.0f, offA = 0.0f, offB = 0.0f;
             for (int t = 0; t < nblk; ++t, ++tg) {
                 const int pb = (int)(tg % TP_NP);
-                if (t + 1 < nblk) {
+                if ((t & 1) == 0) {   // a new 256-key tile: fetch this thread's two offsets
+                    const int kt = t >> 1;
+                    float v[8];
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        nxt[k] = *reinterpret_cast<const uint2 *>(p.S + (grow0 + k) * p.Lk + (t + 1) * TC_BN + 4 * lane);
-                        noff[k] = __ldg(p.rowmax + (grow0 + k) * p.nkt + ((t + 1) >> 1)) - M[k];
+                    for (int k = 0; k < 8; ++k) v[k] = __shfl_sync(0xffffffffu, offs[k], kt);
+                    offA = rl == 0 ? v[0] : rl == 1 ? v[1] : rl == 2 ? v[2] : v[3];
+                    offB = rl == 0 ? v[4] : rl == 1 ? v[5] : rl == 2 ? v[6] : v[7];
+                }
+                TWP(3);
+                TW_FAIL_AT(12, !mbar_wait(&bars.s_full[pb], (tg / TP_NP) & 1, lim));
+                TWP(0);
+                unsigned char *base = p_smem + (size_t)pb * TC_P_BYTES + (8 * w + rl) * 128 + (lane & 7) * 16;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    // i & 1: row A / row B (4 rows = 512 B further); i >> 1: the 64-key half (16 KB further)
+                    uint4 *pp = reinterpret_cast<uint4 *>(base + (i & 1) * 512 + (i >> 1) * (TW_BM * 128));
+                    const uint4 xv = *pp;
+                    const float off = (i & 1) ? offB : offA;
+                    const uint32_t x[4] = {xv.x, xv.y, xv.z, xv.w};
+                    uint32_t o[4];
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float e0 = fast_exp2(__uint_as_float(x[q] << 16) + off);
+                        const float e1 = fast_exp2(__uint_as_float(x[q] & 0xffff0000u) + off);
+                        sum += e0 + e1;
+                        o[q] = pack_bf16x2(e0, e1);
                     }
+                    if (i & 1) lB += sum; else lA += sum;
+                    *pp = make_uint4(o[0], o[1], o[2], o[3]);
                 }
-                TW_FAIL_AT(12, !mbar_wait(&bars.p_empty[pb], ((tg / TP_NP) & 1) ^ 1, lim));
-                unsigned char *pbuf = p_smem + (size_t)pb * TC_P_BYTES + (lane >> 4) * (TW_BM * 128) + (lane & 1) * 8;
-                const int u16 = (lane & 15) >> 1;
-#pragma unroll
-                for (int k = 0; k < 16; ++k) {
-                    const int r = 16 * w + k;
-                    const float e0 = fast_exp2(__uint_as_float(cur[k].x << 16) + off[k]);
-                    const float e1 = fast_exp2(__uint_as_float(cur[k].x & 0xffff0000u) + off[k]);
-                    const float e2 = fast_exp2(__uint_as_float(cur[k].y << 16) + off[k]);
-                    const float e3 = fast_exp2(__uint_as_float(cur[k].y & 0xffff0000u) + off[k]);
-                    l[k] += (e0 + e1) + (e2 + e3);
-                    uint2 o;
-                    o.x = pack_bf16x2(e0, e1);
-                    o.y = pack_bf16x2(e2, e3);
-                    *reinterpret_cast<uint2 *>(pbuf + r * 128 + ((u16 ^ (r & 7)) << 4)) = o;
-                }
-                fence_proxy_async();
+                TWP(1);
+                fence_proxy_async_smem();
+                TWP(2);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.p_full[pb]);
-#pragma unroll
-                for (int k = 0; k < 16; ++k) { cur[k] = nxt[k]; off[k] = noff[k]; }
             }
             if (failed) break;
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                const float s = warp_sum(l[k]);
-                if (lane == k) l_smem[ui & 1][16 * w + k] = s;
+            for (int o = 4; o > 0; o >>= 1) {
+                lA += __shfl_xor_sync(0xffffffffu, lA, o);
+                lB += __shfl_xor_sync(0xffffffffu, lB, o);
             }
+            if ((lane & 7) == 0) { l_smem[ui & 1][8 * w + rl] = lA; l_smem[ui & 1][8 * w + 4 + rl] = lB; }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.l_full);
-            if (w < 4) {
-                // ---- epilogue of the unit: O / row sum -> bf16 -> global, one thread per query row ----
+            {
+                // ---- epilogue of the unit: O / row sum -> bf16 -> global.  A warp may only read the
+                // TMEM lane quadrant warp % 4; the four warps of a quadrant share its 32-column groups ----
                 const int row = 32 * (warp & 3) + lane;
                 const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
                 TW_FAIL_AT(13, !mbar_wait(&bars.l_full, ui & 1, lim));
@@ -443,7 +569,7 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const TcwPvParams p) {
                 const float inv = 1.0f / l_smem[ui & 1][row];
                 __nv_bfloat16 *orow = p.O + (bh * p.Lq + (long long)qt * TW_BM + row) * (long long)p.D + dp * DW;
                 uint32_t r[32];
-                for (int c = 0; c < DW / 32; ++c) {
+                for (int c = (w >> 2); c < DW / 32; c += 4) {
                     tmem_ld32(lane_addr + c * 32, r);
                     tmem_ld_wait();
                     uint4 *dst = reinterpret_cast<uint4 *>(orow + c * 32);
@@ -461,7 +587,9 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const TcwPvParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.o_empty);
             }
+            TWP(4);
         }
+        TWP_FLUSH(16, threadIdx.x == 64);
     }
 
     if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -514,6 +642,7 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
     if (a.dtype != B200ATTN_BF16) return false;
     if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 8192) return false;
     if (a.len_q % TW_BM != 0 || a.len_k % TC_BN != 0) return false;
+    if (a.len_k > 32 * TW_BN) return false;   // the offsets of a row's key tiles live one per lane
     if (a.pe == B200ATTN_PE_ROPE_HALF) { if (a.head_d % 128 != 0 || rd != a.head_d) return false; }
     else if (a.pe != B200ATTN_PE_NONE) return false;
     if (a.cos_cache != nullptr) return false;
@@ -534,7 +663,7 @@ inline int tcw_run(const b200attn_args &a, float base, TcwScratch &sc, unsigned 
     const int DW = D / ndp;
     const int nqt = Lq / TW_BM, nkt = (Lk + TW_BN - 1) / TW_BN, nblk = Lk / TC_BN;
     const size_t smem_s = (size_t)TW_NST * TW_STAGE + 1024;
-    const size_t smem_p = (size_t)TP_NP * TC_P_BYTES + (size_t)TP_NV * TC_VS * DW * 2 + 1024;
+    const size_t smem_p = (size_t)TP_NP * TC_P_BYTES + (size_t)TP_NV * TP_VS * DW * 2 + 1024;
     static std::mutex attr_mu;
     static bool attr_done[64] = {};
     int dev = 0;
@@ -611,15 +740,15 @@ inline int tcw_run(const b200attn_args &a, float base, TcwScratch &sc, unsigned 
             rc = launch_scores(Qg, Kg, 0, nqt * nkt);
         }
         if (rc) return rc;
-        CUtensorMap tmV;
-        if (!tc_make_map(&tmV, Vg, nh * Lk, D, TC_VS)) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
+        CUtensorMap tmV, tmS;
+        if (!tc_make_map(&tmV, Vg, nh * Lk, D, TP_VS) || !tc_make_map(&tmS, S, nh * Lq, Lk, TW_BM)) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
         TcwPvParams pp{};
         pp.Lq = Lq; pp.Lk = Lk; pp.D = D; pp.DW = DW; pp.ndp = ndp; pp.nqt = nqt; pp.nkt = nkt; pp.nblk = nblk;
         pp.n_units = nh * nqt * ndp;
-        pp.S = S; pp.rowmax = rowmax; pp.O = (__nv_bfloat16 *)a.out + h0 * Lq * D;
+        pp.rowmax = rowmax; pp.O = (__nv_bfloat16 *)a.out + h0 * Lq * D;
         pp.err = err_dev; pp.err_sys = err_sys; pp.spin_limit = spin_limit;
         const unsigned grid = (unsigned)(pp.n_units < sm_count ? pp.n_units : sm_count);
-        tcw_pv_kernel<<<grid, TP_THREADS, smem_p, st>>>(tmV, pp);
+        tcw_pv_kernel<<<grid, TP_THREADS, smem_p, st>>>(tmV, tmS, pp);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "tcw_pv_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
         launches->fetch_add(1);
