@@ -582,16 +582,16 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 for (int c = 0; c < D / 32; ++c) {
                     tmem_ld32(lane_addr + c * 32, r);
                     tmem_ld_wait();
-                    uint4 *dst = reinterpret_cast<uint4 *>(orow + c * 32);
+                    uint4 o[4];
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        uint4 o;
-                        o.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
-                        o.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
-                        o.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
-                        o.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
-                        dst[g] = o;
+                        o[g].x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
+                        o[g].y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
+                        o[g].z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
+                        o[g].w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
                     }
+                    st_global_v8(orow + c * 32, o[0], o[1]);
+                    st_global_v8(orow + c * 32 + 16, o[2], o[3]);
                 }
                 tc_fence_before();   // the accumulator reads are ordered before the corr_done arrival of the next unit
             }
@@ -697,6 +697,7 @@ inline bool tc_bf16_supported(const b200attn_args &a, int rd) {
     if (a.pe != B200ATTN_PE_NONE && a.pe != B200ATTN_PE_SINUSOIDAL && (rd % 8 != 0)) return false;
     if (a.cos_cache != nullptr) return false;
     if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return false;
+    if (((uintptr_t)a.out & 31) != 0) return false;   // the epilogue stores 32 bytes at a time
     const long long BH = (long long)a.batch_sz * a.num_heads;
     if (BH * a.len_q >= (1ll << 31) || BH * a.len_k >= (1ll << 31)) return false;
     if (BH * (a.len_q / TC_BM) * 2 >= (1ll << 31)) return false;

@@ -178,6 +178,15 @@ inline bool make_tmap_2d(CUtensorMap *m, CUtensorMapDataType dt, int esize, cons
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 32-byte store (one full sector per thread; the address must be 32-byte aligned).  Row-per-thread
+// epilogues write with this: a 16-byte store covers half a sector, and partial-sector writes make
+// the L2 merge (or fetch) the other half.
+__device__ __forceinline__ void st_global_v8(void *ptr, uint4 a, uint4 b) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x),
+                 "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

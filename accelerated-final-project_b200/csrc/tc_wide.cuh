@@ -229,16 +229,16 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             for (int c = 0; c < ncc; ++c) {
                 tmem_ld32(ta + c * 32, r);
                 tmem_ld_wait();
-                uint4 *dst = reinterpret_cast<uint4 *>(srow + c * 32);
+                uint4 o[4];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
-                    uint4 o;
-                    o.x = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 0]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 1]), p.scale_log2, -mt));
-                    o.y = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 2]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 3]), p.scale_log2, -mt));
-                    o.z = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 4]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 5]), p.scale_log2, -mt));
-                    o.w = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 6]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 7]), p.scale_log2, -mt));
-                    dst[g] = o;
+                    o[g].x = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 0]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 1]), p.scale_log2, -mt));
+                    o[g].y = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 2]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 3]), p.scale_log2, -mt));
+                    o[g].z = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 4]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 5]), p.scale_log2, -mt));
+                    o[g].w = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 6]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 7]), p.scale_log2, -mt));
                 }
+                st_global_v8(srow + c * 32, o[0], o[1]);
+                st_global_v8(srow + c * 32 + 16, o[2], o[3]);
             }
             tc_fence_before();
             __syncwarp();
@@ -563,31 +563,33 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                 // TMEM lane quadrant warp % 4; the four warps of a quadrant share its 32-column groups ----
                 const int row = 32 * (warp & 3) + lane;
                 const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+                TWP(4);
                 TW_FAIL_AT(13, !mbar_wait(&bars.l_full, ui & 1, lim));
                 TW_FAIL_AT(14, !mbar_wait(&bars.o_full, ui & 1, lim));
                 tc_fence_after();
+                TWP(5);
                 const float inv = 1.0f / l_smem[ui & 1][row];
                 __nv_bfloat16 *orow = p.O + (bh * p.Lq + (long long)qt * TW_BM + row) * (long long)p.D + dp * DW;
                 uint32_t r[32];
                 for (int c = (w >> 2); c < DW / 32; c += 4) {
                     tmem_ld32(lane_addr + c * 32, r);
                     tmem_ld_wait();
-                    uint4 *dst = reinterpret_cast<uint4 *>(orow + c * 32);
+                    uint4 o[4];
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        uint4 o;
-                        o.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
-                        o.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
-                        o.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
-                        o.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
-                        dst[g] = o;
+                        o[g].x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
+                        o[g].y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
+                        o[g].z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
+                        o[g].w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
                     }
+                    st_global_v8(orow + c * 32, o[0], o[1]);
+                    st_global_v8(orow + c * 32 + 16, o[2], o[3]);
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.o_empty);
             }
-            TWP(4);
+            TWP(6);
         }
         TWP_FLUSH(16, threadIdx.x == 64);
     }
@@ -647,6 +649,7 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
     else if (a.pe != B200ATTN_PE_NONE) return false;
     if (a.cos_cache != nullptr) return false;
     if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return false;
+    if (((uintptr_t)a.out & 31) != 0) return false;   // the epilogue stores 32 bytes at a time
     const long long BH = (long long)a.batch_sz * a.num_heads;
     if (BH * a.len_q >= (1ll << 31) || BH * (a.len_k + 256) >= (1ll << 31)) return false;
     return true;
