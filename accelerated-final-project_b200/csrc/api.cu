@@ -368,14 +368,19 @@ static int forward_device(const b200attn_args *a) {
         return report_kernel_errors(*c, "an earlier asynchronous call");
     }
     bool done = false;
-    const bool prefer_wide = getenv("B200ATTN_TC_PREFER_WIDE") != nullptr && tcw_supported(*a, rd);
-    if (!prefer_wide && a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC) && tc_bf16_supported(*a, rd)) {
+    // bf16 on the tensor cores: the two-kernel path (scores, then P V) takes every shape it supports;
+    // the one-kernel cluster pipeline takes the rest of its own shapes (and all of them when
+    // B200ATTN_TC_PREFER_PAIR is set: the two are measured against each other that way).
+    const bool tc_ok = a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC);
+    const bool wide_ok = tc_ok && tcw_supported(*a, rd), pair_ok = tc_ok && tc_bf16_supported(*a, rd);
+    const bool use_pair = pair_ok && (!wide_ok || getenv("B200ATTN_TC_PREFER_PAIR") != nullptr);
+    if (use_pair) {
         rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
-    if (!done && a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC) && tcw_supported(*a, rd)) {
-        rc = tcw_run(*a, base, c->tcw, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+    if (!done && wide_ok) {
+        rc = tcw_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_wide"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }

@@ -187,6 +187,36 @@ __device__ __forceinline__ void st_global_v8(void *ptr, uint4 a, uint4 b) {
                  : "memory");
 }
 
+// Row-per-thread epilogues hold, per thread, 128 contiguous bytes of "their" row (w[0..31]).  Stored
+// as they are, every store instruction of a warp touches 32 different cache lines.  This helper
+// first transposes 4x4 blocks of 32-byte pieces among groups of four neighbouring lanes (= four
+// neighbouring rows) with two butterfly rounds of shuffles, after which lane j of a group holds
+// piece j of each of the group's rows, and every store instruction writes full 128-byte lines.
+// `row0_ptr` is the address of the 128-byte segment in the row of the group's FIRST lane,
+// `row_pitch` the distance between rows in bytes.  All 32 lanes must call it.
+__device__ __forceinline__ void store_rows_128B_transposed(unsigned char *row0_ptr, size_t row_pitch, uint32_t (&w)[32], int lane) {
+    const int j = lane & 3;
+#pragma unroll
+    for (int M = 2; M >= 1; M >>= 1) {
+        const bool up = (j & M) != 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (k & M) continue;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t send = up ? w[8 * k + e] : w[8 * (k | M) + e];
+                const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, M);
+                if (up) w[8 * k + e] = recv; else w[8 * (k | M) + e] = recv;
+            }
+        }
+    }
+    // slot m now holds piece j of the row of lane (group base + m)
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+        st_global_v8(row0_ptr + (size_t)m * row_pitch + j * 32, make_uint4(w[8 * m], w[8 * m + 1], w[8 * m + 2], w[8 * m + 3]),
+                     make_uint4(w[8 * m + 4], w[8 * m + 5], w[8 * m + 6], w[8 * m + 7]));
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

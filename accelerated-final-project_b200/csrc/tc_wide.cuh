@@ -44,12 +44,15 @@ struct TcwScoreParams {
     int Lq, Lk, D, nch;        // nch = D / 64
     int nqt, nkt;              // Lq / 128, ceil(Lk / 256)
     int mode;                  // 0: every tile, operands as given; 1: the encoding tile set; 2: all other tiles
+    int pe;                    // mode 1: PE_ROPE_HALF, PE_ROPE_INTERLEAVED or PE_SINUSOIDAL
+    int rotate_k;              // mode 1: 0 = only Q carries the encoding
     int tph;                   // tiles per head in this launch
     long long n_tiles;         // heads * tph
     float scale_log2;          // log2(e) / sqrt(D)
     __nv_bfloat16 *S;          // [heads * Lq][Lk]  scores, log2 units, relative to the tile's row maximum
     float *rowmax;             // [heads * Lq][nkt] row maxima of the tiles, log2 units
-    const __nv_bfloat16 *tab;  // mode 1: [>= max(Lq, 256 * nkt)][D], cos in columns [0, D/2), sin in [D/2, D)
+    const __nv_bfloat16 *tab;  // mode 1: [>= max(Lq, 256 * nkt)][D]; rotate-half: cos in columns [0, D/2), sin in [D/2, D);
+                               // otherwise the layout of tc_build_pe_table (element-wise partner of the data)
     __nv_bfloat16 *q_store, *k_store;   // mode 1: rotated copies, [heads * Lq][D] and [heads * Lk][D]
     unsigned *err, *err_sys;
     unsigned spin_limit;
@@ -126,6 +129,7 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int nch = p.nch;
     const uint32_t lim = p.spin_limit;
     const bool encode = (p.mode == 1);
+    const bool pair_half = encode && p.pe == PE_ROPE_HALF;   // ring slots (s, s+1) hold chunks (c, c + nch/2) instead of (2c, 2c+1)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < TW_NST; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.ready[i], 8); mbar_init(&bars.empty[i], 1); }
@@ -153,7 +157,7 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 tcw_tile_of(p.mode, (int)(tile - bh * p.tph), p.nqt, p.nkt, &qt, &kt);
                 for (int ci = 0; ci < nch; ++ci, ++it) {
                     // encoding tiles take the chunks in pairs (c, c + nch/2) on neighbouring ring slots
-                    const int c = encode ? ((ci >> 1) + (ci & 1) * (nch >> 1)) : ci;
+                    const int c = pair_half ? ((ci >> 1) + (ci & 1) * (nch >> 1)) : ci;
                     const int s = it % TW_NST;
                     TWS(0);
                     TW_FAIL_AT(0, !mbar_wait(&bars.empty[s], ((it / TW_NST) & 1) ^ 1, lim));
@@ -226,26 +230,27 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             const long long grow = bh * p.Lq + (long long)qt * TW_BM + row;
             p.rowmax[grow * p.nkt + kt] = mt;
             __nv_bfloat16 *srow = p.S + grow * p.Lk + (long long)kt * TW_BN;
-            for (int c = 0; c < ncc; ++c) {
-                tmem_ld32(ta + c * 32, r);
-                tmem_ld_wait();
-                uint4 o[4];
+            unsigned char *srow0 = reinterpret_cast<unsigned char *>(srow - (long long)(lane & 3) * p.Lk);
+            uint32_t wds[32];
+            for (int cp = 0; cp < ncc / 2; ++cp) {   // 64 keys = 128 bytes of the row at a time, stored as full lines
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    o[g].x = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 0]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 1]), p.scale_log2, -mt));
-                    o[g].y = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 2]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 3]), p.scale_log2, -mt));
-                    o[g].z = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 4]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 5]), p.scale_log2, -mt));
-                    o[g].w = pack_bf16x2(fmaf(__uint_as_float(r[8 * g + 6]), p.scale_log2, -mt), fmaf(__uint_as_float(r[8 * g + 7]), p.scale_log2, -mt));
+                for (int hh = 0; hh < 2; ++hh) {
+                    tmem_ld32(ta + cp * 64 + hh * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        wds[16 * hh + q] = pack_bf16x2(fmaf(__uint_as_float(r[2 * q]), p.scale_log2, -mt), fmaf(__uint_as_float(r[2 * q + 1]), p.scale_log2, -mt));
                 }
-                st_global_v8(srow + c * 32, o[0], o[1]);
-                st_global_v8(srow + c * 32 + 16, o[2], o[3]);
+                store_rows_128B_transposed(srow0 + cp * 128, (size_t)p.Lk * 2, wds, lane);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.acc_empty[ab]);
         }
     } else if (encode) {
-        // ---- transform warps: rotate-half of the chunk pair in ring slots (s, s+1) ----
+        // ---- transform warps: encoding of the two chunks in ring slots (s, s+1) ----
+        // rotate-half couples the two slots (chunks c and c + nch/2); the other encodings treat them
+        // independently (chunks 2c and 2c+1), each piece with the table piece of the same row and column.
         // A thread owns 12 of the 3072 16-byte piece pairs of a step: pieces 0-3 in the Q chunks and
         // 4-11 in the K chunks, each 32 rows below the last, all in the same logical column.  The
         // cos/sin values come straight from the table in global memory through a 6-deep register
@@ -253,7 +258,10 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // of the piece six further on (of the next step where needed), so the L2 latency of the
         // table reads is covered by the work on the pieces in between.
         const int tid = threadIdx.x - 6 * 32;   // 0..255
-        const int half = p.D >> 1, npairs = nch >> 1;
+        const int npairs = nch >> 1;
+        const int half = pair_half ? (p.D >> 1) : 64;   // column distance between the chunks of slots s and s+1
+        const int cmul = pair_half ? 64 : 128;          // first column of the step's first chunk = c * cmul
+        const bool sinus = (p.pe == PE_SINUSOIDAL);
         const int r0 = tid >> 3;
         const int qcol = (tid & 7) ^ (r0 & 7);   // logical 16-byte column of all pieces of this thread
         struct Step { long long tile, bh; int qt, kt, c; bool valid; };
@@ -271,7 +279,7 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         };
         auto tab_ptr = [&](const Step &s, int i) {
             const int pos = (i >= 4 ? s.kt * TW_BN + 32 * (i - 4) : s.qt * TW_BM + 32 * i) + r0;
-            return p.tab + (long long)pos * p.D + s.c * 64 + qcol * 8;
+            return p.tab + (long long)pos * p.D + s.c * cmul + qcol * 8;
         };
         uint4 tcv[6], tsv[6];
         Step cur;
@@ -304,10 +312,19 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const int pos = (is_k ? cur.kt * TW_BN : cur.qt * TW_BM) + r;
                 const size_t off = (size_t)(is_k ? TW_QCHUNK : 0) + (size_t)(tid + 256 * (is_k ? i - 4 : i)) * 16;
                 uint4 lo = *reinterpret_cast<uint4 *>(lo_st + off), hi = *reinterpret_cast<uint4 *>(hi_st + off);
-                tcw_rotate(lo.x, hi.x, tcv[slot].x, tsv[slot].x);
-                tcw_rotate(lo.y, hi.y, tcv[slot].y, tsv[slot].y);
-                tcw_rotate(lo.z, hi.z, tcv[slot].z, tsv[slot].z);
-                tcw_rotate(lo.w, hi.w, tcv[slot].w, tsv[slot].w);
+                if (is_k && !p.rotate_k) {
+                    // K is taken as given
+                } else if (pair_half) {
+                    tcw_rotate(lo.x, hi.x, tcv[slot].x, tsv[slot].x);
+                    tcw_rotate(lo.y, hi.y, tcv[slot].y, tsv[slot].y);
+                    tcw_rotate(lo.z, hi.z, tcv[slot].z, tsv[slot].z);
+                    tcw_rotate(lo.w, hi.w, tcv[slot].w, tsv[slot].w);
+                } else {
+                    lo.x = tc_pe_pair(lo.x, tcv[slot].x, sinus); hi.x = tc_pe_pair(hi.x, tsv[slot].x, sinus);
+                    lo.y = tc_pe_pair(lo.y, tcv[slot].y, sinus); hi.y = tc_pe_pair(hi.y, tsv[slot].y, sinus);
+                    lo.z = tc_pe_pair(lo.z, tcv[slot].z, sinus); hi.z = tc_pe_pair(hi.z, tsv[slot].z, sinus);
+                    lo.w = tc_pe_pair(lo.w, tcv[slot].w, sinus); hi.w = tc_pe_pair(hi.w, tsv[slot].w, sinus);
+                }
                 if (i < 6 || nx.valid) {
                     const __nv_bfloat16 *tp = (i < 6) ? tab_ptr(cur, i + 6) : tab_ptr(nx, i - 6);
                     tcv[slot] = tcw_ldg_here(tp);
@@ -315,8 +332,8 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
                 *reinterpret_cast<uint4 *>(lo_st + off) = lo;
                 *reinterpret_cast<uint4 *>(hi_st + off) = hi;
-                if (!is_k || pos < p.Lk) {
-                    __nv_bfloat16 *g = (is_k ? p.k_store + (cur.bh * p.Lk + pos) * (long long)p.D : p.q_store + (cur.bh * p.Lq + pos) * (long long)p.D) + cur.c * 64 + qcol * 8;
+                if (is_k ? (p.rotate_k && pos < p.Lk) : true) {
+                    __nv_bfloat16 *g = (is_k ? p.k_store + (cur.bh * p.Lk + pos) * (long long)p.D : p.q_store + (cur.bh * p.Lq + pos) * (long long)p.D) + cur.c * cmul + qcol * 8;
                     *reinterpret_cast<uint4 *>(g) = lo;
                     *reinterpret_cast<uint4 *>(g + half) = hi;
                 }
@@ -570,20 +587,20 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                 TWP(5);
                 const float inv = 1.0f / l_smem[ui & 1][row];
                 __nv_bfloat16 *orow = p.O + (bh * p.Lq + (long long)qt * TW_BM + row) * (long long)p.D + dp * DW;
-                uint32_t r[32];
-                for (int c = (w >> 2); c < DW / 32; c += 4) {
-                    tmem_ld32(lane_addr + c * 32, r);
-                    tmem_ld_wait();
-                    uint4 o[4];
+                uint32_t r[32], wds[32];
+                // 64 output columns (128 bytes of the row) at a time; lanes trade pieces so that the
+                // stores cover full lines
+                unsigned char *row0 = reinterpret_cast<unsigned char *>(orow - (long long)(lane & 3) * p.D);
+                for (int cp = (w >> 2); cp < DW / 64; cp += 4) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        o[g].x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
-                        o[g].y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
-                        o[g].z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
-                        o[g].w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
+                    for (int hh = 0; hh < 2; ++hh) {
+                        tmem_ld32(lane_addr + cp * 64 + hh * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 16; ++q)
+                            wds[16 * hh + q] = pack_bf16x2(__uint_as_float(r[2 * q]) * inv, __uint_as_float(r[2 * q + 1]) * inv);
                     }
-                    st_global_v8(orow + c * 32, o[0], o[1]);
-                    st_global_v8(orow + c * 32 + 16, o[2], o[3]);
+                    store_rows_128B_transposed(row0 + cp * 128, (size_t)p.D * 2, wds, lane);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -646,7 +663,7 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
     if (a.len_q % TW_BM != 0 || a.len_k % TC_BN != 0) return false;
     if (a.len_k > 32 * TW_BN) return false;   // the offsets of a row's key tiles live one per lane
     if (a.pe == B200ATTN_PE_ROPE_HALF) { if (a.head_d % 128 != 0 || rd != a.head_d) return false; }
-    else if (a.pe != B200ATTN_PE_NONE) return false;
+    else if (a.pe != B200ATTN_PE_NONE) { if (a.head_d % 128 != 0 || (a.pe != B200ATTN_PE_SINUSOIDAL && rd % 8 != 0)) return false; }
     if (a.cos_cache != nullptr) return false;
     if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return false;
     if (((uintptr_t)a.out & 31) != 0) return false;   // the epilogue stores 32 bytes at a time
@@ -656,11 +673,13 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
 }
 
 // Returns B200ATTN_OK, -1 when the shape should run on another path, or a status with tc_bf16_error() set.
-inline int tcw_run(const b200attn_args &a, float base, TcwScratch &sc, unsigned *err_dev, unsigned *err_sys, int sm_count,
+inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, TcTables &tables, unsigned *err_dev, unsigned *err_sys, int sm_count,
                    unsigned spin_limit, cudaStream_t st, std::atomic<unsigned long long> *launches) {
     const long long BH = (long long)a.batch_sz * a.num_heads;
     const int D = a.head_d, Lq = a.len_q, Lk = a.len_k;
-    const bool rope = (a.pe == B200ATTN_PE_ROPE_HALF);
+    const bool encoded = (a.pe != B200ATTN_PE_NONE);              // any encoding: two score launches
+    const bool pair_half = (a.pe == B200ATTN_PE_ROPE_HALF);
+    const bool rotate_k = (a.pe != B200ATTN_PE_ROPE_Q_ONLY);
     int ndp = 1;
     while (D % (64 * ndp) != 0 || D / ndp > 512) ++ndp;
     const int DW = D / ndp;
@@ -696,18 +715,25 @@ inline int tcw_run(const b200attn_args &a, float base, TcwScratch &sc, unsigned 
     float *rowmax = (float *)sc.get(1, (size_t)G * Lq * nkt * sizeof(float));
     __nv_bfloat16 *qs = nullptr, *ks = nullptr, *tab = nullptr;
     if (!S || !rowmax) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the score scratch"); return B200ATTN_ERR_CUDA; }
-    if (rope) {
+    if (encoded) {
         qs = (__nv_bfloat16 *)sc.get(2, (size_t)G * Lq * D * 2);
         ks = (__nv_bfloat16 *)sc.get(3, (size_t)G * Lk * D * 2);
         const int Lt = (Lq > nkt * TW_BN ? Lq : nkt * TW_BN);
-        const bool have = sc.buf[4] && sc.tab_L >= Lt && sc.tab_D == D && sc.tab_base == base;
-        tab = (__nv_bfloat16 *)(have ? sc.buf[4] : sc.get(4, (size_t)Lt * D * 2));
-        if (!qs || !ks || !tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the rotated-operand scratch"); return B200ATTN_ERR_CUDA; }
-        if (!have) {
-            if (sc.tab_L != 0) cudaDeviceSynchronize();   // no kernel may still be reading the table that is replaced
-            tcw_build_half_table<<<296, 256, 0, st>>>(tab, Lt, D, base);
-            launches->fetch_add(1);
-            sc.tab_L = Lt; sc.tab_D = D; sc.tab_base = base;
+        if (!qs || !ks) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the rotated-operand scratch"); return B200ATTN_ERR_CUDA; }
+        if (pair_half) {
+            const bool have = sc.buf[4] && sc.tab_L >= Lt && sc.tab_D == D && sc.tab_base == base;
+            tab = (__nv_bfloat16 *)(have ? sc.buf[4] : sc.get(4, (size_t)Lt * D * 2));
+            if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the cos/sin table"); return B200ATTN_ERR_CUDA; }
+            if (!have) {
+                if (sc.tab_L != 0) cudaDeviceSynchronize();   // no kernel may still be reading the table that is replaced
+                tcw_build_half_table<<<296, 256, 0, st>>>(tab, Lt, D, base);
+                launches->fetch_add(1);
+                sc.tab_L = Lt; sc.tab_D = D; sc.tab_base = base;
+            }
+        } else {
+            int rows = 0;
+            tab = tables.get(a.pe, Lt, D, rd, a.pe == B200ATTN_PE_SINUSOIDAL ? 10000.0f : base, st, launches, &rows);
+            if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the positional-encoding table"); return B200ATTN_ERR_CUDA; }
         }
     }
     for (long long h0 = 0; h0 < BH; h0 += G) {
@@ -718,6 +744,7 @@ inline int tcw_run(const b200attn_args &a, float base, TcwScratch &sc, unsigned 
         sp.Lq = Lq; sp.Lk = Lk; sp.D = D; sp.nch = D / 64; sp.nqt = nqt; sp.nkt = nkt;
         sp.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
         sp.S = S; sp.rowmax = rowmax; sp.tab = tab; sp.q_store = qs; sp.k_store = ks;
+        sp.pe = a.pe == B200ATTN_PE_ROPE_Q_ONLY ? (int)PE_ROPE_INTERLEAVED : a.pe; sp.rotate_k = rotate_k ? 1 : 0;
         sp.err = err_dev; sp.err_sys = err_sys; sp.spin_limit = spin_limit;
         auto launch_scores = [&](const void *Qp, const void *Kp, int mode, int tph) -> int {
             if (tph <= 0) return B200ATTN_OK;
@@ -735,10 +762,10 @@ inline int tcw_run(const b200attn_args &a, float base, TcwScratch &sc, unsigned 
             return B200ATTN_OK;
         };
         int rc;
-        if (rope) {
+        if (encoded) {
             const int nA = nqt > nkt ? nqt : nkt;
             rc = launch_scores(Qg, Kg, 1, nA);
-            if (rc == B200ATTN_OK) rc = launch_scores(qs, ks, 2, nqt * nkt - nA);
+            if (rc == B200ATTN_OK) rc = launch_scores(qs, rotate_k ? (const void *)ks : (const void *)Kg, 2, nqt * nkt - nA);
         } else {
             rc = launch_scores(Qg, Kg, 0, nqt * nkt);
         }

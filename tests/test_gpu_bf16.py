@@ -1,5 +1,7 @@
 """GPU parity of the bf16 entry points: bf16 in/out, fp32 scores/softmax/accumulate.  Oracle: the
 fp32 CPU attention on the bf16-rounded inputs; tolerance stated by the task: max-abs <= 2e-2."""
+import os
+
 import numpy as np
 import pytest
 
@@ -52,6 +54,16 @@ def test_bf16_both_paths_against_oracle(pkg, cuda, pe, shape):
     got = run(pkg, cuda, bits, pe=pe)
     err = float(np.abs(got - want).max())
     assert err <= TOL, (pkg.last_path(), shape, pe, err)
+    # the one-kernel cluster pipeline, where it takes the shape
+    os.environ["B200ATTN_TC_PREFER_PAIR"] = "1"
+    try:
+        got = run(pkg, cuda, bits, pe=pe)
+    finally:
+        del os.environ["B200ATTN_TC_PREFER_PAIR"]
+    if D <= 512 and D % 64 == 0 and Lq % 128 == 0 and Lk % 128 == 0 and pe != ol.PE_ROPE_HALF:
+        assert pkg.last_path() == "tc_bf16"
+    err = float(np.abs(got - want).max())
+    assert err <= TOL, (pkg.last_path(), shape, pe, err)
 
 
 @pytest.mark.parametrize("cfg", [
@@ -73,16 +85,27 @@ def test_benchmark_bf16_configs_sampled(pkg, cuda, cfg):
     Q, K, V = (torch.empty(n, dtype=torch.bfloat16, device=cuda).view(B, H, L, D) for _ in range(3))
     for t, tid in ((Q, 0), (K, 1), (V, 2)):
         pkg.synth_fill(t, 44, tid, "normal")
-    out = pkg.forward(Q, K, V, pe=pe)
-    torch.cuda.synchronize()
     heads = [0, B * H // 2 + 1, B * H - 1]
     rows = sorted({0, 1, 63, 64, 127, min(128, L - 1), L // 2 + 5, L - 1})
-    o = out.view(B * H, L, D)
     q3, k3, v3 = (t.view(B * H, L, D) for t in (Q, K, V))
+    wants = []
     for h in heads:
         qs, ks, vs = (bf16_from_dev(t[h].contiguous()).reshape(1, 1, L, D) for t in (q3, k3, v3))
-        want = ol.attention_rows(qs, ks, vs, np.zeros(len(rows), np.int64), np.array(rows), pe=pe)
-        got = bf16_from_dev(o[h][rows].contiguous())
-        err = float(np.abs(got - want).max())
-        assert err <= TOL, (name, pkg.last_path(), h, err)
-    assert bool(torch.isfinite(out.float()).all())
+        wants.append(ol.attention_rows(qs, ks, vs, np.zeros(len(rows), np.int64), np.array(rows), pe=pe))
+    # the default tensor-core path and, for the shapes it takes, the one-kernel cluster pipeline
+    for prefer_pair in ((False, True) if D <= 512 else (False,)):
+        if prefer_pair:
+            os.environ["B200ATTN_TC_PREFER_PAIR"] = "1"
+        try:
+            out = pkg.forward(Q, K, V, pe=pe)
+            torch.cuda.synchronize()
+        finally:
+            os.environ.pop("B200ATTN_TC_PREFER_PAIR", None)
+        assert pkg.last_path() == ("tc_bf16" if prefer_pair else "tc_wide")
+        o = out.view(B * H, L, D)
+        for h, want in zip(heads, wants):
+            got = bf16_from_dev(o[h][rows].contiguous())
+            err = float(np.abs(got - want).max())
+            assert err <= TOL, (name, pkg.last_path(), h, err)
+        assert bool(torch.isfinite(out.float()).all())
+        del out, o

@@ -62,3 +62,41 @@ def test_wide_path_twice_in_a_row_same_result(pkg, cuda):
     a = run(pkg, cuda, bits, pe=ol.PE_ROPE_HALF)
     b = run(pkg, cuda, bits, pe=ol.PE_ROPE_HALF)
     assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("pe", [ol.PE_SINUSOIDAL, ol.PE_ROPE_INTERLEAVED], ids=["sinusoidal", "rope_pairs"])
+@pytest.mark.parametrize("shape", [
+    (1, 2, 256, 256, 1024),
+    (1, 2, 512, 256, 1024),
+    (1, 1, 128, 768, 1024),
+    (1, 1, 256, 384, 768),
+    (1, 1, 128, 256, 2048),
+], ids=lambda s: "x".join(map(str, s)))
+def test_wide_path_other_encodings(pkg, cuda, pe, shape):
+    B, H, Lq, Lk, D = shape
+    bits, up = bf16_problem(B, H, Lq, Lk, D, 74, "normal")
+    want = ol.attention(*up, pe=pe)
+    got = run(pkg, cuda, bits, pe=pe)
+    assert pkg.last_path() == "tc_wide"
+    err = float(np.abs(got - want).max())
+    assert err <= TOL, (shape, pe, err)
+
+
+def test_wide_path_partial_rotary_dim_and_q_only(pkg, cuda):
+    B, H, L, D, rd = 1, 2, 256, 1024, 256
+    bits, up = bf16_problem(B, H, L, L, D, 75, "normal")
+    for pe in (ol.PE_ROPE_INTERLEAVED, ol.PE_ROPE_Q_ONLY):
+        want = ol.attention(*up, pe=pe, rotary_dim=rd)
+        got = run(pkg, cuda, bits, pe=pe, rotary_dim=rd)
+        assert pkg.last_path() == "tc_wide"
+        assert float(np.abs(got - want).max()) <= TOL, pe
+
+
+@pytest.mark.parametrize("pe", [ol.PE_NONE, ol.PE_SINUSOIDAL, ol.PE_ROPE_INTERLEAVED, ol.PE_ROPE_HALF])
+def test_narrow_heads_on_the_two_kernel_path(pkg, cuda, pe):
+    """head_d <= 512 runs here too (the one-kernel pipeline only when asked for)."""
+    bits, up = bf16_problem(1, 3, 384, 512, 512, 76, "normal")
+    want = ol.attention(*up, pe=pe)
+    got = run(pkg, cuda, bits, pe=pe)
+    assert pkg.last_path() == "tc_wide"
+    assert float(np.abs(got - want).max()) <= TOL
