@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libb200attn.so")
+# B200ATTN_LIB names another build of the same library (a profiling build, an older build to compare with)
+LIB_PATH = os.environ.get("B200ATTN_LIB") or os.path.join(_HERE, "lib", "libb200attn.so")
 
 F32, BF16 = 0, 1
 PE_NONE, PE_ROPE_INTERLEAVED, PE_ROPE_HALF, PE_SINUSOIDAL, PE_ROPE_Q_ONLY = 0, 1, 2, 3, 4

@@ -1,10 +1,11 @@
-// bf16 attention forward for wide heads (head_d > 512) and for the rotate-half RoPE pairing, on the
-// 5th-generation tensor cores.  A 128-row fp32 output accumulator of a 1024-wide head is twice the
-// tensor memory of an SM and the query tile is more shared memory than an SM has, so the one-kernel
-// pipeline of tc_bf16.cuh does not fit; this path runs two persistent kernels per call instead:
+// bf16 attention forward on the 5th-generation tensor cores as two persistent kernels per call, with
+// the scores passing through a bf16 scratch in HBM.  It began as the path for wide heads (a 128-row
+// fp32 output accumulator of a 1024-wide head is twice the tensor memory of an SM and the query tile
+// is more shared memory than an SM has, so the one-kernel pipeline of tc_bf16.cuh does not fit) and
+// measured faster than that pipeline on the narrow heads too, so it takes every shape it supports.
 //
 //   tcw_scores_kernel   S tiles [128 queries x 256 keys] = Q Kt, a K-loop over 64-wide chunks of
-//                       head_d with both operands streamed by TMA through a 4-stage ring, the
+//                       head_d with both operands streamed by TMA through a 4-slot ring, the
 //                       accumulator double-buffered in tensor memory (2 x 256 columns) so that the
 //                       epilogue of one tile runs under the MMAs of the next.  The epilogue takes the
 //                       row maximum of the tile and writes the scores in log2 units RELATIVE to that
@@ -12,20 +13,22 @@
 //                       then small numbers and keep their precision) plus the maximum itself in fp32.
 //   tcw_pv_kernel       per (head, query tile, block of <= 512 output columns): the global row
 //                       maximum is the maximum of the tile maxima, so P = exp2(S - max) is final when
-//                       it is computed (no running rescale of the accumulator); sixteen warps turn the
-//                       stored scores into bf16 P tiles in shared memory, one thread issues
-//                       O += P V with V streamed by TMA, and the accumulator [128 x <=512] fp32 stays
-//                       in tensor memory until the unit's epilogue divides by the row sums.
+//                       it is computed (no running rescale of the accumulator).  A score block arrives
+//                       by TMA in the swizzled K-major layout of the MMA's A operand and sixteen warps
+//                       turn it into P in place; one thread issues O += P V with V streamed by TMA;
+//                       the accumulator [128 x <=512] fp32 stays in tensor memory until the unit's
+//                       epilogue divides by the row sums.
 //
-// Rotate-half RoPE (pairs (i, i + head_d/2)) is applied inside the operand load of the score kernel:
-// the ring is filled with chunk pairs (c, c + n_chunks/2), eight transform warps rotate the pair in
-// shared memory between TMA arrival and MMA, and while the rotated pieces are in registers they are
-// also written to a scratch copy.  The tiles that do this are one "diagonal" set per head that
-// touches every query tile and every key tile once; a second launch computes all the other tiles
-// from the rotated copies without any transform.
+// A positional encoding (rotate-half or interleaved-pair RoPE, sinusoidal) is applied inside the
+// operand load of the score kernel: the ring is filled two chunks at a time (rotate-half: chunks c
+// and c + n_chunks/2), eight transform warps encode the two slots in shared memory between TMA
+// arrival and MMA, and while the encoded pieces are in registers they are also written to a scratch
+// copy.  The tiles that do this are one "diagonal" set per head that touches every query tile and
+// every key tile once; a second launch computes all the other tiles from the encoded copies without
+// any transform.
 //
-// Shapes taken here: bf16, head_d % 64 == 0 (rotate-half: % 128 and rotary_dim == head_d),
-// len_q % 128 == 0, len_k % 128 == 0.  Every wait is bounded.
+// Shapes taken here: bf16, head_d % 64 == 0 (with an encoding: % 128; rotate-half: rotary_dim ==
+// head_d), len_q % 128 == 0, len_k % 128 == 0, len_k <= 8192.  Every wait is bounded.
 #pragma once
 
 #include "tc_bf16.cuh"
@@ -514,18 +517,27 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
         int ui = 0;
         long long tg = 0;
         TWS_DECL;
+        // lane j keeps (tile maximum - row maximum) of key tile j for each of the warp's eight rows
+        auto load_stats = [&](long long g0, float (&oo)[8]) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float m = lane < p.nkt ? __ldg(p.rowmax + (g0 + k) * p.nkt + lane) : -INFINITY;
+                oo[k] = m - warp_max(m);
+            }
+        };
+        auto grow0_of = [&](long long unit) {
+            const long long rest = unit / p.ndp;
+            return (rest / p.nqt) * p.Lq + (rest % p.nqt) * (long long)TW_BM + 8 * w;
+        };
+        float offs[8], offsn[8];
         for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x, ++ui) {
             const int dp = (int)(unit % p.ndp);
             const long long rest = unit / p.ndp;
             const int qt = (int)(rest % p.nqt);
             const long long bh = rest / p.nqt;
             const long long grow0 = bh * p.Lq + (long long)qt * TW_BM + 8 * w;
-            float offs[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float m = lane < p.nkt ? __ldg(p.rowmax + (grow0 + k) * p.nkt + lane) : -INFINITY;
-                offs[k] = m - warp_max(m);
-            }
+            // (the statistics of the unit were loaded while the previous unit was finishing)
+            if (ui == 0) load_stats(grow0, offs);
             float lA = 0.0f, lB = 0.0f, offA = 0.0f, offB = 0.0f;
             for (int t = 0; t < nblk; ++t, ++tg) {
                 const int pb = (int)(tg % TP_NP);
@@ -567,6 +579,8 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                 if (lane == 0) mbar_arrive(&bars.p_full[pb]);
             }
             if (failed) break;
+            const bool have_next = unit + gridDim.x < p.n_units;
+            if (have_next) load_stats(grow0_of(unit + gridDim.x), offsn);   // lands while this unit drains
 #pragma unroll
             for (int o = 4; o > 0; o >>= 1) {
                 lA += __shfl_xor_sync(0xffffffffu, lA, o);
@@ -607,6 +621,10 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                 if (lane == 0) mbar_arrive(&bars.o_empty);
             }
             TWP(6);
+            if (have_next) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) offs[k] = offsn[k];
+            }
         }
         TWP_FLUSH(16, threadIdx.x == 64);
     }

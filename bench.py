@@ -39,8 +39,9 @@ CONFIGS = {
     "cfg3": ("bf16", "none", 8, 16, 1024, 1024, 512, "normal", "tensor"),
     "cfg4": ("bf16", "rope_half", 4, 32, 2048, 2048, 1024, "normal", "tensor"),
     "cfg5": ("bf16", "sinusoidal", 16, 32, 4096, 4096, 512, "normal", "tensor"),
-    # profiling-size variant of cfg4 (an eighth of the heads): small enough for a multi-pass ncu capture
+    # profiling-size variants of cfg4 and cfg5 (16 heads): small enough for a multi-pass ncu capture
     "cfg4p": ("bf16", "rope_half", 1, 16, 2048, 2048, 1024, "normal", "tensor"),
+    "cfg5p": ("bf16", "sinusoidal", 1, 16, 4096, 4096, 512, "normal", "tensor"),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
