@@ -83,6 +83,8 @@ def lib():
         L.b200attn_synth_fill.argtypes = [C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong,
                                           C.c_int, C.c_int, C.c_void_p]
         L.b200attn_synth_fill.restype = C.c_int
+        L.b200attn_debug_kernel_times.argtypes = [C.c_int, C.POINTER(C.c_double)]
+        L.b200attn_debug_kernel_times.restype = C.c_int
         L.b200attn_debug_lost_arrival.argtypes = [C.c_uint, C.c_uint]
         L.b200attn_debug_lost_arrival.restype = None
         _lib = L
@@ -130,6 +132,17 @@ def args_for(Q, K, V, out, pe=PE_NONE, rotary_dim=0, rope_base=0.0, stream=None,
         stream = torch.cuda.current_stream(Q.device).cuda_stream
     return make_args(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), B, H, Lq, K.shape[2], D,
                      F32 if Q.dtype == torch.float32 else BF16, pe, rotary_dim, rope_base, None, None, stream, flags)
+
+
+def kernel_times(enable, collect=False):
+    """Per-kernel timing of the two-kernel bf16 path (b200attn_debug_kernel_times).  With collect,
+    returns {"scores_encode": (ms, launches), "scores": (...), "pv": (...)} for the launches recorded
+    since the last collection."""
+    out = (C.c_double * 6)() if collect else None
+    check(lib().b200attn_debug_kernel_times(1 if enable else 0, out))
+    if not collect:
+        return None
+    return {k: (out[i], int(out[3 + i])) for i, k in enumerate(("scores_encode", "scores", "pv"))}
 
 
 def forward_many(arg_list):

@@ -644,6 +644,22 @@ void b200attn_debug_lost_arrival(unsigned extra, unsigned spin_limit) {
     g_test_spin_limit.store(spin_limit);
 }
 
+// Per-kernel timing of the two-kernel bf16 path.  enable = 1 / 0 switches the recording on / off
+// (single-threaded use, one device); with out != NULL the call synchronises the device and returns
+// the summed milliseconds of [encoding score launches, score launches, P V launches] in out[0..2]
+// and the launch counts in out[3..5], clearing the record.
+int b200attn_debug_kernel_times(int enable, double *out) {
+    TcwTimer &t = tcw_timer();
+    if (out != nullptr) {
+        if (cudaDeviceSynchronize() != cudaSuccess) return B200ATTN_ERR_CUDA;
+        int cnt[3];
+        t.collect(out, cnt);
+        for (int k = 0; k < 3; ++k) out[3 + k] = (double)cnt[k];
+    }
+    t.on = (enable != 0);
+    return B200ATTN_OK;
+}
+
 const char *b200attn_last_error(void) { return t_last_error.c_str(); }
 const char *b200attn_last_path(void) { return t_last_path; }
 unsigned long long b200attn_launch_count(void) { return g_launches.load(); }

@@ -652,6 +652,39 @@ __global__ void tcw_build_half_table(__nv_bfloat16 *table, int L, int D, float b
     }
 }
 
+// Optional per-kernel timing (b200attn_debug_kernel_times): while it is switched on, every launch of
+// this path is bracketed by two events on its stream; the sums per kernel kind are collected after
+// a synchronisation.  Kinds: 0 = score kernel, encoding launch; 1 = score kernel; 2 = P V kernel.
+struct TcwTimer {
+    static constexpr int kMax = 2048;
+    bool on = false;
+    int n = 0;
+    cudaEvent_t ev[2 * kMax];
+    int kind[kMax];
+    bool have_events = false;
+    void begin(int k, cudaStream_t st) {
+        if (!on || n >= kMax) return;
+        if (!have_events) { for (int i = 0; i < 2 * kMax; ++i) cudaEventCreate(&ev[i]); have_events = true; }
+        kind[n] = k;
+        cudaEventRecord(ev[2 * n], st);
+    }
+    void end(cudaStream_t st) {
+        if (!on || n >= kMax) return;
+        cudaEventRecord(ev[2 * n + 1], st);
+        ++n;
+    }
+    // ms[0..2] = summed durations per kind, cnt[0..2] = launches per kind; clears the record
+    void collect(double *ms, int *cnt) {
+        for (int k = 0; k < 3; ++k) { ms[k] = 0.0; cnt[k] = 0; }
+        for (int i = 0; i < n; ++i) {
+            float t = 0.0f;
+            if (cudaEventElapsedTime(&t, ev[2 * i], ev[2 * i + 1]) == cudaSuccess) { ms[kind[i]] += t; cnt[kind[i]]++; }
+        }
+        n = 0;
+    }
+};
+inline TcwTimer &tcw_timer() { static TcwTimer t; return t; }
+
 // Scratch of the wide path, kept per device and grown on demand.
 struct TcwScratch {
     void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};   // S, rowmax, rotated Q, rotated K, table
@@ -773,7 +806,9 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
             }
             sp.mode = mode; sp.tph = tph; sp.n_tiles = nh * tph;
             const unsigned grid = (unsigned)(sp.n_tiles < sm_count ? sp.n_tiles : sm_count);
+            tcw_timer().begin(mode == 1 ? 0 : 1, st);
             tcw_scores_kernel<<<grid, TW_THREADS, smem_s, st>>>(tmQ, tmK, sp);
+            tcw_timer().end(st);
             cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "tcw_scores_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
             launches->fetch_add(1);
@@ -796,7 +831,9 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         pp.rowmax = rowmax; pp.O = (__nv_bfloat16 *)a.out + h0 * Lq * D;
         pp.err = err_dev; pp.err_sys = err_sys; pp.spin_limit = spin_limit;
         const unsigned grid = (unsigned)(pp.n_units < sm_count ? pp.n_units : sm_count);
+        tcw_timer().begin(2, st);
         tcw_pv_kernel<<<grid, TP_THREADS, smem_p, st>>>(tmV, tmS, pp);
+        tcw_timer().end(st);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "tcw_pv_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
         launches->fetch_add(1);

@@ -47,10 +47,11 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (null until a capture exists for the kernel in use)
 NCU_TRAFFIC_BYTES = {
+    # per STEP (a step of the two-kernel path is several launches; `achieved` is per step as well)
+    ("cfg5", "tc_wide"): 49.3e9,        # profiles/tcw_kernels_cfg5.md: the 16-head capture (1540.6 MB over the three launches) x 32
+    ("cfg4", "tc_wide"): 5.73e9,        # profiles/tcw_kernels_cfg4.md: the 16-head capture (716.4 MB) x 8
     ("cfg3", "tc_bf16"): 514.8e6,       # profiles/tc_bf16_pair_kernel_cfg3.md: 402.8 MB read + 112.0 MB written
-    # cfg 5 is too large to capture with more than one pass: scaled from the cfg 3 capture by input/output
-    # bytes (traffic equalled the algorithmic bytes there) plus the write of the encoded-K scratch (|K|)
-    ("cfg5", "tc_bf16"): 8 * 2.0**30 + 2 * 2.0**30,
+    ("cfg5", "tc_bf16"): 8 * 2.0**30 + 2 * 2.0**30,   # scaled from the cfg 3 capture by input/output bytes plus the encoded-K scratch
     ("cfg2c", "splitd_fused"): 33.7e6,  # profiles/splitd_fused_kernel_cfg2c.md: 25.3 MB read, 8.4 MB output
 }
 
@@ -134,6 +135,7 @@ def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None):
     if warmup:
         pkg.forward_many([mk(i) for i in range(warmup)])
     torch.cuda.synchronize()
+    pkg.kernel_times(True, collect=True)   # per-kernel events of the two-kernel bf16 path: on, record cleared
     if barrier:
         barrier()
     torch.cuda.synchronize()
@@ -145,6 +147,7 @@ def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None):
     e1.record()
     torch.cuda.synchronize()
     time_steps.launches = pkg.launch_count() - n0
+    time_steps.kernels = pkg.kernel_times(False, collect=True)
     if barrier:
         barrier()
     return e0.elapsed_time(e1) / steps
@@ -342,7 +345,26 @@ def main():
         ach = fl / (ms * 1e-3) / 1e12
         line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                             "traffic": NCU_TRAFFIC_BYTES.get((cfg, path)), "peak_source": pk_src + " (sustained cuBLAS bf16)",
-                            "kernel": path, "launches_per_step": launches_per_step}
+                            "kernel": path, "launches_per_step": launches_per_step,
+                            "per": "step (all launches of the path; the per-kernel figures are in `kernels`)"}
+        kt = getattr(time_steps, "kernels", None)
+        if path == "tc_wide" and kt and sum(v[1] for v in kt.values()) > 0:
+            # live CUDA-event times of this rank's launches inside the timed region, per kernel
+            nqt, nkt = Lq // 128, (Lk + 255) // 256
+            n_enc = max(nqt, nkt) if pe != 0 else 0
+            tile_fl = 2.0 * 128 * 256 * D
+            k_fl = {"scores_encode": B * H * n_enc * tile_fl, "scores": B * H * (nqt * nkt - n_enc) * tile_fl, "pv": fl / 2.0}
+            names = {"scores_encode": "tcw_scores_kernel (encoding launch)", "scores": "tcw_scores_kernel", "pv": "tcw_pv_kernel"}
+            tot = sum(v[0] for v in kt.values())
+            rows = []
+            for k, (kms, cnt) in kt.items():
+                if cnt:
+                    rows.append({"kernel": names[k], "launches": cnt, "ms_per_step": kms / args.steps, "share": kms / tot,
+                                 "tflops": k_fl[k] * args.steps / (kms * 1e-3) / 1e12})
+            line["kernels"] = rows
+            dom = max(rows, key=lambda r: r["ms_per_step"])
+            line["roofline"].update({"dominant_kernel": dom["kernel"], "dominant_achieved": dom["tflops"],
+                                     "dominant_frac": dom["tflops"] / peak, "dominant_share": dom["share"]})
     else:
         peak = pk["hbm_gbs"]
         ach = nbytes / (ms * 1e-3) / 1e9
