@@ -92,13 +92,23 @@ struct TwBars {
         break;                                                                                      \
     }
 
-// Tile j of a head for the three launch modes.  Mode 1 is a set of max(nqt, nkt) tiles that contains
-// every query tile and every key tile; mode 2 is its complement.
+// Tile j of a head for the three launch modes.  Mode 1 (the encoding launch) is a set of max(nqt, nkt)
+// tiles that contains every query tile and every key tile; mode 2 is its complement.  With at least
+// as many query tiles as key tiles, query tile q is paired with key tile a(q): q/2 where that
+// reaches every key tile (then the 128 query rows have the positions of one half of the 256 key
+// rows, and one set of table values serves both), else q mod nkt.
+__device__ __forceinline__ int tcw_diag_kt(int q, int nqt, int nkt) {
+    return (nqt >= 2 * nkt - 1) ? (q >> 1) % nkt : q % nkt;
+}
 __device__ __forceinline__ void tcw_tile_of(int mode, int j, int nqt, int nkt, int *qt, int *kt) {
     if (mode == 0) { *qt = j / nkt; *kt = j - *qt * nkt; }
-    else if (mode == 1) { *qt = j % nqt; *kt = j % nkt; }
-    else if (nkt <= nqt) { const int q = j / (nkt - 1), r = j - q * (nkt - 1); *qt = q; *kt = (q % nkt + 1 + r) % nkt; }
-    else { const int k = j / (nqt - 1), r = j - k * (nqt - 1); *kt = k; *qt = (k % nqt + 1 + r) % nqt; }
+    else if (nkt <= nqt) {
+        if (mode == 1) { *qt = j; *kt = tcw_diag_kt(j, nqt, nkt); }
+        else { const int q = j / (nkt - 1), r = j - q * (nkt - 1); *qt = q; *kt = (tcw_diag_kt(q, nqt, nkt) + 1 + r) % nkt; }
+    } else {
+        if (mode == 1) { *qt = j % nqt; *kt = j; }
+        else { const int k = j / (nqt - 1), r = j - k * (nqt - 1); *kt = k; *qt = (k % nqt + 1 + r) % nqt; }
+    }
 }
 
 // (lo, hi) -> (lo*c - hi*s, hi*c + lo*s) on packed bf16 pairs
@@ -254,25 +264,39 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // ---- transform warps: encoding of the two chunks in ring slots (s, s+1) ----
         // rotate-half couples the two slots (chunks c and c + nch/2); the other encodings treat them
         // independently (chunks 2c and 2c+1), each piece with the table piece of the same row and column.
-        // A thread owns 12 of the 3072 16-byte piece pairs of a step: pieces 0-3 in the Q chunks and
-        // 4-11 in the K chunks, each 32 rows below the last, all in the same logical column.  The
-        // cos/sin values come straight from the table in global memory through a 6-deep register
-        // pipeline: the slot of a piece is refilled, as soon as it has been used, with the values
-        // of the piece six further on (of the next step where needed), so the L2 latency of the
-        // table reads is covered by the work on the pieces in between.
+        // A thread owns 12 of the 3072 16-byte piece pairs of a step: 4 in the Q chunks and 8 in the K
+        // chunks, each 32 rows below the last, all in the same logical column.  Where the query rows
+        // have the positions of one half of the key rows (kt == qt / 2), Q piece i and K piece
+        // i + 4 (qt & 1) use the same table values: the step then needs 8 table fetches, not 12.
+        // The fetches run through four register slots, each refilled as soon as it has been used:
+        // first half of a step = Q piece i and its twin K piece, then slot i takes the values of
+        // the i-th remaining K piece; second half = those K pieces, then slot m takes the values of
+        // Q piece m of the next step.  Every fetch so has half a step of work to land.
         const int tid = threadIdx.x - 6 * 32;   // 0..255
         const int npairs = nch >> 1;
         const int half = pair_half ? (p.D >> 1) : 64;   // column distance between the chunks of slots s and s+1
         const int cmul = pair_half ? 64 : 128;          // first column of the step's first chunk = c * cmul
         const bool sinus = (p.pe == PE_SINUSOIDAL);
+        const bool rotate_k = (p.rotate_k != 0);
         const int r0 = tid >> 3;
         const int qcol = (tid & 7) ^ (r0 & 7);   // logical 16-byte column of all pieces of this thread
-        struct Step { long long tile, bh; int qt, kt, c; bool valid; };
+        struct Step { long long tile, bh; int qt, kt, c, h; bool valid, shared, store_q, store_k; };
         auto decode = [&](Step &s) {
             s.valid = s.tile < p.n_tiles;
             if (s.valid) {
                 s.bh = s.tile / p.tph;
-                tcw_tile_of(p.mode, (int)(s.tile - s.bh * p.tph), p.nqt, p.nkt, &s.qt, &s.kt);
+                const int j = (int)(s.tile - s.bh * p.tph);
+                tcw_tile_of(p.mode, j, p.nqt, p.nkt, &s.qt, &s.kt);
+                s.shared = rotate_k && (s.kt == (s.qt >> 1));          // query rows = half (qt & 1) of the key rows
+                s.h = s.shared ? (s.qt & 1) : 0;
+                if (p.nkt <= p.nqt) {
+                    s.store_q = true;
+                    // key tile kt is met by several query tiles: its first meeting stores it
+                    s.store_k = rotate_k && ((p.nqt >= 2 * p.nkt - 1) ? ((s.qt & 1) == 0 && (s.qt >> 1) < p.nkt) : (s.qt < p.nkt));
+                } else {
+                    s.store_q = j < p.nqt;
+                    s.store_k = rotate_k;
+                }
             }
         };
         auto next_of = [&](const Step &s) {   // the step after s: next chunk pair, or the first of this CTA's next tile
@@ -280,20 +304,38 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (++n.c == npairs) { n.c = 0; n.tile += gridDim.x; decode(n); }
             return n;
         };
-        auto tab_ptr = [&](const Step &s, int i) {
-            const int pos = (i >= 4 ? s.kt * TW_BN + 32 * (i - 4) : s.qt * TW_BM + 32 * i) + r0;
-            return p.tab + (long long)pos * p.D + s.c * cmul + qcol * 8;
+        auto tab_q = [&](const Step &s, int i) {
+            return p.tab + (long long)(s.qt * TW_BM + 32 * i + r0) * p.D + s.c * cmul + qcol * 8;
         };
-        uint4 tcv[6], tsv[6];
+        auto tab_k = [&](const Step &s, int i) {   // i = 0..7
+            return p.tab + (long long)(s.kt * TW_BN + 32 * i + r0) * p.D + s.c * cmul + qcol * 8;
+        };
+        auto encode_piece = [&](uint4 &lo, uint4 &hi, const uint4 &ta, const uint4 &tb) {
+            if (pair_half) {
+                tcw_rotate(lo.x, hi.x, ta.x, tb.x);
+                tcw_rotate(lo.y, hi.y, ta.y, tb.y);
+                tcw_rotate(lo.z, hi.z, ta.z, tb.z);
+                tcw_rotate(lo.w, hi.w, ta.w, tb.w);
+            } else {
+                lo.x = tc_pe_pair(lo.x, ta.x, sinus); hi.x = tc_pe_pair(hi.x, tb.x, sinus);
+                lo.y = tc_pe_pair(lo.y, ta.y, sinus); hi.y = tc_pe_pair(hi.y, tb.y, sinus);
+                lo.z = tc_pe_pair(lo.z, ta.z, sinus); hi.z = tc_pe_pair(hi.z, tb.z, sinus);
+                lo.w = tc_pe_pair(lo.w, ta.w, sinus); hi.w = tc_pe_pair(hi.w, tb.w, sinus);
+            }
+        };
+        uint4 ta[4], tb[4];   // table values for the chunk in slot s (a) and in slot s+1 (b)
         Step cur;
-        cur.tile = blockIdx.x; cur.bh = 0; cur.qt = 0; cur.kt = 0; cur.c = 0;
+        cur.tile = blockIdx.x; cur.bh = 0; cur.qt = 0; cur.kt = 0; cur.c = 0; cur.h = 0;
+        cur.shared = false; cur.store_q = false; cur.store_k = false;
         decode(cur);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { ta[i] = make_uint4(0, 0, 0, 0); tb[i] = ta[i]; }
         if (cur.valid) {
 #pragma unroll
-            for (int i = 0; i < 6; ++i) {
-                const __nv_bfloat16 *tp = tab_ptr(cur, i);
-                tcv[i] = tcw_ldg_here(tp);
-                tsv[i] = tcw_ldg_here(tp + half);
+            for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat16 *tp = tab_q(cur, i);
+                ta[i] = tcw_ldg_here(tp);
+                tb[i] = tcw_ldg_here(tp + half);
             }
         }
         int it = 0;
@@ -307,38 +349,73 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             TW_FAIL_AT(5, !mbar_wait(&bars.full[s + 1], (it / TW_NST) & 1, lim));
             TWS(1);
             unsigned char *lo_st = smem + (size_t)s * TW_STAGE, *hi_st = lo_st + TW_STAGE;
+            const long long qrow0 = cur.bh * p.Lq + (long long)cur.qt * TW_BM, krow0 = cur.bh * p.Lk + (long long)cur.kt * TW_BN;
+            const int gcol = cur.c * cmul + qcol * 8;
+            // ---- first half: Q piece i and, with K encoded, the K piece 4h + i ----
 #pragma unroll
-            for (int i = 0; i < 12; ++i) {
-                const int slot = i % 6;
-                const bool is_k = (i >= 4);
-                const int r = r0 + 32 * (is_k ? i - 4 : i);
-                const int pos = (is_k ? cur.kt * TW_BN : cur.qt * TW_BM) + r;
-                const size_t off = (size_t)(is_k ? TW_QCHUNK : 0) + (size_t)(tid + 256 * (is_k ? i - 4 : i)) * 16;
-                uint4 lo = *reinterpret_cast<uint4 *>(lo_st + off), hi = *reinterpret_cast<uint4 *>(hi_st + off);
-                if (is_k && !p.rotate_k) {
-                    // K is taken as given
-                } else if (pair_half) {
-                    tcw_rotate(lo.x, hi.x, tcv[slot].x, tsv[slot].x);
-                    tcw_rotate(lo.y, hi.y, tcv[slot].y, tsv[slot].y);
-                    tcw_rotate(lo.z, hi.z, tcv[slot].z, tsv[slot].z);
-                    tcw_rotate(lo.w, hi.w, tcv[slot].w, tsv[slot].w);
-                } else {
-                    lo.x = tc_pe_pair(lo.x, tcv[slot].x, sinus); hi.x = tc_pe_pair(hi.x, tsv[slot].x, sinus);
-                    lo.y = tc_pe_pair(lo.y, tcv[slot].y, sinus); hi.y = tc_pe_pair(hi.y, tsv[slot].y, sinus);
-                    lo.z = tc_pe_pair(lo.z, tcv[slot].z, sinus); hi.z = tc_pe_pair(hi.z, tsv[slot].z, sinus);
-                    lo.w = tc_pe_pair(lo.w, tcv[slot].w, sinus); hi.w = tc_pe_pair(hi.w, tsv[slot].w, sinus);
+            for (int i = 0; i < 4; ++i) {
+                {
+                    const size_t off = (size_t)(tid + 256 * i) * 16;
+                    uint4 lo = *reinterpret_cast<uint4 *>(lo_st + off), hi = *reinterpret_cast<uint4 *>(hi_st + off);
+                    encode_piece(lo, hi, ta[i], tb[i]);
+                    *reinterpret_cast<uint4 *>(lo_st + off) = lo;
+                    *reinterpret_cast<uint4 *>(hi_st + off) = hi;
+                    if (cur.store_q) {
+                        __nv_bfloat16 *g = p.q_store + (qrow0 + 32 * i + r0) * (long long)p.D + gcol;
+                        *reinterpret_cast<uint4 *>(g) = lo;
+                        *reinterpret_cast<uint4 *>(g + half) = hi;
+                    }
                 }
-                if (i < 6 || nx.valid) {
-                    const __nv_bfloat16 *tp = (i < 6) ? tab_ptr(cur, i + 6) : tab_ptr(nx, i - 6);
-                    tcv[slot] = tcw_ldg_here(tp);
-                    tsv[slot] = tcw_ldg_here(tp + half);
+                if (rotate_k) {
+                    const int ik = 4 * cur.h + i;   // K piece of the same positions when shared
+                    uint4 ka = ta[i], kb = tb[i];
+                    if (!cur.shared) {              // different positions: fetch the values now (not pipelined; rare shapes)
+                        const __nv_bfloat16 *tp = tab_k(cur, ik);
+                        ka = tcw_ldg_here(tp);
+                        kb = tcw_ldg_here(tp + half);
+                    }
+                    const size_t off = (size_t)TW_QCHUNK + (size_t)(tid + 256 * ik) * 16;
+                    uint4 lo = *reinterpret_cast<uint4 *>(lo_st + off), hi = *reinterpret_cast<uint4 *>(hi_st + off);
+                    encode_piece(lo, hi, ka, kb);
+                    *reinterpret_cast<uint4 *>(lo_st + off) = lo;
+                    *reinterpret_cast<uint4 *>(hi_st + off) = hi;
+                    const int krow = 32 * ik + r0;
+                    if (cur.store_k && cur.kt * TW_BN + krow < p.Lk) {
+                        __nv_bfloat16 *g = p.k_store + (krow0 + krow) * (long long)p.D + gcol;
+                        *reinterpret_cast<uint4 *>(g) = lo;
+                        *reinterpret_cast<uint4 *>(g + half) = hi;
+                    }
+                    // slot i next serves the i-th remaining K piece of this step
+                    const __nv_bfloat16 *tp = tab_k(cur, 4 * (1 - cur.h) + i);
+                    ta[i] = tcw_ldg_here(tp);
+                    tb[i] = tcw_ldg_here(tp + half);
+                } else if (nx.valid) {
+                    const __nv_bfloat16 *tp = tab_q(nx, i);
+                    ta[i] = tcw_ldg_here(tp);
+                    tb[i] = tcw_ldg_here(tp + half);
                 }
-                *reinterpret_cast<uint4 *>(lo_st + off) = lo;
-                *reinterpret_cast<uint4 *>(hi_st + off) = hi;
-                if (is_k ? (p.rotate_k && pos < p.Lk) : true) {
-                    __nv_bfloat16 *g = (is_k ? p.k_store + (cur.bh * p.Lk + pos) * (long long)p.D : p.q_store + (cur.bh * p.Lq + pos) * (long long)p.D) + cur.c * cmul + qcol * 8;
-                    *reinterpret_cast<uint4 *>(g) = lo;
-                    *reinterpret_cast<uint4 *>(g + half) = hi;
+            }
+            // ---- second half: the other four K pieces ----
+            if (rotate_k) {
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const int ik = 4 * (1 - cur.h) + m;
+                    const size_t off = (size_t)TW_QCHUNK + (size_t)(tid + 256 * ik) * 16;
+                    uint4 lo = *reinterpret_cast<uint4 *>(lo_st + off), hi = *reinterpret_cast<uint4 *>(hi_st + off);
+                    encode_piece(lo, hi, ta[m], tb[m]);
+                    *reinterpret_cast<uint4 *>(lo_st + off) = lo;
+                    *reinterpret_cast<uint4 *>(hi_st + off) = hi;
+                    const int krow = 32 * ik + r0;
+                    if (cur.store_k && cur.kt * TW_BN + krow < p.Lk) {
+                        __nv_bfloat16 *g = p.k_store + (krow0 + krow) * (long long)p.D + gcol;
+                        *reinterpret_cast<uint4 *>(g) = lo;
+                        *reinterpret_cast<uint4 *>(g + half) = hi;
+                    }
+                    if (nx.valid) {   // slot m next serves Q piece m of the next step
+                        const __nv_bfloat16 *tp = tab_q(nx, m);
+                        ta[m] = tcw_ldg_here(tp);
+                        tb[m] = tcw_ldg_here(tp + half);
+                    }
                 }
             }
             TWS(2);
@@ -359,11 +436,9 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
 // ---------------------------------------------------------------------------------------------------
 constexpr int TP_THREADS = 608;   // warp 0 V loads, warp 1 MMA, warps 2-17 softmax and the unit's epilogue, warp 18 S loads
-#ifndef B200ATTN_TP_VS
-#define B200ATTN_TP_VS 64
-#endif
-constexpr int TP_VS = B200ATTN_TP_VS;           // keys per V stage
-constexpr int TP_NV = 128 / TP_VS;   // V stage ring depth: 128 keys in flight
+constexpr int TP_VS = 64;         // keys per V stage
+constexpr int TP_VW = 256;        // output columns per V stage (one MMA N): a stage is [64 keys x <= 256 columns], 32 KB
+constexpr int TP_NV = 4;          // V stage ring depth
 constexpr int TP_NP = 3;          // score / P buffers
 
 struct TcwPvParams {
@@ -400,10 +475,11 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
     const uint32_t raw_addr = smem_u32(tw_smem_raw);
     unsigned char *smem = tw_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     unsigned char *p_smem = smem;                                   // TP_NP x 32 KB
-    unsigned char *v_smem = smem + (size_t)TP_NP * TC_P_BYTES;      // TP_NV x (32 keys x DW x 2 B)
+    unsigned char *v_smem = smem + (size_t)TP_NP * TC_P_BYTES;      // TP_NV x 32 KB
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int DW = p.DW, nblk = p.nblk;
-    const int v_stage_bytes = TP_VS * DW * 2;
+    const int v_stage_bytes = TP_VS * TP_VW * 2;   // ring pitch; a stage of the last column part may hold less
+    const int nvw = (DW + TP_VW - 1) / TP_VW;      // column parts per 64 keys
     const uint32_t lim = p.spin_limit;
 
     if (threadIdx.x == 0) {
@@ -433,16 +509,18 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                 const int dp = (int)(unit % p.ndp);
                 const long long bh = unit / p.ndp / p.nqt;
                 for (int t = 0; t < nblk && !failed; ++t)
-                    for (int vs = 0; vs < TC_BN / TP_VS; ++vs, ++it) {
-                        const int s = it % TP_NV;
-                        TWP(1);
-                        TW_FAIL_AT(8, !mbar_wait(&bars.v_empty[s], ((it / TP_NV) & 1) ^ 1, lim));
-                        TWP(0);
-                        mbar_expect_tx(&bars.v_full[s], (uint32_t)v_stage_bytes);
-                        for (int g = 0; g < DW / 64; ++g)
-                            tma_load_2d(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TP_VS * 128), &tmV, dp * DW + g * 64,
-                                        (int)(bh * p.Lk + t * TC_BN + vs * TP_VS), &bars.v_full[s]);
-                    }
+                    for (int vs = 0; vs < TC_BN / TP_VS && !failed; ++vs)
+                        for (int vw = 0; vw < nvw; ++vw, ++it) {
+                            const int s = it % TP_NV;
+                            const int ng = min(TP_VW, DW - vw * TP_VW) / 64;   // 64-column groups in this stage
+                            TWP(1);
+                            TW_FAIL_AT(8, !mbar_wait(&bars.v_empty[s], ((it / TP_NV) & 1) ^ 1, lim));
+                            TWP(0);
+                            mbar_expect_tx(&bars.v_full[s], (uint32_t)(ng * TP_VS * 128));
+                            for (int g = 0; g < ng; ++g)
+                                tma_load_2d(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TP_VS * 128), &tmV, dp * DW + vw * TP_VW + g * 64,
+                                            (int)(bh * p.Lk + t * TC_BN + vs * TP_VS), &bars.v_full[s]);
+                        }
             }
             TWP_FLUSH(0, true);
         }
@@ -481,25 +559,23 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                     TW_FAIL_AT(10, !mbar_wait(&bars.p_full[pb], (tg / TP_NP) & 1, lim));
                     tc_fence_after();
                     TWP(1);
-                    for (int vs = 0; vs < TC_BN / TP_VS; ++vs, ++it) {
-                        const int s = it % TP_NV;
-                        TWP(3);
-                        TW_FAIL_AT(11, !mbar_wait(&bars.v_full[s], (it / TP_NV) & 1, lim));
-                        tc_fence_after();
-                        TWP(2);
+                    for (int vs = 0; vs < TC_BN / TP_VS && !failed; ++vs)
+                        for (int vw = 0; vw < nvw; ++vw, ++it) {
+                            const int s = it % TP_NV;
+                            const int N = min(TP_VW, DW - vw * TP_VW);
+                            TWP(3);
+                            TW_FAIL_AT(11, !mbar_wait(&bars.v_full[s], (it / TP_NV) & 1, lim));
+                            tc_fence_after();
+                            TWP(2);
 #pragma unroll
-                        for (int kk = 0; kk < TP_VS / 16; ++kk) {
-                            const int kg = vs * (TP_VS / 16) + kk;   // 16-key step within the block, 0..7
-                            const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TW_BM * 128))) + 2 * (kg & 3);
-                            for (int n0 = 0; n0 < DW; n0 += 256) {
-                                const int N = min(256, DW - n0);
-                                const uint64_t db = umma_desc_mn_sw128(
-                                    smem_u32(v_smem + (size_t)s * v_stage_bytes + (size_t)(n0 >> 6) * (TP_VS * 128) + kk * 2048), TP_VS * 128);
-                                umma_bf16(tmem + n0, da, db, umma_idesc_bf16(TW_BM, N, 0, 1), (t | kg) != 0);
+                            for (int kk = 0; kk < TP_VS / 16; ++kk) {
+                                const int kg = vs * (TP_VS / 16) + kk;   // 16-key step within the block, 0..7
+                                const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TW_BM * 128))) + 2 * (kg & 3);
+                                const uint64_t db = umma_desc_mn_sw128(smem_u32(v_smem + (size_t)s * v_stage_bytes + kk * 2048), TP_VS * 128);
+                                umma_bf16(tmem + vw * TP_VW, da, db, umma_idesc_bf16(TW_BM, N, 0, 1), (t | kg) != 0);
                             }
+                            umma_commit(&bars.v_empty[s]);
                         }
-                        umma_commit(&bars.v_empty[s]);
-                    }
                     if (failed) break;
                     umma_commit(&bars.p_empty[pb]);
                 }
@@ -736,7 +812,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
     const int DW = D / ndp;
     const int nqt = Lq / TW_BM, nkt = (Lk + TW_BN - 1) / TW_BN, nblk = Lk / TC_BN;
     const size_t smem_s = (size_t)TW_NST * TW_STAGE + 1024;
-    const size_t smem_p = (size_t)TP_NP * TC_P_BYTES + (size_t)TP_NV * TP_VS * DW * 2 + 1024;
+    const size_t smem_p = (size_t)TP_NP * TC_P_BYTES + (size_t)TP_NV * TP_VS * TP_VW * 2 + 1024;
     static std::mutex attr_mu;
     static bool attr_done[64] = {};
     int dev = 0;

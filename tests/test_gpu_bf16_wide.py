@@ -30,6 +30,9 @@ def run(pkg, cuda, bits, **kw):
     (1, 1, 128, 256, 640),      # output column blocks of 320 (MMA N = 256 + 64)
     (1, 1, 128, 256, 2048),     # four output column blocks
     (1, 3, 256, 256, 256),      # narrow head: only rotate-half comes here
+    (1, 2, 256, 512, 1024),     # as many query tiles as key tiles: pairing q mod nkt, positions not shared
+    (1, 1, 640, 256, 1024),     # five query tiles on one key tile
+    (1, 1, 768, 512, 512),      # six query tiles on two key tiles
 ], ids=lambda s: "x".join(map(str, s)))
 def test_wide_path_against_oracle(pkg, cuda, pe, shape):
     B, H, Lq, Lk, D = shape
