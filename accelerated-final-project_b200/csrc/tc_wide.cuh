@@ -435,6 +435,162 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 }
 
 // ---------------------------------------------------------------------------------------------------
+// The same score GEMM with a [256 queries x 256 keys] tile per CTA: two accumulators of 128 rows
+// (TMEM columns 0-255 and 256-511) share every K chunk, so an operand chunk pair is 64 KB for eight
+// MMAs instead of 48 KB for four, i.e. two thirds of the L2 -> SM bytes per FLOP.  The accumulators
+// cannot be double-buffered any more; instead they are staggered: accumulator 0 finishes (and is
+// drained by warps 2-5) four MMAs before accumulator 1 (warps 6-9), and the next tile's MMAs into
+// accumulator 0 start as soon as it is drained.  Used for launches without the transform (modes 0 and
+// 2) when the query tiles pair up; mode 2 relies on both tiles of a pair having the same key tile in
+// the encoding launch (tcw_diag_kt with q / 2).
+constexpr int T2_THREADS = 320;            // warp 0 TMA, warp 1 MMA, warps 2-5 / 6-9 epilogue of accumulator 0 / 1
+constexpr int T2_NST = 3;
+constexpr int T2_QCHUNK = 2 * TW_QCHUNK;   // [256 rows x 64 bf16]
+constexpr int T2_STAGE = T2_QCHUNK + TW_KCHUNK;
+
+struct T2Bars {
+    uint64_t full[T2_NST], empty[T2_NST];
+    uint64_t acc_full[2], acc_empty[2];
+};
+
+// tile j of a head: query-tile pair qp and key tile kt
+__device__ __forceinline__ void tcw_tile256_of(int mode, int j, int nkt, int *qp, int *kt) {
+    if (mode == 0) { *qp = j / nkt; *kt = j - *qp * nkt; }
+    else { const int q = j / (nkt - 1), r = j - q * (nkt - 1); *qp = q; *kt = (q % nkt + 1 + r) % nkt; }
+}
+
+__global__ void __launch_bounds__(T2_THREADS, 1)
+tcw_scores256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const TcwScoreParams p) {
+    extern __shared__ unsigned char tw_smem_raw[];
+    __shared__ T2Bars bars;
+    __shared__ uint32_t tmem_slot;
+    const uint32_t raw_addr = smem_u32(tw_smem_raw);
+    unsigned char *smem = tw_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nch = p.nch;
+    const uint32_t lim = p.spin_limit;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < T2_NST; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&bars.acc_full[i], 1); mbar_init(&bars.acc_empty[i], 4); }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    bool failed = false;
+    const bool skip = (*reinterpret_cast<volatile unsigned *>(p.err) != 0);
+
+    if (skip) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x) {
+                const long long bh = tile / p.tph;
+                int qp, kt;
+                tcw_tile256_of(p.mode, (int)(tile - bh * p.tph), p.nkt, &qp, &kt);
+                for (int ci = 0; ci < nch; ++ci, ++it) {
+                    const int s = it % T2_NST;
+                    TW_FAIL_AT(16, !mbar_wait(&bars.empty[s], ((it / T2_NST) & 1) ^ 1, lim));
+                    unsigned char *st = smem + (size_t)s * T2_STAGE;
+                    mbar_expect_tx(&bars.full[s], T2_STAGE);
+                    tma_load_2d(st, &tmQ, ci * 64, (int)(bh * p.Lq + qp * 256), &bars.full[s]);
+                    tma_load_2d(st + T2_QCHUNK, &tmK, ci * 64, (int)(bh * p.Lk + kt * TW_BN), &bars.full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(TW_BM, TW_BN, 0, 0);
+            int it = 0;
+            long long tc = 0;
+            for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x, ++tc) {
+                for (int ci = 0; ci < nch; ++ci, ++it) {
+                    const int s = it % T2_NST;
+                    TW_FAIL_AT(17, !mbar_wait(&bars.full[s], (it / T2_NST) & 1, lim));
+                    tc_fence_after();
+                    const uint64_t da0 = umma_desc_k_sw128(smem_u32(smem + (size_t)s * T2_STAGE));
+                    const uint64_t da1 = umma_desc_k_sw128(smem_u32(smem + (size_t)s * T2_STAGE + TW_QCHUNK));
+                    const uint64_t db = umma_desc_k_sw128(smem_u32(smem + (size_t)s * T2_STAGE + T2_QCHUNK));
+                    if (ci == 0) {   // the previous tile's rows 0-127 have been read out of accumulator 0
+                        TW_FAIL_AT(18, !mbar_wait(&bars.acc_empty[0], (tc & 1) ^ 1, lim));
+                        tc_fence_after();
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma_bf16(tmem, da0 + 2 * k, db + 2 * k, idesc, (ci | k) != 0);
+                    if (ci == nch - 1) umma_commit(&bars.acc_full[0]);
+                    if (ci == 0) {
+                        TW_FAIL_AT(19, !mbar_wait(&bars.acc_empty[1], (tc & 1) ^ 1, lim));
+                        tc_fence_after();
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma_bf16(tmem + TW_BN, da1 + 2 * k, db + 2 * k, idesc, (ci | k) != 0);
+                    umma_commit(&bars.empty[s]);
+                }
+                if (failed) break;
+                umma_commit(&bars.acc_full[1]);
+            }
+        }
+    } else {
+        // ---- epilogue: warps 2-5 read accumulator 0 (rows 0-127 of the tile), warps 6-9 accumulator 1 ----
+        const int acc = warp >= 6 ? 1 : 0;
+        const int row = 128 * acc + 32 * (warp & 3) + lane;
+        const uint32_t ta = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + acc * TW_BN;
+        uint32_t r[32], wds[32];
+        long long tc = 0;
+        for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x, ++tc) {
+            const long long bh = tile / p.tph;
+            int qp, kt;
+            tcw_tile256_of(p.mode, (int)(tile - bh * p.tph), p.nkt, &qp, &kt);
+            TW_FAIL_AT(20, !mbar_wait(&bars.acc_full[acc], tc & 1, lim));
+            tc_fence_after();
+            const int ncc = min(TW_BN, p.Lk - kt * TW_BN) / 32;   // 32-column groups that hold real keys
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            for (int c = 0; c < ncc; ++c) {
+                tmem_ld32(ta + c * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(r[j]));
+                    mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
+                }
+            }
+            const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+            const long long grow = bh * p.Lq + (long long)qp * 256 + row;
+            p.rowmax[grow * p.nkt + kt] = mt;
+            __nv_bfloat16 *srow = p.S + grow * p.Lk + (long long)kt * TW_BN;
+            unsigned char *srow0 = reinterpret_cast<unsigned char *>(srow - (long long)(lane & 3) * p.Lk);
+            for (int cp = 0; cp < ncc / 2; ++cp) {   // 64 keys = 128 bytes of the row at a time, stored as full lines
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    tmem_ld32(ta + cp * 64 + hh * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        wds[16 * hh + q] = pack_bf16x2(fmaf(__uint_as_float(r[2 * q]), p.scale_log2, -mt), fmaf(__uint_as_float(r[2 * q + 1]), p.scale_log2, -mt));
+                }
+                store_rows_128B_transposed(srow0 + cp * 128, (size_t)p.Lk * 2, wds, lane);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.acc_empty[acc]);
+        }
+    }
+
+    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------------
 constexpr int TP_THREADS = 608;   // warp 0 V loads, warp 1 MMA, warps 2-17 softmax and the unit's epilogue, warp 18 S loads
 constexpr int TP_VS = 64;         // keys per V stage
 constexpr int TP_VW = 256;        // output columns per V stage (one MMA N): a stage is [64 keys x <= 256 columns], 32 KB
@@ -825,6 +981,8 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
             cudaGetDeviceProperties(&prop, dev);
             bool ok = cudaFuncGetAttributes(&fa, tcw_scores_kernel) == cudaSuccess &&
                       cudaFuncSetAttribute(tcw_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
+            ok = ok && cudaFuncGetAttributes(&fa, tcw_scores256_kernel) == cudaSuccess &&
+                 cudaFuncSetAttribute(tcw_scores256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
             ok = ok && cudaFuncGetAttributes(&fa, tcw_pv_kernel) == cudaSuccess &&
                  cudaFuncSetAttribute(tcw_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
             if (!ok) { (void)cudaGetLastError(); snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncSetAttribute(max dynamic shared memory) failed"); return B200ATTN_ERR_CUDA; }
@@ -873,20 +1031,26 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         sp.S = S; sp.rowmax = rowmax; sp.tab = tab; sp.q_store = qs; sp.k_store = ks;
         sp.pe = a.pe == B200ATTN_PE_ROPE_Q_ONLY ? (int)PE_ROPE_INTERLEAVED : a.pe; sp.rotate_k = rotate_k ? 1 : 0;
         sp.err = err_dev; sp.err_sys = err_sys; sp.spin_limit = spin_limit;
+        // launches without the transform use the [256 x 256] tile kernel when the query tiles pair up
+        // (and, for the complement of the encoding launch, when both tiles of a pair met the same key tile there)
+        const bool big_ok = (nqt % 2 == 0) && !getenv("B200ATTN_TCW_NO_BM256");
         auto launch_scores = [&](const void *Qp, const void *Kp, int mode, int tph) -> int {
             if (tph <= 0) return B200ATTN_OK;
+            const bool big = big_ok && (mode == 0 || (mode == 2 && nkt <= nqt && nqt >= 2 * nkt - 1));
             CUtensorMap tmQ, tmK;
-            if (!tc_make_map(&tmQ, Qp, nh * Lq, D, TW_BM) || !tc_make_map(&tmK, Kp, nh * Lk, D, TW_BN)) {
+            if (!tc_make_map(&tmQ, Qp, nh * Lq, D, big ? 256 : TW_BM) || !tc_make_map(&tmK, Kp, nh * Lk, D, TW_BN)) {
                 snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
                 return B200ATTN_ERR_CUDA;
             }
+            if (big) tph /= 2;   // tiles of two query tiles each
             sp.mode = mode; sp.tph = tph; sp.n_tiles = nh * tph;
             const unsigned grid = (unsigned)(sp.n_tiles < sm_count ? sp.n_tiles : sm_count);
             tcw_timer().begin(mode == 1 ? 0 : 1, st);
-            tcw_scores_kernel<<<grid, TW_THREADS, smem_s, st>>>(tmQ, tmK, sp);
+            if (big) tcw_scores256_kernel<<<grid, T2_THREADS, (size_t)T2_NST * T2_STAGE + 1024, st>>>(tmQ, tmK, sp);
+            else tcw_scores_kernel<<<grid, TW_THREADS, smem_s, st>>>(tmQ, tmK, sp);
             tcw_timer().end(st);
             cudaError_t e = cudaGetLastError();
-            if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "tcw_scores_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
+            if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "score kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
             launches->fetch_add(1);
             return B200ATTN_OK;
         };
