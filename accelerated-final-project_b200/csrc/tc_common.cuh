@@ -68,6 +68,13 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *t
         "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *tmap, int x, int y, int z, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -151,6 +158,40 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- the same for a pair of CTAs working as one (cta_group::2): both CTAs of a 2-CTA cluster allocate
+// together, the MMA is issued by one thread of the LEADER CTA (cluster rank 0) with M = 256 (128 rows
+// from each CTA's A tile, into each CTA's own tensor memory) and the B tile split along N between
+// the two CTAs' shared memories at the same offsets; a commit arrives on ONE mbarrier given by its
+// shared::cluster address (so it may be the peer's); a bulk-tensor load may complete on the peer's
+// mbarrier.  No multicast is used anywhere. ----
+__device__ __forceinline__ void tmem_alloc_2cta(uint32_t *slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2cta(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_2cta(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// one arrival on the mbarrier at this shared::cluster address when every MMA issued so far has completed
+__device__ __forceinline__ void umma_commit_2cta(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tiled load into THIS CTA's shared memory whose bytes are counted on the mbarrier at `mbar_cluster_addr`
+__device__ __forceinline__ void tma_load_2d_2cta(void *smem_dst, const CUtensorMap *tmap, int x, int y, uint32_t mbar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(tmap), "r"(x), "r"(y), "r"(mbar_cluster_addr)
+        : "memory");
+}
+
 // ---- host: tensor maps (the encoder is taken from the driver at run time; no -lcuda) -------------
 typedef CUresult (*PFN_tmapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                          const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -215,6 +256,22 @@ __device__ __forceinline__ void store_rows_128B_transposed(unsigned char *row0_p
     for (int m = 0; m < 4; ++m)
         st_global_v8(row0_ptr + (size_t)m * row_pitch + j * 32, make_uint4(w[8 * m], w[8 * m + 1], w[8 * m + 2], w[8 * m + 3]),
                      make_uint4(w[8 * m + 4], w[8 * m + 5], w[8 * m + 6], w[8 * m + 7]));
+}
+
+// A bf16 row-major [rows][cols] matrix seen as [cols/64 groups][rows][64 columns], so that ONE request
+// fetches a box of `box_groups` 64-column groups x `box_rows` rows and lays it down as consecutive
+// [box_rows x 128 B] slabs with the 128-byte swizzle: the shared-memory layout of a K-major tile
+// wider than 64 elements, or of an MN-major operand, which otherwise takes one request per slab.
+// (A bulk-tensor request costs the SM about 130 cycles whatever its size.)
+inline bool make_tmap_grouped(CUtensorMap *m, const void *base, long long rows, long long cols, int box_rows, int box_groups) {
+    PFN_tmapEncodeTiled enc = tmap_encode_fn();
+    if (!enc || cols % 64 != 0) return false;
+    cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_groups};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

@@ -48,8 +48,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # captures summarised under profiles/ (null until a capture exists for the kernel in use)
 NCU_TRAFFIC_BYTES = {
     # per STEP (a step of the two-kernel path is several launches; `achieved` is per step as well)
-    ("cfg5", "tc_wide"): 49.3e9,        # profiles/tcw_kernels_cfg5.md: the 16-head capture (1540.6 MB over the three launches) x 32
-    ("cfg4", "tc_wide"): 5.73e9,        # profiles/tcw_kernels_cfg4.md: the 16-head capture (716.4 MB) x 8
+    ("cfg5", "tc_wide"): 48.9e9,        # profiles/tcw_kernels_cfg5.md: the 16-head capture (1526.5 MB over the three launches) x 32
+    ("cfg4", "tc_wide"): 5.68e9,        # profiles/tcw_kernels_cfg4.md: the 16-head capture (709.9 MB) x 8
     ("cfg3", "tc_bf16"): 514.8e6,       # profiles/tc_bf16_pair_kernel_cfg3.md: 402.8 MB read + 112.0 MB written
     ("cfg5", "tc_bf16"): 8 * 2.0**30 + 2 * 2.0**30,   # scaled from the cfg 3 capture by input/output bytes plus the encoded-K scratch
     ("cfg2c", "splitd_fused"): 33.7e6,  # profiles/splitd_fused_kernel_cfg2c.md: 25.3 MB read, 8.4 MB output
