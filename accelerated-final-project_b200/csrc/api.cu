@@ -660,6 +660,25 @@ int b200attn_debug_kernel_times(int enable, double *out) {
     return B200ATTN_OK;
 }
 
+// Host copy of the tile enumeration of the two-kernel bf16 path, for tests (no GPU needed).  big = 0:
+// tile j of a head in launch `mode` (0 all tiles, 1 encoding launch, 2 its complement) -> (query tile,
+// key tile); big = 1: the 256-row variant -> (query-tile pair, key tile).  Returns the number of tiles
+// per head of that launch, or -1 when the launch does not exist for the shape.
+int b200attn_debug_tile_of(int big, int mode, int j, int nqt, int nkt, int *qt, int *kt) {
+    if (nqt <= 0 || nkt <= 0 || mode < 0 || mode > 2) return -1;
+    const int nA = nqt > nkt ? nqt : nkt;
+    int count = mode == 0 ? nqt * nkt : mode == 1 ? nA : nqt * nkt - nA;
+    if (big) {
+        if (mode == 1 || nqt % 2 != 0) return -1;
+        if (mode == 2 && !(nkt <= nqt && nqt >= 2 * nkt - 1)) return -1;
+        count /= 2;
+        if (j >= 0 && j < count) tcw_tile256_of(mode, j, nkt, qt, kt);
+    } else if (j >= 0 && j < count) {
+        tcw_tile_of(mode, j, nqt, nkt, qt, kt);
+    }
+    return count;
+}
+
 const char *b200attn_last_error(void) { return t_last_error.c_str(); }
 const char *b200attn_last_path(void) { return t_last_path; }
 unsigned long long b200attn_launch_count(void) { return g_launches.load(); }

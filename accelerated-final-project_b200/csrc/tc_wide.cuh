@@ -97,10 +97,10 @@ struct TwBars {
 // as many query tiles as key tiles, query tile q is paired with key tile a(q): q/2 where that
 // reaches every key tile (then the 128 query rows have the positions of one half of the 256 key
 // rows, and one set of table values serves both), else q mod nkt.
-__device__ __forceinline__ int tcw_diag_kt(int q, int nqt, int nkt) {
+__host__ __device__ __forceinline__ int tcw_diag_kt(int q, int nqt, int nkt) {
     return (nqt >= 2 * nkt - 1) ? (q >> 1) % nkt : q % nkt;
 }
-__device__ __forceinline__ void tcw_tile_of(int mode, int j, int nqt, int nkt, int *qt, int *kt) {
+__host__ __device__ __forceinline__ void tcw_tile_of(int mode, int j, int nqt, int nkt, int *qt, int *kt) {
     if (mode == 0) { *qt = j / nkt; *kt = j - *qt * nkt; }
     else if (nkt <= nqt) {
         if (mode == 1) { *qt = j; *kt = tcw_diag_kt(j, nqt, nkt); }
@@ -454,7 +454,7 @@ struct T2Bars {
 };
 
 // tile j of a head: query-tile pair qp and key tile kt
-__device__ __forceinline__ void tcw_tile256_of(int mode, int j, int nkt, int *qp, int *kt) {
+__host__ __device__ __forceinline__ void tcw_tile256_of(int mode, int j, int nkt, int *qp, int *kt) {
     if (mode == 0) { *qp = j / nkt; *kt = j - *qp * nkt; }
     else { const int q = j / (nkt - 1), r = j - q * (nkt - 1); *qp = q; *kt = (q % nkt + 1 + r) % nkt; }
 }

@@ -165,7 +165,8 @@ void b200attn_shard_ranges(long long total_bh, int n_parts, long long *begin, lo
 const char *b200attn_last_error(void);
 
 /* Name of the kernel path the last successful b200attn_forward_ex on this thread used:
- * "splitd_fused", "splitd_two_pass" or "tc_bf16". */
+ * "splitd_fused", "splitd_two_pass", "tc_wide" (bf16 on the tensor cores: score kernel, then P V kernel)
+ * or "tc_bf16" (bf16 on the tensor cores, one-kernel cluster pipeline). */
 const char *b200attn_last_path(void);
 
 /* Number of kernel launches issued by this library in this process so far. */
