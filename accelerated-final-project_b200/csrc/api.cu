@@ -383,6 +383,11 @@ static int forward_device(const b200attn_args *a) {
         rc = tcw_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_wide"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
+        else if (pair_ok && !use_pair) {   // no room for the score scratch: the one-kernel pipeline needs none
+            rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+            if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
+            else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
+        }
     }
     if (!done) {
         rc = (a->dtype == B200ATTN_F32) ? run_splitd<float>(*c, *a, rd, base, st) : run_splitd<__nv_bfloat16>(*c, *a, rd, base, st);

@@ -1217,7 +1217,8 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
     return true;
 }
 
-// Returns B200ATTN_OK, -1 when the shape should run on another path, or a status with tc_bf16_error() set.
+// Returns B200ATTN_OK, -1 when the shape should run on another path (also when the scratch could not be
+// allocated: nothing has been launched then), or a status with tc_bf16_error() set.
 inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, TcTables &tables, unsigned *err_dev, unsigned *err_sys, int sm_count,
                    unsigned spin_limit, cudaStream_t st, std::atomic<unsigned long long> *launches) {
     const long long BH = (long long)a.batch_sz * a.num_heads;
@@ -1263,16 +1264,16 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
     __nv_bfloat16 *S = (__nv_bfloat16 *)sc.get(0, (size_t)G * s_head);
     float *rowmax = (float *)sc.get(1, (size_t)G * Lq * nkt * sizeof(float));
     __nv_bfloat16 *qs = nullptr, *ks = nullptr, *tab = nullptr;
-    if (!S || !rowmax) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the score scratch"); return B200ATTN_ERR_CUDA; }
+    if (!S || !rowmax) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the score scratch"); return -1; }
     if (encoded) {
         qs = (__nv_bfloat16 *)sc.get(2, (size_t)G * Lq * D * 2);
         ks = (__nv_bfloat16 *)sc.get(3, (size_t)G * Lk * D * 2);
         const int Lt = (Lq > nkt * TW_BN ? Lq : nkt * TW_BN);
-        if (!qs || !ks) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the rotated-operand scratch"); return B200ATTN_ERR_CUDA; }
+        if (!qs || !ks) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the rotated-operand scratch"); return -1; }
         if (pair_half) {
             const bool have = sc.buf[4] && sc.tab_L >= Lt && sc.tab_D == D && sc.tab_base == base;
             tab = (__nv_bfloat16 *)(have ? sc.buf[4] : sc.get(4, (size_t)Lt * D * 2));
-            if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the cos/sin table"); return B200ATTN_ERR_CUDA; }
+            if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the cos/sin table"); return -1; }
             if (!have) {
                 if (sc.tab_L != 0) cudaDeviceSynchronize();   // no kernel may still be reading the table that is replaced
                 tcw_build_half_table<<<296, 256, 0, st>>>(tab, Lt, D, base);
@@ -1282,7 +1283,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         } else {
             int rows = 0;
             tab = tables.get(a.pe, Lt, D, rd, a.pe == B200ATTN_PE_SINUSOIDAL ? 10000.0f : base, st, launches, &rows);
-            if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the positional-encoding table"); return B200ATTN_ERR_CUDA; }
+            if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the positional-encoding table"); return -1; }
         }
     }
     for (long long h0 = 0; h0 < BH; h0 += G) {

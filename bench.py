@@ -354,7 +354,8 @@ def main():
             n_enc = max(nqt, nkt) if pe != 0 else 0
             tile_fl = 2.0 * 128 * 256 * D
             k_fl = {"scores_encode": B * H * n_enc * tile_fl, "scores": B * H * (nqt * nkt - n_enc) * tile_fl, "pv": fl / 2.0}
-            names = {"scores_encode": "tcw_scores_kernel (encoding launch)", "scores": "tcw_scores_kernel", "pv": "tcw_pv_kernel"}
+            names = {"scores_encode": "tcw_scores_kernel (encoding launch)",
+                     "scores": "tcw_scores256_kernel (score GEMM; tcw_scores_kernel when the query tiles do not pair up)", "pv": "tcw_pv_kernel"}
             tot = sum(v[0] for v in kt.values())
             rows = []
             for k, (kms, cnt) in kt.items():
