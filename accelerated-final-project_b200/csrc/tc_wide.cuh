@@ -594,8 +594,15 @@ tcw_scores256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 constexpr int TP_THREADS = 608;   // warp 0 V loads, warp 1 MMA, warps 2-17 softmax and the unit's epilogue, warp 18 S loads
 constexpr int TP_VS = 64;         // keys per V stage
 constexpr int TP_VW = 256;        // output columns per V stage (one MMA N): a stage is [64 keys x <= 256 columns], 32 KB
-constexpr int TP_NV = 4;          // V stage ring depth
-constexpr int TP_NP = 3;          // score / P buffers
+#ifndef B200ATTN_TP_NV
+#define B200ATTN_TP_NV 3
+#endif
+constexpr int TP_NV = B200ATTN_TP_NV;   // V stage ring depth (32 KB each; TP_NV + TP_NP <= 7 fits the shared memory;
+                                        // measured on cfg 4 / cfg 5: 4 + 3 is 1 % faster than 3 + 4, 5 + 2 is 6 % slower)
+#ifndef B200ATTN_TP_NP
+#define B200ATTN_TP_NP 4
+#endif
+constexpr int TP_NP = B200ATTN_TP_NP;   // score / P buffers (32 KB each)
 
 struct TcwPvParams {
     int Lq, Lk, D;
@@ -878,9 +885,10 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
 // accumulator drained) live in the leader and count both CTAs; "slot free" barriers live in both
 // CTAs and get one commit each.
 constexpr int TP2_NV = 8;         // V stage ring depth (16 KB per CTA and stage)
+constexpr int TP2_NP = 3;         // score / P buffers
 struct Tp2Bars {
     uint64_t v_full[TP2_NV], v_empty[TP2_NV];
-    uint64_t s_full[TP_NP], p_full[TP_NP], p_empty[TP_NP];
+    uint64_t s_full[TP2_NP], p_full[TP2_NP], p_empty[TP2_NP];
     uint64_t o_full, o_empty;
     uint64_t l_full;
 };
@@ -894,8 +902,8 @@ tcw_pv2_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ 
     __shared__ float l_smem[2][TW_BM];
     const uint32_t raw_addr = smem_u32(tw_smem_raw);
     unsigned char *smem = tw_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-    unsigned char *p_smem = smem;                                   // TP_NP x 32 KB
-    unsigned char *v_smem = smem + (size_t)TP_NP * TC_P_BYTES;      // TP2_NV x 16 KB: this CTA's half of the columns of each stage
+    unsigned char *p_smem = smem;                                   // TP2_NP x 32 KB
+    unsigned char *v_smem = smem + (size_t)TP2_NP * TC_P_BYTES;      // TP2_NV x 16 KB: this CTA's half of the columns of each stage
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int DW = p.DW, nblk = p.nblk;
     const int v_stage_bytes = TP_VS * (TP_VW / 2) * 2;   // ring pitch: [64 keys x 128 columns] per CTA
@@ -907,7 +915,7 @@ tcw_pv2_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < TP2_NV; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
-        for (int i = 0; i < TP_NP; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.p_full[i], 32); mbar_init(&bars.p_empty[i], 1); }
+        for (int i = 0; i < TP2_NP; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.p_full[i], 32); mbar_init(&bars.p_empty[i], 1); }
         mbar_init(&bars.o_full, 1);
         mbar_init(&bars.o_empty, 32);
         mbar_init(&bars.l_full, 16);
@@ -962,8 +970,8 @@ tcw_pv2_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ 
             for (long long unit = cluster_id; unit < p.n_units && !failed; unit += n_clusters) {
                 const long long rest = (unit / p.ndp) * 2 + rank;   // = bh * nqt + qt: the row tile of the score matrix
                 for (int t = 0; t < nblk; ++t, ++tg) {
-                    const int pb = (int)(tg % TP_NP);
-                    TW_FAIL_AT(15, !mbar_wait_cluster(&bars.p_empty[pb], ((tg / TP_NP) & 1) ^ 1, lim));
+                    const int pb = (int)(tg % TP2_NP);
+                    TW_FAIL_AT(15, !mbar_wait_cluster(&bars.p_empty[pb], ((tg / TP2_NP) & 1) ^ 1, lim));
                     mbar_expect_tx(&bars.s_full[pb], TC_P_BYTES);
                     tma_load_2d(p_smem + (size_t)pb * TC_P_BYTES, &tmS, t * TC_BN, (int)(rest * TW_BM), &bars.s_full[pb]);
                     tma_load_2d(p_smem + (size_t)pb * TC_P_BYTES + TW_BM * 128, &tmS, t * TC_BN + 64, (int)(rest * TW_BM), &bars.s_full[pb]);
@@ -979,8 +987,8 @@ tcw_pv2_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ 
                 TW_FAIL_AT(9, !mbar_wait_cluster(&bars.o_empty, (ui & 1) ^ 1, lim));
                 tc_fence_after();
                 for (int t = 0; t < nblk && !failed; ++t, ++tg) {
-                    const int pb = (int)(tg % TP_NP);
-                    TW_FAIL_AT(10, !mbar_wait_cluster(&bars.p_full[pb], (tg / TP_NP) & 1, lim));
+                    const int pb = (int)(tg % TP2_NP);
+                    TW_FAIL_AT(10, !mbar_wait_cluster(&bars.p_full[pb], (tg / TP2_NP) & 1, lim));
                     tc_fence_after();
                     for (int vs = 0; vs < TC_BN / TP_VS && !failed; ++vs)
                         for (int vw = 0; vw < nvw; ++vw, ++it) {
@@ -1038,7 +1046,7 @@ tcw_pv2_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ 
             if (ui == 0) load_stats(grow0, offs);
             float lA = 0.0f, lB = 0.0f, offA = 0.0f, offB = 0.0f;
             for (int t = 0; t < nblk; ++t, ++tg) {
-                const int pb = (int)(tg % TP_NP);
+                const int pb = (int)(tg % TP2_NP);
                 if ((t & 1) == 0) {   // a new 256-key tile: fetch this thread's two offsets
                     const int kt = t >> 1;
                     float v[8];
@@ -1047,7 +1055,7 @@ tcw_pv2_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ 
                     offA = rl == 0 ? v[0] : rl == 1 ? v[1] : rl == 2 ? v[2] : v[3];
                     offB = rl == 0 ? v[4] : rl == 1 ? v[5] : rl == 2 ? v[6] : v[7];
                 }
-                TW_FAIL_AT(12, !mbar_wait(&bars.s_full[pb], (tg / TP_NP) & 1, lim));
+                TW_FAIL_AT(12, !mbar_wait(&bars.s_full[pb], (tg / TP2_NP) & 1, lim));
                 unsigned char *base = p_smem + (size_t)pb * TC_P_BYTES + (8 * w + rl) * 128 + (lane & 7) * 16;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -1343,7 +1351,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         if (pv2) {
             pp.n_units = nh * (nqt / 2) * ndp;
             const long long clusters = pp.n_units < sm_count / 2 ? pp.n_units : sm_count / 2;
-            const size_t smem_p2 = (size_t)TP_NP * TC_P_BYTES + (size_t)TP2_NV * TP_VS * (TP_VW / 2) * 2 + 1024;
+            const size_t smem_p2 = (size_t)TP2_NP * TC_P_BYTES + (size_t)TP2_NV * TP_VS * (TP_VW / 2) * 2 + 1024;
             tcw_pv2_kernel<<<(unsigned)(2 * clusters), TP_THREADS, smem_p2, st>>>(tmV, tmS, pp);
         } else {
             const unsigned grid = (unsigned)(pp.n_units < sm_count ? pp.n_units : sm_count);
