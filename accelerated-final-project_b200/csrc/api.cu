@@ -16,6 +16,7 @@
 
 #include "../../include/b200attn.h"
 #include "splitd.cuh"
+#include "splitd_tc.cuh"
 #include "synth.cuh"
 #include "tc_bf16.cuh"
 #include "tc_wide.cuh"
@@ -47,6 +48,33 @@ constexpr int kMaxDevices = 64;
 constexpr int kSplitDMaxDs = 272;                      // widest slice whose Q,K,V tiles fit 227 KB
 constexpr size_t kDefaultScratchCap = 1ull << 30;      // two-pass scores scratch per launch chunk
 
+// Tensor maps are a function of (base address, shape, box) only; encoding one costs the host about a
+// microsecond, which matters next to a kernel of a few microseconds, so they are kept.
+struct TmapCache {
+    struct alignas(64) Entry {
+        CUtensorMap map;
+        const void *base = nullptr;
+        long long rows = 0;
+        int cols = 0, box_rows = 0, swz = 0;
+        bool valid = false;
+    };
+    static constexpr size_t kEntries = 4096;   // direct-mapped
+    std::vector<Entry> e;
+    // fp32 [rows][cols] matrix, box [box_rows x 32 columns], one of the 128-byte swizzles
+    const CUtensorMap *get(const void *base, long long rows, int cols, int box_rows, CUtensorMapSwizzle swz) {
+        if (e.empty()) e.resize(kEntries);
+        size_t h = (size_t)((uintptr_t)base >> 4) * 0x9E3779B97F4A7C15ull;
+        h ^= (size_t)rows * 0xC2B2AE3D27D4EB4Full + (size_t)cols * 1315423911u + (size_t)box_rows + ((size_t)swz << 40);
+        Entry &x = e[(h >> 20) % kEntries];
+        if (!(x.valid && x.base == base && x.rows == rows && x.cols == cols && x.box_rows == box_rows && x.swz == (int)swz)) {
+            x.valid = make_tmap_2d(&x.map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, rows, cols, ST_ATOM, box_rows, swz);
+            x.base = base; x.rows = rows; x.cols = cols; x.box_rows = box_rows; x.swz = (int)swz;
+            if (!x.valid) return nullptr;
+        }
+        return &x.map;
+    }
+};
+
 // Per-device state.  Guarded by `mu`: calls for one device are serialised on the host.
 struct DeviceCtx {
     std::mutex mu;
@@ -70,6 +98,15 @@ struct DeviceCtx {
     cudaStream_t host_streams[3] = {nullptr, nullptr, nullptr};   // copy-in, compute, copy-out
     cudaEvent_t host_events[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     cudaStream_t shard_stream = nullptr;
+    // tensor-core split-head_d path: double-buffered score scratch (see splitd_tc.cuh)
+    float *sdtc_S = nullptr;
+    unsigned *sdtc_cnt = nullptr;
+    int sdtc_cap = 0;              // heads per half
+    int sdtc_epoch = 0;            // half the next call sums into
+    int sdtc_prev_bh = 0;          // heads the last call left non-zero in the other half
+    bool sdtc_attr = false;
+    size_t sdtc_smem_max = 0;
+    TmapCache tmaps;
     TcTables tc_tables;            // positional-encoding tables of the tensor-core path
     TcwScratch tcw;                // scratch of the wide-head tensor-core path
 };
@@ -124,8 +161,13 @@ static int ensure_scratch(DeviceCtx &c, size_t s_bytes, size_t n_counters, cudaS
         c.counters_n = want;
     }
     if (c.scratch_dirty) {
-        CU_TRY(cudaMemsetAsync(c.S, 0, c.S_bytes, st));
-        CU_TRY(cudaMemsetAsync(c.counters, 0, c.counters_n * sizeof(unsigned), st));
+        if (c.S) CU_TRY(cudaMemsetAsync(c.S, 0, c.S_bytes, st));
+        if (c.counters) CU_TRY(cudaMemsetAsync(c.counters, 0, c.counters_n * sizeof(unsigned), st));
+        if (c.sdtc_S) {
+            CU_TRY(cudaMemsetAsync(c.sdtc_S, 0, (size_t)2 * c.sdtc_cap * 4096 * sizeof(float), st));
+            CU_TRY(cudaMemsetAsync(c.sdtc_cnt, 0, (size_t)2 * c.sdtc_cap * sizeof(unsigned), st));
+            c.sdtc_prev_bh = 0;
+        }
         CU_TRY(cudaMemsetAsync(c.err_dev, 0, sizeof(unsigned), st));
         c.scratch_dirty = false;
     }
@@ -303,6 +345,77 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
     return B200ATTN_OK;
 }
 
+#ifdef B200ATTN_DEVTOOLS
+static float *g_sdtc_dbg = nullptr;
+static unsigned long long *g_sdtc_stamps = nullptr;
+#endif
+// ---- split-head_d path on the tensor cores (fp32, no positional encoding, len <= 64) ---------------
+// Slices are whole 32-column atoms; a head gets as many slices as the SM count allows.  Returns -1 when
+// the shape belongs to the CUDA-core kernels (an encoding, an odd head_d, more heads than SMs, a slice
+// wider than 256 columns).
+static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st) {
+    const long long BH = (long long)a.batch_sz * a.num_heads;
+    const int Lq = a.len_q, Lk = a.len_k, D = a.head_d;
+    if (a.dtype != B200ATTN_F32 || a.pe != B200ATTN_PE_NONE || Lq > 64 || Lk > 64 || D % 4 != 0) return -1;
+    if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return -1;
+    if (BH > c.sm_count || BH > 65535) return -1;
+    const int natoms = (D + ST_ATOM - 1) / ST_ATOM;
+    const int slots = (int)(c.sm_count / BH);
+    const int apc = (natoms + slots - 1) / slots;
+    if (apc > ST_MAX_ATOMS) return -1;
+    const int nsplit = (natoms + apc - 1) / apc;
+    const int nst = apc < ST_MAX_STAGES ? apc : ST_MAX_STAGES;
+    const size_t smem = sdtc_smem_bytes(apc, nst);
+    if (!c.sdtc_attr) {
+        cudaFuncAttributes fa;
+        CU_TRY(cudaFuncGetAttributes(&fa, sdtc_kernel));
+        c.sdtc_smem_max = c.max_smem_optin - fa.sharedSizeBytes;
+        CU_TRY(cudaFuncSetAttribute(sdtc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)c.sdtc_smem_max));
+        c.sdtc_attr = true;
+    }
+    if (smem > c.sdtc_smem_max) return -1;
+    if (c.sdtc_S == nullptr) {
+        const int cap = c.sm_count;
+        CU_TRY(cudaMalloc(&c.sdtc_S, (size_t)2 * cap * 4096 * sizeof(float)));
+        CU_TRY(cudaMalloc(&c.sdtc_cnt, (size_t)2 * cap * sizeof(unsigned)));
+        c.sdtc_cap = cap;
+        c.scratch_dirty = true;   // cleared below, on this call's stream
+    }
+    if (c.scratch_dirty) {
+        int rc = ensure_scratch(c, 0, 0, st);
+        if (rc) return rc;
+    }
+    // (the four maps are copied before the next lookup can evict one: the cache is direct-mapped)
+    CUtensorMap tmQ, tmK, tmV, tmO;
+    const CUtensorMap *m;
+    bool ok = (m = c.tmaps.get(a.Q, BH * Lq, D, Lq, CU_TENSOR_MAP_SWIZZLE_128B)) != nullptr;
+    if (ok) { tmQ = *m; ok = (m = c.tmaps.get(a.K, BH * Lk, D, Lk, CU_TENSOR_MAP_SWIZZLE_128B)) != nullptr; }
+    if (ok) { tmK = *m; ok = (m = c.tmaps.get(a.V, BH * Lk, D, Lk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != nullptr; }
+    if (ok) { tmV = *m; ok = (m = c.tmaps.get(a.out, BH * Lq, D, Lq, CU_TENSOR_MAP_SWIZZLE_128B)) != nullptr; }
+    if (ok) tmO = *m;
+    if (!ok) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the split-head_d slices");
+    SdtcParams p{};
+    p.BH = BH; p.Lq = Lq; p.Lk = Lk; p.D = D;
+    p.apc = apc; p.natoms = natoms; p.nsplit = nsplit; p.nst = nst;
+    p.epoch = c.sdtc_epoch; p.cap_bh = c.sdtc_cap; p.zero_bh = c.sdtc_prev_bh;
+    p.scale = 1.0f / sqrtf((float)D);
+    p.S = c.sdtc_S; p.counters = c.sdtc_cnt;
+    p.err = c.err_dev; p.err_sys = c.err_host_dev;
+    p.spin_limit = spin_limit_from_env();
+    p.wait_extra = g_test_wait_extra.load();
+#ifdef B200ATTN_DEVTOOLS
+    p.dbg = g_sdtc_dbg;
+    p.stamps = g_sdtc_stamps;
+#endif
+    sdtc_kernel<<<dim3((unsigned)nsplit, (unsigned)BH), ST_THREADS, smem, st>>>(tmQ, tmK, tmV, tmO, p);
+    CU_TRY(cudaGetLastError());
+    c.sdtc_epoch ^= 1;
+    c.sdtc_prev_bh = (int)BH;
+    g_launches.fetch_add(1);
+    t_last_path = "splitd_tc";
+    return B200ATTN_OK;
+}
+
 // ---- validation + dispatch ----------------------------------------------------------------------
 static int validate(const b200attn_args *a, int *rd_out, float *base_out) {
     if (a == nullptr) return fail(B200ATTN_ERR_INVALID_ARG, "args is NULL");
@@ -388,6 +501,11 @@ static int forward_device(const b200attn_args *a) {
             if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
             else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
         }
+    }
+    if (!done && !(a->flags & (B200ATTN_FLAG_FORCE_GENERIC | B200ATTN_FLAG_FORCE_TWO_PASS))) {
+        rc = run_sdtc(*c, *a, st);
+        if (rc == B200ATTN_OK) done = true;
+        else if (rc != -1) return rc;
     }
     if (!done) {
         rc = (a->dtype == B200ATTN_F32) ? run_splitd<float>(*c, *a, rd, base, st) : run_splitd<__nv_bfloat16>(*c, *a, rd, base, st);
@@ -489,6 +607,11 @@ int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
     if (rc) return fail(rc, "%s", tc_bf16_error());
     return check_kernel_errors(*c, (cudaStream_t)a->stream, true);
 }
+
+#ifdef B200ATTN_DEVTOOLS
+void b200attn_debug_sdtc_dump(float *dev_buf) { g_sdtc_dbg = dev_buf; }
+void b200attn_debug_sdtc_stamps(unsigned long long *dev_buf) { g_sdtc_stamps = dev_buf; }
+#endif
 
 #ifdef B200ATTN_SD_PROFILE
 int b200attn_debug_sd_stamps(unsigned long long *out, int n) {
@@ -702,6 +825,9 @@ void b200attn_release_workspace(void) {
         c.S = nullptr; c.S_bytes = 0;
         if (c.counters) cudaFree(c.counters);
         c.counters = nullptr; c.counters_n = 0;
+        if (c.sdtc_S) cudaFree(c.sdtc_S);
+        if (c.sdtc_cnt) cudaFree(c.sdtc_cnt);
+        c.sdtc_S = nullptr; c.sdtc_cnt = nullptr; c.sdtc_cap = 0; c.sdtc_epoch = 0; c.sdtc_prev_bh = 0;
         for (int i = 0; i < 8; ++i) { if (c.stage[i]) cudaFree(c.stage[i]); c.stage[i] = nullptr; c.stage_bytes[i] = 0; }
         c.tc_tables.release();
         c.tcw.release();

@@ -1,0 +1,423 @@
+// fp32 attention forward for short sequences (len_q, len_k <= 64) and wide heads on the tensor cores:
+// the split-head_d decomposition of splitd.cuh (a CTA owns a column slice of Q, K and V of one head,
+// every input byte is read from HBM once) with both contractions done by tcgen05.mma.kind::tf32 on
+// error-compensated operands, so that the result keeps fp32 accuracy.
+//
+// An fp32 value x is split into hi = x with the low 13 mantissa bits cleared (exactly representable
+// as tf32) and the residual lo = x - hi (exact in fp32, at most 13 significant bits, of which the
+// tensor core keeps 11).  A product a*b is taken as hi_a*hi_b + hi_a*lo_b + lo_a*hi_b with fp32
+// accumulation; the dropped term lo_a*lo_b is below 2^-22 |a b|.  (Replaces the scalar loops of the
+// reference kernel, final/attention.cu:120-142 and :169-181; the reference's own arithmetic is fp32
+// FMA, and the result here agrees with it to a few 1e-7.)
+//
+//   load      Q and K slices arrive by TMA one 32-column "atom" (128 bytes per row, 128-byte
+//             swizzle: the K-major operand layout of the MMA) at a time through a ring of stages;
+//             the V slice arrives as [keys x 32 columns] slabs with the 128-byte swizzle on 32-byte
+//             units, which is the MN-major operand layout of 32-bit elements.
+//   split     six warps rewrite each landed atom as hi (in place) and lo (next to it);
+//   scores    one thread issues, per 8 columns, S[64 x 128] = Qhi [Khi;Klo]^T and S[:, 0:64] += Qlo Khi^T
+//             (M = 64: the accumulator row r sits in tensor-memory lane 32*(r/16) + r%16);
+//   reduce    the partial scores of the slices of a head are summed in an L2-resident scratch with
+//             16-byte vector reductions; a per-head arrival counter tells when the sum is complete.
+//             The grid holds at most one CTA per SM, so all slices of a head are resident together;
+//             the wait is bounded all the same and reports an error instead of hanging.
+//   softmax   every slice CTA reads the 64 x 64 scores back, one warp per row (shuffle max / sum), and
+//             writes P as hi and lo in the K-major operand layout;
+//   output    O[:, slice] = Phi Vhi + Phi Vlo + Plo Vhi (N = slice width), read from tensor memory into
+//             a swizzled staging tile and written by TMA stores.
+//
+// The scratch is double-buffered by call parity: a call sums into buffer `epoch` and clears the part
+// of buffer `1 - epoch` that the next call will use, so nothing has to be cleaned on the critical path.
+#pragma once
+
+#include "tc_common.cuh"
+
+namespace b200attn {
+
+constexpr int ST_THREADS = 256;        // warp 0: TMA + arrival counter, warp 1: MMA, warps 2-7: split, warps 4-7: score read-out
+constexpr int ST_SPLIT_THREADS = 192;
+constexpr int ST_ATOM = 32;            // fp32 columns in a 128-byte swizzled row
+constexpr int ST_SLAB = 64 * 128;      // [64 rows x 128 B]
+constexpr int ST_STAGE = 4 * ST_SLAB;  // Q hi | Q lo | K hi | K lo
+constexpr int ST_MAX_ATOMS = 8;        // widest slice: 256 columns (one MMA N; V hi + V lo + ring fit 227 KB)
+constexpr int ST_MAX_STAGES = 3;
+constexpr int ST_TMEM_COLS = 256;
+
+struct SdtcParams {
+    long long BH;
+    int Lq, Lk, D;
+    int apc;                 // atoms per slice
+    int natoms;              // ceil(D / 32)
+    int nsplit;              // slices per head
+    int nst;                 // ring depth, min(apc, ST_MAX_STAGES)
+    int epoch;               // 0 / 1: which half of the scratch this call sums into
+    float scale;
+    float *S;                // [2][cap_bh][64][64] partial-score sums; all zero outside the heads in use
+    unsigned *counters;      // [2][cap_bh] slices of the head that have added their scores
+    int cap_bh;              // heads each half of the scratch has room for
+    int zero_bh;             // heads the previous call on this device left non-zero in half 1 - epoch
+    unsigned *err, *err_sys;
+    unsigned spin_limit;
+    unsigned wait_extra;     // 0; a test makes the head wait for arrivals that never come
+#ifdef B200ATTN_DEVTOOLS
+    float *dbg;              // bring-up dump of CTA (0, 0): see the ST_DBG sites
+    unsigned long long *stamps;   // [CTAs][16] globaltimer at the ST_STAMP sites
+#endif
+};
+
+struct StBars {
+    uint64_t full[ST_MAX_STAGES], ready[ST_MAX_STAGES], empty[ST_MAX_STAGES];
+    uint64_t v_full, s_full, s_pub, o_full;
+};
+
+inline size_t sdtc_smem_bytes(int apc, int nst) { return (size_t)2 * apc * ST_SLAB + (size_t)nst * ST_STAGE + 1024; }
+
+// x -> (x with the low 13 mantissa bits cleared, the exact remainder)
+__device__ __forceinline__ void st_split4(const float4 x, float4 &hi, float4 &lo) {
+    hi.x = __uint_as_float(__float_as_uint(x.x) & 0xffffe000u); lo.x = x.x - hi.x;
+    hi.y = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u); lo.y = x.y - hi.y;
+    hi.z = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u); lo.z = x.z - hi.z;
+    hi.w = __uint_as_float(__float_as_uint(x.w) & 0xffffe000u); lo.w = x.w - hi.w;
+}
+
+// byte offset of fp32 element (row, col) of a [64 rows x 32 columns] slab in the 128-byte swizzle
+__device__ __forceinline__ uint32_t st_swz(int row, int col) {
+    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 2) ^ (row & 7)) << 4)) + (col & 3) * 4);
+}
+
+#ifdef B200ATTN_DEVTOOLS
+#define ST_DBG(slot, expr) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) { expr; } } while (0)
+#define ST_STAMP(k) do { if (p.stamps) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+    p.stamps[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16 + (k)] = t_; } } while (0)
+#else
+#define ST_DBG(slot, expr)
+#define ST_STAMP(k)
+#endif
+
+#define ST_FAIL_AT(site, cond)                                                                       \
+    if (cond) {                                                                                      \
+        report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << (7 + (site))));   \
+        *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;                                        \
+        failed = true;                                                                               \
+        break;                                                                                       \
+    }
+
+__global__ void __launch_bounds__(ST_THREADS, 1)
+sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+            const __grid_constant__ CUtensorMap tmO, const SdtcParams p) {
+    extern __shared__ unsigned char st_smem_raw[];
+    if (threadIdx.x == 0) ST_STAMP(0);
+    __shared__ StBars bars;
+    __shared__ uint32_t tmem_slot;
+    __shared__ unsigned s_fail;
+    const uint32_t raw_addr = smem_u32(st_smem_raw);
+    unsigned char *smem = st_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slice = blockIdx.x;
+    const long long bh = blockIdx.y;
+    const int Lq = p.Lq, Lk = p.Lk, nst = p.nst;
+    const int a0 = slice * p.apc;
+    const int nat = min(p.apc, p.natoms - a0);   // >= 1 by construction of the grid
+    const int kpad = (Lk + 7) & ~7;              // keys covered by the P V contraction (8 per MMA)
+    const uint32_t lim = p.spin_limit;
+
+    unsigned char *v_hi = smem;                                  // nat slabs [keys x 32 columns]
+    unsigned char *v_lo = smem + (size_t)p.apc * ST_SLAB;
+    unsigned char *ring = smem + (size_t)2 * p.apc * ST_SLAB;    // nst stages
+    unsigned char *p_hi = ring;                                  // after the score MMAs: P, two atoms of 32 keys
+    unsigned char *p_lo = ring + 2 * ST_SLAB;
+    unsigned char *o_stage = v_hi;                               // after the P V MMAs: output slabs
+
+    float *S_cur = p.S + ((size_t)p.epoch * p.cap_bh + bh) * 4096;
+    unsigned *cnt_cur = p.counters + (size_t)p.epoch * p.cap_bh + bh;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < ST_MAX_STAGES; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.ready[i], 6); mbar_init(&bars.empty[i], 1); }
+        mbar_init(&bars.v_full, 1);
+        mbar_init(&bars.s_full, 1);
+        mbar_init(&bars.s_pub, 4);
+        mbar_init(&bars.o_full, 1);
+        s_fail = 0u;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, ST_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    bool failed = false;
+    if (threadIdx.x == 0) ST_STAMP(1);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- loads: the first ring fill, then V, then the remaining atoms as stages come free ----
+            const int first = min(nst, nat);
+            for (int c = 0; c < nat; ++c) {
+                const int s = c % nst;
+                ST_FAIL_AT(0, !mbar_wait(&bars.empty[s], ((c / nst) & 1) ^ 1, lim));
+                unsigned char *st = ring + (size_t)s * ST_STAGE;
+                mbar_expect_tx(&bars.full[s], (uint32_t)(Lq + Lk) * 128u);
+                tma_load_2d(st, &tmQ, (a0 + c) * ST_ATOM, (int)(bh * Lq), &bars.full[s]);
+                tma_load_2d(st + 2 * ST_SLAB, &tmK, (a0 + c) * ST_ATOM, (int)(bh * Lk), &bars.full[s]);
+                if (c == first - 1) {
+                    mbar_expect_tx(&bars.v_full, (uint32_t)nat * (uint32_t)Lk * 128u);
+                    for (int a = 0; a < nat; ++a) tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, (a0 + a) * ST_ATOM, (int)(bh * Lk), &bars.v_full);
+                }
+            }
+            // ---- arrival: the four read-out warps have added this slice's scores and fenced ----
+            do {
+                if (failed) break;
+                ST_FAIL_AT(1, !mbar_wait(&bars.s_pub, 0, lim));
+                ST_STAMP(6);
+                __threadfence();
+                atomicAdd(cnt_cur, 1u);
+                const unsigned want = (unsigned)p.nsplit + p.wait_extra;
+                unsigned seen = 0;
+                for (unsigned it = 0; it < lim; ++it) {
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt_cur) : "memory");
+                    if (seen >= want) break;
+                    __nanosleep(20);
+                }
+                ST_STAMP(7);
+                if (seen < want) {
+                    report_kernel_error(p.err, p.err_sys, (unsigned)KERR_HEAD_BARRIER_TIMEOUT);
+                    *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
+                }
+            } while (false);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- score MMAs ----
+            const uint32_t id128 = umma_idesc_tf32(64, 128, 0, 0), id64 = umma_idesc_tf32(64, 64, 0, 0);
+            for (int c = 0; c < nat; ++c) {
+                const int s = c % nst;
+                ST_FAIL_AT(2, !mbar_wait(&bars.ready[s], (c / nst) & 1, lim));
+                tc_fence_after();
+                const uint32_t sa = smem_u32(ring + (size_t)s * ST_STAGE);
+                const uint64_t dq_hi = umma_desc_k_sw128(sa), dq_lo = umma_desc_k_sw128(sa + ST_SLAB), dk = umma_desc_k_sw128(sa + 2 * ST_SLAB);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    umma_tf32(tmem, dq_hi + 2 * k, dk + 2 * k, id128, (c | k) != 0);   // [Qhi Khi^T | Qhi Klo^T]
+                    umma_tf32(tmem, dq_lo + 2 * k, dk + 2 * k, id64, 1u);              // columns 0-63 += Qlo Khi^T
+                }
+                umma_commit(&bars.empty[s]);
+            }
+            if (!failed) umma_commit(&bars.s_full);
+        }
+    } else {
+        const int t = threadIdx.x - 64;   // 0..191
+        // ---- clear what the previous call summed into: the next call will use that half of the
+        // scratch, and nothing reads it during this call ----
+        {
+            float4 *z = reinterpret_cast<float4 *>(p.S + (size_t)(1 - p.epoch) * p.cap_bh * 4096);
+            unsigned *zc = p.counters + (size_t)(1 - p.epoch) * p.cap_bh;
+            const long long cta = bh * p.nsplit + slice, ncta = p.BH * p.nsplit, nz = (long long)p.zero_bh * 1024;
+            for (long long i = cta * ST_SPLIT_THREADS + t; i < nz; i += ncta * ST_SPLIT_THREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (cta == 0)
+                for (int i = t; i < p.zero_bh; i += ST_SPLIT_THREADS) zc[i] = 0u;
+        }
+        // ---- hi / lo split of the landed Q and K atoms ----
+        for (int c = 0; c < nat; ++c) {
+            const int s = c % nst;
+            ST_FAIL_AT(3, !mbar_wait(&bars.full[s], (c / nst) & 1, lim));
+            if (t == 0 && c == 0) ST_STAMP(2);
+            if (t == 0 && c == nat - 1) ST_STAMP(3);
+            unsigned char *st = ring + (size_t)s * ST_STAGE;
+            for (int idx = t; idx < 1024; idx += ST_SPLIT_THREADS) {
+                const int part = idx >> 9, i = idx & 511;
+                if ((i >> 3) < (part ? Lk : Lq)) {
+                    float4 *ph = reinterpret_cast<float4 *>(st + (size_t)part * 2 * ST_SLAB + (size_t)i * 16);
+                    float4 hi, lo;
+                    st_split4(*ph, hi, lo);
+                    *ph = hi;
+                    *reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(ph) + ST_SLAB) = lo;
+                }
+            }
+            ST_DBG(0, if (c == 0 && t < 64) { p.dbg[t] = reinterpret_cast<float *>(st)[t]; p.dbg[64 + t] = reinterpret_cast<float *>(st + ST_SLAB)[t];
+                                              p.dbg[128 + t] = reinterpret_cast<float *>(st + 2 * ST_SLAB)[t]; p.dbg[192 + t] = reinterpret_cast<float *>(st + 3 * ST_SLAB)[t]; });
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.ready[s]);
+        }
+        failed = __any_sync(0xffffffffu, failed);   // the collective tensor-memory loads below need whole warps
+        // ---- read-out of the partial scores (warps 4-7: one tensor-memory lane quadrant each) ----
+        if (warp >= 4 && !failed) {
+            do {
+                ST_FAIL_AT(4, !mbar_wait(&bars.s_full, 0, lim));
+                if (threadIdx.x == 128) ST_STAMP(4);
+                tc_fence_after();
+                const int q = warp & 3;
+                const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
+                const int row = 16 * q + lane;
+                float *srow = S_cur + (size_t)row * 64;
+                uint32_t r0[32], r1[32];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    tmem_ld32(ta + hh * 32, r0);        // Qhi Khi^T + Qlo Khi^T
+                    tmem_ld32(ta + 64 + hh * 32, r1);   // Qhi Klo^T
+                    tmem_ld_wait();
+                    ST_DBG(1, if (warp == 4 && hh == 0 && lane < 2) { for (int j = 0; j < 32; ++j) { p.dbg[256 + lane * 64 + j] = __uint_as_float(r0[j]); p.dbg[256 + lane * 64 + 32 + j] = __uint_as_float(r1[j]); } });
+                    if (lane < 16 && row < Lq) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            red_add_v4(srow + hh * 32 + j, __uint_as_float(r0[j]) + __uint_as_float(r1[j]),
+                                       __uint_as_float(r0[j + 1]) + __uint_as_float(r1[j + 1]),
+                                       __uint_as_float(r0[j + 2]) + __uint_as_float(r1[j + 2]),
+                                       __uint_as_float(r0[j + 3]) + __uint_as_float(r1[j + 3]));
+                    }
+                }
+                if (threadIdx.x == 128) ST_STAMP(5);
+                __threadfence();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.s_pub);
+            } while (false);
+        }
+        // ---- hi / lo split of V; key rows [Lk, kpad) enter the contraction and must be zero ----
+        if (!failed) {
+            do {
+                ST_FAIL_AT(5, !mbar_wait(&bars.v_full, 0, lim));
+                if (t == 0) ST_STAMP(8);
+                for (int idx = t; idx < nat * 512; idx += ST_SPLIT_THREADS) {
+                    const int slab = idx >> 9, i = idx & 511, row = i >> 3;
+                    if (row < kpad) {
+                        float4 *ph = reinterpret_cast<float4 *>(v_hi + (size_t)slab * ST_SLAB + (size_t)i * 16);
+                        float4 hi = make_float4(0.f, 0.f, 0.f, 0.f), lo = hi;
+                        if (row < Lk) st_split4(*ph, hi, lo);
+                        *ph = hi;
+                        *reinterpret_cast<float4 *>(v_lo + (size_t)slab * ST_SLAB + (size_t)i * 16) = lo;
+                    }
+                }
+                fence_proxy_async_smem();
+            } while (false);
+        }
+    }
+    if (threadIdx.x == 64) ST_STAMP(9);
+    __syncthreads();   // the head's scores are complete (or the wait gave up); V is split
+    if (threadIdx.x == 0) ST_STAMP(10);
+    failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
+
+    // ---- softmax of the head's scores, one warp per row; P written as hi / lo operand tiles ----
+    if (!failed) {
+        constexpr int RPW = 8;
+        float s0[RPW], s1[RPW];
+#pragma unroll
+        for (int k = 0; k < RPW; ++k) {
+            const int i = warp + 8 * k;
+            s0[k] = -INFINITY; s1[k] = -INFINITY;
+            if (i < Lq) {
+                if (lane < Lk) s0[k] = __ldcg(S_cur + (size_t)i * 64 + lane);
+                if (lane + 32 < Lk) s1[k] = __ldcg(S_cur + (size_t)i * 64 + lane + 32);
+            }
+        }
+        float mx[RPW], e0[RPW], e1[RPW], tot[RPW];
+#pragma unroll
+        for (int k = 0; k < RPW; ++k) {
+            s0[k] *= p.scale; s1[k] *= p.scale;
+            mx[k] = fmaxf(s0[k], s1[k]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int k = 0; k < RPW; ++k) mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+#pragma unroll
+        for (int k = 0; k < RPW; ++k) {
+            const int i = warp + 8 * k;
+            e0[k] = (i < Lq && lane < Lk) ? __expf(s0[k] - mx[k]) : 0.0f;   // arguments are <= 0: 2 ulp
+            e1[k] = (i < Lq && lane + 32 < Lk) ? __expf(s1[k] - mx[k]) : 0.0f;
+            tot[k] = e0[k] + e1[k];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int k = 0; k < RPW; ++k) tot[k] += __shfl_xor_sync(0xffffffffu, tot[k], o);
+#pragma unroll
+        for (int k = 0; k < RPW; ++k) {
+            const int i = warp + 8 * k;
+            if (i < Lq) {
+                const float inv = __frcp_rn(tot[k]);
+                const uint32_t off = st_swz(i, lane);
+                if (lane < kpad) {
+                    const float pv = e0[k] * inv, ph = __uint_as_float(__float_as_uint(pv) & 0xffffe000u);
+                    *reinterpret_cast<float *>(p_hi + off) = ph;
+                    *reinterpret_cast<float *>(p_lo + off) = pv - ph;
+                }
+                if (lane + 32 < kpad) {
+                    const float pv = e1[k] * inv, ph = __uint_as_float(__float_as_uint(pv) & 0xffffe000u);
+                    *reinterpret_cast<float *>(p_hi + ST_SLAB + off) = ph;
+                    *reinterpret_cast<float *>(p_lo + ST_SLAB + off) = pv - ph;
+                }
+            }
+        }
+        fence_proxy_async_smem();
+        ST_DBG(2, if (warp == 0) { p.dbg[384 + lane] = s0[0]; p.dbg[416 + lane] = s1[0]; p.dbg[448 + lane] = e0[0] / tot[0]; p.dbg[480 + lane] = e1[0] / tot[0]; });
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    ST_DBG(3, if (threadIdx.x < 64) { p.dbg[512 + threadIdx.x] = reinterpret_cast<float *>(p_hi)[threadIdx.x]; p.dbg[576 + threadIdx.x] = reinterpret_cast<float *>(v_hi)[threadIdx.x];
+                                      p.dbg[640 + threadIdx.x] = reinterpret_cast<float *>(v_lo)[threadIdx.x]; });
+
+    if (threadIdx.x == 0) ST_STAMP(11);
+    // ---- O[:, slice] = P V ----
+    if (warp == 1 && lane == 0 && !failed) {
+        const uint32_t idv = umma_idesc_tf32(64, nat * ST_ATOM, 0, 1);
+        const int ksteps = kpad >> 3;
+        for (int kk = 0; kk < ksteps; ++kk) {
+            const uint64_t dp_hi = umma_desc_k_sw128(smem_u32(p_hi + (size_t)(kk >> 2) * ST_SLAB)) + 2 * (kk & 3);
+            const uint64_t dp_lo = umma_desc_k_sw128(smem_u32(p_lo + (size_t)(kk >> 2) * ST_SLAB)) + 2 * (kk & 3);
+            const uint64_t dv_hi = umma_desc_mn_sw128_32b(smem_u32(v_hi + (size_t)kk * 1024), ST_SLAB, 512);
+            const uint64_t dv_lo = umma_desc_mn_sw128_32b(smem_u32(v_lo + (size_t)kk * 1024), ST_SLAB, 512);
+            umma_tf32(tmem, dp_hi, dv_hi, idv, kk != 0);
+            umma_tf32(tmem, dp_hi, dv_lo, idv, 1u);
+            umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
+        }
+        umma_commit(&bars.o_full);
+    }
+    if (!failed) {
+        do {
+            ST_FAIL_AT(6, !mbar_wait(&bars.o_full, 0, lim));
+            if (threadIdx.x == 0) ST_STAMP(12);
+            tc_fence_after();
+            // warp w reads lane quadrant w % 4 (rows 16 (w % 4) .. + 15 in its lanes 0-15), every second slab
+            const int q = warp & 3, row = 16 * q + lane;
+            const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
+            uint32_t r[32];
+            for (int a = warp >> 2; a < nat; a += 2) {
+                tmem_ld32(ta + a * ST_ATOM, r);
+                tmem_ld_wait();
+                ST_DBG(4, if (warp == 0 && a == 0 && lane < 2) { for (int j = 0; j < 32; ++j) p.dbg[704 + lane * 32 + j] = __uint_as_float(r[j]); });
+                if (lane < 16) {
+                    unsigned char *dst = o_stage + (size_t)a * ST_SLAB + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4 *>(dst + ((c ^ (row & 7)) << 4)) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                }
+            }
+            fence_proxy_async_smem();
+        } while (false);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
+    if (threadIdx.x == 0) ST_STAMP(13);
+    if (threadIdx.x == 0 && !failed) {
+        for (int a = 0; a < nat; ++a) tma_store_2d(&tmO, o_stage + (size_t)a * ST_SLAB, (a0 + a) * ST_ATOM, (int)(bh * Lq));
+        tma_store_commit();
+        tma_store_wait_all();
+        ST_STAMP(14);
+    }
+    if (failed && threadIdx.x == 0) {
+        // never leave while this CTA's own bulk copies or MMAs may still be in flight
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, ST_TMEM_COLS);
+    if (threadIdx.x == 32) ST_STAMP(15);
+}
+
+#undef ST_FAIL_AT
+
+}  // namespace b200attn

@@ -137,6 +137,15 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t saddr, uint32_t 
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
+// MN-major operand tile of 32-bit elements (tf32): the only swizzled layout the tensor core takes for
+// it is the 128-byte swizzle on 32-byte units (layout type 1; what TMA writes with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B): 32 MN-elements (128 B) contiguous per K row, the 32-byte
+// quarter q of K row r stored at quarter q ^ (r % 4), groups of 4 K rows `sbo_bytes` apart, the next
+// 32 MN-elements `lbo_bytes` further.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128_32b(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)1 << 61);
+}
 // Instruction descriptor, kind::f16 with bf16 operands and fp32 accumulation: D format fp32 (bits
 // [4,6) = 1), A/B format bf16 (bits [7,10) and [10,13) = 1), major bits 15/16 (0 = K-major,
 // 1 = MN-major), N >> 3 in [17,23), M >> 4 in [24,29).
@@ -156,6 +165,36 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
 // The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// ---- the same for kind::tf32: fp32 containers of which the tensor core uses sign, exponent and the upper
+// ten mantissa bits; fp32 accumulation.  A/B format code 2 (bits [7,10) and [10,13)); K = 8 per
+// instruction (32 bytes of a K-major row, one 8-row group of an MN-major tile). ----
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// ---- TMA tiled store shared -> global (bulk async-group completion) ---------------------------------
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *tmap, const void *smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(smem_u32(smem_src)),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Four fp32 additions to global memory in one L2 operation (16-byte aligned address).
+__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
+    asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 // ---- the same for a pair of CTAs working as one (cta_group::2): both CTAs of a 2-CTA cluster allocate

@@ -1,4 +1,4 @@
-"""Failure detection on the device, without faulting anything: the per-head barrier of the fused
+"""Failure detection on the device, without faulting anything: the per-head barrier of the
 split-head_d kernel is made to wait (with a short limit) for an arrival that never comes.  The
 kernel gives up, reports its error bits, the call returns B200ATTN_ERR_KERNEL, and the next call on
 the same context cleans the scratch and is correct again."""
@@ -30,7 +30,7 @@ def test_lost_arrival_is_reported_and_the_context_recovers(pkg, cuda):
     L = pkg.lib()
     q, k, v, want = _case(7)
     assert np.abs(_run(pkg, q, k, v) - want).max() <= 1e-4
-    assert pkg.last_path() == "splitd_fused"
+    assert pkg.last_path() == "splitd_tc"
     L.b200attn_debug_lost_arrival(1, 20000)
     try:
         with pytest.raises(pkg.B200AttnError) as ei:

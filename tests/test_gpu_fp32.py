@@ -45,6 +45,13 @@ def test_benchmark_configs_fused_and_two_pass(pkg, cuda, shape):
     want = ol.attention(Q, K, V)
     q, k, v = (to_dev(x, cuda) for x in (Q, K, V))
     got = pkg.forward(q, k, v).cpu().numpy()
+    assert pkg.last_path() == "splitd_tc"
+    res = ol.compare(got, want)
+    assert res["ok"] and res["max_abs"] <= 5e-6, res   # error-compensated tf32 keeps fp32 accuracy
+    # twice more: both halves of the double-buffered score scratch, each cleared by the call before
+    for _ in range(2):
+        assert ol.compare(pkg.forward(q, k, v).cpu().numpy(), want)["ok"]
+    got = pkg.forward(q, k, v, flags=pkg.FLAG_FORCE_GENERIC).cpu().numpy()
     assert pkg.last_path() == "splitd_fused"
     assert ol.compare(got, want)["ok"], ol.compare(got, want)
     got2 = pkg.forward(q, k, v, flags=pkg.FLAG_FORCE_TWO_PASS).cpu().numpy()
@@ -55,7 +62,8 @@ def test_benchmark_configs_fused_and_two_pass(pkg, cuda, shape):
     assert ol.compare(got3, want)["ok"]
 
 
-@pytest.mark.parametrize("shape", [(1, 4, 64, 64, 2048), (1, 4, 64, 64, 512), (1, 4, 32, 64, 4096)])
+@pytest.mark.parametrize("shape", [(1, 4, 64, 64, 2048), (1, 4, 64, 64, 512), (1, 4, 64, 64, 4096), (1, 4, 64, 64, 8192),
+                                   (1, 4, 32, 64, 4096)])
 def test_against_the_reference_gpu_kernel(pkg, cuda, shape):
     """The reference's own kernel (compiled from the reference tree into oracle/_ref) on the same GPU."""
     import torch
@@ -83,6 +91,35 @@ def test_positional_encodings_all_kinds(pkg, cuda, pe, rd, shape):
     got = pkg.forward(to_dev(Q, cuda), to_dev(K, cuda), to_dev(V, cuda), pe=pe, rotary_dim=rd).cpu().numpy()
     res = ol.compare(got, want)
     assert res["ok"], (pkg.last_path(), res)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1, 8), (1, 1, 64, 64, 32), (1, 3, 17, 23, 100), (2, 5, 7, 64, 36), (1, 148, 16, 16, 64),
+                                   (1, 2, 33, 9, 1028), (1, 37, 64, 64, 1024), (1, 1, 64, 64, 16384), (1, 1, 16, 16, 32768),
+                                   (2, 4, 64, 40, 4096), (1, 8, 5, 3, 2052)])
+def test_tensor_core_split_path_ragged_shapes(pkg, cuda, shape):
+    """fp32 on the tensor cores: ragged lengths (rows beyond len are never loaded; key rows up to the next
+    multiple of 8 are zero-filled), head_d that is not a multiple of 32 (zero-filled columns), one slice
+    per head up to all SMs on one head, and the extreme head_d of kernels/attention_kernel_ultra_large.cu:414-419."""
+    B, H, Lq, Lk, D = shape
+    Q, K, V = ol.make_qkv(B, H, Lq, Lk, D, 50, "uniform")
+    want = ol.attention(Q, K, V)
+    q, k, v = (to_dev(x, cuda) for x in (Q, K, V))
+    for rep in range(2):
+        got = pkg.forward(q, k, v).cpu().numpy()
+        assert pkg.last_path() == "splitd_tc", shape
+        res = ol.compare(got, want)
+        assert res["ok"] and res["max_abs"] <= 5e-6, (shape, rep, res)
+
+
+def test_tensor_core_split_path_changing_head_counts(pkg, cuda):
+    """Consecutive calls with different numbers of heads: each call clears what the previous one left in
+    the other half of the score scratch, however many heads that was."""
+    for (B, H, L, D) in [(1, 40, 64, 256), (1, 3, 64, 2048), (1, 100, 32, 128), (1, 1, 64, 4096), (1, 100, 32, 128), (1, 40, 64, 256)]:
+        Q, K, V = ol.make_qkv(B, H, L, L, D, 51, "uniform")
+        got = pkg.forward(to_dev(Q, cuda), to_dev(K, cuda), to_dev(V, cuda)).cpu().numpy()
+        assert pkg.last_path() == "splitd_tc"
+        res = ol.compare(got, ol.attention(Q, K, V))
+        assert res["ok"] and res["max_abs"] <= 5e-6, ((B, H, L, D), res)
 
 
 def test_rope_with_caller_supplied_caches_and_hybrid_entry(pkg, cuda):
