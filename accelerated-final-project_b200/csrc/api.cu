@@ -106,6 +106,11 @@ struct DeviceCtx {
     int sdtc_prev_bh = 0;          // heads the last call left non-zero in the other half
     bool sdtc_attr = false;
     size_t sdtc_smem_max = 0;
+    // the last enqueued call, when it was this kernel: a following call that is declared independent of it
+    // (b200attn_forward_many) may be launched as its programmatic dependent
+    bool prev_sdtc = false;
+    cudaStream_t prev_stream = nullptr;
+    uintptr_t prev_out_lo = 0, prev_out_hi = 0;
     TmapCache tmaps;
     TcTables tc_tables;            // positional-encoding tables of the tensor-core path
     TcwScratch tcw;                // scratch of the wide-head tensor-core path
@@ -353,7 +358,7 @@ static unsigned long long *g_sdtc_stamps = nullptr;
 // Slices are whole 32-column atoms; a head gets as many slices as the SM count allows.  Returns -1 when
 // the shape belongs to the CUDA-core kernels (an encoding, an odd head_d, more heads than SMs, a slice
 // wider than 256 columns).
-static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st) {
+static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool independent_of_prev) {
     const long long BH = (long long)a.batch_sz * a.num_heads;
     const int Lq = a.len_q, Lk = a.len_k, D = a.head_d;
     if (a.dtype != B200ATTN_F32 || a.pe != B200ATTN_PE_NONE || Lq > 64 || Lk > 64 || D % 4 != 0) return -1;
@@ -364,7 +369,17 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st) {
     const int apc = (natoms + slots - 1) / slots;
     if (apc > ST_MAX_ATOMS) return -1;
     const int nsplit = (natoms + apc - 1) / apc;
-    const int nst = apc < ST_MAX_STAGES ? apc : ST_MAX_STAGES;
+    // Overlap with the previous call: this call's inputs must not be that call's output.  Two CTAs
+    // share an SM only below half of its shared memory, so the ring is shortened where that makes it fit
+    // (the loads of this call then run under the tail of the previous one).
+    const size_t in_q = (size_t)BH * Lq * D * 4, in_k = (size_t)BH * Lk * D * 4;
+    auto hits_prev_out = [&](const void *ptr, size_t n) { return (uintptr_t)ptr < c.prev_out_hi && (uintptr_t)ptr + n > c.prev_out_lo; };
+    const bool overlap = independent_of_prev && c.prev_sdtc && c.prev_stream == st && !c.scratch_dirty &&
+                         !hits_prev_out(a.Q, in_q) && !hits_prev_out(a.K, in_k) && !hits_prev_out(a.V, in_k);
+    int nst = apc < ST_MAX_STAGES ? apc : ST_MAX_STAGES;
+    if (overlap && apc <= 4) {
+        while (nst > 1 && sdtc_smem_bytes(apc, nst) > (size_t)112 * 1024) --nst;
+    }
     const size_t smem = sdtc_smem_bytes(apc, nst);
     if (!c.sdtc_attr) {
         cudaFuncAttributes fa;
@@ -407,10 +422,23 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st) {
     p.dbg = g_sdtc_dbg;
     p.stamps = g_sdtc_stamps;
 #endif
-    sdtc_kernel<<<dim3((unsigned)nsplit, (unsigned)BH), ST_THREADS, smem, st>>>(tmQ, tmK, tmV, tmO, p);
-    CU_TRY(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)nsplit, (unsigned)BH);
+    cfg.blockDim = dim3(ST_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CU_TRY(cudaLaunchKernelEx(&cfg, sdtc_kernel, tmQ, tmK, tmV, tmO, p));
     c.sdtc_epoch ^= 1;
     c.sdtc_prev_bh = (int)BH;
+    c.prev_sdtc = true;
+    c.prev_stream = st;
+    c.prev_out_lo = (uintptr_t)a.out;
+    c.prev_out_hi = (uintptr_t)a.out + in_q;
     g_launches.fetch_add(1);
     t_last_path = "splitd_tc";
     return B200ATTN_OK;
@@ -466,7 +494,7 @@ static int check_kernel_errors(DeviceCtx &c, cudaStream_t st, bool sync) {
     return report_kernel_errors(c, "kernel");
 }
 
-static int forward_device(const b200attn_args *a) {
+static int forward_device(const b200attn_args *a, bool independent_of_prev = false) {
     int rd; float base;
     int rc = validate(a, &rd, &base);
     if (rc) return rc;
@@ -481,6 +509,8 @@ static int forward_device(const b200attn_args *a) {
         return report_kernel_errors(*c, "an earlier asynchronous call");
     }
     bool done = false;
+    const bool chain = independent_of_prev && c->prev_sdtc;
+    c->prev_sdtc = false;   // set again by the kernel that supports being overlapped
     // bf16 on the tensor cores: the two-kernel path (scores, then P V) takes every shape it supports;
     // the one-kernel cluster pipeline takes the rest of its own shapes (and all of them when
     // B200ATTN_TC_PREFER_PAIR is set: the two are measured against each other that way).
@@ -503,7 +533,9 @@ static int forward_device(const b200attn_args *a) {
         }
     }
     if (!done && !(a->flags & (B200ATTN_FLAG_FORCE_GENERIC | B200ATTN_FLAG_FORCE_TWO_PASS))) {
-        rc = run_sdtc(*c, *a, st);
+        c->prev_sdtc = chain;
+        rc = run_sdtc(*c, *a, st, independent_of_prev);
+        if (rc != B200ATTN_OK) c->prev_sdtc = false;
         if (rc == B200ATTN_OK) done = true;
         else if (rc != -1) return rc;
     }
@@ -629,7 +661,8 @@ int b200attn_debug_tc_prof(unsigned long long *out32, int reset) {
 int b200attn_forward_many(const b200attn_args *args, int n) {
     if (args == nullptr || n < 0) return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_many: NULL args or negative n");
     for (int i = 0; i < n; ++i) {
-        int rc = forward_device(&args[i]);
+        // the entries are independent problems by contract: entry i may overlap the tail of entry i - 1
+        int rc = forward_device(&args[i], i > 0);
         if (rc) return rc;
     }
     return B200ATTN_OK;

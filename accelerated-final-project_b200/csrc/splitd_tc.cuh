@@ -53,7 +53,7 @@ struct SdtcParams {
     int epoch;               // 0 / 1: which half of the scratch this call sums into
     float scale;
     float *S;                // [2][cap_bh][64][64] partial-score sums; all zero outside the heads in use
-    unsigned *counters;      // [2][cap_bh] slices of the head that have added their scores
+    unsigned *counters;      // [2][cap_bh] read-out warps (four per slice) that have added their scores
     int cap_bh;              // heads each half of the scratch has room for
     int zero_bh;             // heads the previous call on this device left non-zero in half 1 - epoch
     unsigned *err, *err_sys;
@@ -61,13 +61,13 @@ struct SdtcParams {
     unsigned wait_extra;     // 0; a test makes the head wait for arrivals that never come
 #ifdef B200ATTN_DEVTOOLS
     float *dbg;              // bring-up dump of CTA (0, 0): see the ST_DBG sites
-    unsigned long long *stamps;   // [CTAs][16] globaltimer at the ST_STAMP sites
+    unsigned long long *stamps;   // [CTAs][32] globaltimer at the ST_STAMP sites
 #endif
 };
 
 struct StBars {
     uint64_t full[ST_MAX_STAGES], ready[ST_MAX_STAGES], empty[ST_MAX_STAGES];
-    uint64_t v_full, s_full, s_pub, o_full;
+    uint64_t v_full, s_full, o_full;
 };
 
 inline size_t sdtc_smem_bytes(int apc, int nst) { return (size_t)2 * apc * ST_SLAB + (size_t)nst * ST_STAGE + 1024; }
@@ -88,7 +88,7 @@ __device__ __forceinline__ uint32_t st_swz(int row, int col) {
 #ifdef B200ATTN_DEVTOOLS
 #define ST_DBG(slot, expr) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) { expr; } } while (0)
 #define ST_STAMP(k) do { if (p.stamps) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
-    p.stamps[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16 + (k)] = t_; } } while (0)
+    p.stamps[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 + (k)] = t_; } } while (0)
 #else
 #define ST_DBG(slot, expr)
 #define ST_STAMP(k)
@@ -131,15 +131,26 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     float *S_cur = p.S + ((size_t)p.epoch * p.cap_bh + bh) * 4096;
     unsigned *cnt_cur = p.counters + (size_t)p.epoch * p.cap_bh + bh;
 
+    // one thread sets the barriers up and at once issues the first ring fill and the V loads: they are
+    // in flight while the other warps allocate tensor memory and meet at the barrier below
+    const int first = min(nst, nat);
     if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
         for (int i = 0; i < ST_MAX_STAGES; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.ready[i], 6); mbar_init(&bars.empty[i], 1); }
         mbar_init(&bars.v_full, 1);
         mbar_init(&bars.s_full, 1);
-        mbar_init(&bars.s_pub, 4);
         mbar_init(&bars.o_full, 1);
         s_fail = 0u;
         mbar_fence_init();
-        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
+        for (int c = 0; c < first; ++c) {
+            unsigned char *st = ring + (size_t)c * ST_STAGE;
+            mbar_expect_tx(&bars.full[c], (uint32_t)(Lq + Lk) * 128u);
+            tma_load_2d(st, &tmQ, (a0 + c) * ST_ATOM, (int)(bh * Lq), &bars.full[c]);
+            tma_load_2d(st + 2 * ST_SLAB, &tmK, (a0 + c) * ST_ATOM, (int)(bh * Lk), &bars.full[c]);
+        }
+        mbar_expect_tx(&bars.v_full, (uint32_t)nat * (uint32_t)Lk * 128u);
+        for (int a = 0; a < nat; ++a) tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, (a0 + a) * ST_ATOM, (int)(bh * Lk), &bars.v_full);
+        tma_prefetch_desc(&tmO);
     }
     if (warp == 1) tmem_alloc(&tmem_slot, ST_TMEM_COLS);
     tc_fence_before();
@@ -148,31 +159,24 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     const uint32_t tmem = tmem_slot;
     bool failed = false;
     if (threadIdx.x == 0) ST_STAMP(1);
+    // a following call that was declared independent of this one may start its loads now
+    grid_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- loads: the first ring fill, then V, then the remaining atoms as stages come free ----
-            const int first = min(nst, nat);
-            for (int c = 0; c < nat; ++c) {
+            // ---- the remaining atoms, as ring stages come free ----
+            for (int c = first; c < nat; ++c) {
                 const int s = c % nst;
                 ST_FAIL_AT(0, !mbar_wait(&bars.empty[s], ((c / nst) & 1) ^ 1, lim));
                 unsigned char *st = ring + (size_t)s * ST_STAGE;
                 mbar_expect_tx(&bars.full[s], (uint32_t)(Lq + Lk) * 128u);
                 tma_load_2d(st, &tmQ, (a0 + c) * ST_ATOM, (int)(bh * Lq), &bars.full[s]);
                 tma_load_2d(st + 2 * ST_SLAB, &tmK, (a0 + c) * ST_ATOM, (int)(bh * Lk), &bars.full[s]);
-                if (c == first - 1) {
-                    mbar_expect_tx(&bars.v_full, (uint32_t)nat * (uint32_t)Lk * 128u);
-                    for (int a = 0; a < nat; ++a) tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, (a0 + a) * ST_ATOM, (int)(bh * Lk), &bars.v_full);
-                }
             }
-            // ---- arrival: the four read-out warps have added this slice's scores and fenced ----
-            do {
-                if (failed) break;
-                ST_FAIL_AT(1, !mbar_wait(&bars.s_pub, 0, lim));
-                ST_STAMP(6);
-                __threadfence();
-                atomicAdd(cnt_cur, 1u);
-                const unsigned want = (unsigned)p.nsplit + p.wait_extra;
+            // ---- the head's scores are complete when every read-out warp of every slice has arrived ----
+            if (!failed) {
+                grid_dependency_wait();
+                const unsigned want = 4u * (unsigned)p.nsplit + p.wait_extra;
                 unsigned seen = 0;
                 for (unsigned it = 0; it < lim; ++it) {
                     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt_cur) : "memory");
@@ -184,7 +188,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     report_kernel_error(p.err, p.err_sys, (unsigned)KERR_HEAD_BARRIER_TIMEOUT);
                     *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
                 }
-            } while (false);
+            }
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -193,6 +197,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             for (int c = 0; c < nat; ++c) {
                 const int s = c % nst;
                 ST_FAIL_AT(2, !mbar_wait(&bars.ready[s], (c / nst) & 1, lim));
+                if (c == nat - 1) ST_STAMP(18);
                 tc_fence_after();
                 const uint32_t sa = smem_u32(ring + (size_t)s * ST_STAGE);
                 const uint64_t dq_hi = umma_desc_k_sw128(sa), dq_lo = umma_desc_k_sw128(sa + ST_SLAB), dk = umma_desc_k_sw128(sa + 2 * ST_SLAB);
@@ -204,19 +209,10 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 umma_commit(&bars.empty[s]);
             }
             if (!failed) umma_commit(&bars.s_full);
+            ST_STAMP(19);
         }
     } else {
         const int t = threadIdx.x - 64;   // 0..191
-        // ---- clear what the previous call summed into: the next call will use that half of the
-        // scratch, and nothing reads it during this call ----
-        {
-            float4 *z = reinterpret_cast<float4 *>(p.S + (size_t)(1 - p.epoch) * p.cap_bh * 4096);
-            unsigned *zc = p.counters + (size_t)(1 - p.epoch) * p.cap_bh;
-            const long long cta = bh * p.nsplit + slice, ncta = p.BH * p.nsplit, nz = (long long)p.zero_bh * 1024;
-            for (long long i = cta * ST_SPLIT_THREADS + t; i < nz; i += ncta * ST_SPLIT_THREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (cta == 0)
-                for (int i = t; i < p.zero_bh; i += ST_SPLIT_THREADS) zc[i] = 0u;
-        }
         // ---- hi / lo split of the landed Q and K atoms ----
         for (int c = 0; c < nat; ++c) {
             const int s = c % nst;
@@ -234,9 +230,11 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     *reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(ph) + ST_SLAB) = lo;
                 }
             }
+            if (t == 0 && c == nat - 1) ST_STAMP(16);
             ST_DBG(0, if (c == 0 && t < 64) { p.dbg[t] = reinterpret_cast<float *>(st)[t]; p.dbg[64 + t] = reinterpret_cast<float *>(st + ST_SLAB)[t];
                                               p.dbg[128 + t] = reinterpret_cast<float *>(st + 2 * ST_SLAB)[t]; p.dbg[192 + t] = reinterpret_cast<float *>(st + 3 * ST_SLAB)[t]; });
             fence_proxy_async_smem();
+            if (t == 0 && c == nat - 1) ST_STAMP(17);
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.ready[s]);
         }
@@ -247,6 +245,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 ST_FAIL_AT(4, !mbar_wait(&bars.s_full, 0, lim));
                 if (threadIdx.x == 128) ST_STAMP(4);
                 tc_fence_after();
+                grid_dependency_wait();   // the scratch half summed into was cleared by the previous call
                 const int q = warp & 3;
                 const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
                 const int row = 16 * q + lane;
@@ -268,10 +267,10 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     }
                 }
                 if (threadIdx.x == 128) ST_STAMP(5);
-                __threadfence();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.s_pub);
+                // release at gpu scope, cumulative over the warp's additions (ordered before it by the warp barrier)
+                if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt_cur) : "memory");
             } while (false);
         }
         // ---- hi / lo split of V; key rows [Lk, kpad) enter the contraction and must be zero ----
@@ -292,66 +291,77 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 fence_proxy_async_smem();
             } while (false);
         }
+        // ---- clear what the previous call summed into: the next call will use that half of the
+        // scratch.  The previous call has to be over first (it may still be running when this kernel
+        // was launched as its programmatic dependent). ----
+        {
+            grid_dependency_wait();
+            float4 *z = reinterpret_cast<float4 *>(p.S + (size_t)(1 - p.epoch) * p.cap_bh * 4096);
+            unsigned *zc = p.counters + (size_t)(1 - p.epoch) * p.cap_bh;
+            const long long cta = bh * p.nsplit + slice, ncta = p.BH * p.nsplit, nz = (long long)p.zero_bh * 1024;
+            for (long long i = cta * ST_SPLIT_THREADS + t; i < nz; i += ncta * ST_SPLIT_THREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (cta == 0)
+                for (int i = t; i < p.zero_bh; i += ST_SPLIT_THREADS) zc[i] = 0u;
+        }
     }
     if (threadIdx.x == 64) ST_STAMP(9);
     __syncthreads();   // the head's scores are complete (or the wait gave up); V is split
     if (threadIdx.x == 0) ST_STAMP(10);
     failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
 
-    // ---- softmax of the head's scores, one warp per row; P written as hi / lo operand tiles ----
+    // ---- softmax of the head's scores: half a warp per row, four keys per lane (16-byte loads and
+    // stores); P written as hi / lo operand tiles ----
     if (!failed) {
-        constexpr int RPW = 8;
-        float s0[RPW], s1[RPW];
+        constexpr int RPW = 4;   // row pairs per warp: warp w owns rows [8w, 8w + 8)
+        const int cg = lane & 15, r2 = lane >> 4;
+        float4 sv[RPW];
 #pragma unroll
         for (int k = 0; k < RPW; ++k) {
-            const int i = warp + 8 * k;
-            s0[k] = -INFINITY; s1[k] = -INFINITY;
-            if (i < Lq) {
-                if (lane < Lk) s0[k] = __ldcg(S_cur + (size_t)i * 64 + lane);
-                if (lane + 32 < Lk) s1[k] = __ldcg(S_cur + (size_t)i * 64 + lane + 32);
-            }
+            const int i = 8 * warp + 2 * k + r2;
+            sv[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            if (i < Lq && 4 * cg < Lk) sv[k] = __ldcg(reinterpret_cast<const float4 *>(S_cur + (size_t)i * 64) + cg);
         }
-        float mx[RPW], e0[RPW], e1[RPW], tot[RPW];
+        float mx[RPW], tot[RPW];
 #pragma unroll
         for (int k = 0; k < RPW; ++k) {
-            s0[k] *= p.scale; s1[k] *= p.scale;
-            mx[k] = fmaxf(s0[k], s1[k]);
+            sv[k].x = (4 * cg + 0 < Lk) ? sv[k].x * p.scale : -INFINITY;
+            sv[k].y = (4 * cg + 1 < Lk) ? sv[k].y * p.scale : -INFINITY;
+            sv[k].z = (4 * cg + 2 < Lk) ? sv[k].z * p.scale : -INFINITY;
+            sv[k].w = (4 * cg + 3 < Lk) ? sv[k].w * p.scale : -INFINITY;
+            mx[k] = fmaxf(fmaxf(sv[k].x, sv[k].y), fmaxf(sv[k].z, sv[k].w));
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
+        for (int o = 8; o > 0; o >>= 1)
 #pragma unroll
             for (int k = 0; k < RPW; ++k) mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+        if (threadIdx.x == 0 && mx[0] > -1e30f) ST_STAMP(6);
 #pragma unroll
         for (int k = 0; k < RPW; ++k) {
-            const int i = warp + 8 * k;
-            e0[k] = (i < Lq && lane < Lk) ? __expf(s0[k] - mx[k]) : 0.0f;   // arguments are <= 0: 2 ulp
-            e1[k] = (i < Lq && lane + 32 < Lk) ? __expf(s1[k] - mx[k]) : 0.0f;
-            tot[k] = e0[k] + e1[k];
+            // arguments are <= 0 (2 ulp); masked keys give exp(-inf) = 0
+            sv[k].x = __expf(sv[k].x - mx[k]); sv[k].y = __expf(sv[k].y - mx[k]);
+            sv[k].z = __expf(sv[k].z - mx[k]); sv[k].w = __expf(sv[k].w - mx[k]);
+            tot[k] = (sv[k].x + sv[k].y) + (sv[k].z + sv[k].w);
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
+        for (int o = 8; o > 0; o >>= 1)
 #pragma unroll
             for (int k = 0; k < RPW; ++k) tot[k] += __shfl_xor_sync(0xffffffffu, tot[k], o);
 #pragma unroll
         for (int k = 0; k < RPW; ++k) {
-            const int i = warp + 8 * k;
-            if (i < Lq) {
+            const int i = 8 * warp + 2 * k + r2;
+            if (i < Lq && 4 * cg < kpad) {
                 const float inv = __frcp_rn(tot[k]);
-                const uint32_t off = st_swz(i, lane);
-                if (lane < kpad) {
-                    const float pv = e0[k] * inv, ph = __uint_as_float(__float_as_uint(pv) & 0xffffe000u);
-                    *reinterpret_cast<float *>(p_hi + off) = ph;
-                    *reinterpret_cast<float *>(p_lo + off) = pv - ph;
-                }
-                if (lane + 32 < kpad) {
-                    const float pv = e1[k] * inv, ph = __uint_as_float(__float_as_uint(pv) & 0xffffe000u);
-                    *reinterpret_cast<float *>(p_hi + ST_SLAB + off) = ph;
-                    *reinterpret_cast<float *>(p_lo + ST_SLAB + off) = pv - ph;
-                }
+                float4 hi, lo;
+                st_split4(make_float4(sv[k].x * inv, sv[k].y * inv, sv[k].z * inv, sv[k].w * inv), hi, lo);
+                const uint32_t off = (uint32_t)((cg >> 3) * ST_SLAB) + st_swz(i, 4 * (cg & 7));
+                *reinterpret_cast<float4 *>(p_hi + off) = hi;
+                *reinterpret_cast<float4 *>(p_lo + off) = lo;
             }
         }
+        if (threadIdx.x == 0) ST_STAMP(20);
         fence_proxy_async_smem();
-        ST_DBG(2, if (warp == 0) { p.dbg[384 + lane] = s0[0]; p.dbg[416 + lane] = s1[0]; p.dbg[448 + lane] = e0[0] / tot[0]; p.dbg[480 + lane] = e1[0] / tot[0]; });
+        if (threadIdx.x == 0) ST_STAMP(21);
+        ST_DBG(2, if (warp == 0 && lane < 16) { p.dbg[384 + 4 * lane] = sv[0].x; });
     }
     tc_fence_before();
     __syncthreads();
@@ -361,19 +371,29 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 
     if (threadIdx.x == 0) ST_STAMP(11);
     // ---- O[:, slice] = P V ----
+    // With a slice of at most 128 columns, V hi and V lo (contiguous slabs) are one B operand of
+    // N = 2 * width: P hi [V hi | V lo] and then columns [0, width) += P lo V hi, two MMAs per 8 keys
+    // instead of three (an MMA of this size costs its issue latency, not its arithmetic).
+    const bool v_cat = (nat == p.apc) && (2 * nat * ST_ATOM <= 256);
     if (warp == 1 && lane == 0 && !failed) {
-        const uint32_t idv = umma_idesc_tf32(64, nat * ST_ATOM, 0, 1);
+        const uint32_t idv = umma_idesc_tf32(64, nat * ST_ATOM, 0, 1), idv2 = umma_idesc_tf32(64, 2 * nat * ST_ATOM, 0, 1);
         const int ksteps = kpad >> 3;
         for (int kk = 0; kk < ksteps; ++kk) {
             const uint64_t dp_hi = umma_desc_k_sw128(smem_u32(p_hi + (size_t)(kk >> 2) * ST_SLAB)) + 2 * (kk & 3);
             const uint64_t dp_lo = umma_desc_k_sw128(smem_u32(p_lo + (size_t)(kk >> 2) * ST_SLAB)) + 2 * (kk & 3);
             const uint64_t dv_hi = umma_desc_mn_sw128_32b(smem_u32(v_hi + (size_t)kk * 1024), ST_SLAB, 512);
             const uint64_t dv_lo = umma_desc_mn_sw128_32b(smem_u32(v_lo + (size_t)kk * 1024), ST_SLAB, 512);
-            umma_tf32(tmem, dp_hi, dv_hi, idv, kk != 0);
-            umma_tf32(tmem, dp_hi, dv_lo, idv, 1u);
-            umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
+            if (v_cat) {
+                umma_tf32(tmem, dp_hi, dv_hi, idv2, kk != 0);
+                umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
+            } else {
+                umma_tf32(tmem, dp_hi, dv_hi, idv, kk != 0);
+                umma_tf32(tmem, dp_hi, dv_lo, idv, 1u);
+                umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
+            }
         }
         umma_commit(&bars.o_full);
+        ST_STAMP(22);
     }
     if (!failed) {
         do {
@@ -386,6 +406,13 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             uint32_t r[32];
             for (int a = warp >> 2; a < nat; a += 2) {
                 tmem_ld32(ta + a * ST_ATOM, r);
+                if (v_cat) {
+                    uint32_t r2[32];
+                    tmem_ld32(ta + (nat + a) * ST_ATOM, r2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+                }
                 tmem_ld_wait();
                 ST_DBG(4, if (warp == 0 && a == 0 && lane < 2) { for (int j = 0; j < 32; ++j) p.dbg[704 + lane * 32 + j] = __uint_as_float(r[j]); });
                 if (lane < 16) {
@@ -406,7 +433,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     if (threadIdx.x == 0 && !failed) {
         for (int a = 0; a < nat; ++a) tma_store_2d(&tmO, o_stage + (size_t)a * ST_SLAB, (a0 + a) * ST_ATOM, (int)(bh * Lq));
         tma_store_commit();
-        tma_store_wait_all();
+        tma_store_wait_read();   // the writes themselves complete with the kernel
         ST_STAMP(14);
     }
     if (failed && threadIdx.x == 0) {

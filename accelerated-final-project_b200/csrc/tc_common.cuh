@@ -183,6 +183,12 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
         : "memory");
 }
 
+// ---- programmatic dependent launch: no-ops unless the kernel was launched with the attribute ---------
+// Lets the next kernel of the stream, if it was launched as a programmatic dependent, start now.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Returns once the kernel this one programmatically depends on has completed and its writes are visible.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- TMA tiled store shared -> global (bulk async-group completion) ---------------------------------
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *tmap, const void *smem_src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(smem_u32(smem_src)),
@@ -191,6 +197,8 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *tmap, const void
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// ... until the stores have read their shared-memory source (it may then be reused, or the CTA may exit)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 // Four fp32 additions to global memory in one L2 operation (16-byte aligned address).
 __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {

@@ -139,9 +139,12 @@ typedef struct b200attn_args {
  * one device must not overlap in time on different host threads (they share per-device scratch). */
 int b200attn_forward_ex(const b200attn_args *args);
 
-/* Enqueues n independent problems (args[i] for i < n) in one call; stops at the first failure.
- * Each entry is handled exactly as by b200attn_forward_ex (give them B200ATTN_FLAG_ASYNC to
- * enqueue them back to back without a host synchronisation in between). */
+/* Enqueues n INDEPENDENT problems (args[i] for i < n) in one call; stops at the first failure.
+ * Each entry is handled as by b200attn_forward_ex (give them B200ATTN_FLAG_ASYNC to enqueue them back
+ * to back without a host synchronisation in between), with one difference: because no entry may read
+ * what another entry of the same call writes, the library lets consecutive entries on one stream
+ * overlap on the GPU (entry i starts loading its inputs while entry i-1 is finishing; an entry whose
+ * Q, K or V overlaps the previous entry's `out` is simply not overlapped). */
 int b200attn_forward_many(const b200attn_args *args, int n);
 
 /* Same computation with HOST buffers (pageable or pinned): copies Q, K, V to device staging

@@ -122,6 +122,35 @@ def test_tensor_core_split_path_changing_head_counts(pkg, cuda):
         assert res["ok"] and res["max_abs"] <= 5e-6, ((B, H, L, D), res)
 
 
+def test_forward_many_overlaps_consecutive_entries_correctly(pkg, cuda):
+    """b200attn_forward_many launches an entry as the programmatic dependent of the one before it (its loads
+    run under the other's tail).  Every entry of a long mixed batch must still be right, including an
+    entry that reads the previous entry's output (the library detects that and does not overlap it)."""
+    import torch
+    shapes = [(1, 4, 64, 64, 2048), (1, 4, 64, 64, 512), (1, 4, 32, 64, 4096), (1, 2, 64, 64, 64), (1, 4, 64, 64, 8192),
+              (1, 4, 64, 64, 2048), (1, 7, 16, 48, 256), (1, 4, 64, 64, 4096)] * 3
+    probs, args = [], []
+    for n, (B, H, Lq, Lk, D) in enumerate(shapes):
+        Q, K, V = ol.make_qkv(B, H, Lq, Lk, D, 60 + n, "uniform")
+        q, k, v = (to_dev(x, cuda) for x in (Q, K, V))
+        o = torch.full_like(q, float("nan"))
+        probs.append((Q, K, V, q, k, v, o))
+        args.append(pkg.args_for(q, k, v, o, flags=pkg.FLAG_ASYNC))
+    # a dependent pair at the end: the second reads the first one's output as its Q
+    Q, K, V, q, k, v, o = probs[0]
+    o2 = torch.full_like(q, float("nan"))
+    args.append(pkg.args_for(o, k, v, o2, flags=pkg.FLAG_ASYNC))
+    for rep in range(2):
+        pkg.forward_many(args)
+        torch.cuda.synchronize()
+        for (Q, K, V, q, k, v, o) in probs:
+            res = ol.compare(o.cpu().numpy(), ol.attention(Q, K, V))
+            assert res["ok"] and res["max_abs"] <= 5e-6, (Q.shape, res)
+        first = probs[0]
+        want2 = ol.attention(first[6].cpu().numpy(), first[1], first[2])
+        assert ol.compare(o2.cpu().numpy(), want2)["ok"]
+
+
 def test_rope_with_caller_supplied_caches_and_hybrid_entry(pkg, cuda):
     B, H, L, D, rd = 1, 4, 64, 512, 128
     Q, K, V = ol.make_qkv(B, H, L, L, D, 46, "uniform")
