@@ -369,18 +369,14 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     const int apc = (natoms + slots - 1) / slots;
     if (apc > ST_MAX_ATOMS) return -1;
     const int nsplit = (natoms + apc - 1) / apc;
-    // Overlap with the previous call: this call's inputs must not be that call's output.  Two CTAs
-    // share an SM only below half of its shared memory, so the ring is shortened where that makes it fit
-    // (the loads of this call then run under the tail of the previous one).
+    // Overlap with the previous call: this call's inputs must not be that call's output.  (Two CTAs
+    // share an SM below half of its shared memory, i.e. with slices of up to 96 columns; the loads of
+    // this call then run under the tail of the previous one.  Wider slices still gain the launch latency.)
     const size_t in_q = (size_t)BH * Lq * D * 4, in_k = (size_t)BH * Lk * D * 4;
     auto hits_prev_out = [&](const void *ptr, size_t n) { return (uintptr_t)ptr < c.prev_out_hi && (uintptr_t)ptr + n > c.prev_out_lo; };
     const bool overlap = independent_of_prev && c.prev_sdtc && c.prev_stream == st && !c.scratch_dirty &&
                          !hits_prev_out(a.Q, in_q) && !hits_prev_out(a.K, in_k) && !hits_prev_out(a.V, in_k);
-    int nst = apc < ST_MAX_STAGES ? apc : ST_MAX_STAGES;
-    if (overlap && apc <= 4) {
-        while (nst > 1 && sdtc_smem_bytes(apc, nst) > (size_t)112 * 1024) --nst;
-    }
-    const size_t smem = sdtc_smem_bytes(apc, nst);
+    const size_t smem = sdtc_smem_bytes(apc);
     if (!c.sdtc_attr) {
         cudaFuncAttributes fa;
         CU_TRY(cudaFuncGetAttributes(&fa, sdtc_kernel));
@@ -411,7 +407,7 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     if (!ok) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the split-head_d slices");
     SdtcParams p{};
     p.BH = BH; p.Lq = Lq; p.Lk = Lk; p.D = D;
-    p.apc = apc; p.natoms = natoms; p.nsplit = nsplit; p.nst = nst;
+    p.apc = apc; p.natoms = natoms; p.nsplit = nsplit;
     p.epoch = c.sdtc_epoch; p.cap_bh = c.sdtc_cap; p.zero_bh = c.sdtc_prev_bh;
     p.scale = 1.0f / sqrtf((float)D);
     p.S = c.sdtc_S; p.counters = c.sdtc_cnt;

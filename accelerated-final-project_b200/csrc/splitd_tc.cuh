@@ -10,12 +10,12 @@
 // reference kernel, final/attention.cu:120-142 and :169-181; the reference's own arithmetic is fp32
 // FMA, and the result here agrees with it to a few 1e-7.)
 //
-//   load      Q and K slices arrive by TMA one 32-column "atom" (128 bytes per row, 128-byte
-//             swizzle: the K-major operand layout of the MMA) at a time through a ring of stages;
-//             the V slice arrives as [keys x 32 columns] slabs with the 128-byte swizzle on 32-byte
-//             units, which is the MN-major operand layout of 32-bit elements.
-//   split     six warps rewrite each landed atom as hi (in place) and lo (next to it);
-//   scores    one thread issues, per 8 columns, S[64 x 128] = Qhi [Khi;Klo]^T and S[:, 0:64] += Qlo Khi^T
+//   load      the whole slice is requested at once when the CTA starts (the bytes in flight per SM are
+//             what decides the HBM rate): Q and K as 32-column "atoms" (128 bytes per row, 128-byte
+//             swizzle: the K-major operand layout of the MMA), V as [keys x 32 columns] slabs with
+//             the 128-byte swizzle on 32-byte units, the MN-major operand layout of 32-bit elements.
+//   split     six warps rewrite each landed atom as hi (in place) and lo (into a two-deep ring);
+//   scores    one thread issues, per 8 columns, S[64 x 64] += Qhi Khi^T + Qhi Klo^T + Qlo Khi^T
 //             (M = 64: the accumulator row r sits in tensor-memory lane 32*(r/16) + r%16);
 //   reduce    the partial scores of the slices of a head are summed in an L2-resident scratch with
 //             16-byte vector reductions; a per-head arrival counter tells when the sum is complete.
@@ -38,9 +38,9 @@ constexpr int ST_THREADS = 256;        // warp 0: TMA + arrival counter, warp 1:
 constexpr int ST_SPLIT_THREADS = 192;
 constexpr int ST_ATOM = 32;            // fp32 columns in a 128-byte swizzled row
 constexpr int ST_SLAB = 64 * 128;      // [64 rows x 128 B]
-constexpr int ST_STAGE = 4 * ST_SLAB;  // Q hi | Q lo | K hi | K lo
-constexpr int ST_MAX_ATOMS = 8;        // widest slice: 256 columns (one MMA N; V hi + V lo + ring fit 227 KB)
-constexpr int ST_MAX_STAGES = 3;
+constexpr int ST_CHUNK = 2 * ST_SLAB;  // one atom of Q and of K
+constexpr int ST_MAX_ATOMS = 8;        // widest slice: 256 columns (one MMA N; 24 KB per atom + the residual ring fit 227 KB)
+constexpr int ST_NLO = 2;              // residual ring depth
 constexpr int ST_TMEM_COLS = 256;
 
 struct SdtcParams {
@@ -49,7 +49,6 @@ struct SdtcParams {
     int apc;                 // atoms per slice
     int natoms;              // ceil(D / 32)
     int nsplit;              // slices per head
-    int nst;                 // ring depth, min(apc, ST_MAX_STAGES)
     int epoch;               // 0 / 1: which half of the scratch this call sums into
     float scale;
     float *S;                // [2][cap_bh][64][64] partial-score sums; all zero outside the heads in use
@@ -66,11 +65,13 @@ struct SdtcParams {
 };
 
 struct StBars {
-    uint64_t full[ST_MAX_STAGES], ready[ST_MAX_STAGES], empty[ST_MAX_STAGES];
+    uint64_t full[ST_MAX_ATOMS];            // atom c of Q and K has landed
+    uint64_t ready[ST_NLO], lo_free[ST_NLO];   // residual ring: split done / read by the MMAs
     uint64_t v_full, s_full, o_full;
 };
 
-inline size_t sdtc_smem_bytes(int apc, int nst) { return (size_t)2 * apc * ST_SLAB + (size_t)nst * ST_STAGE + 1024; }
+// V slabs | Q,K atoms | residual ring (+ 1 KB to align the base)
+inline size_t sdtc_smem_bytes(int apc) { return (size_t)apc * (ST_SLAB + ST_CHUNK) + (size_t)ST_NLO * ST_CHUNK + 1024; }
 
 // x -> (x with the low 13 mantissa bits cleared, the exact remainder)
 __device__ __forceinline__ void st_split4(const float4 x, float4 &hi, float4 &lo) {
@@ -115,41 +116,46 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slice = blockIdx.x;
     const long long bh = blockIdx.y;
-    const int Lq = p.Lq, Lk = p.Lk, nst = p.nst;
-    const int a0 = slice * p.apc;
-    const int nat = min(p.apc, p.natoms - a0);   // >= 1 by construction of the grid
+    const int Lq = p.Lq, Lk = p.Lk;
+    // The slice of CTA s is the atoms s, s + nsplit, s + 2 nsplit, ...: at any moment the CTAs of a head
+    // are then fetching neighbouring 128-byte pieces of the same rows, which DRAM serves from open pages.
+    const int nat = (p.natoms - slice + p.nsplit - 1) / p.nsplit;   // >= 1: nsplit <= natoms
+    auto atom_col = [&](int c) { return (slice + c * p.nsplit) * ST_ATOM; };
     const int kpad = (Lk + 7) & ~7;              // keys covered by the P V contraction (8 per MMA)
     const uint32_t lim = p.spin_limit;
 
-    unsigned char *v_hi = smem;                                  // nat slabs [keys x 32 columns]
-    unsigned char *v_lo = smem + (size_t)p.apc * ST_SLAB;
-    unsigned char *ring = smem + (size_t)2 * p.apc * ST_SLAB;    // nst stages
-    unsigned char *p_hi = ring;                                  // after the score MMAs: P, two atoms of 32 keys
-    unsigned char *p_lo = ring + 2 * ST_SLAB;
-    unsigned char *o_stage = v_hi;                               // after the P V MMAs: output slabs
+    unsigned char *v_hi = smem;                                      // apc slabs [keys x 32 columns]
+    unsigned char *qk = smem + (size_t)p.apc * ST_SLAB;              // apc atoms: Q [64 x 32] | K [64 x 32]
+    unsigned char *lo_ring = qk + (size_t)p.apc * ST_CHUNK;          // ST_NLO stages: Q lo | K lo
+    // once the score MMAs are done: V lo where the first Q, K atoms were (so that V hi | V lo is one
+    // run of slabs when the slice is full), P behind it or in the residual ring, whichever has 32 KB
+    unsigned char *v_lo = qk;
+    unsigned char *p_hi = (p.apc >= 4) ? qk + (size_t)p.apc * ST_SLAB : lo_ring;   // two atoms of 32 keys
+    unsigned char *p_lo = p_hi + 2 * ST_SLAB;
+    unsigned char *o_stage = v_hi;                                   // after the P V MMAs: output slabs
 
     float *S_cur = p.S + ((size_t)p.epoch * p.cap_bh + bh) * 4096;
     unsigned *cnt_cur = p.counters + (size_t)p.epoch * p.cap_bh + bh;
 
-    // one thread sets the barriers up and at once issues the first ring fill and the V loads: they are
-    // in flight while the other warps allocate tensor memory and meet at the barrier below
-    const int first = min(nst, nat);
+    // one thread sets the barriers up and at once requests the whole slice: the loads are in flight
+    // while the other warps allocate tensor memory and meet at the barrier below
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-        for (int i = 0; i < ST_MAX_STAGES; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.ready[i], 6); mbar_init(&bars.empty[i], 1); }
+        for (int i = 0; i < ST_MAX_ATOMS; ++i) mbar_init(&bars.full[i], 1);
+        for (int i = 0; i < ST_NLO; ++i) { mbar_init(&bars.ready[i], 6); mbar_init(&bars.lo_free[i], 1); }
         mbar_init(&bars.v_full, 1);
         mbar_init(&bars.s_full, 1);
         mbar_init(&bars.o_full, 1);
         s_fail = 0u;
         mbar_fence_init();
-        for (int c = 0; c < first; ++c) {
-            unsigned char *st = ring + (size_t)c * ST_STAGE;
+        for (int c = 0; c < nat; ++c) {
+            unsigned char *st = qk + (size_t)c * ST_CHUNK;
             mbar_expect_tx(&bars.full[c], (uint32_t)(Lq + Lk) * 128u);
-            tma_load_2d(st, &tmQ, (a0 + c) * ST_ATOM, (int)(bh * Lq), &bars.full[c]);
-            tma_load_2d(st + 2 * ST_SLAB, &tmK, (a0 + c) * ST_ATOM, (int)(bh * Lk), &bars.full[c]);
+            tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[c]);
+            tma_load_2d(st + ST_SLAB, &tmK, atom_col(c), (int)(bh * Lk), &bars.full[c]);
         }
         mbar_expect_tx(&bars.v_full, (uint32_t)nat * (uint32_t)Lk * 128u);
-        for (int a = 0; a < nat; ++a) tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, (a0 + a) * ST_ATOM, (int)(bh * Lk), &bars.v_full);
+        for (int a = 0; a < nat; ++a) tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, atom_col(a), (int)(bh * Lk), &bars.v_full);
         tma_prefetch_desc(&tmO);
     }
     if (warp == 1) tmem_alloc(&tmem_slot, ST_TMEM_COLS);
@@ -164,49 +170,40 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- the remaining atoms, as ring stages come free ----
-            for (int c = first; c < nat; ++c) {
-                const int s = c % nst;
-                ST_FAIL_AT(0, !mbar_wait(&bars.empty[s], ((c / nst) & 1) ^ 1, lim));
-                unsigned char *st = ring + (size_t)s * ST_STAGE;
-                mbar_expect_tx(&bars.full[s], (uint32_t)(Lq + Lk) * 128u);
-                tma_load_2d(st, &tmQ, (a0 + c) * ST_ATOM, (int)(bh * Lq), &bars.full[s]);
-                tma_load_2d(st + 2 * ST_SLAB, &tmK, (a0 + c) * ST_ATOM, (int)(bh * Lk), &bars.full[s]);
-            }
             // ---- the head's scores are complete when every read-out warp of every slice has arrived ----
-            if (!failed) {
-                grid_dependency_wait();
-                const unsigned want = 4u * (unsigned)p.nsplit + p.wait_extra;
-                unsigned seen = 0;
-                for (unsigned it = 0; it < lim; ++it) {
-                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt_cur) : "memory");
-                    if (seen >= want) break;
-                    __nanosleep(20);
-                }
-                ST_STAMP(7);
-                if (seen < want) {
-                    report_kernel_error(p.err, p.err_sys, (unsigned)KERR_HEAD_BARRIER_TIMEOUT);
-                    *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
-                }
+            grid_dependency_wait();
+            const unsigned want = 4u * (unsigned)p.nsplit + p.wait_extra;
+            unsigned seen = 0;
+            for (unsigned it = 0; it < lim; ++it) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt_cur) : "memory");
+                if (seen >= want) break;
+                __nanosleep(20);
+            }
+            ST_STAMP(7);
+            if (seen < want) {
+                report_kernel_error(p.err, p.err_sys, (unsigned)KERR_HEAD_BARRIER_TIMEOUT);
+                *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- score MMAs ----
-            const uint32_t id128 = umma_idesc_tf32(64, 128, 0, 0), id64 = umma_idesc_tf32(64, 64, 0, 0);
+            const uint32_t id64 = umma_idesc_tf32(64, 64, 0, 0);
             for (int c = 0; c < nat; ++c) {
-                const int s = c % nst;
-                ST_FAIL_AT(2, !mbar_wait(&bars.ready[s], (c / nst) & 1, lim));
+                const int j = c % ST_NLO;
+                ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (c / ST_NLO) & 1, lim));
                 if (c == nat - 1) ST_STAMP(18);
                 tc_fence_after();
-                const uint32_t sa = smem_u32(ring + (size_t)s * ST_STAGE);
-                const uint64_t dq_hi = umma_desc_k_sw128(sa), dq_lo = umma_desc_k_sw128(sa + ST_SLAB), dk = umma_desc_k_sw128(sa + 2 * ST_SLAB);
+                const uint32_t sa = smem_u32(qk + (size_t)c * ST_CHUNK), sl = smem_u32(lo_ring + (size_t)j * ST_CHUNK);
+                const uint64_t dq_hi = umma_desc_k_sw128(sa), dk_hi = umma_desc_k_sw128(sa + ST_SLAB);
+                const uint64_t dq_lo = umma_desc_k_sw128(sl), dk_lo = umma_desc_k_sw128(sl + ST_SLAB);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    umma_tf32(tmem, dq_hi + 2 * k, dk + 2 * k, id128, (c | k) != 0);   // [Qhi Khi^T | Qhi Klo^T]
-                    umma_tf32(tmem, dq_lo + 2 * k, dk + 2 * k, id64, 1u);              // columns 0-63 += Qlo Khi^T
+                    umma_tf32(tmem, dq_hi + 2 * k, dk_hi + 2 * k, id64, (c | k) != 0);
+                    umma_tf32(tmem, dq_hi + 2 * k, dk_lo + 2 * k, id64, 1u);
+                    umma_tf32(tmem, dq_lo + 2 * k, dk_hi + 2 * k, id64, 1u);
                 }
-                umma_commit(&bars.empty[s]);
+                umma_commit(&bars.lo_free[j]);
             }
             if (!failed) umma_commit(&bars.s_full);
             ST_STAMP(19);
@@ -215,63 +212,65 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const int t = threadIdx.x - 64;   // 0..191
         // ---- hi / lo split of the landed Q and K atoms ----
         for (int c = 0; c < nat; ++c) {
-            const int s = c % nst;
-            ST_FAIL_AT(3, !mbar_wait(&bars.full[s], (c / nst) & 1, lim));
+            const int j = c % ST_NLO;
+            ST_FAIL_AT(3, !mbar_wait(&bars.full[c], 0, lim));
+            ST_FAIL_AT(7, !mbar_wait(&bars.lo_free[j], ((c / ST_NLO) & 1) ^ 1, lim));
             if (t == 0 && c == 0) ST_STAMP(2);
             if (t == 0 && c == nat - 1) ST_STAMP(3);
-            unsigned char *st = ring + (size_t)s * ST_STAGE;
+            unsigned char *st = qk + (size_t)c * ST_CHUNK, *sl = lo_ring + (size_t)j * ST_CHUNK;
             for (int idx = t; idx < 1024; idx += ST_SPLIT_THREADS) {
-                const int part = idx >> 9, i = idx & 511;
+                const int part = idx >> 9, i = idx & 511;   // idx * 16 is the byte offset in both the atom pair and the ring stage
                 if ((i >> 3) < (part ? Lk : Lq)) {
-                    float4 *ph = reinterpret_cast<float4 *>(st + (size_t)part * 2 * ST_SLAB + (size_t)i * 16);
+                    float4 *ph = reinterpret_cast<float4 *>(st + (size_t)idx * 16);
                     float4 hi, lo;
                     st_split4(*ph, hi, lo);
                     *ph = hi;
-                    *reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(ph) + ST_SLAB) = lo;
+                    *reinterpret_cast<float4 *>(sl + (size_t)idx * 16) = lo;
                 }
             }
             if (t == 0 && c == nat - 1) ST_STAMP(16);
-            ST_DBG(0, if (c == 0 && t < 64) { p.dbg[t] = reinterpret_cast<float *>(st)[t]; p.dbg[64 + t] = reinterpret_cast<float *>(st + ST_SLAB)[t];
-                                              p.dbg[128 + t] = reinterpret_cast<float *>(st + 2 * ST_SLAB)[t]; p.dbg[192 + t] = reinterpret_cast<float *>(st + 3 * ST_SLAB)[t]; });
+            ST_DBG(0, if (c == 0 && t < 64) { p.dbg[t] = reinterpret_cast<float *>(st)[t]; p.dbg[64 + t] = reinterpret_cast<float *>(sl)[t];
+                                              p.dbg[128 + t] = reinterpret_cast<float *>(st + ST_SLAB)[t]; p.dbg[192 + t] = reinterpret_cast<float *>(sl + ST_SLAB)[t]; });
             fence_proxy_async_smem();
             if (t == 0 && c == nat - 1) ST_STAMP(17);
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.ready[s]);
+            if (lane == 0) mbar_arrive(&bars.ready[j]);
         }
         failed = __any_sync(0xffffffffu, failed);   // the collective tensor-memory loads below need whole warps
-        // ---- read-out of the partial scores (warps 4-7: one tensor-memory lane quadrant each) ----
-        if (warp >= 4 && !failed) {
+        // ---- the score MMAs are done: the Q, K atoms may be overwritten (V lo, P) ----
+        if (!failed) {
             do {
                 ST_FAIL_AT(4, !mbar_wait(&bars.s_full, 0, lim));
-                if (threadIdx.x == 128) ST_STAMP(4);
-                tc_fence_after();
-                grid_dependency_wait();   // the scratch half summed into was cleared by the previous call
-                const int q = warp & 3;
-                const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
-                const int row = 16 * q + lane;
-                float *srow = S_cur + (size_t)row * 64;
-                uint32_t r0[32], r1[32];
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    tmem_ld32(ta + hh * 32, r0);        // Qhi Khi^T + Qlo Khi^T
-                    tmem_ld32(ta + 64 + hh * 32, r1);   // Qhi Klo^T
-                    tmem_ld_wait();
-                    ST_DBG(1, if (warp == 4 && hh == 0 && lane < 2) { for (int j = 0; j < 32; ++j) { p.dbg[256 + lane * 64 + j] = __uint_as_float(r0[j]); p.dbg[256 + lane * 64 + 32 + j] = __uint_as_float(r1[j]); } });
-                    if (lane < 16 && row < Lq) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            red_add_v4(srow + hh * 32 + j, __uint_as_float(r0[j]) + __uint_as_float(r1[j]),
-                                       __uint_as_float(r0[j + 1]) + __uint_as_float(r1[j + 1]),
-                                       __uint_as_float(r0[j + 2]) + __uint_as_float(r1[j + 2]),
-                                       __uint_as_float(r0[j + 3]) + __uint_as_float(r1[j + 3]));
-                    }
-                }
-                if (threadIdx.x == 128) ST_STAMP(5);
-                tc_fence_before();
-                __syncwarp();
-                // release at gpu scope, cumulative over the warp's additions (ordered before it by the warp barrier)
-                if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt_cur) : "memory");
             } while (false);
+            failed = __any_sync(0xffffffffu, failed);
+        }
+        // ---- read-out of the partial scores (warps 4-7: one tensor-memory lane quadrant each) ----
+        if (warp >= 4 && !failed) {
+            if (threadIdx.x == 128) ST_STAMP(4);
+            tc_fence_after();
+            grid_dependency_wait();   // the scratch half summed into was cleared by the previous call
+            const int q = warp & 3;
+            const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
+            const int row = 16 * q + lane;
+            float *srow = S_cur + (size_t)row * 64;
+            uint32_t r0[32];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                tmem_ld32(ta + hh * 32, r0);
+                tmem_ld_wait();
+                ST_DBG(1, if (warp == 4 && hh == 0 && lane < 2) { for (int jj = 0; jj < 32; ++jj) p.dbg[256 + lane * 64 + jj] = __uint_as_float(r0[jj]); });
+                if (lane < 16 && row < Lq) {
+#pragma unroll
+                    for (int jj = 0; jj < 32; jj += 4)
+                        red_add_v4(srow + hh * 32 + jj, __uint_as_float(r0[jj]), __uint_as_float(r0[jj + 1]), __uint_as_float(r0[jj + 2]),
+                                   __uint_as_float(r0[jj + 3]));
+                }
+            }
+            if (threadIdx.x == 128) ST_STAMP(5);
+            tc_fence_before();
+            __syncwarp();
+            // release at gpu scope, cumulative over the warp's additions (ordered before it by the warp barrier)
+            if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt_cur) : "memory");
         }
         // ---- hi / lo split of V; key rows [Lk, kpad) enter the contraction and must be zero ----
         if (!failed) {
@@ -279,13 +278,13 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 ST_FAIL_AT(5, !mbar_wait(&bars.v_full, 0, lim));
                 if (t == 0) ST_STAMP(8);
                 for (int idx = t; idx < nat * 512; idx += ST_SPLIT_THREADS) {
-                    const int slab = idx >> 9, i = idx & 511, row = i >> 3;
+                    const int i = idx & 511, row = i >> 3;   // idx * 16 is the byte offset in the run of slabs
                     if (row < kpad) {
-                        float4 *ph = reinterpret_cast<float4 *>(v_hi + (size_t)slab * ST_SLAB + (size_t)i * 16);
+                        float4 *ph = reinterpret_cast<float4 *>(v_hi + (size_t)idx * 16);
                         float4 hi = make_float4(0.f, 0.f, 0.f, 0.f), lo = hi;
                         if (row < Lk) st_split4(*ph, hi, lo);
                         *ph = hi;
-                        *reinterpret_cast<float4 *>(v_lo + (size_t)slab * ST_SLAB + (size_t)i * 16) = lo;
+                        *reinterpret_cast<float4 *>(v_lo + (size_t)idx * 16) = lo;
                     }
                 }
                 fence_proxy_async_smem();
@@ -431,7 +430,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
     if (threadIdx.x == 0) ST_STAMP(13);
     if (threadIdx.x == 0 && !failed) {
-        for (int a = 0; a < nat; ++a) tma_store_2d(&tmO, o_stage + (size_t)a * ST_SLAB, (a0 + a) * ST_ATOM, (int)(bh * Lq));
+        for (int a = 0; a < nat; ++a) tma_store_2d(&tmO, o_stage + (size_t)a * ST_SLAB, atom_col(a), (int)(bh * Lq));
         tma_store_commit();
         tma_store_wait_read();   // the writes themselves complete with the kernel
         ST_STAMP(14);
