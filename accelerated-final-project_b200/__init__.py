@@ -13,7 +13,8 @@ LIB_PATH = os.environ.get("B200ATTN_LIB") or os.path.join(_HERE, "lib", "libb200
 
 F32, BF16 = 0, 1
 PE_NONE, PE_ROPE_INTERLEAVED, PE_ROPE_HALF, PE_SINUSOIDAL, PE_ROPE_Q_ONLY = 0, 1, 2, 3, 4
-FLAG_ASYNC, FLAG_FORCE_GENERIC, FLAG_FORCE_TWO_PASS = 1, 2, 4
+FLAG_ASYNC, FLAG_FORCE_GENERIC, FLAG_FORCE_TWO_PASS, FLAG_PREFER_ONE_KERNEL = 1, 2, 4, 8
+OPT_SCORE_SCRATCH_MB, OPT_SPIN_LIMIT = 1, 2
 OK = 0
 
 # every symbol include/b200attn.h declares (checked by the CPU test-suite against the header)
@@ -83,6 +84,8 @@ def lib():
         L.b200attn_synth_fill.argtypes = [C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong,
                                           C.c_int, C.c_int, C.c_void_p]
         L.b200attn_synth_fill.restype = C.c_int
+        L.b200attn_set_option.argtypes = [C.c_int, C.c_longlong]
+        L.b200attn_set_option.restype = C.c_int
         L.b200attn_debug_kernel_times.argtypes = [C.c_int, C.POINTER(C.c_double)]
         L.b200attn_debug_kernel_times.restype = C.c_int
         L.b200attn_debug_lost_arrival.argtypes = [C.c_uint, C.c_uint]
@@ -161,6 +164,10 @@ def forward_host(Q, K, V, out, pe=PE_NONE, rotary_dim=0, rope_base=0.0, flags=0)
                   rope_base, None, None, None, flags)
     check(lib().b200attn_forward_host(C.byref(a)))
     return out
+
+
+def set_option(option, value):
+    check(lib().b200attn_set_option(option, value))
 
 
 def shard_ranges(total_bh, n_parts):

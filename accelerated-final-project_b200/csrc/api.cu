@@ -78,7 +78,7 @@ struct TmapCache {
 // Per-device state.  Guarded by `mu`: calls for one device are serialised on the host.
 struct DeviceCtx {
     std::mutex mu;
-    bool ready = false;
+    std::atomic<bool> ready{false};
     int sm_count = 0;
     int cc_major = 0;
     size_t max_smem_optin = 0;
@@ -111,6 +111,11 @@ struct DeviceCtx {
     bool prev_sdtc = false;
     cudaStream_t prev_stream = nullptr;
     uintptr_t prev_out_lo = 0, prev_out_hi = 0;
+    // Calls for one device share scratch and tables.  When a call comes on another stream than the
+    // call before it, it is made to wait (on the device) for everything enqueued on that stream so far.
+    bool have_last_stream = false;
+    cudaStream_t last_stream = nullptr;
+    cudaEvent_t last_event = nullptr;
     TmapCache tmaps;
     TcTables tc_tables;            // positional-encoding tables of the tensor-core path
     TcwScratch tcw;                // scratch of the wide-head tensor-core path
@@ -123,9 +128,9 @@ static int get_ctx(DeviceCtx **out, int *dev_out = nullptr) {
     if (e != cudaSuccess) return fail(B200ATTN_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= kMaxDevices) return fail(B200ATTN_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
     DeviceCtx &c = g_ctx[dev];
-    if (!c.ready) {
+    if (!c.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lk(c.mu);
-        if (!c.ready) {
+        if (!c.ready.load(std::memory_order_relaxed)) {
             cudaDeviceProp prop;
             CU_TRY(cudaGetDeviceProperties(&prop, dev));
             if (prop.major != 10)
@@ -134,13 +139,21 @@ static int get_ctx(DeviceCtx **out, int *dev_out = nullptr) {
             c.sm_count = prop.multiProcessorCount;
             c.cc_major = prop.major;
             c.max_smem_optin = prop.sharedMemPerBlockOptin;
-            CU_TRY(cudaMalloc(&c.err_dev, sizeof(unsigned)));
-            CU_TRY(cudaMemset(c.err_dev, 0, sizeof(unsigned)));
-            CU_TRY(cudaHostAlloc(&c.err_host, 2 * sizeof(unsigned), cudaHostAllocMapped | cudaHostAllocPortable));
-            c.err_host[0] = c.err_host[1] = 0;
-            c.err_bits = c.err_host + 1;
-            CU_TRY(cudaHostGetDevicePointer(reinterpret_cast<void **>(&c.err_host_dev), c.err_host, 0));
-            c.ready = true;
+            // on a failure nothing stays allocated, so that a retry does not leak
+            unsigned *err_dev = nullptr, *err_host = nullptr, *err_host_dev = nullptr;
+            cudaError_t e = cudaMalloc(&err_dev, sizeof(unsigned));
+            if (e == cudaSuccess) e = cudaMemset(err_dev, 0, sizeof(unsigned));
+            if (e == cudaSuccess) e = cudaHostAlloc(&err_host, 2 * sizeof(unsigned), cudaHostAllocMapped | cudaHostAllocPortable);
+            if (e == cudaSuccess) e = cudaHostGetDevicePointer(reinterpret_cast<void **>(&err_host_dev), err_host, 0);
+            if (e != cudaSuccess) {
+                if (err_dev) cudaFree(err_dev);
+                if (err_host) cudaFreeHost(err_host);
+                (void)cudaGetLastError();
+                return fail(B200ATTN_ERR_CUDA, "CUDA error %d (%s) while setting up device %d", (int)e, cudaGetErrorString(e), dev);
+            }
+            err_host[0] = err_host[1] = 0;
+            c.err_dev = err_dev; c.err_host = err_host; c.err_bits = err_host + 1; c.err_host_dev = err_host_dev;
+            c.ready.store(true, std::memory_order_release);
         }
     }
     *out = &c;
@@ -200,22 +213,13 @@ static int set_smem_attr(DeviceCtx &c, int slot, Kern kern) {
 // arrivals more than there are slices, i.e. waits for a flag that nothing sets, with this poll limit.
 static std::atomic<unsigned> g_test_wait_extra{0}, g_test_spin_limit{0};
 
+// b200attn_set_option
+static std::atomic<unsigned> g_spin_limit{1u << 21};
+static std::atomic<long long> g_score_scratch_mb{2048};
+
 static unsigned spin_limit_from_env() {
     if (unsigned t = g_test_spin_limit.load()) return t;
-    static unsigned v = [] {
-        const char *s = getenv("B200ATTN_SPIN_LIMIT");
-        long x = s ? atol(s) : 0;
-        return (unsigned)(x > 0 ? x : (1 << 21));
-    }();
-    return v;
-}
-static int ctas_per_sm_from_env() {
-    static int v = [] {
-        const char *s = getenv("B200ATTN_SPLITD_CTAS_PER_SM");
-        int x = s ? atoi(s) : 0;
-        return x > 0 ? x : 1;
-    }();
-    return v;
+    return g_spin_limit.load();
 }
 
 // ---- split-head_d path --------------------------------------------------------------------------
@@ -235,15 +239,13 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
     p.wait_extra = g_test_wait_extra.load();
     const bool aligned16 = ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V) & 15) == 0);
     p.use_tma = (sizeof(T) == 4 && a.pe == B200ATTN_PE_NONE && D % 4 == 0 && aligned16) ? 1 : 0;
-    if (getenv("B200ATTN_NO_TMA")) p.use_tma = 0;
 
     // -- fused cooperative launch: whole heads co-resident, one CTA per slice --
     bool fused = !(a.flags & B200ATTN_FLAG_FORCE_TWO_PASS) && Lq <= SD_TILE && Lk <= SD_TILE;
     int ds = 0, nsplit = 0;
     size_t smem = 0;
     if (fused) {
-        const long long target = (long long)c.sm_count * ctas_per_sm_from_env();
-        long long nsplit_max = target / BH;
+        long long nsplit_max = c.sm_count / BH;
         if (nsplit_max < 1) fused = false;
         else {
             ds = (int)((D + nsplit_max - 1) / nsplit_max);
@@ -289,12 +291,7 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
         }
         dim3 grid(nsplit, (unsigned)BH);
         void *kargs[] = {&tmQ, &tmK, &tmV, &p};
-        if (getenv("B200ATTN_SPLITD_PLAIN_LAUNCH")) {   // experiment: no co-residency guarantee, waits are bounded
-            splitd_fused_kernel<T><<<grid, SD_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
-            CU_TRY(cudaGetLastError());
-        } else {
-            CU_TRY(cudaLaunchCooperativeKernel((const void *)splitd_fused_kernel<T>, grid, dim3(SD_THREADS), kargs, smem, st));
-        }
+        CU_TRY(cudaLaunchCooperativeKernel((const void *)splitd_fused_kernel<T>, grid, dim3(SD_THREADS), kargs, smem, st));
         g_launches.fetch_add(1);
         t_last_path = "splitd_fused";
         return B200ATTN_OK;
@@ -504,22 +501,34 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
         cudaDeviceSynchronize();   // let the failed work drain before the scratch is cleaned
         return report_kernel_errors(*c, "an earlier asynchronous call");
     }
+    if (c->have_last_stream && c->last_stream != st) {
+        if (!c->last_event) CU_TRY(cudaEventCreateWithFlags(&c->last_event, cudaEventDisableTiming));
+        cudaError_t e = cudaEventRecord(c->last_event, c->last_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(st, c->last_event, 0);
+        if (e != cudaSuccess) {   // the earlier stream is gone or unusable: order by waiting for the device
+            (void)cudaGetLastError();
+            CU_TRY(cudaDeviceSynchronize());
+        }
+    }
+    c->last_stream = st;
+    c->have_last_stream = true;
     bool done = false;
     const bool chain = independent_of_prev && c->prev_sdtc;
     c->prev_sdtc = false;   // set again by the kernel that supports being overlapped
     // bf16 on the tensor cores: the two-kernel path (scores, then P V) takes every shape it supports;
-    // the one-kernel cluster pipeline takes the rest of its own shapes (and all of them when
-    // B200ATTN_TC_PREFER_PAIR is set: the two are measured against each other that way).
+    // the one-kernel cluster pipeline takes the rest of its own shapes (and all of them when the call
+    // asks for it with B200ATTN_FLAG_PREFER_ONE_KERNEL: the two are measured against each other that way).
     const bool tc_ok = a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC);
     const bool wide_ok = tc_ok && tcw_supported(*a, rd), pair_ok = tc_ok && tc_bf16_supported(*a, rd);
-    const bool use_pair = pair_ok && (!wide_ok || getenv("B200ATTN_TC_PREFER_PAIR") != nullptr);
+    const bool use_pair = pair_ok && (!wide_ok || (a->flags & B200ATTN_FLAG_PREFER_ONE_KERNEL));
     if (use_pair) {
         rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
     if (!done && wide_ok) {
-        rc = tcw_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        rc = tcw_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(),
+                     (size_t)g_score_scratch_mb.load() << 20, st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_wide"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
         else if (pair_ok && !use_pair) {   // no room for the score scratch: the one-kernel pipeline needs none
@@ -602,14 +611,15 @@ void attention_forward_rope_fused(const float *Q, const float *K, const float *V
 }
 void attention_forward_rope_fused_v7_hybrid(const float *Q, const float *Kr, const float *V, float *out, int B, int H, int Lq,
                                             int Lk, int D, int rotary_dim) {
-    legacy(Q, Kr, V, out, B, H, Lq, Lk, D, B200ATTN_F32, B200ATTN_PE_ROPE_Q_ONLY, rotary_dim, nullptr, nullptr);
+    // the reference rotates the columns d < rotary_dim (final/rope.cu:129-149): none when it is 0
+    legacy(Q, Kr, V, out, B, H, Lq, Lk, D, B200ATTN_F32, rotary_dim == 0 ? B200ATTN_PE_NONE : B200ATTN_PE_ROPE_Q_ONLY, rotary_dim, nullptr, nullptr);
 }
 void attention_forward_rope_bf16(const void *Q, const void *K, const void *V, void *out, int B, int H, int Lq, int Lk, int D) {
     legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_BF16, B200ATTN_PE_ROPE_INTERLEAVED, D, nullptr, nullptr);
 }
 void attention_forward_rope_bf16_v7(const void *Q, const void *Kr, const void *V, void *out, int B, int H, int Lq, int Lk, int D,
                                     int rotary_dim) {
-    legacy(Q, Kr, V, out, B, H, Lq, Lk, D, B200ATTN_BF16, B200ATTN_PE_ROPE_Q_ONLY, rotary_dim, nullptr, nullptr);
+    legacy(Q, Kr, V, out, B, H, Lq, Lk, D, B200ATTN_BF16, rotary_dim == 0 ? B200ATTN_PE_NONE : B200ATTN_PE_ROPE_Q_ONLY, rotary_dim, nullptr, nullptr);
 }
 void attention_forward_sinusoidal_fused(const float *Q, const float *K, const float *V, float *out, int B, int H, int Lq, int Lk, int D) {
     legacy(Q, K, V, out, B, H, Lq, Lk, D, B200ATTN_F32, B200ATTN_PE_SINUSOIDAL, 0, nullptr, nullptr);
@@ -620,7 +630,8 @@ void attention_forward_sinusoidal_bf16(const void *Q, const void *K, const void 
 
 int b200attn_forward_ex(const b200attn_args *args) { return forward_device(args); }
 
-// Bring-up aid (not part of the public header): runs the tensor-core kernel and also returns the
+#ifdef B200ATTN_DEVTOOLS
+// Bring-up aid (development builds only): runs the one-kernel tensor-core pipeline and also returns the
 // raw scores Q K^T of key block 0, [B*H*(Lq/128)][128][128] fp32, for checking the first MMA stage.
 int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
     int rd; float base;
@@ -636,10 +647,8 @@ int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
     return check_kernel_errors(*c, (cudaStream_t)a->stream, true);
 }
 
-#ifdef B200ATTN_DEVTOOLS
 void b200attn_debug_sdtc_dump(float *dev_buf) { g_sdtc_dbg = dev_buf; }
 void b200attn_debug_sdtc_stamps(unsigned long long *dev_buf) { g_sdtc_stamps = dev_buf; }
-#endif
 
 #ifdef B200ATTN_SD_PROFILE
 int b200attn_debug_sd_stamps(unsigned long long *out, int n) {
@@ -653,6 +662,7 @@ int b200attn_debug_tc_prof(unsigned long long *out32, int reset) {
     return (int)cudaMemcpyFromSymbol(out32, tc_prof, 32 * sizeof(unsigned long long));
 }
 #endif
+#endif  // B200ATTN_DEVTOOLS
 
 int b200attn_forward_many(const b200attn_args *args, int n) {
     if (args == nullptr || n < 0) return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_many: NULL args or negative n");
@@ -836,6 +846,21 @@ int b200attn_debug_tile_of(int big, int mode, int j, int nqt, int nkt, int *qt, 
     return count;
 }
 
+int b200attn_set_option(int option, long long value) {
+    switch (option) {
+    case B200ATTN_OPT_SCORE_SCRATCH_MB:
+        if (value < 1) return fail(B200ATTN_ERR_INVALID_ARG, "the score scratch cap must be at least 1 MiB");
+        g_score_scratch_mb.store(value);
+        return B200ATTN_OK;
+    case B200ATTN_OPT_SPIN_LIMIT:
+        if (value < 1 || value > 0x7fffffffLL) return fail(B200ATTN_ERR_INVALID_ARG, "the poll limit must be in [1, 2^31)");
+        g_spin_limit.store((unsigned)value);
+        return B200ATTN_OK;
+    default:
+        return fail(B200ATTN_ERR_INVALID_ARG, "unknown option %d", option);
+    }
+}
+
 const char *b200attn_last_error(void) { return t_last_error.c_str(); }
 const char *b200attn_last_path(void) { return t_last_path; }
 unsigned long long b200attn_launch_count(void) { return g_launches.load(); }
@@ -860,6 +885,7 @@ void b200attn_release_workspace(void) {
         for (int i = 0; i < 8; ++i) { if (c.stage[i]) cudaFree(c.stage[i]); c.stage[i] = nullptr; c.stage_bytes[i] = 0; }
         c.tc_tables.release();
         c.tcw.release();
+        c.prev_sdtc = false;
     }
     cudaSetDevice(prev);
 }

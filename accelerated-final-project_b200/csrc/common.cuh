@@ -9,6 +9,13 @@
 #error "b200attn is written for sm_100a only"
 #endif
 
+// The in-kernel cycle accounting and the bring-up exports exist only in builds made with
+// -DB200ATTN_DEVTOOLS (the shipped library is built without it).
+#ifndef B200ATTN_DEVTOOLS
+#undef B200ATTN_SD_PROFILE
+#undef B200ATTN_TC_PROFILE
+#endif
+
 namespace b200attn {
 
 // Positional-encoding selector; values match enum b200attn_pe in include/b200attn.h.

@@ -356,10 +356,12 @@ tc_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                             mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
                             mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
                         }
+#ifdef B200ATTN_DEVTOOLS
                         if (p.debug_scores != nullptr && t == 0) {
                             float *dbg = p.debug_scores + ((long long)unit * TC_BM + row) * TC_BN + c * 32;
                             for (int j = 0; j < 32; ++j) dbg[j] = __uint_as_float(r[j]);
                         }
+#endif
                     }
                     const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
                     TC_PROF(1);
@@ -676,7 +678,7 @@ struct TcTables {
             release();
         }
         __nv_bfloat16 *ptr = nullptr;
-        if (cudaMalloc(&ptr, (size_t)L * D * sizeof(__nv_bfloat16)) != cudaSuccess) return nullptr;
+        if (cudaMalloc(&ptr, (size_t)L * D * sizeof(__nv_bfloat16)) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
         tc_build_pe_table<<<296, 256, 0, st>>>(ptr, L, D, kind, rd, base);
         launches->fetch_add(1);
         e[n++] = Entry{kind, L, D, rd, base, ptr};
@@ -689,7 +691,6 @@ static thread_local char t_tc_error[256] = "";
 inline const char *tc_bf16_error() { return t_tc_error; }
 
 inline bool tc_bf16_supported(const b200attn_args &a, int rd) {
-    if (getenv("B200ATTN_NO_TC")) return false;
     if (a.dtype != B200ATTN_BF16) return false;
     if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 512) return false;
     if (a.len_q % TC_BM != 0 || a.len_k % TC_BN != 0) return false;
@@ -776,7 +777,6 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
         const long long units = BH * n_qt;
         p.n_units = units;
         long long clusters = sm_count / 2;   // persistent: one cluster per SM pair, units dealt round-robin
-        if (const char *e = getenv("B200ATTN_TC_CLUSTERS")) { long long v = atoll(e); if (v > 0) clusters = v; }
         if (clusters > units) clusters = units;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(2 * clusters));
@@ -798,7 +798,7 @@ inline int tc_bf16_run(const b200attn_args &a, int rd, float base, TcTables &tab
     // tiles of that head then load the encoded K and run without the transform (second launch,
     // stream-ordered after the first).  The encoding is still applied once, inside a K load, by
     // the attention kernel itself; the scratch is as large as K.
-    if (pe_k && p.n_qtiles >= 3 && !getenv("B200ATTN_NO_KCACHE")) {
+    if (pe_k && p.n_qtiles >= 3) {
         const size_t kbytes = (size_t)BH * a.len_k * D * sizeof(__nv_bfloat16);
         __nv_bfloat16 *kc = tables.get_kcache(kbytes);
         CUtensorMap tmKc;

@@ -594,15 +594,9 @@ tcw_scores256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 constexpr int TP_THREADS = 608;   // warp 0 V loads, warp 1 MMA, warps 2-17 softmax and the unit's epilogue, warp 18 S loads
 constexpr int TP_VS = 64;         // keys per V stage
 constexpr int TP_VW = 256;        // output columns per V stage (one MMA N): a stage is [64 keys x <= 256 columns], 32 KB
-#ifndef B200ATTN_TP_NV
-#define B200ATTN_TP_NV 3
-#endif
-constexpr int TP_NV = B200ATTN_TP_NV;   // V stage ring depth (32 KB each; TP_NV + TP_NP <= 7 fits the shared memory;
+constexpr int TP_NV = 3;   // V stage ring depth (32 KB each; TP_NV + TP_NP <= 7 fits the shared memory;
                                         // measured on cfg 4 / cfg 5: 4 + 3 is 1 % faster than 3 + 4, 5 + 2 is 6 % slower)
-#ifndef B200ATTN_TP_NP
-#define B200ATTN_TP_NP 4
-#endif
-constexpr int TP_NP = B200ATTN_TP_NP;   // score / P buffers (32 KB each)
+constexpr int TP_NP = 4;   // score / P buffers (32 KB each)
 
 struct TcwPvParams {
     int Lq, Lk, D;
@@ -875,268 +869,6 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
     tc_fence_after();
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
-// The same for a pair of CTAs working as one (cluster of two, tcgen05 cta_group::2): the pair takes two
-// neighbouring query tiles, each CTA turns its own tile's scores into P in its own shared memory
-// (the A operand, M = 256 over the pair) and loads only HALF of the columns of every V stage (the B
-// operand is split along N between the two shared memories), so the V bytes per CTA and FLOP halve:
-// the one-CTA kernel is bound by the L2 -> SM bandwidth of its V and score loads, not by the MMA.
-// The leader CTA issues the MMAs; each CTA's [128 x <=512] accumulator lives in its own tensor
-// memory and is drained by its own warps.  Barriers that the leader waits on (P ready, V landed,
-// accumulator drained) live in the leader and count both CTAs; "slot free" barriers live in both
-// CTAs and get one commit each.
-constexpr int TP2_NV = 8;         // V stage ring depth (16 KB per CTA and stage)
-constexpr int TP2_NP = 3;         // score / P buffers
-struct Tp2Bars {
-    uint64_t v_full[TP2_NV], v_empty[TP2_NV];
-    uint64_t s_full[TP2_NP], p_full[TP2_NP], p_empty[TP2_NP];
-    uint64_t o_full, o_empty;
-    uint64_t l_full;
-};
-
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TP_THREADS, 1)
-tcw_pv2_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmS, const TcwPvParams p) {
-    extern __shared__ unsigned char tw_smem_raw[];
-    __shared__ Tp2Bars bars;
-    __shared__ unsigned skip_flag;
-    __shared__ uint32_t tmem_slot;
-    __shared__ float l_smem[2][TW_BM];
-    const uint32_t raw_addr = smem_u32(tw_smem_raw);
-    unsigned char *smem = tw_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-    unsigned char *p_smem = smem;                                   // TP2_NP x 32 KB
-    unsigned char *v_smem = smem + (size_t)TP2_NP * TC_P_BYTES;      // TP2_NV x 16 KB: this CTA's half of the columns of each stage
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int DW = p.DW, nblk = p.nblk;
-    const int v_stage_bytes = TP_VS * (TP_VW / 2) * 2;   // ring pitch: [64 keys x 128 columns] per CTA
-    const int nvw = (DW + TP_VW - 1) / TP_VW;      // column parts per 64 keys
-    const uint32_t lim = p.spin_limit;
-    const uint32_t rank = cluster_ctarank();
-    const long long cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-    const int nqp = p.nqt >> 1;   // pairs of query tiles; this CTA takes tile 2 * qp + rank
-
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < TP2_NV; ++i) { mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_empty[i], 1); }
-        for (int i = 0; i < TP2_NP; ++i) { mbar_init(&bars.s_full[i], 1); mbar_init(&bars.p_full[i], 32); mbar_init(&bars.p_empty[i], 1); }
-        mbar_init(&bars.o_full, 1);
-        mbar_init(&bars.o_empty, 32);
-        mbar_init(&bars.l_full, 16);
-        mbar_fence_init();
-        tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmS);
-    }
-    if (warp == 0) tmem_alloc_2cta(&tmem_slot, 512);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_slot;
-    bool failed = false;
-    // both CTAs have initialised their barriers; the leader samples the error word for both
-    cluster_arrive();
-    cluster_wait();
-    if (rank == 0 && threadIdx.x == 0) {
-        const unsigned seen = *reinterpret_cast<volatile unsigned *>(p.err);
-        skip_flag = seen;
-        asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_rank(smem_u32(&skip_flag), 1)), "r"(seen) : "memory");
-    }
-    cluster_arrive();
-    cluster_wait();
-    const bool skip = (skip_flag != 0);
-
-    if (skip) {
-        // fall through to the common exit
-    } else if (warp == 0) {
-        if (lane == 0) {
-            int it = 0;
-            for (long long unit = cluster_id; unit < p.n_units && !failed; unit += n_clusters) {
-                const int dp = (int)(unit % p.ndp);
-                const long long bh = unit / p.ndp / nqp;
-                for (int t = 0; t < nblk && !failed; ++t)
-                    for (int vs = 0; vs < TC_BN / TP_VS && !failed; ++vs)
-                        for (int vw = 0; vw < nvw; ++vw, ++it) {
-                            const int s = it % TP2_NV;
-                            const int N = min(TP_VW, DW - vw * TP_VW);   // columns of this stage; this CTA loads half of them
-                            const int ng = N / 128;                      // 64-column groups per CTA
-                            TW_FAIL_AT(8, !mbar_wait_cluster(&bars.v_empty[s], ((it / TP2_NV) & 1) ^ 1, lim));
-                            // the bytes of both CTAs are counted on the leader's barrier
-                            if (rank == 0) mbar_expect_tx(&bars.v_full[s], (uint32_t)(2 * ng * TP_VS * 128));
-                            const uint32_t full0 = map_to_rank(smem_u32(&bars.v_full[s]), 0);
-                            for (int g = 0; g < ng; ++g)
-                                tma_load_2d_2cta(v_smem + (size_t)s * v_stage_bytes + (size_t)g * (TP_VS * 128), &tmV,
-                                                 dp * DW + vw * TP_VW + (int)rank * (N / 2) + g * 64, (int)(bh * p.Lk + t * TC_BN + vs * TP_VS), full0);
-                        }
-            }
-        }
-    } else if (warp == 18) {
-        if (lane == 0) {
-            long long tg = 0;
-            for (long long unit = cluster_id; unit < p.n_units && !failed; unit += n_clusters) {
-                const long long rest = (unit / p.ndp) * 2 + rank;   // = bh * nqt + qt: the row tile of the score matrix
-                for (int t = 0; t < nblk; ++t, ++tg) {
-                    const int pb = (int)(tg % TP2_NP);
-                    TW_FAIL_AT(15, !mbar_wait_cluster(&bars.p_empty[pb], ((tg / TP2_NP) & 1) ^ 1, lim));
-                    mbar_expect_tx(&bars.s_full[pb], TC_P_BYTES);
-                    tma_load_2d(p_smem + (size_t)pb * TC_P_BYTES, &tmS, t * TC_BN, (int)(rest * TW_BM), &bars.s_full[pb]);
-                    tma_load_2d(p_smem + (size_t)pb * TC_P_BYTES + TW_BM * 128, &tmS, t * TC_BN + 64, (int)(rest * TW_BM), &bars.s_full[pb]);
-                }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
-            int it = 0, ui = 0;
-            long long tg = 0;
-            for (long long unit = cluster_id; unit < p.n_units && !failed; unit += n_clusters, ++ui) {
-                // the epilogue of the previous unit has read the accumulator
-                TW_FAIL_AT(9, !mbar_wait_cluster(&bars.o_empty, (ui & 1) ^ 1, lim));
-                tc_fence_after();
-                for (int t = 0; t < nblk && !failed; ++t, ++tg) {
-                    const int pb = (int)(tg % TP2_NP);
-                    TW_FAIL_AT(10, !mbar_wait_cluster(&bars.p_full[pb], (tg / TP2_NP) & 1, lim));
-                    tc_fence_after();
-                    for (int vs = 0; vs < TC_BN / TP_VS && !failed; ++vs)
-                        for (int vw = 0; vw < nvw; ++vw, ++it) {
-                            const int s = it % TP2_NV;
-                            const int N = min(TP_VW, DW - vw * TP_VW);
-                            TW_FAIL_AT(11, !mbar_wait_cluster(&bars.v_full[s], (it / TP2_NV) & 1, lim));
-                            tc_fence_after();
-#pragma unroll
-                            for (int kk = 0; kk < TP_VS / 16; ++kk) {
-                                const int kg = vs * (TP_VS / 16) + kk;   // 16-key step within the block, 0..7
-                                const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TW_BM * 128))) + 2 * (kg & 3);
-                                const uint64_t db = umma_desc_mn_sw128(smem_u32(v_smem + (size_t)s * v_stage_bytes + kk * 2048), TP_VS * 128);
-                                umma_bf16_2cta(tmem + vw * TP_VW, da, db, umma_idesc_bf16(2 * TW_BM, N, 0, 1), (t | kg) != 0);
-                            }
-                            umma_commit_2cta(smem_u32(&bars.v_empty[s]));
-                            umma_commit_2cta(map_to_rank(smem_u32(&bars.v_empty[s]), 1));
-                        }
-                    if (failed) break;
-                    umma_commit_2cta(smem_u32(&bars.p_empty[pb]));
-                    umma_commit_2cta(map_to_rank(smem_u32(&bars.p_empty[pb]), 1));
-                }
-                if (failed) break;
-                umma_commit_2cta(smem_u32(&bars.o_full));
-                umma_commit_2cta(map_to_rank(smem_u32(&bars.o_full), 1));
-            }
-        }
-    } else {
-        // ---- softmax warps: warp w owns rows [8w, 8w+8) of every key block.  Eight lanes cover one
-        // 128-byte row of a 64-key half (conflict-free 16-byte accesses), so a thread works on rows
-        // 8w + lane/8 and 8w + 4 + lane/8, in both halves: four 16-byte pieces per block.  The offset
-        // (tile maximum - row maximum) of row 8w + k for key tile j is kept in lane j of offs[k]. ----
-        const int w = warp - 2, rl = lane >> 3;
-        int ui = 0;
-        long long tg = 0;
-        // lane j keeps (tile maximum - row maximum) of key tile j for each of the warp's eight rows
-        auto load_stats = [&](long long g0, float (&oo)[8]) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float m = lane < p.nkt ? __ldg(p.rowmax + (g0 + k) * p.nkt + lane) : -INFINITY;
-                oo[k] = m - warp_max(m);
-            }
-        };
-        auto grow0_of = [&](long long unit) {
-            const long long rest = (unit / p.ndp) * 2 + rank;
-            return (rest / p.nqt) * p.Lq + (rest % p.nqt) * (long long)TW_BM + 8 * w;
-        };
-        float offs[8], offsn[8];
-        for (long long unit = cluster_id; unit < p.n_units && !failed; unit += n_clusters, ++ui) {
-            const int dp = (int)(unit % p.ndp);
-            const long long rest = (unit / p.ndp) * 2 + rank;
-            const int qt = (int)(rest % p.nqt);
-            const long long bh = rest / p.nqt;
-            const long long grow0 = bh * p.Lq + (long long)qt * TW_BM + 8 * w;
-            // (the statistics of the unit were loaded while the previous unit was finishing)
-            if (ui == 0) load_stats(grow0, offs);
-            float lA = 0.0f, lB = 0.0f, offA = 0.0f, offB = 0.0f;
-            for (int t = 0; t < nblk; ++t, ++tg) {
-                const int pb = (int)(tg % TP2_NP);
-                if ((t & 1) == 0) {   // a new 256-key tile: fetch this thread's two offsets
-                    const int kt = t >> 1;
-                    float v[8];
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) v[k] = __shfl_sync(0xffffffffu, offs[k], kt);
-                    offA = rl == 0 ? v[0] : rl == 1 ? v[1] : rl == 2 ? v[2] : v[3];
-                    offB = rl == 0 ? v[4] : rl == 1 ? v[5] : rl == 2 ? v[6] : v[7];
-                }
-                TW_FAIL_AT(12, !mbar_wait(&bars.s_full[pb], (tg / TP2_NP) & 1, lim));
-                unsigned char *base = p_smem + (size_t)pb * TC_P_BYTES + (8 * w + rl) * 128 + (lane & 7) * 16;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    // i & 1: row A / row B (4 rows = 512 B further); i >> 1: the 64-key half (16 KB further)
-                    uint4 *pp = reinterpret_cast<uint4 *>(base + (i & 1) * 512 + (i >> 1) * (TW_BM * 128));
-                    const uint4 xv = *pp;
-                    const float off = (i & 1) ? offB : offA;
-                    const uint32_t x[4] = {xv.x, xv.y, xv.z, xv.w};
-                    uint32_t o[4];
-                    float sum = 0.0f;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float e0 = fast_exp2(__uint_as_float(x[q] << 16) + off);
-                        const float e1 = fast_exp2(__uint_as_float(x[q] & 0xffff0000u) + off);
-                        sum += e0 + e1;
-                        o[q] = pack_bf16x2(e0, e1);
-                    }
-                    if (i & 1) lB += sum; else lA += sum;
-                    *pp = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.p_full[pb]), 0));   // the leader's barrier counts both CTAs
-            }
-            if (failed) break;
-            const bool have_next = unit + n_clusters < p.n_units;
-            if (have_next) load_stats(grow0_of(unit + n_clusters), offsn);   // lands while this unit drains
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
-                lA += __shfl_xor_sync(0xffffffffu, lA, o);
-                lB += __shfl_xor_sync(0xffffffffu, lB, o);
-            }
-            if ((lane & 7) == 0) { l_smem[ui & 1][8 * w + rl] = lA; l_smem[ui & 1][8 * w + 4 + rl] = lB; }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.l_full);
-            {
-                // ---- epilogue of the unit: O / row sum -> bf16 -> global.  A warp may only read the
-                // TMEM lane quadrant warp % 4; the four warps of a quadrant share its 32-column groups ----
-                const int row = 32 * (warp & 3) + lane;
-                const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
-                TW_FAIL_AT(13, !mbar_wait(&bars.l_full, ui & 1, lim));
-                TW_FAIL_AT(14, !mbar_wait_cluster(&bars.o_full, ui & 1, lim));
-                tc_fence_after();
-                const float inv = 1.0f / l_smem[ui & 1][row];
-                __nv_bfloat16 *orow = p.O + (bh * p.Lq + (long long)qt * TW_BM + row) * (long long)p.D + dp * DW;
-                uint32_t r[32], wds[32];
-                // 64 output columns (128 bytes of the row) at a time; lanes trade pieces so that the
-                // stores cover full lines
-                unsigned char *row0 = reinterpret_cast<unsigned char *>(orow - (long long)(lane & 3) * p.D);
-                for (int cp = (w >> 2); cp < DW / 64; cp += 4) {
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        tmem_ld32(lane_addr + cp * 64 + hh * 32, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int q = 0; q < 16; ++q)
-                            wds[16 * hh + q] = pack_bf16x2(__uint_as_float(r[2 * q]) * inv, __uint_as_float(r[2 * q + 1]) * inv);
-                    }
-                    store_rows_128B_transposed(row0 + cp * 128, (size_t)p.D * 2, wds, lane);
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&bars.o_empty), 0));
-            }
-            if (have_next) {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) offs[k] = offsn[k];
-            }
-        }
-    }
-
-    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    // neither CTA leaves while the pair's MMAs may still read its shared memory
-    cluster_arrive();
-    cluster_wait();
-    if (warp == 0) tmem_dealloc_2cta(tmem, 512);
-}
-
 #undef TW_FAIL_AT
 
 // ---- host side ------------------------------------------------------------------------------------
@@ -1210,7 +942,6 @@ struct TcwScratch {
 };
 
 inline bool tcw_supported(const b200attn_args &a, int rd) {
-    if (getenv("B200ATTN_NO_TC") || getenv("B200ATTN_NO_TC_WIDE")) return false;
     if (a.dtype != B200ATTN_BF16) return false;
     if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 8192) return false;
     if (a.len_q % TW_BM != 0 || a.len_k % TC_BN != 0) return false;
@@ -1228,7 +959,7 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
 // Returns B200ATTN_OK, -1 when the shape should run on another path (also when the scratch could not be
 // allocated: nothing has been launched then), or a status with tc_bf16_error() set.
 inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, TcTables &tables, unsigned *err_dev, unsigned *err_sys, int sm_count,
-                   unsigned spin_limit, cudaStream_t st, std::atomic<unsigned long long> *launches) {
+                   unsigned spin_limit, size_t score_scratch_cap, cudaStream_t st, std::atomic<unsigned long long> *launches) {
     const long long BH = (long long)a.batch_sz * a.num_heads;
     const int D = a.head_d, Lq = a.len_q, Lk = a.len_k;
     const bool encoded = (a.pe != B200ATTN_PE_NONE);              // any encoding: two score launches
@@ -1254,8 +985,6 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
                       cudaFuncSetAttribute(tcw_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
             ok = ok && cudaFuncGetAttributes(&fa, tcw_scores256_kernel) == cudaSuccess &&
                  cudaFuncSetAttribute(tcw_scores256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
-            ok = ok && cudaFuncGetAttributes(&fa, tcw_pv2_kernel) == cudaSuccess &&
-                 cudaFuncSetAttribute(tcw_pv2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
             ok = ok && cudaFuncGetAttributes(&fa, tcw_pv_kernel) == cudaSuccess &&
                  cudaFuncSetAttribute(tcw_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
             if (!ok) { (void)cudaGetLastError(); snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncSetAttribute(max dynamic shared memory) failed"); return B200ATTN_ERR_CUDA; }
@@ -1263,8 +992,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         }
     }
     // heads per pass: the score scratch of one pass stays below a cap (default 2 GiB)
-    size_t cap = (size_t)2 << 30;
-    if (const char *e = getenv("B200ATTN_TCW_SCRATCH_MB")) { long long v = atoll(e); if (v > 0) cap = (size_t)v << 20; }
+    const size_t cap = score_scratch_cap;
     const size_t s_head = (size_t)Lq * Lk * sizeof(__nv_bfloat16);
     long long G = (long long)(cap / s_head);
     if (G < 1) G = 1;
@@ -1306,7 +1034,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         sp.err = err_dev; sp.err_sys = err_sys; sp.spin_limit = spin_limit;
         // launches without the transform use the [256 x 256] tile kernel when the query tiles pair up
         // (and, for the complement of the encoding launch, when both tiles of a pair met the same key tile there)
-        const bool big_ok = (nqt % 2 == 0) && !getenv("B200ATTN_TCW_NO_BM256");
+        const bool big_ok = (nqt % 2 == 0);
         auto launch_scores = [&](const void *Qp, const void *Kp, int mode, int tph) -> int {
             if (tph <= 0) return B200ATTN_OK;
             const bool big = big_ok && (mode == 0 || (mode == 2 && nkt <= nqt && nqt >= 2 * nkt - 1));
@@ -1336,11 +1064,8 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
             rc = launch_scores(Qg, Kg, 0, nqt * nkt);
         }
         if (rc) return rc;
-        // pairs of CTAs working as one (each loads half of the V columns): opt-in, it measured slower
-        const bool pv2 = (nqt % 2 == 0) && (DW % 128 == 0) && sm_count >= 2 && getenv("B200ATTN_TCW_PV2") != nullptr;
         CUtensorMap tmV, tmS;
-        const bool maps_ok = pv2 ? (tc_make_map(&tmV, Vg, nh * Lk, D, TP_VS) && tc_make_map(&tmS, S, nh * Lq, Lk, TW_BM))
-                                 : (make_tmap_grouped(&tmV, Vg, nh * Lk, D, TP_VS, TP_VW / 64) && make_tmap_grouped(&tmS, S, nh * Lq, Lk, TW_BM, 2));
+        const bool maps_ok = make_tmap_grouped(&tmV, Vg, nh * Lk, D, TP_VS, TP_VW / 64) && make_tmap_grouped(&tmS, S, nh * Lq, Lk, TW_BM, 2);
         if (!maps_ok) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
         TcwPvParams pp{};
         pp.Lq = Lq; pp.Lk = Lk; pp.D = D; pp.DW = DW; pp.ndp = ndp; pp.nqt = nqt; pp.nkt = nkt; pp.nblk = nblk;
@@ -1348,12 +1073,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         pp.rowmax = rowmax; pp.O = (__nv_bfloat16 *)a.out + h0 * Lq * D;
         pp.err = err_dev; pp.err_sys = err_sys; pp.spin_limit = spin_limit;
         tcw_timer().begin(2, st);
-        if (pv2) {
-            pp.n_units = nh * (nqt / 2) * ndp;
-            const long long clusters = pp.n_units < sm_count / 2 ? pp.n_units : sm_count / 2;
-            const size_t smem_p2 = (size_t)TP2_NP * TC_P_BYTES + (size_t)TP2_NV * TP_VS * (TP_VW / 2) * 2 + 1024;
-            tcw_pv2_kernel<<<(unsigned)(2 * clusters), TP_THREADS, smem_p2, st>>>(tmV, tmS, pp);
-        } else {
+        {
             const unsigned grid = (unsigned)(pp.n_units < sm_count ? pp.n_units : sm_count);
             tcw_pv_kernel<<<grid, TP_THREADS, smem_p, st>>>(tmV, tmS, pp);
         }

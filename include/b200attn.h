@@ -40,7 +40,10 @@ extern "C" {
 void attention_forward_optimized(const float *Q, const float *K, const float *V, float *out,
                                  int batch_sz, int num_heads, int len_q, int len_k, int head_d);
 
-/* bf16 in/out, fp32 scores, softmax and accumulation.  Replaces attention_forward_bf16,
+/* bf16 in/out; the products accumulate in fp32 and the row maxima, exponentials' sums and the final
+ * division are fp32.  On the default tensor-core path the scores pass through a bf16 scratch (stored
+ * relative to the fp32 maximum of their 256-key tile) and a positional encoding is applied to the bf16
+ * operands with a single rounding.  Replaces attention_forward_bf16,
  * kernels/attention_bf16_optimized_fused.cu:493-505. */
 void attention_forward_bf16(const void *Q, const void *K, const void *V, void *out,
                             int batch_sz, int num_heads, int len_q, int len_k, int head_d);
@@ -115,8 +118,9 @@ enum b200attn_pe {
 
 enum b200attn_flags {
     B200ATTN_FLAG_ASYNC = 1,          /* enqueue only; do not synchronise the stream */
-    B200ATTN_FLAG_FORCE_GENERIC = 2,  /* use the CUDA-core split-head_d kernels even where the tensor-core kernel applies */
-    B200ATTN_FLAG_FORCE_TWO_PASS = 4  /* split-head_d path: two launches instead of the fused cooperative launch */
+    B200ATTN_FLAG_FORCE_GENERIC = 2,  /* use the CUDA-core split-head_d kernels even where a tensor-core kernel applies */
+    B200ATTN_FLAG_FORCE_TWO_PASS = 4, /* split-head_d path: two launches instead of one fused launch */
+    B200ATTN_FLAG_PREFER_ONE_KERNEL = 8 /* bf16: where both tensor-core paths take the shape, run the one-kernel cluster pipeline */
 };
 
 typedef struct b200attn_args {
@@ -136,7 +140,10 @@ typedef struct b200attn_args {
 
 /* The general entry point: validates, launches on args->stream, synchronises that stream unless
  * B200ATTN_FLAG_ASYNC is set.  Never exits the process.  Thread-compatible per device: calls for
- * one device must not overlap in time on different host threads (they share per-device scratch). */
+ * one device must not overlap in time on different host threads.  Calls for one device share scratch
+ * and tables: a call on another stream than the previous call of that device is ordered, on the
+ * device, after everything enqueued on the previous call's stream (so asynchronous calls on several
+ * streams are safe but do not run concurrently). */
 int b200attn_forward_ex(const b200attn_args *args);
 
 /* Enqueues n INDEPENDENT problems (args[i] for i < n) in one call; stops at the first failure.
@@ -181,6 +188,28 @@ void b200attn_release_workspace(void);
 /* Library version string. */
 const char *b200attn_version(void);
 
+/* Process-wide settings (they apply to calls made after the change). */
+enum b200attn_option {
+    B200ATTN_OPT_SCORE_SCRATCH_MB = 1, /* bf16 two-kernel path: cap, in MiB, of the score scratch of one pass over the heads (default 2048) */
+    B200ATTN_OPT_SPIN_LIMIT = 2        /* polls after which a wait inside a kernel gives up and reports B200ATTN_ERR_KERNEL (default 2^21) */
+};
+int b200attn_set_option(int option, long long value);
+
+/* Measurement and test hooks (no counterpart in the reference).
+ * b200attn_debug_kernel_times: enable = 1 / 0 switches per-launch CUDA-event timing of the bf16
+ *   two-kernel path on / off (single-threaded use, one device); with out != NULL the call first
+ *   synchronises the device and returns the summed milliseconds of [encoding score launches, score
+ *   launches, P V launches] in out[0..2] and the launch counts in out[3..5], clearing the record.
+ * b200attn_debug_lost_arrival: failure detection without a fault.  With extra > 0 the per-head barrier
+ *   of the fp32 split-head_d kernels waits (at most spin_limit polls) for arrivals that never come, gives
+ *   up, and the call reports B200ATTN_ERR_KERNEL; (0, 0) restores normal operation.
+ * b200attn_debug_tile_of: host copy of the tile enumeration of the bf16 two-kernel path (big = 0: tile j
+ *   of a head in launch `mode` -> query tile, key tile; big = 1: the 256-row variant); returns the number
+ *   of tiles per head of that launch or -1 when the launch does not exist for the shape.  Needs no GPU. */
+int b200attn_debug_kernel_times(int enable, double *out);
+void b200attn_debug_lost_arrival(unsigned extra, unsigned spin_limit);
+int b200attn_debug_tile_of(int big, int mode, int j, int nqt, int nkt, int *qt, int *kt);
+
 /* fp32 forward without positional encoding that never allocates device memory: its scratch is a
  * fixed array inside the library image (B200ATTN_STATIC_SCRATCH_BYTES per GPU, held from library
  * load to process exit).  For callers that cannot call cudaMalloc when they need attention: code
@@ -188,9 +217,12 @@ const char *b200attn_version(void);
  * afford the implicit synchronisation of an allocation.
  * No counterpart in the reference (its launcher needs no scratch).  Device pointers as for
  * attention_forward_optimized; the work is enqueued on `stream` and NOT waited for.  Limits:
- * len_q, len_k <= 64, batch_sz*num_heads <= SM count, and
+ * len_q, len_k <= 64, batch_sz*num_heads <= SM count,
  * 256 + round_up(8*batch_sz*num_heads, 256) + 4*batch_sz*num_heads*len_q*len_k bytes within the
- * static scratch; beyond them the call returns B200ATTN_ERR_TOO_LARGE and does nothing.  The first
+ * static scratch, and a head's column slices must fit one per SM: with
+ * s = floor(SM count / (batch_sz*num_heads)) slices per head, ceil(head_d / s) <= about 270 columns
+ * (e.g. 148 heads of head_d 8192 are refused); beyond them the call returns B200ATTN_ERR_TOO_LARGE
+ * and does nothing.  The first
  * call on a device does host-side set-up (symbol address, shared-memory limit): make it before any
  * stream capture.  All calls share the one array, so calls that overlap on the GPU race; the kernel's
  * error word is not read back (check the output, or use b200attn_forward_ex).  Message of the last

@@ -55,11 +55,7 @@ def test_bf16_both_paths_against_oracle(pkg, cuda, pe, shape):
     err = float(np.abs(got - want).max())
     assert err <= TOL, (pkg.last_path(), shape, pe, err)
     # the one-kernel cluster pipeline, where it takes the shape
-    os.environ["B200ATTN_TC_PREFER_PAIR"] = "1"
-    try:
-        got = run(pkg, cuda, bits, pe=pe)
-    finally:
-        del os.environ["B200ATTN_TC_PREFER_PAIR"]
+    got = run(pkg, cuda, bits, pe=pe, flags=pkg.FLAG_PREFER_ONE_KERNEL)
     if D <= 512 and D % 64 == 0 and Lq % 128 == 0 and Lk % 128 == 0 and pe != ol.PE_ROPE_HALF:
         assert pkg.last_path() == "tc_bf16"
     err = float(np.abs(got - want).max())
@@ -94,13 +90,8 @@ def test_benchmark_bf16_configs_sampled(pkg, cuda, cfg):
         wants.append(ol.attention_rows(qs, ks, vs, np.zeros(len(rows), np.int64), np.array(rows), pe=pe))
     # the default tensor-core path and, for the shapes it takes, the one-kernel cluster pipeline
     for prefer_pair in ((False, True) if D <= 512 else (False,)):
-        if prefer_pair:
-            os.environ["B200ATTN_TC_PREFER_PAIR"] = "1"
-        try:
-            out = pkg.forward(Q, K, V, pe=pe)
-            torch.cuda.synchronize()
-        finally:
-            os.environ.pop("B200ATTN_TC_PREFER_PAIR", None)
+        out = pkg.forward(Q, K, V, pe=pe, flags=pkg.FLAG_PREFER_ONE_KERNEL if prefer_pair else 0)
+        torch.cuda.synchronize()
         assert pkg.last_path() == ("tc_bf16" if prefer_pair else "tc_wide")
         o = out.view(B * H, L, D)
         for h, want in zip(heads, wants):

@@ -51,11 +51,11 @@ def test_wide_path_in_several_passes_over_the_heads(pkg, cuda):
     B, H, L, D = 1, 5, 512, 1024
     bits, up = bf16_problem(B, H, L, L, D, 72, "normal")
     want = ol.attention(*up, pe=ol.PE_ROPE_HALF)
-    os.environ["B200ATTN_TCW_SCRATCH_MB"] = "1"   # 512 x 512 bf16 scores are 512 KiB per head: two heads per pass
+    pkg.set_option(pkg.OPT_SCORE_SCRATCH_MB, 1)   # 512 x 512 bf16 scores are 512 KiB per head: two heads per pass
     try:
         got = run(pkg, cuda, bits, pe=ol.PE_ROPE_HALF)
     finally:
-        del os.environ["B200ATTN_TCW_SCRATCH_MB"]
+        pkg.set_option(pkg.OPT_SCORE_SCRATCH_MB, 2048)
     assert pkg.last_path() == "tc_wide"
     assert float(np.abs(got - want).max()) <= 8e-3
 
@@ -103,21 +103,3 @@ def test_narrow_heads_on_the_two_kernel_path(pkg, cuda, pe):
     got = run(pkg, cuda, bits, pe=pe)
     assert pkg.last_path() == "tc_wide"
     assert float(np.abs(got - want).max()) <= TOL
-
-
-@pytest.mark.parametrize("shape,pe", [((1, 3, 512, 512, 512), ol.PE_SINUSOIDAL), ((1, 2, 256, 384, 1024), ol.PE_ROPE_HALF),
-                                      ((2, 2, 256, 256, 768), ol.PE_NONE)], ids=["d512", "d1024", "d768"])
-def test_pv_kernel_as_a_pair_of_ctas(pkg, cuda, shape, pe):
-    """B200ATTN_TCW_PV2 selects the P V kernel that runs two CTAs as one (tcgen05 cta_group::2, each CTA
-    loading half of the V columns); it is kept as an option because it measured slower."""
-    B, H, Lq, Lk, D = shape
-    bits, up = bf16_problem(B, H, Lq, Lk, D, 77, "normal")
-    want = ol.attention(*up, pe=pe)
-    os.environ["B200ATTN_TCW_PV2"] = "1"
-    try:
-        got = run(pkg, cuda, bits, pe=pe)
-    finally:
-        del os.environ["B200ATTN_TCW_PV2"]
-    assert pkg.last_path() == "tc_wide"
-    assert float(np.abs(got - want).max()) <= TOL
-    assert np.array_equal(got, run(pkg, cuda, bits, pe=pe)) or float(np.abs(got - run(pkg, cuda, bits, pe=pe)).max()) <= 1e-2

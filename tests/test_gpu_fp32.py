@@ -151,6 +151,46 @@ def test_forward_many_overlaps_consecutive_entries_correctly(pkg, cuda):
         assert ol.compare(o2.cpu().numpy(), want2)["ok"]
 
 
+def test_asynchronous_calls_on_two_streams_share_the_scratch_safely(pkg, cuda):
+    """Two B200ATTN_FLAG_ASYNC calls on two different streams from one thread: the library orders the second
+    after the first on the device (they share per-device scratch and tables), so both are right."""
+    import torch
+    s1, s2 = torch.cuda.Stream(device=cuda), torch.cuda.Stream(device=cuda)
+    cases = []
+    for n, (shape, pe) in enumerate([((1, 4, 64, 64, 2048), ol.PE_NONE), ((1, 4, 64, 64, 4096), ol.PE_NONE),
+                                     ((1, 2, 64, 64, 512), ol.PE_SINUSOIDAL), ((1, 3, 96, 130, 64), ol.PE_ROPE_INTERLEAVED)]):
+        B, H, Lq, Lk, D = shape
+        Q, K, V = ol.make_qkv(B, H, Lq, Lk, D, 70 + n, "uniform")
+        cases.append((Q, K, V, pe) + tuple(to_dev(x, cuda) for x in (Q, K, V)))
+    torch.cuda.synchronize()
+    for rep in range(3):
+        outs = []
+        for n, (Q, K, V, pe, q, k, v) in enumerate(cases):
+            st = (s1, s2)[n % 2]
+            outs.append(pkg.forward(q, k, v, pe=pe, stream=st.cuda_stream, flags=pkg.FLAG_ASYNC))
+        s1.synchronize(); s2.synchronize()
+        for (Q, K, V, pe, q, k, v), o in zip(cases, outs):
+            res = ol.compare(o.cpu().numpy(), ol.attention(Q, K, V, pe=pe))
+            assert res["ok"], (Q.shape, pe, rep, res)
+
+
+def test_hybrid_entry_with_rotary_dim_zero_is_plain_attention(pkg, cuda):
+    """The reference kernel rotates the columns d < rotary_dim (final/rope.cu:129-149): with 0 there is no
+    rotation at all, and the hybrid entry is plain attention on Q and the K it was given."""
+    import torch
+    B, H, L, D = 1, 4, 64, 512
+    Q, K, V = ol.make_qkv(B, H, L, L, D, 52, "uniform")
+    q, k, v = (to_dev(x, cuda) for x in (Q, K, V))
+    got = call_legacy(pkg, "attention_forward_rope_fused_v7_hybrid", q, k, v, extra_ints=(0,))
+    assert ol.compare(got.cpu().numpy(), ol.attention(Q, K, V))["ok"]
+    ref = ol.ref()
+    if ref is not None and hasattr(ref, "ref_attention_forward_rope_fused_v7_hybrid"):
+        ref_out = torch.empty_like(q)
+        torch.cuda.synchronize()
+        ref.ref_attention_forward_rope_fused_v7_hybrid(q.data_ptr(), k.data_ptr(), v.data_ptr(), ref_out.data_ptr(), B, H, L, L, D, 0)
+        assert ol.compare(got.cpu().numpy(), ref_out.cpu().numpy())["ok"]
+
+
 def test_rope_with_caller_supplied_caches_and_hybrid_entry(pkg, cuda):
     B, H, L, D, rd = 1, 4, 64, 512, 128
     Q, K, V = ol.make_qkv(B, H, L, L, D, 46, "uniform")

@@ -59,4 +59,10 @@ def test_static_scratch_entry_rejects_what_does_not_fit(pkg, cuda):
     oo = torch.empty_like(qq)
     assert L.b200attn_forward_static(qq.data_ptr(), qq.data_ptr(), qq.data_ptr(), oo.data_ptr(), 1, 100, 64, 64, 16, st) == 5
     assert b"static scratch" in L.b200attn_static_last_error()
+    # every other limit holds (148 heads x 16 x 16 scores are 150 KB), but a head gets one slice and a slice
+    # of 8192 columns does not fit an SM's shared memory
+    qw = torch.zeros(1, 148, 16, 8192, device=cuda)
+    ow = torch.empty_like(qw)
+    assert L.b200attn_forward_static(qw.data_ptr(), qw.data_ptr(), qw.data_ptr(), ow.data_ptr(), 1, 148, 16, 16, 8192, st) == 5
+    assert b"one slice per SM" in L.b200attn_static_last_error()
     assert L.b200attn_forward_static(None, None, None, None, 1, 1, 4, 4, 8, st) == 1
