@@ -44,16 +44,19 @@ CONFIGS = {
     "cfg5p": ("bf16", "sinusoidal", 1, 16, 4096, 4096, 512, "normal", "tensor"),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (null until a capture exists for the kernel in use)
+# dram__bytes_read.sum + dram__bytes_write.sum from ncu captures of the kernels in use, per STEP (a
+# step of the two-kernel bf16 path is several launches; `achieved` is per step as well); null until a
+# capture exists for the kernel in use
 NCU_TRAFFIC_BYTES = {
-    # per STEP (a step of the two-kernel path is several launches; `achieved` is per step as well)
-    ("cfg5", "tc_wide"): 48.9e9,        # profiles/tcw_kernels_cfg5.md: the 16-head capture (1526.5 MB over the three launches) x 32
-    ("cfg4", "tc_wide"): 5.68e9,        # profiles/tcw_kernels_cfg4.md: the 16-head capture (709.9 MB) x 8
-    ("cfg3", "tc_bf16"): 514.8e6,       # profiles/tc_bf16_pair_kernel_cfg3.md: 402.8 MB read + 112.0 MB written
+    ("cfg5", "tc_wide"): 48.9e9,        # a 16-head capture (1526.5 MB over the three launches) x 32
+    ("cfg4", "tc_wide"): 5.68e9,        # a 16-head capture (709.9 MB) x 8
+    ("cfg3", "tc_bf16"): 514.8e6,       # 402.8 MB read + 112.0 MB written
     ("cfg5", "tc_bf16"): 8 * 2.0**30 + 2 * 2.0**30,   # scaled from the cfg 3 capture by input/output bytes plus the encoded-K scratch
-    ("cfg2c", "splitd_fused"): 33.7e6,  # profiles/splitd_fused_kernel_cfg2c.md: 25.3 MB read, 8.4 MB output
 }
+# nominal fp32 FMA rate of the CUDA cores: 148 SMs x 128 lanes x 2 flops x 1.965 GHz (the fp32 path now
+# does its products on the tensor cores as three tf32 MMAs per product; the figure is reported as the
+# "compute roof" the task statement asks for next to the HBM roof)
+FFMA_ROOF_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 
 def flops_of(cfg):
@@ -153,9 +156,60 @@ def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None):
     return e0.elapsed_time(e1) / steps
 
 
-def fp32_sweep(pkg, torch, dev, pk):
-    """The fp32 small-sequence configurations: L2-cold (rotation through >= 512 MiB of distinct
-    inputs), L2-warm (one set re-used) and single blocking-call latency, each vs the HBM peak."""
+def isolated_launch_us(pkg, torch, sets, pe, reps=60):
+    """Median device time of ONE launch with nothing queued behind or in front of it (CUDA events on the
+    launching stream, the device idle before each): the kernel's own duration plus its launch."""
+    ts = []
+    n = len(sets)
+    for i in range(reps):
+        Q, K, V, O = sets[i % n]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        pkg.forward(Q, K, V, out=O, pe=pe, flags=pkg.FLAG_ASYNC)
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def cpu_full(cfg, threads):
+    """The reference's attention_cpu on the WHOLE problem of an fp32 configuration: with one thread exactly
+    as written, or with the (b,h) slices fanned over `threads` host threads.  Returns seconds."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    _, _, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
+    Q, K, V = ol.make_qkv(B, H, Lq, Lk, D, 42, "uniform")
+    out = np.empty_like(Q)
+    f, ref = ol._f, ol.ref()
+
+    def run(bh0, n):
+        q, k, v, o = (x.reshape(B * H, -1, D)[bh0:bh0 + n] for x in (Q, K, V, out))
+        if ref is not None:
+            ref.ref_attention_cpu(f(q), f(k), f(v), f(o), 1, n, Lq, Lk, D)
+        else:
+            ol.oracle().oracle_attention_pe_f32(f(q), f(k), f(v), f(o), 1, n, Lq, Lk, D, ol.PE_NONE, D, 10000.0, 0, 1)
+    t0 = time.perf_counter()
+    if threads <= 1:
+        run(0, B * H)
+    else:
+        th = [threading.Thread(target=run, args=(i, 1)) for i in range(B * H)]
+        for t in th:
+            t.start()
+        for t in th:
+            t.join()
+    return time.perf_counter() - t0
+
+
+def fp32_sweep(pkg, torch, dev, pk, with_cpu=True):
+    """The fp32 small-sequence configurations.  Per configuration: step time of back-to-back asynchronous
+    launches through b200attn_forward_many, L2-cold (rotation through >= 512 MiB of distinct inputs) and
+    L2-warm (one set re-used); the duration of one isolated launch; a blocking call's host latency; the
+    HBM and compute rooflines; and the reference's CPU attention on the whole problem."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
     out = []
     for cfg in ("cfg1", "cfg2a", "cfg2b", "cfg2c", "cfg2d"):
         nbytes = bytes_of(cfg)
@@ -163,6 +217,7 @@ def fp32_sweep(pkg, torch, dev, pk):
         sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(nsets)]
         cold = min(time_steps(pkg, torch, sets, 0, nsets, nsets if r == 0 else 0) for r in range(3))
         warm = time_steps(pkg, torch, sets[:1], 0, 200, 20)
+        kern = isolated_launch_us(pkg, torch, sets, 0)
         Q, K, V, O = sets[0]
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -170,10 +225,25 @@ def fp32_sweep(pkg, torch, dev, pk):
             pkg.forward(Q, K, V, out=O)
         lat = (time.perf_counter() - t0) / 50 * 1e3
         _, _, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
-        out.append({"config": cfg, "shape": [B, H, Lq, Lk, D], "path": pkg.last_path(), "cold_ms": round(cold, 5),
-                    "warm_ms": round(warm, 5), "blocking_call_ms": round(lat, 5),
-                    "cold_gbs": round(nbytes / cold / 1e6, 1), "cold_tflops": round(flops_of(cfg) / cold / 1e9, 2),
-                    "cold_frac_of_hbm_peak": round(nbytes / cold / 1e6 / pk["hbm_gbs"], 4), "rotation_sets": nsets})
+        tfl = flops_of(cfg) / cold / 1e9
+        row = {"config": cfg, "shape": [B, H, Lq, Lk, D], "path": pkg.last_path(), "cold_ms": round(cold, 5),
+               "warm_ms": round(warm, 5), "blocking_call_ms": round(lat, 5),
+               "isolated_launch_us": round(kern, 2),
+               # step minus isolated launch: negative when consecutive independent launches overlap on the GPU
+               "step_minus_isolated_us": round(cold * 1e3 - kern, 2),
+               "cold_gbs": round(nbytes / cold / 1e6, 1), "cold_tflops": round(tfl, 2),
+               "cold_frac_of_hbm_peak": round(nbytes / cold / 1e6 / pk["hbm_gbs"], 4),
+               "hbm_floor_us": round(nbytes / pk["hbm_gbs"] / 1e3, 2),
+               "frac_of_fp32_compute_roof": round(tfl / FFMA_ROOF_TFLOPS, 4), "fp32_compute_roof_tflops": round(FFMA_ROOF_TFLOPS, 1),
+               "rotation_sets": nsets}
+        if with_cpu:
+            one = cpu_full(cfg, 1)
+            fan = cpu_full(cfg, B * H)
+            row["cpu_baseline"] = {"kind": "reference" if ol.ref() is not None else "port", "sample": "whole problem",
+                                   "single_thread_ms": round(one * 1e3, 2), "fanned_ms": round(fan * 1e3, 2),
+                                   "fanned_threads": B * H, "host_cores": os.cpu_count(),
+                                   "single_thread_tflops": round(flops_of(cfg) / one / 1e12, 6)}
+        out.append(row)
         del sets
         torch.cuda.empty_cache()
     return out
@@ -275,6 +345,51 @@ def reference_arm(args):
     print(json.dumps(line))
 
 
+def torch_sdpa_arm(args):
+    """A timed competitor, never on the product path: torch.nn.functional.scaled_dot_product_attention on
+    the same shapes and dtype (what the reference's final/benchmark_pytorch_wrapper.cu:40-60 measured on
+    its GPU).  The positional encoding of cfg 4 / cfg 5 is NOT applied (torch has no fused equivalent), so
+    those lines time plain attention of the same shape.  Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+    import torch.nn.functional as F
+    dev = torch.device("cuda:0")
+    names = [args.config] if args.config != "cfg5" or args.no_extras else ["cfg1", "cfg2a", "cfg2b", "cfg2c", "cfg2d", "cfg3", "cfg4", "cfg5"]
+    rows = []
+    for cfg in names:
+        dt, pe, B, H, Lq, Lk, D, dist, _ = CONFIGS[cfg]
+        td = torch_dtype(torch, dt)
+        nbytes = bytes_of(cfg)
+        nsets = 1 if nbytes > (200 << 20) else max(2, min(64, (512 << 20) // nbytes))
+        sets = []
+        for i in range(nsets):
+            g = torch.Generator(device=dev).manual_seed(42 + i)
+            mk = (lambda *sh: (torch.rand(*sh, device=dev, generator=g) * 2 - 1).to(td)) if dist == "uniform" else \
+                 (lambda *sh: torch.randn(*sh, device=dev, generator=g).to(td))
+            sets.append((mk(B, H, Lq, D), mk(B, H, Lk, D), mk(B, H, Lk, D)))
+        steps = max(args.steps, nsets)
+        for i in range(max(args.warmup, 3)):
+            F.scaled_dot_product_attention(*sets[i % nsets])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            F.scaled_dot_product_attention(*sets[i % nsets])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        rows.append({"config": cfg, "shape": [B, H, Lq, Lk, D], "dtype": dt, "pe_applied": False, "ms_per_step": ms,
+                     "tflops": flops_of(cfg) / (ms * 1e-3) / 1e12, "gbs_algorithmic": nbytes / (ms * 1e-3) / 1e9})
+        del sets
+        torch.cuda.empty_cache()
+    main_row = next(r for r in rows if r["config"] == args.config)
+    print(json.dumps({"impl": "torch_sdpa", "metric": "attn_fwd_tflops", "value": main_row["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main_row["ms_per_step"], "higher_is_better": True,
+                      "dtype": CONFIGS[args.config][0], "data": "synthetic", "config": workload_config(args.config),
+                      "torch": torch.__version__, "note": "competitor timing only; no positional encoding applied", "configs": rows}))
+
+
 def workload_config(cfg):
     dt, pe, B, H, Lq, Lk, D, dist, bound = CONFIGS[cfg]
     return {"workload": f"{cfg}: {dt} SDPA forward, pe={pe}, B={B} H={H} Lq={Lq} Lk={Lk} head_d={D} per GPU, non-causal",
@@ -288,11 +403,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", default="cfg5", choices=sorted(CONFIGS))
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "torch_sdpa"])
     ap.add_argument("--no-extras", action="store_true", help="skip the fp32 sweep, e2e and CPU baseline legs")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.impl == "torch_sdpa":
+        torch_sdpa_arm(args)
         return
 
     import torch
@@ -375,6 +493,47 @@ def main():
     if clocks:
         line["clocks"] = clocks
 
+    # ---- ONE problem of the configuration cut by (batch, head) over the ranks: rank r runs the contiguous
+    # range of B*H/N flat slices b200attn_shard_ranges gives it (no collective on the data path) ----
+    if world > 1:
+        begin, count = pkg.shard_ranges(B * H, world)
+        nh = count[rank]
+        if nh > 0:
+            shard = tuple(t.view(B * H, -1, D)[:nh].unsqueeze(0) for t in sets[0])   # the bytes differ per rank (seeded by rank); the work is that of the rank's slice range
+            s_ms = time_steps(pkg, torch, [shard], pe, args.steps, warm, barrier)
+        else:
+            barrier(); barrier()
+            s_ms = 0.0
+        t = torch.tensor([s_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        s_max = float(t.item())
+        line["strong"] = {"what": f"one {cfg} problem, its {B * H} (batch, head) slices cut into {world} contiguous ranges, one per GPU",
+                          "slices_per_gpu": count, "ms_per_step": s_max, "value": fl / (s_max * 1e-3) / 1e12, "unit": "TFLOP/s",
+                          "one_gpu_ms_per_step": ms_max,
+                          "speedup_over_one_gpu": ms_max / s_max, "efficiency": ms_max / s_max / world}
+
+    # ---- host -> device copy rate of this rank's PCIe link (pinned memory, one cudaMemcpyAsync per copy) ----
+    h2d_gbs = None
+    if not args.no_extras:
+        try:
+            nb = 1 << 30
+            hsrc = torch.empty(nb, dtype=torch.uint8).pin_memory()
+            ddst = torch.empty(nb, dtype=torch.uint8, device=dev)
+            ddst.copy_(hsrc, non_blocking=True)
+            torch.cuda.synchronize()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                ddst.copy_(hsrc, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize()
+            h2d_gbs = 3 * nb / (e0.elapsed_time(e1) * 1e-3) / 1e9
+            del hsrc, ddst
+        except RuntimeError:
+            h2d_gbs = None
+        torch.cuda.empty_cache()
+
     # ---- end to end through the host-buffer entry point (pinned host memory, copies timed) ----
     if not args.no_extras:
         Q, K, V, O = sets[0]
@@ -405,9 +564,19 @@ def main():
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if float(t[1].item()) == 0.0:
+            h2d_b, d2h_b = esz * B * H * D * (Lq + 2 * Lk), esz * B * H * D * Lq
             line["e2e"] = {"value": fl * world / (float(t[0].item()) * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": float(t[0].item()),
-                           "steps": e2e_steps, "h2d_bytes_per_step": esz * B * H * D * (Lq + 2 * Lk), "d2h_bytes_per_step": esz * B * H * D * Lq,
+                           "steps": e2e_steps, "h2d_bytes_per_step": h2d_b, "d2h_bytes_per_step": d2h_b,
                            "api": "b200attn_forward_host (pinned host buffers)"}
+            tg = torch.tensor([h2d_gbs if h2d_gbs else 0.0], dtype=torch.float64, device=dev)
+            if dist is not None:
+                dist.all_reduce(tg, op=dist.ReduceOp.MIN)
+            if float(tg.item()) > 0:
+                # the copies in (and out, on the other direction of the link) bound the step from below
+                floor_ms = h2d_b / (float(tg.item()) * 1e9) * 1e3
+                line["e2e"].update({"h2d_gbs_measured_min_over_ranks": float(tg.item()), "h2d_floor_ms": floor_ms,
+                                    "frac_of_h2d_roof": floor_ms / float(t[0].item()),
+                                    "bound": "host-to-device link (PCIe): the copies of a step take longer than its kernels"})
         else:
             line["e2e"] = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": esz * B * H * D * (Lq + 2 * Lk),
                            "d2h_bytes_per_step": esz * B * H * D * Lq, "error": e2e_err or "pinned host allocation failed on another rank"}
@@ -417,6 +586,7 @@ def main():
 
     if rank == 0 and world == 1 and not args.no_extras:
         line["fp32_configs"] = fp32_sweep(pkg, torch, dev, pk)
+        line["cpu_baseline_fp32"] = "per configuration in fp32_configs[].cpu_baseline: the reference's attention_cpu on the whole problem"
         cpu = CpuRef(cfg)
         rows = cpu.calibrate(15.0)
         sec, cfl = cpu.run(rows)

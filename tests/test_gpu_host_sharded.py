@@ -71,6 +71,44 @@ def test_sharded_launcher_equals_single_call(pkg, cuda):
     torch.cuda.set_device(0)
 
 
+@pytest.mark.parametrize("dtype,pe,shape", [("f32", "none", (2, 4, 64, 64, 2048)), ("bf16", "sinusoidal", (2, 8, 512, 512, 512)),
+                                            ("bf16", "rope_half", (1, 6, 256, 256, 1024))])
+def test_sharded_launcher_on_different_physical_gpus(pkg, cuda, dtype, pe, shape):
+    """b200attn_forward_sharded with one shard per physical GPU (needs at least two; skipped otherwise):
+    every device runs its contiguous range of (batch, head) slices on its own stream, and the result
+    equals the single-GPU call on the same bytes bit for bit (bf16) or within the fp32 tolerance."""
+    import torch
+    ndev = torch.cuda.device_count()
+    if ndev < 2:
+        pytest.skip("needs two GPUs")
+    B, H, Lq, Lk, D = shape
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    pe_id = {"none": pkg.PE_NONE, "sinusoidal": pkg.PE_SINUSOIDAL, "rope_half": pkg.PE_ROPE_HALF}[pe]
+    Q, K, V = (torch.empty(B, H, L, D, dtype=td, device=cuda) for L in (Lq, Lk, Lk))
+    for t, tid in ((Q, 0), (K, 1), (V, 2)):
+        pkg.synth_fill(t, 75, tid, "uniform" if dtype == "f32" else "normal")
+    want = pkg.forward(Q, K, V, pe=pe_id)
+    torch.cuda.synchronize()
+    G = min(ndev, 4)
+    begin, count = pkg.shard_ranges(B * H, G)
+    parts = []
+    for g in range(G):
+        d = torch.device(f"cuda:{g}")
+        sl = slice(begin[g], begin[g] + count[g])
+        parts.append(tuple(t.view(B * H, -1, D)[sl].to(d) for t in (Q, K, V)) + (torch.empty(count[g], Lq, D, dtype=td, device=d),))
+    arr = lambda i: (C.c_void_p * G)(*[parts[g][i].data_ptr() for g in range(G)])
+    proto = pkg.make_args(None, None, None, None, 0, 0, Lq, Lk, D, pkg.F32 if dtype == "f32" else pkg.BF16, pe=pe_id)
+    for rep in range(2):
+        rc = pkg.lib().b200attn_forward_sharded(C.byref(proto), G, (C.c_int * G)(*range(G)), arr(0), arr(1), arr(2), arr(3), (C.c_int * G)(*count))
+        pkg.check(rc)
+        got = torch.cat([parts[g][3].to(cuda) for g in range(G)]).view(B, H, Lq, D)
+        if dtype == "bf16":
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+        else:
+            assert (got - want).abs().max().item() <= 2e-6
+    torch.cuda.set_device(0)
+
+
 def test_device_generator_matches_host_generator(pkg, cuda):
     import torch
     n = 1 << 16
