@@ -100,3 +100,56 @@ def test_benchmark_bf16_configs_sampled(pkg, cuda, cfg):
             assert err <= TOL, (name, pkg.last_path(), h, err)
         assert bool(torch.isfinite(out.float()).all())
         del out, o
+
+
+# Bounds a regression has to stay under; the tolerance of the task statement is TOL = 2e-2.  Observed on
+# B200 with the stratified sample below: cfg3 1.2e-3, cfg4 1.1e-3, cfg5 1.6e-2.  The sinusoidal
+# configuration is the thin one, and not because of the tables: the encoded operands q + pe, k + pe
+# (magnitude up to 4) are rounded to bf16 once before the product (relative 2^-9 per element, about 3e-3 in
+# a scaled score after 512 columns), and the encoding makes the softmax peaky, so a score error reaches the
+# output undiluted.  Rotated operands (cfg4) are rounded the same way but meet a flat softmax over 2048 keys.
+BENCH_REGRESSION_BOUND = {"cfg3": 2.5e-3, "cfg4": 2.5e-3, "cfg5": 1.9e-2}
+
+
+@pytest.mark.parametrize("name,B,H,L,D,pe", [("cfg3", 8, 16, 1024, 512, ol.PE_NONE), ("cfg4", 4, 32, 2048, 1024, ol.PE_ROPE_HALF),
+                                              ("cfg5", 16, 32, 4096, 512, ol.PE_SINUSOIDAL)], ids=["cfg3", "cfg4", "cfg5"])
+def test_benchmark_bf16_error_on_a_stratified_sample_of_every_head(pkg, cuda, name, B, H, L, D, pe):
+    """The three bf16 benchmark configurations at full size: EVERY (batch, head) slice is checked on 16 query
+    rows (first and last rows, the rows on both sides of the 128- and 256-row tile boundaries, two rows
+    that vary with the head) against the fp32 oracle evaluated on the very bytes the device holds; the
+    configuration without an encoding also on two whole slices.  The maximum error is printed and held
+    under a regression bound well inside the 2e-2 tolerance."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+    import torch
+    Q, K, V = (torch.empty(B * H * L * D, dtype=torch.bfloat16, device=cuda).view(B, H, L, D) for _ in range(3))
+    for t, tid in ((Q, 0), (K, 1), (V, 2)):
+        pkg.synth_fill(t, 45, tid, "normal")
+    out = pkg.forward(Q, K, V, pe=pe)
+    torch.cuda.synchronize()
+    assert pkg.last_path() == "tc_wide"
+    q3, k3, v3, o3 = (t.view(B * H, L, D) for t in (Q, K, V, out))
+    fixed = [0, 1, 126, 127, 128, 129, 255, 256, L // 2 - 1, L // 2, L - 257, L - 256, L - 2, L - 1]
+
+    def rows_of(h):
+        return sorted(set(fixed + [(37 * h + 11) % L, (101 * h + 300) % L]))
+
+    def check(h, rows=None):
+        rows = rows_of(h) if rows is None else rows
+        ridx = torch.tensor(rows, device=cuda)
+        qs = np.zeros((1, 1, L, D), np.float32)
+        qs[0, 0, rows] = bf16_from_dev(q3[h][ridx].contiguous())
+        ks, vs = (bf16_from_dev(t[h].contiguous()).reshape(1, 1, L, D) for t in (k3, v3))
+        want = ol.attention_rows(qs, ks, vs, np.zeros(len(rows), np.int64), np.array(rows), pe=pe)
+        got = bf16_from_dev(o3[h][ridx].contiguous())
+        return float(np.abs(got - want).max())
+
+    with ThreadPoolExecutor(max_workers=min(32, os.cpu_count() or 4)) as ex:
+        errs = list(ex.map(check, range(B * H)))
+        if pe == ol.PE_NONE:
+            errs += list(ex.map(lambda h: check(h, list(range(L))), [3, B * H - 2]))
+    worst = max(errs)
+    print(f"\n[bf16 error] {name}: max_abs {worst:.3e} over {len(errs)} slice checks (mean of per-slice maxima {np.mean(errs):.3e}); "
+          f"regression bound {BENCH_REGRESSION_BOUND[name]:.1e}, tolerance {TOL:.0e}")
+    assert worst <= TOL, (name, worst)
+    assert worst <= BENCH_REGRESSION_BOUND[name], (name, worst)
