@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("B200ATTN_LIB") or os.path.join(_HERE, "lib", "libb200attn.so")
 
 F32, BF16 = 0, 1
-PE_NONE, PE_ROPE_INTERLEAVED, PE_ROPE_HALF, PE_SINUSOIDAL, PE_ROPE_Q_ONLY = 0, 1, 2, 3, 4
+PE_NONE, PE_ROPE_INTERLEAVED, PE_ROPE_HALF, PE_SINUSOIDAL, PE_ROPE_Q_ONLY, PE_ROPE_HALF_Q_ONLY = 0, 1, 2, 3, 4, 5
 FLAG_ASYNC, FLAG_FORCE_GENERIC, FLAG_FORCE_TWO_PASS, FLAG_PREFER_ONE_KERNEL = 1, 2, 4, 8
 OPT_SCORE_SCRATCH_MB, OPT_SPIN_LIMIT = 1, 2
 OK = 0
@@ -84,6 +84,8 @@ def lib():
         L.b200attn_synth_fill.argtypes = [C.c_void_p, C.c_longlong, C.c_ulonglong, C.c_ulonglong, C.c_longlong,
                                           C.c_int, C.c_int, C.c_void_p]
         L.b200attn_synth_fill.restype = C.c_int
+        L.b200attn_rope_k.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 7 + [C.c_float, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.b200attn_rope_k.restype = C.c_int
         L.b200attn_set_option.argtypes = [C.c_int, C.c_longlong]
         L.b200attn_set_option.restype = C.c_int
         L.b200attn_debug_kernel_times.argtypes = [C.c_int, C.POINTER(C.c_double)]
@@ -163,6 +165,21 @@ def forward_host(Q, K, V, out, pe=PE_NONE, rotary_dim=0, rope_base=0.0, flags=0)
     a = make_args(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), B, H, Lq, Lk, D, dtype, pe, rotary_dim,
                   rope_base, None, None, None, flags)
     check(lib().b200attn_forward_host(C.byref(a)))
+    return out
+
+
+def rope_k(X, out=None, pairing=PE_ROPE_INTERLEAVED, rotary_dim=0, rope_base=0.0, pos0=0, cos_cache=None, sin_cache=None, stream=None):
+    """RoPE(X) for a torch CUDA tensor [B,H,L,D] through b200attn_rope_k.  Returns `out`."""
+    import torch
+    B, H, L, D = X.shape
+    if out is None:
+        out = torch.empty_like(X)
+    if stream is None:
+        stream = torch.cuda.current_stream(X.device).cuda_stream
+    with torch.cuda.device(X.device):
+        check(lib().b200attn_rope_k(X.data_ptr(), out.data_ptr(), B, H, L, D, F32 if X.dtype == torch.float32 else BF16, pairing, rotary_dim,
+                                    rope_base, pos0, cos_cache.data_ptr() if cos_cache is not None else None,
+                                    sin_cache.data_ptr() if sin_cache is not None else None, stream))
     return out
 
 

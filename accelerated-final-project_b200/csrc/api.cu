@@ -17,6 +17,7 @@
 #include "../../include/b200attn.h"
 #include "splitd.cuh"
 #include "splitd_tc.cuh"
+#include "rope_k.cuh"
 #include "synth.cuh"
 #include "tc_bf16.cuh"
 #include "tc_wide.cuh"
@@ -447,13 +448,13 @@ static int validate(const b200attn_args *a, int *rd_out, float *base_out) {
         return fail(B200ATTN_ERR_INVALID_ARG, "batch_sz, num_heads, len_q, len_k, head_d must be positive (got %d,%d,%d,%d,%d)",
                     a->batch_sz, a->num_heads, a->len_q, a->len_k, a->head_d);
     if (a->dtype != B200ATTN_F32 && a->dtype != B200ATTN_BF16) return fail(B200ATTN_ERR_INVALID_ARG, "unknown dtype %d", a->dtype);
-    if (a->pe < B200ATTN_PE_NONE || a->pe > B200ATTN_PE_ROPE_Q_ONLY) return fail(B200ATTN_ERR_INVALID_ARG, "unknown pe kind %d", a->pe);
+    if (a->pe < B200ATTN_PE_NONE || a->pe > B200ATTN_PE_ROPE_HALF_Q_ONLY) return fail(B200ATTN_ERR_INVALID_ARG, "unknown pe kind %d", a->pe);
     const size_t esz = a->dtype == B200ATTN_F32 ? 4 : 2;
     if (((uintptr_t)a->Q | (uintptr_t)a->K | (uintptr_t)a->V | (uintptr_t)a->out) & (esz - 1))
         return fail(B200ATTN_ERR_INVALID_ARG, "tensor pointers must be aligned to the element size");
     if (a->out == a->Q || a->out == a->K || a->out == a->V) return fail(B200ATTN_ERR_INVALID_ARG, "out must not alias an input");
     int rd = a->rotary_dim == 0 ? a->head_d : a->rotary_dim;
-    const bool rope = a->pe == B200ATTN_PE_ROPE_INTERLEAVED || a->pe == B200ATTN_PE_ROPE_HALF || a->pe == B200ATTN_PE_ROPE_Q_ONLY;
+    const bool rope = pe_is_rope(a->pe);
     if (rope) {
         if (rd < 0 || rd > a->head_d || (rd & 1))
             return fail(B200ATTN_ERR_INVALID_ARG, "rotary_dim must be even and within [0, head_d] (got %d, head_d %d)", rd, a->head_d);
@@ -844,6 +845,35 @@ int b200attn_debug_tile_of(int big, int mode, int j, int nqt, int nkt, int *qt, 
         tcw_tile_of(mode, j, nqt, nkt, qt, kt);
     }
     return count;
+}
+
+int b200attn_rope_k(const void *X, void *X_rot, int batch_sz, int num_heads, int len, int head_d, int dtype, int pairing,
+                    int rotary_dim, float rope_base, int pos0, const float *cos_cache, const float *sin_cache, void *stream) {
+    if (!X || !X_rot || batch_sz <= 0 || num_heads <= 0 || len <= 0 || head_d <= 0 || pos0 < 0)
+        return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_rope_k: NULL pointer, non-positive size or negative position");
+    if (dtype != B200ATTN_F32 && dtype != B200ATTN_BF16) return fail(B200ATTN_ERR_INVALID_ARG, "unknown dtype %d", dtype);
+    if (pairing != B200ATTN_PE_ROPE_INTERLEAVED && pairing != B200ATTN_PE_ROPE_HALF)
+        return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_rope_k: pairing must be B200ATTN_PE_ROPE_INTERLEAVED or B200ATTN_PE_ROPE_HALF");
+    const int rd = rotary_dim == 0 ? head_d : rotary_dim;
+    if (rd < 0 || rd > head_d || (rd & 1)) return fail(B200ATTN_ERR_INVALID_ARG, "rotary_dim must be even and within [0, head_d] (got %d, head_d %d)", rd, head_d);
+    if ((cos_cache == nullptr) != (sin_cache == nullptr)) return fail(B200ATTN_ERR_INVALID_ARG, "cos_cache and sin_cache must be given together");
+    const float base = rope_base == 0.0f ? 10000.0f : rope_base;
+    if (!(base > 0.0f)) return fail(B200ATTN_ERR_INVALID_ARG, "rope_base must be positive");
+    const size_t esz = dtype == B200ATTN_F32 ? 4 : 2;
+    if (((uintptr_t)X | (uintptr_t)X_rot) & (esz - 1)) return fail(B200ATTN_ERR_INVALID_ARG, "tensor pointers must be aligned to the element size");
+    DeviceCtx *c;
+    int rc = get_ctx(&c);
+    if (rc) return rc;
+    RopeKParams p{};
+    p.X = X; p.Y = X_rot;
+    p.BH = (long long)batch_sz * num_heads; p.L = len; p.D = head_d; p.rd = rd;
+    p.half = pairing == B200ATTN_PE_ROPE_HALF ? 1 : 0;
+    p.pos0 = pos0; p.base = base; p.cos_cache = cos_cache; p.sin_cache = sin_cache;
+    cudaError_t e = dtype == B200ATTN_F32 ? launch_rope_k<float>(p, c->sm_count, (cudaStream_t)stream)
+                                          : launch_rope_k<__nv_bfloat16>(p, c->sm_count, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "CUDA error %d (%s) launching the rotation kernel", (int)e, cudaGetErrorString(e));
+    g_launches.fetch_add(1);
+    return B200ATTN_OK;
 }
 
 int b200attn_set_option(int option, long long value) {

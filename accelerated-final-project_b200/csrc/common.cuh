@@ -19,7 +19,10 @@
 namespace b200attn {
 
 // Positional-encoding selector; values match enum b200attn_pe in include/b200attn.h.
-enum PeKind : int { PE_NONE = 0, PE_ROPE_INTERLEAVED = 1, PE_ROPE_HALF = 2, PE_SINUSOIDAL = 3, PE_ROPE_Q_ONLY = 4 };
+enum PeKind : int { PE_NONE = 0, PE_ROPE_INTERLEAVED = 1, PE_ROPE_HALF = 2, PE_SINUSOIDAL = 3, PE_ROPE_Q_ONLY = 4, PE_ROPE_HALF_Q_ONLY = 5 };
+__host__ __device__ __forceinline__ bool pe_pairs_halves(int pe) { return pe == PE_ROPE_HALF || pe == PE_ROPE_HALF_Q_ONLY; }
+__host__ __device__ __forceinline__ bool pe_is_rope(int pe) { return pe == PE_ROPE_INTERLEAVED || pe == PE_ROPE_HALF || pe == PE_ROPE_Q_ONLY || pe == PE_ROPE_HALF_Q_ONLY; }
+__host__ __device__ __forceinline__ bool pe_encodes_k(int pe) { return pe != PE_NONE && pe != PE_ROPE_Q_ONLY && pe != PE_ROPE_HALF_Q_ONLY; }
 
 // Error bits a kernel may OR into its error word (read back by the host after the launch).
 enum KernelErr : unsigned {

@@ -51,7 +51,7 @@ struct SplitDParams {
 // (2t, 2t+1): identity for every kind except rotate-half, where virtual 2t is physical t and
 // virtual 2t+1 is physical t + rotary_dim/2.  Q and K use the same order, so scores are unchanged.
 __device__ __forceinline__ int phys_col(int v, int pe, int rd) {
-    return (pe == PE_ROPE_HALF && v < rd) ? ((v >> 1) + (v & 1) * (rd >> 1)) : v;
+    return (pe_pairs_halves(pe) && v < rd) ? ((v >> 1) + (v & 1) * (rd >> 1)) : v;
 }
 
 // Loads rows [0, rows) x virtual columns [v0, v0+w) of a [*, D] matrix into shared memory as fp32
@@ -62,8 +62,8 @@ __device__ void load_slice(float *dst, int pitch, const T *src, int rows, int ro
                            int D, int v0, int w, int pe, int rd, bool apply_pe,
                            const float *freq_s, const float *cos_cache, const float *sin_cache) {
     const int ngroups = (w + 7) >> 3;
-    const bool half = (pe == PE_ROPE_HALF);
-    const bool rope = apply_pe && (pe == PE_ROPE_INTERLEAVED || pe == PE_ROPE_HALF || pe == PE_ROPE_Q_ONLY);
+    const bool half = pe_pairs_halves(pe);
+    const bool rope = apply_pe && pe_is_rope(pe);
     const bool sinus = apply_pe && (pe == PE_SINUSOIDAL);
     constexpr int VEC = 16 / (int)sizeof(T);  // elements per 16-byte vector: 4 (fp32) or 8 (bf16)
     const bool base_aligned = ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
@@ -336,7 +336,7 @@ splitd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             __syncthreads();
         }
         load_slice<T>(Qs, pitch, Qg, Lq, rq_pad, 0, D, v0, w, p.pe, p.rotary_dim, true, freq_s, p.cos_cache, p.sin_cache);
-        load_slice<T>(Ks, pitch, Kg, Lk, rk_pad, 0, D, v0, w, p.pe, p.rotary_dim, p.pe != PE_ROPE_Q_ONLY, freq_s,
+        load_slice<T>(Ks, pitch, Kg, Lk, rk_pad, 0, D, v0, w, p.pe, p.rotary_dim, pe_encodes_k(p.pe), freq_s,
                       p.cos_cache, p.sin_cache);
         load_slice<T>(Vs, pitch, Vg, Lk, Lk, 0, D, v0, w, PE_NONE, 0, false, nullptr, nullptr, nullptr);
     }
@@ -510,7 +510,7 @@ __global__ void __launch_bounds__(SD_THREADS) splitd_scores_kernel(const SplitDP
             __syncthreads();
         }
         load_slice<T>(Qs, pitch, Qg, nq, rq_pad, i0, p.D, v0, w, p.pe, p.rotary_dim, true, freq_s, p.cos_cache, p.sin_cache);
-        load_slice<T>(Ks, pitch, Kg, nk, rk_pad, j0, p.D, v0, w, p.pe, p.rotary_dim, p.pe != PE_ROPE_Q_ONLY, freq_s,
+        load_slice<T>(Ks, pitch, Kg, nk, rk_pad, j0, p.D, v0, w, p.pe, p.rotary_dim, pe_encodes_k(p.pe), freq_s,
                       p.cos_cache, p.sin_cache);
         __syncthreads();
         qk_dispatch(Qs, Ks, pitch, (w + 3) & ~3, nq, nk, acc);

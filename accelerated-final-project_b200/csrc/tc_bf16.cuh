@@ -694,7 +694,7 @@ inline bool tc_bf16_supported(const b200attn_args &a, int rd) {
     if (a.dtype != B200ATTN_BF16) return false;
     if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 512) return false;
     if (a.len_q % TC_BM != 0 || a.len_k % TC_BN != 0) return false;
-    if (a.pe == B200ATTN_PE_ROPE_HALF) return false;
+    if (pe_pairs_halves(a.pe)) return false;
     if (a.pe != B200ATTN_PE_NONE && a.pe != B200ATTN_PE_SINUSOIDAL && (rd % 8 != 0)) return false;
     if (a.cos_cache != nullptr) return false;
     if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return false;

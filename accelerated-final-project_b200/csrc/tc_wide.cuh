@@ -886,6 +886,29 @@ __global__ void tcw_build_half_table(__nv_bfloat16 *table, int L, int D, float b
     }
 }
 
+// The same two table layouts filled from caller-supplied caches [cache_rows][rd] (value of pair i at columns
+// 2i and 2i+1, final/rope.cu:20-40) instead of computed angles: half != 0 gives the rotate-half layout
+// (needs rd == D), otherwise the element-wise partner layout of tc_build_pe_table (cos at even columns, sin
+// at odd ones, identity beyond rd).  Rows beyond the cache are the identity rotation (no real key or query
+// has those positions).
+__global__ void tcw_table_from_cache(__nv_bfloat16 *table, int L, int D, int rd, int half, int cache_rows, const float *cos_cache,
+                                     const float *sin_cache) {
+    const long long n = (long long)L * D;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int pos = (int)(i / D), d = (int)(i % D);
+        float v;
+        if (half) {
+            const int f = d < (D >> 1) ? d : d - (D >> 1);
+            v = d < (D >> 1) ? 1.0f : 0.0f;
+            if (pos < cache_rows) v = d < (D >> 1) ? cos_cache[(long long)pos * rd + 2 * f] : sin_cache[(long long)pos * rd + 2 * f];
+        } else {
+            v = (d & 1) ? 0.0f : 1.0f;
+            if (pos < cache_rows && d < rd) v = (d & 1) ? sin_cache[(long long)pos * rd + d] : cos_cache[(long long)pos * rd + d];
+        }
+        table[i] = __float2bfloat16_rn(v);
+    }
+}
+
 // Optional per-kernel timing (b200attn_debug_kernel_times): while it is switched on, every launch of
 // this path is bracketed by two events on its stream; the sums per kernel kind are collected after
 // a synchronisation.  Kinds: 0 = score kernel, encoding launch; 1 = score kernel; 2 = P V kernel.
@@ -921,8 +944,8 @@ inline TcwTimer &tcw_timer() { static TcwTimer t; return t; }
 
 // Scratch of the wide path, kept per device and grown on demand.
 struct TcwScratch {
-    void *buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};   // S, rowmax, rotated Q, rotated K, table
-    size_t bytes[5] = {0, 0, 0, 0, 0};
+    void *buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // S, rowmax, rotated Q, rotated K, table, table made from caller caches
+    size_t bytes[6] = {0, 0, 0, 0, 0, 0};
     int tab_L = 0, tab_D = 0;
     float tab_base = 0.0f;
     void *get(int i, size_t want) {
@@ -936,7 +959,7 @@ struct TcwScratch {
         return buf[i];
     }
     void release() {
-        for (int i = 0; i < 5; ++i) { if (buf[i]) cudaFree(buf[i]); buf[i] = nullptr; bytes[i] = 0; }
+        for (int i = 0; i < 6; ++i) { if (buf[i]) cudaFree(buf[i]); buf[i] = nullptr; bytes[i] = 0; }
         tab_L = 0;
     }
 };
@@ -946,9 +969,9 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
     if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 8192) return false;
     if (a.len_q % TW_BM != 0 || a.len_k % TC_BN != 0) return false;
     if (a.len_k > 32 * TW_BN) return false;   // the offsets of a row's key tiles live one per lane
-    if (a.pe == B200ATTN_PE_ROPE_HALF) { if (a.head_d % 128 != 0 || rd != a.head_d) return false; }
+    if (a.cos_cache != nullptr && !pe_is_rope(a.pe)) return false;
+    if (pe_pairs_halves(a.pe)) { if (a.head_d % 128 != 0 || rd != a.head_d) return false; }
     else if (a.pe != B200ATTN_PE_NONE) { if (a.head_d % 128 != 0 || (a.pe != B200ATTN_PE_SINUSOIDAL && rd % 8 != 0)) return false; }
-    if (a.cos_cache != nullptr) return false;
     if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return false;
     if (((uintptr_t)a.out & 31) != 0) return false;   // the epilogue stores 32 bytes at a time
     const long long BH = (long long)a.batch_sz * a.num_heads;
@@ -963,8 +986,8 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
     const long long BH = (long long)a.batch_sz * a.num_heads;
     const int D = a.head_d, Lq = a.len_q, Lk = a.len_k;
     const bool encoded = (a.pe != B200ATTN_PE_NONE);              // any encoding: two score launches
-    const bool pair_half = (a.pe == B200ATTN_PE_ROPE_HALF);
-    const bool rotate_k = (a.pe != B200ATTN_PE_ROPE_Q_ONLY);
+    const bool pair_half = pe_pairs_halves(a.pe);
+    const bool rotate_k = pe_encodes_k(a.pe);
     int ndp = 1;
     while (D % (64 * ndp) != 0 || D / ndp > 512) ++ndp;
     const int DW = D / ndp;
@@ -1006,7 +1029,13 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         ks = (__nv_bfloat16 *)sc.get(3, (size_t)G * Lk * D * 2);
         const int Lt = (Lq > nkt * TW_BN ? Lq : nkt * TW_BN);
         if (!qs || !ks) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the rotated-operand scratch"); return -1; }
-        if (pair_half) {
+        if (a.cos_cache != nullptr) {
+            // the caller's angles: the table is rebuilt on every call (the caches may have changed)
+            tab = (__nv_bfloat16 *)sc.get(5, (size_t)Lt * D * 2);
+            if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the cos/sin table"); return -1; }
+            tcw_table_from_cache<<<296, 256, 0, st>>>(tab, Lt, D, rd, pair_half ? 1 : 0, Lq > Lk ? Lq : Lk, a.cos_cache, a.sin_cache);
+            launches->fetch_add(1);
+        } else if (pair_half) {
             const bool have = sc.buf[4] && sc.tab_L >= Lt && sc.tab_D == D && sc.tab_base == base;
             tab = (__nv_bfloat16 *)(have ? sc.buf[4] : sc.get(4, (size_t)Lt * D * 2));
             if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the cos/sin table"); return -1; }
@@ -1030,7 +1059,8 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         sp.Lq = Lq; sp.Lk = Lk; sp.D = D; sp.nch = D / 64; sp.nqt = nqt; sp.nkt = nkt;
         sp.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
         sp.S = S; sp.rowmax = rowmax; sp.tab = tab; sp.q_store = qs; sp.k_store = ks;
-        sp.pe = a.pe == B200ATTN_PE_ROPE_Q_ONLY ? (int)PE_ROPE_INTERLEAVED : a.pe; sp.rotate_k = rotate_k ? 1 : 0;
+        sp.pe = a.pe == B200ATTN_PE_ROPE_Q_ONLY ? (int)PE_ROPE_INTERLEAVED : a.pe == B200ATTN_PE_ROPE_HALF_Q_ONLY ? (int)PE_ROPE_HALF : a.pe;
+        sp.rotate_k = rotate_k ? 1 : 0;
         sp.err = err_dev; sp.err_sys = err_sys; sp.spin_limit = spin_limit;
         // launches without the transform use the [256 x 256] tile kernel when the query tiles pair up
         // (and, for the complement of the encoding launch, when both tiles of a pair met the same key tile there)

@@ -113,7 +113,8 @@ enum b200attn_pe {
     B200ATTN_PE_ROPE_INTERLEAVED = 1, /* pairs (2i, 2i+1), final/rope.cu:138-149 */
     B200ATTN_PE_ROPE_HALF = 2,        /* pairs (i, i + rotary_dim/2) ("rotate-half") */
     B200ATTN_PE_SINUSOIDAL = 3,       /* additive, final/sinusoidal.cu:143-161 */
-    B200ATTN_PE_ROPE_Q_ONLY = 4       /* interleaved on Q only; K is pre-rotated, final/rope.cu:102-228 */
+    B200ATTN_PE_ROPE_Q_ONLY = 4,      /* interleaved on Q only; K is pre-rotated, final/rope.cu:102-228 */
+    B200ATTN_PE_ROPE_HALF_Q_ONLY = 5  /* rotate-half on Q only; K is pre-rotated (e.g. by b200attn_rope_k) */
 };
 
 enum b200attn_flags {
@@ -132,7 +133,7 @@ typedef struct b200attn_args {
     int pe;                  /* enum b200attn_pe */
     int rotary_dim;          /* RoPE kinds: even, <= head_d; 0 means head_d */
     float rope_base;         /* RoPE kinds: theta; 0 means 10000 */
-    const float *cos_cache;  /* optional (RoPE interleaved/half/q-only): device [max(Lq,Lk), rotary_dim] caches */
+    const float *cos_cache;  /* optional (all RoPE kinds): device [max(Lq,Lk), rotary_dim] caches */
     const float *sin_cache;  /*   in the precompute_rope_cache layout; NULL = angles computed by the library */
     void *stream;            /* cudaStream_t; NULL = legacy default stream */
     unsigned flags;          /* enum b200attn_flags */
@@ -187,6 +188,18 @@ void b200attn_release_workspace(void);
 
 /* Library version string. */
 const char *b200attn_version(void);
+
+/* "Rotate once and keep it": X_rot = RoPE(X) for a device tensor X [B,H,len,head_d] (fp32 or bf16), the
+ * first rotary_dim columns rotated and the rest copied; row l of every (b,h) slice has position pos0 + l
+ * (pos0 > 0 when keys are appended to a cache).  A KV-cache caller rotates K with this once and then calls
+ * attention with a *_Q_ONLY encoding.  pairing is B200ATTN_PE_ROPE_INTERLEAVED or B200ATTN_PE_ROPE_HALF;
+ * rotary_dim 0 means head_d; rope_base 0 means 10000; cos_cache / sin_cache are optional device caches
+ * [>= pos0 + len][rotary_dim] in the precompute_rope_cache layout (NULL: angles computed with the fp32
+ * arithmetic of that function, final/rope.cu:20-40).  X_rot may be X (in place).  Enqueued on `stream`, not
+ * waited for.  Replaces rope_kernel, final/rope.cu:1240-1280, as used by attention_forward_separate_rope
+ * (final/rope.cu:1379-1416); that kernel takes the position modulo 64 (:1257), this one does not. */
+int b200attn_rope_k(const void *X, void *X_rot, int batch_sz, int num_heads, int len, int head_d, int dtype, int pairing,
+                    int rotary_dim, float rope_base, int pos0, const float *cos_cache, const float *sin_cache, void *stream);
 
 /* Process-wide settings (they apply to calls made after the change). */
 enum b200attn_option {

@@ -11,6 +11,7 @@ sys.path.insert(0, os.path.join(ROOT, "oracle"))
 import build as oracle_build  # noqa: E402
 
 PE_NONE, PE_ROPE_INTERLEAVED, PE_ROPE_HALF, PE_SINUSOIDAL, PE_ROPE_Q_ONLY = 0, 1, 2, 3, 4
+PE_ROPE_HALF_Q_ONLY = 5   # the library rotates Q only; the oracle is given the rotated K (see apply_rope)
 
 _fp = C.POINTER(C.c_float)
 _i64 = C.c_longlong
@@ -103,6 +104,22 @@ def rope_cache(max_len, rotary_dim, base=10000.0):
     s = np.empty((max_len, rotary_dim), dtype=np.float32)
     oracle().oracle_rope_cache(_f(c), _f(s), max_len, rotary_dim, base)
     return c, s
+
+
+def apply_rope(X, half=False, rotary_dim=None, base=10000.0, pos0=0):
+    """RoPE of every (b,h) slice of X [B,H,L,D] with positions pos0 + l: oracle_apply_rope_interleaved
+    (final/rope.cu:1418-1437) or its rotate-half counterpart, on caches from oracle_rope_cache."""
+    X = np.ascontiguousarray(X, dtype=np.float32)
+    B, H, L, D = X.shape
+    rd = D if rotary_dim is None else rotary_dim
+    c, s = rope_cache(pos0 + L, rd, base)
+    c, s = np.ascontiguousarray(c[pos0:]), np.ascontiguousarray(s[pos0:])
+    out = np.empty_like(X)
+    fn = oracle().oracle_apply_rope_half if half else oracle().oracle_apply_rope_interleaved
+    xf, of = X.reshape(B * H, L, D), out.reshape(B * H, L, D)
+    for i in range(B * H):
+        fn(_f(xf[i]), _f(of[i]), _f(c), _f(s), L, D, rd)
+    return out
 
 
 def sinusoidal_tables(max_len, D):
