@@ -944,8 +944,9 @@ inline TcwTimer &tcw_timer() { static TcwTimer t; return t; }
 
 // Scratch of the wide path, kept per device and grown on demand.
 struct TcwScratch {
-    void *buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // S, rowmax, rotated Q, rotated K, table, table made from caller caches
-    size_t bytes[6] = {0, 0, 0, 0, 0, 0};
+    // S, rowmax, rotated Q, rotated K, table, table made from caller caches, key-split partial outputs, their (max, sum)
+    void *buf[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t bytes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     int tab_L = 0, tab_D = 0;
     float tab_base = 0.0f;
     void *get(int i, size_t want) {
@@ -959,10 +960,24 @@ struct TcwScratch {
         return buf[i];
     }
     void release() {
-        for (int i = 0; i < 6; ++i) { if (buf[i]) cudaFree(buf[i]); buf[i] = nullptr; bytes[i] = 0; }
+        for (int i = 0; i < 8; ++i) { if (buf[i]) cudaFree(buf[i]); buf[i] = nullptr; bytes[i] = 0; }
         tab_L = 0;
     }
 };
+
+// The rotate-half cos/sin table [>= Lt][D] for `base`, kept between calls; nullptr when it cannot be allocated.
+inline __nv_bfloat16 *tcw_half_table(TcwScratch &sc, int Lt, int D, float base, cudaStream_t st, std::atomic<unsigned long long> *launches) {
+    const bool have = sc.buf[4] && sc.tab_L >= Lt && sc.tab_D == D && sc.tab_base == base;
+    __nv_bfloat16 *tab = (__nv_bfloat16 *)(have ? sc.buf[4] : sc.get(4, (size_t)Lt * D * 2));
+    if (!tab) return nullptr;
+    if (!have) {
+        if (sc.tab_L != 0) cudaDeviceSynchronize();   // no kernel may still be reading the table that is replaced
+        tcw_build_half_table<<<296, 256, 0, st>>>(tab, Lt, D, base);
+        launches->fetch_add(1);
+        sc.tab_L = Lt; sc.tab_D = D; sc.tab_base = base;
+    }
+    return tab;
+}
 
 inline bool tcw_supported(const b200attn_args &a, int rd) {
     if (a.dtype != B200ATTN_BF16) return false;
@@ -1036,15 +1051,8 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
             tcw_table_from_cache<<<296, 256, 0, st>>>(tab, Lt, D, rd, pair_half ? 1 : 0, Lq > Lk ? Lq : Lk, a.cos_cache, a.sin_cache);
             launches->fetch_add(1);
         } else if (pair_half) {
-            const bool have = sc.buf[4] && sc.tab_L >= Lt && sc.tab_D == D && sc.tab_base == base;
-            tab = (__nv_bfloat16 *)(have ? sc.buf[4] : sc.get(4, (size_t)Lt * D * 2));
+            tab = tcw_half_table(sc, Lt, D, base, st, launches);
             if (!tab) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the cos/sin table"); return -1; }
-            if (!have) {
-                if (sc.tab_L != 0) cudaDeviceSynchronize();   // no kernel may still be reading the table that is replaced
-                tcw_build_half_table<<<296, 256, 0, st>>>(tab, Lt, D, base);
-                launches->fetch_add(1);
-                sc.tab_L = Lt; sc.tab_D = D; sc.tab_base = base;
-            }
         } else {
             int rows = 0;
             tab = tables.get(a.pe, Lt, D, rd, a.pe == B200ATTN_PE_SINUSOIDAL ? 10000.0f : base, st, launches, &rows);

@@ -28,7 +28,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-PE = {"none": 0, "rope_half": 2, "sinusoidal": 3}
+PE = {"none": 0, "rope_half": 2, "sinusoidal": 3, "rope_half_q_only": 5}
 CONFIGS = {
     # name: (dtype, pe, B, H, Lq, Lk, D, dist, bound)
     "cfg1": ("f32", "none", 1, 4, 64, 64, 2048, "uniform", "hbm"),
@@ -39,6 +39,9 @@ CONFIGS = {
     "cfg3": ("bf16", "none", 8, 16, 1024, 1024, 512, "normal", "tensor"),
     "cfg4": ("bf16", "rope_half", 4, 32, 2048, 2048, 1024, "normal", "tensor"),
     "cfg5": ("bf16", "sinusoidal", 16, 32, 4096, 4096, 512, "normal", "tensor"),
+    # the decode regime (few queries against a long key cache): K rotated beforehand (KV-cache use) / in the load
+    "decode": ("bf16", "rope_half_q_only", 1, 32, 4, 32768, 128, "normal", "hbm"),
+    "decode_rope": ("bf16", "rope_half", 1, 32, 4, 32768, 128, "normal", "hbm"),
     # profiling-size variants of cfg4 and cfg5 (16 heads): small enough for a multi-pass ncu capture
     "cfg4p": ("bf16", "rope_half", 1, 16, 2048, 2048, 1024, "normal", "tensor"),
     "cfg5p": ("bf16", "sinusoidal", 1, 16, 4096, 4096, 512, "normal", "tensor"),
@@ -275,7 +278,8 @@ class CpuRef:
         L = max(Lq, Lk)
         if pe == "sinusoidal":
             self.t0, self.t1 = ol.sinusoidal_tables(L, D)
-        elif pe == "rope_half":
+        elif pe in ("rope_half", "rope_half_q_only"):   # (q-only: the CPU code rotates K itself, the same mathematics)
+            pe = self.pe = "rope_half"
             self.t0, self.t1 = ol.rope_cache(L, D)
             perm = np.empty(D, dtype=np.int64)   # rotate-half == interleaved under this column order
             perm[0::2] = np.arange(D // 2)

@@ -176,8 +176,10 @@ void b200attn_shard_ranges(long long total_bh, int n_parts, long long *begin, lo
 const char *b200attn_last_error(void);
 
 /* Name of the kernel path the last successful b200attn_forward_ex on this thread used:
- * "splitd_fused", "splitd_two_pass", "tc_wide" (bf16 on the tensor cores: score kernel, then P V kernel)
- * or "tc_bf16" (bf16 on the tensor cores, one-kernel cluster pipeline). */
+ * "splitd_tc" (fp32, short sequences, tensor cores with error-compensated tf32), "splitd_fused" and
+ * "splitd_two_pass" (CUDA cores), "tc_wide" (bf16 on the tensor cores: score kernel, then P V kernel),
+ * "tc_bf16" (bf16 on the tensor cores, one-kernel cluster pipeline) or "tc_decode" (bf16, up to 64 queries
+ * against a long K/V: key splits on the tensor cores plus a combine kernel). */
 const char *b200attn_last_path(void);
 
 /* Number of kernel launches issued by this library in this process so far. */
