@@ -207,7 +207,7 @@ dec_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int qd = warp & 3, row = 16 * qd + lane;
         const uint32_t lane_addr = ((uint32_t)(32 * qd) << 16);
         const bool active = lane < 16 && row < p.Lq;
-        float m_run = -INFINITY, l_run = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f, m_prev = -INFINITY, l_prev = 0.0f;
         float o_run[D];
 #pragma unroll
         for (int j = 0; j < D; ++j) o_run[j] = 0.0f;
@@ -255,23 +255,47 @@ dec_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.p_full[st]);
-            // fold O_c = P V of this chunk into the running output
-            DC_FAIL_AT(9, !mbar_wait(&bars.o_full[st], (t >> 1) & 1, lim));
-            tc_fence_after();
-            const float m_new = fmaxf(m_run, m_c);
-            const float a = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_new), b = fast_exp2(m_c - m_new);
+            // fold O_c = P V of the PREVIOUS chunk into the running output: its MMAs ran while this chunk's
+            // softmax was computed, so this wait is over when it is reached
+            if (t > 0) {
+                const int sp = (t - 1) & 1;
+                DC_FAIL_AT(9, !mbar_wait(&bars.o_full[sp], ((t - 1) >> 1) & 1, lim));
+                tc_fence_after();
+                const float m_new = fmaxf(m_run, m_prev);
+                const float a = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_new), b = fast_exp2(m_prev - m_new);
 #pragma unroll
-            for (int g = 0; g < D / 32; ++g) {
-                tmem_ld32(tmem_o + lane_addr + st * 128 + g * 32, r);
-                tmem_ld_wait();
+                for (int g = 0; g < D / 32; ++g) {
+                    tmem_ld32(tmem_o + lane_addr + sp * 128 + g * 32, r);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o_run[g * 32 + j] = fmaf(o_run[g * 32 + j], a, __uint_as_float(r[j]) * b);
+                    for (int j = 0; j < 32; ++j) o_run[g * 32 + j] = fmaf(o_run[g * 32 + j], a, __uint_as_float(r[j]) * b);
+                }
+                l_run = fmaf(l_run, a, l_prev * b);
+                m_run = m_new;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.o_free[sp]);
             }
-            l_run = fmaf(l_run, a, l_c * b);
-            m_run = m_new;
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.o_free[st]);
+            m_prev = m_c;
+            l_prev = l_c;
+        }
+        if (!failed) {
+            do {   // the last chunk
+                const int sp = (n - 1) & 1;
+                DC_FAIL_AT(12, !mbar_wait(&bars.o_full[sp], ((n - 1) >> 1) & 1, lim));
+                tc_fence_after();
+                const float m_new = fmaxf(m_run, m_prev);
+                const float a = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_new), b = fast_exp2(m_prev - m_new);
+#pragma unroll
+                for (int g = 0; g < D / 32; ++g) {
+                    tmem_ld32(tmem_o + lane_addr + sp * 128 + g * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o_run[g * 32 + j] = fmaf(o_run[g * 32 + j], a, __uint_as_float(r[j]) * b);
+                }
+                l_run = fmaf(l_run, a, l_prev * b);
+                m_run = m_new;
+            } while (false);
         }
         if (!failed && active) {
             if (p.nsplit == 1) {
@@ -325,6 +349,271 @@ dec_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tc_fence_after();
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same unit for AT MOST 32 QUERIES, transposed: St [128 keys x NQ] = K Qt and Ot [head_d x NQ] = Vt Pt
+// (NQ = 16 or 32 query columns).  With the keys along the 128 tensor-memory lanes every softmax thread is
+// busy (a row per query leaves 60 of 64 rows idle for 4 queries) and the work per chunk is NQ values per
+// thread instead of 128.  The reference maximum of P is the RUNNING row maximum, the same for all
+// threads, so each thread rescales what it holds itself: its partial row sums (one per key lane, reduced
+// over the lanes once at the end of the split) and its row of the running Ot.
+// ---------------------------------------------------------------------------------------------------
+template <int N> __device__ __forceinline__ void dec_tmem_ld(uint32_t taddr, uint32_t (&r)[N]);
+template <> __device__ __forceinline__ void dec_tmem_ld<32>(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+template <> __device__ __forceinline__ void dec_tmem_ld<16>(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+template <int NCH, int NQ>   // head_d / 64; query columns (16 or 32)
+__global__ void __launch_bounds__(DC_THREADS, 1)
+dec_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+             const DecParams p) {
+    extern __shared__ unsigned char dc_smem_raw[];
+    __shared__ DcBars bars;
+    __shared__ uint32_t tmem_slot;
+    __shared__ float wmax[2][4][NQ];   // chunk maxima of the four softmax warps, double-buffered by chunk parity
+    __shared__ float wsum[4][NQ];
+    __shared__ uint64_t mx_full[2], sum_full;   // the four warps have written wmax[i] / wsum (bounded waits, like every other)
+    const uint32_t raw_addr = smem_u32(dc_smem_raw);
+    unsigned char *smem = dc_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int nch = NCH, D = 64 * NCH;
+    const uint32_t lim = p.spin_limit;
+    const int split = blockIdx.x;
+    const long long bh = blockIdx.y;
+    const int total_chunks = (p.Lk + DC_NK - 1) / DC_NK;
+    const int c0 = split * p.cps, c1 = min(total_chunks, c0 + p.cps);
+    const int n = c1 - c0;
+
+    unsigned char *q_smem = smem;
+    unsigned char *k_smem = q_smem + (size_t)nch * DC_QSLAB;
+    unsigned char *v_smem = k_smem + (size_t)2 * nch * DC_KSLAB;
+    unsigned char *p_smem = v_smem + (size_t)2 * nch * DC_KSLAB;
+    constexpr int kv_stage = nch * DC_KSLAB;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars.q_full, 1);
+        mbar_init(&bars.q_ready, 4);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars.k_full[i], 1); mbar_init(&bars.k_ready[i], 4); mbar_init(&bars.k_free[i], 1);
+            mbar_init(&bars.v_full[i], 1); mbar_init(&bars.v_free[i], 1);
+            mbar_init(&bars.s_full[i], 1); mbar_init(&bars.p_full[i], 4); mbar_init(&bars.o_full[i], 1); mbar_init(&bars.o_free[i], 4);
+        }
+        mbar_init(&mx_full[0], 4); mbar_init(&mx_full[1], 4); mbar_init(&sum_full, 4);
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, 256);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;   // St buffers at columns 0 / 64, Ot buffers at 128 / 192
+    bool failed = false;
+    const bool skip = (*reinterpret_cast<volatile unsigned *>(p.err) != 0);
+
+    if (skip) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&bars.q_full, (uint32_t)nch * (uint32_t)p.Lq * 128u);
+            for (int c = 0; c < nch; ++c) tma_load_2d(q_smem + (size_t)c * DC_QSLAB, &tmQ, c * 64, (int)(bh * p.Lq), &bars.q_full);
+            for (int t = 0; t < n; ++t) {
+                const int st = t & 1;
+                const int row0 = (int)(bh * p.Lk + (long long)(c0 + t) * DC_NK);
+                DC_FAIL_AT(0, !mbar_wait(&bars.k_free[st], ((t >> 1) & 1) ^ 1, lim));
+                mbar_expect_tx(&bars.k_full[st], (uint32_t)kv_stage);
+                tma_load_3d(k_smem + (size_t)st * kv_stage, &tmK, 0, row0, 0, &bars.k_full[st]);
+                DC_FAIL_AT(1, !mbar_wait(&bars.v_free[st], ((t >> 1) & 1) ^ 1, lim));
+                mbar_expect_tx(&bars.v_full[st], (uint32_t)kv_stage);
+                tma_load_3d(v_smem + (size_t)st * kv_stage, &tmV, 0, row0, 0, &bars.v_full[st]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t id_s = umma_idesc_bf16(DC_NK, NQ, 0, 0), id_o = umma_idesc_bf16(D, NQ, 1, 0);
+            auto issue_scores = [&](int t) -> bool {
+                const int st = t & 1;
+                if (!mbar_wait(p.rotate_k ? &bars.k_ready[st] : &bars.k_full[st], (t >> 1) & 1, lim)) return false;
+                tc_fence_after();
+                for (int c = 0; c < nch; ++c) {
+                    const uint64_t da = umma_desc_k_sw128(smem_u32(k_smem + (size_t)st * kv_stage + (size_t)c * DC_KSLAB));
+                    const uint64_t db = umma_desc_k_sw128(smem_u32(q_smem + (size_t)c * DC_QSLAB));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma_bf16(tmem_s + st * 64, da + 2 * k, db + 2 * k, id_s, (c | k) != 0);
+                }
+                umma_commit(&bars.k_free[st]);
+                umma_commit(&bars.s_full[st]);
+                return true;
+            };
+            do {
+                DC_FAIL_AT(2, !mbar_wait(p.rotate_q ? &bars.q_ready : &bars.q_full, 0, lim));
+                tc_fence_after();
+                DC_FAIL_AT(3, !issue_scores(0));
+                for (int t = 0; t < n; ++t) {
+                    const int st = t & 1;
+                    if (t + 1 < n) DC_FAIL_AT(4, !issue_scores(t + 1));
+                    DC_FAIL_AT(5, !mbar_wait(&bars.p_full[st], (t >> 1) & 1, lim));
+                    DC_FAIL_AT(6, !mbar_wait(&bars.v_full[st], (t >> 1) & 1, lim));
+                    DC_FAIL_AT(7, !mbar_wait(&bars.o_free[st], ((t >> 1) & 1) ^ 1, lim));
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < DC_NK / 16; ++kk) {
+                        const uint64_t da = umma_desc_mn_sw128(smem_u32(v_smem + (size_t)st * kv_stage + (size_t)kk * 2048), DC_KSLAB);
+                        const uint64_t db = umma_desc_k_sw128(smem_u32(p_smem + (size_t)st * DC_PBUF + (size_t)(kk >> 2) * DC_QSLAB)) + 2 * (kk & 3);
+                        umma_bf16(tmem_o + st * 64, da, db, id_o, kk != 0);
+                    }
+                    umma_commit(&bars.v_free[st]);
+                    umma_commit(&bars.o_full[st]);
+                }
+            } while (false);
+        }
+    } else if (warp < 6) {
+        // ---- key lane j = 32 (warp % 4) + lane of every chunk; the same thread owns row d of Ot (head_d 128:
+        // d = j; head_d 64, an M = 64 accumulator: d = 16 (warp % 4) + lane for lane < 16) ----
+        const int qd = warp & 3, j = 32 * qd + lane;
+        const uint32_t lane_addr = ((uint32_t)(32 * qd) << 16);
+        const int drow = (D == 128) ? j : 16 * qd + lane;
+        const bool d_active = (D == 128) || lane < 16;
+        float m_run[NQ], l_part[NQ], o_run[NQ];
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) { m_run[q] = -INFINITY; l_part[q] = 0.0f; o_run[q] = 0.0f; }
+        uint32_t r[NQ];
+        for (int t = 0; t < n && !failed; ++t) {
+            const int st = t & 1;
+            const bool valid = (c0 + t) * DC_NK + j < p.Lk;
+            DC_FAIL_AT(8, !mbar_wait(&bars.s_full[st], (t >> 1) & 1, lim));
+            tc_fence_after();
+            dec_tmem_ld<NQ>(tmem_s + lane_addr + st * 64, r);
+            tmem_ld_wait();
+            float sv[NQ], mx[NQ];
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) { sv[q] = valid ? __uint_as_float(r[q]) * p.scale_log2 : -INFINITY; mx[q] = sv[q]; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], o));
+            if (lane < NQ) {   // lane q publishes the warp's maximum of query q
+                float v = mx[0];
+#pragma unroll
+                for (int q = 1; q < NQ; ++q) v = (lane == q) ? mx[q] : v;
+                wmax[t & 1][qd][lane] = v;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&mx_full[t & 1]);
+            DC_FAIL_AT(13, !mbar_wait(&mx_full[t & 1], (t >> 1) & 1, lim));
+            // new running maxima (the same in every thread), factors for what is held relative to the old ones
+            float alpha[NQ];
+            unsigned char *pbase = p_smem + (size_t)st * DC_PBUF + (size_t)(j >> 6) * DC_QSLAB + (j & 7) * 2;
+            const int piece = (j & 63) >> 3;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                const float mc = fmaxf(fmaxf(wmax[t & 1][0][q], wmax[t & 1][1][q]), fmaxf(wmax[t & 1][2][q], wmax[t & 1][3][q]));
+                const float mn = fmaxf(m_run[q], mc);
+                alpha[q] = (m_run[q] == -INFINITY) ? 0.0f : fast_exp2(m_run[q] - mn);
+                m_run[q] = mn;
+                const float e = valid ? fast_exp2(sv[q] - mn) : 0.0f;
+                l_part[q] = fmaf(l_part[q], alpha[q], e);
+                // Pt as the K-major B operand [NQ rows x 128 keys]: row q, key j
+                *reinterpret_cast<__nv_bfloat16 *>(pbase + (q >> 3) * 1024 + (q & 7) * 128 + ((piece ^ (q & 7)) << 4)) = __float2bfloat16_rn(e);
+            }
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.p_full[st]);
+            // Ot of the previous chunk was computed relative to the maxima before this update
+            if (t > 0) {
+                const int sp = (t - 1) & 1;
+                DC_FAIL_AT(9, !mbar_wait(&bars.o_full[sp], ((t - 1) >> 1) & 1, lim));
+                tc_fence_after();
+                dec_tmem_ld<NQ>(tmem_o + lane_addr + sp * 64, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) o_run[q] = (o_run[q] + __uint_as_float(r[q])) * alpha[q];
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.o_free[sp]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) o_run[q] *= alpha[q];
+            }
+        }
+        if (!failed) {
+            do {
+                const int sp = (n - 1) & 1;
+                DC_FAIL_AT(12, !mbar_wait(&bars.o_full[sp], ((n - 1) >> 1) & 1, lim));
+                tc_fence_after();
+                dec_tmem_ld<NQ>(tmem_o + lane_addr + sp * 64, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) o_run[q] += __uint_as_float(r[q]);
+                // row sums: over the 32 lanes, then over the four warps
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) l_part[q] += __shfl_xor_sync(0xffffffffu, l_part[q], o);
+                if (lane < NQ) {
+                    float v = l_part[0];
+#pragma unroll
+                    for (int q = 1; q < NQ; ++q) v = (lane == q) ? l_part[q] : v;
+                    wsum[qd][lane] = v;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sum_full);
+                DC_FAIL_AT(14, !mbar_wait(&sum_full, 0, lim));
+                if (d_active) {
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) {
+                        if (q >= p.Lq) break;
+                        const float l = (wsum[0][q] + wsum[1][q]) + (wsum[2][q] + wsum[3][q]);
+                        if (p.nsplit == 1) {
+                            p.O[(bh * p.Lq + q) * (long long)D + drow] = __float2bfloat16_rn(o_run[q] / l);
+                        } else {
+                            p.part_O[((bh * p.nsplit + split) * DC_MQ + q) * (long long)D + drow] = o_run[q];
+                            if (drow == 0) {
+                                float *pm = p.part_ml + ((bh * p.nsplit + split) * DC_MQ + q) * 2;
+                                pm[0] = m_run[q];
+                                pm[1] = l;
+                            }
+                        }
+                    }
+                }
+            } while (false);
+        }
+    } else if (p.rotate_q || p.rotate_k) {
+        const int tid = threadIdx.x - 6 * 32;
+        do {
+            if (p.rotate_q) {
+                DC_FAIL_AT(10, !mbar_wait(&bars.q_full, 0, lim));
+                dec_encode_tile(q_smem, DC_MQ, DC_QSLAB, nch, D, 0, p.table_kind, p.sinus != 0, p.tab, tid);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.q_ready);
+            }
+            if (p.rotate_k) {
+                for (int t = 0; t < n; ++t) {
+                    const int st = t & 1;
+                    DC_FAIL_AT(11, !mbar_wait(&bars.k_full[st], (t >> 1) & 1, lim));
+                    dec_encode_tile(k_smem + (size_t)st * kv_stage, DC_NK, DC_KSLAB, nch, D, (c0 + t) * DC_NK, p.table_kind, p.sinus != 0, p.tab, tid);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.k_ready[st]);
+                }
+            }
+        } while (false);
+    }
+
+    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem, 256);
+}
 #undef DC_FAIL_AT
 
 // out[bh][i][:] from the splits' (max, sum, O): grid (Lq, BH), one thread per output column pair.
@@ -347,6 +636,13 @@ __global__ void dec_combine_kernel(const DecParams p) {
         }
         *reinterpret_cast<uint32_t *>(p.O + (bh * p.Lq + i) * (long long)p.D + d) = pack_bf16x2(o0 * inv, o1 * inv);
     }
+}
+
+template <typename Kern>
+inline bool dec_set_smem(Kern kern, size_t optin) {
+    cudaFuncAttributes fa;
+    return cudaFuncGetAttributes(&fa, kern) == cudaSuccess &&
+           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(optin - fa.sharedSizeBytes)) == cudaSuccess;
 }
 
 inline bool dec_supported(const b200attn_args &a, int rd) {
@@ -381,7 +677,9 @@ inline int dec_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
             if (cudaFuncGetAttributes(&fa, dec_split_kernel<1>) != cudaSuccess ||
                 cudaFuncSetAttribute(dec_split_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) != cudaSuccess ||
                 cudaFuncGetAttributes(&fa, dec_split_kernel<2>) != cudaSuccess ||
-                cudaFuncSetAttribute(dec_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) != cudaSuccess) {
+                cudaFuncSetAttribute(dec_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) != cudaSuccess ||
+                !dec_set_smem(dec_t_kernel<1, 16>, prop.sharedMemPerBlockOptin) || !dec_set_smem(dec_t_kernel<1, 32>, prop.sharedMemPerBlockOptin) ||
+                !dec_set_smem(dec_t_kernel<2, 16>, prop.sharedMemPerBlockOptin) || !dec_set_smem(dec_t_kernel<2, 32>, prop.sharedMemPerBlockOptin)) {
                 (void)cudaGetLastError();
                 snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncSetAttribute(max dynamic shared memory) failed");
                 return B200ATTN_ERR_CUDA;
@@ -434,8 +732,13 @@ inline int dec_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
         return B200ATTN_ERR_CUDA;
     }
-    if (nch == 1) dec_split_kernel<1><<<dim3((unsigned)p.nsplit, (unsigned)BH), DC_THREADS, dec_smem_bytes(nch), st>>>(tmQ, tmK, tmV, p);
-    else dec_split_kernel<2><<<dim3((unsigned)p.nsplit, (unsigned)BH), DC_THREADS, dec_smem_bytes(nch), st>>>(tmQ, tmK, tmV, p);
+    const dim3 grid((unsigned)p.nsplit, (unsigned)BH);
+    const size_t smem = dec_smem_bytes(nch);
+    // up to 32 queries: the transposed kernel (keys along the tensor-memory lanes); more: a row per query
+    if (Lq <= 16) { if (nch == 1) dec_t_kernel<1, 16><<<grid, DC_THREADS, smem, st>>>(tmQ, tmK, tmV, p); else dec_t_kernel<2, 16><<<grid, DC_THREADS, smem, st>>>(tmQ, tmK, tmV, p); }
+    else if (Lq <= 32) { if (nch == 1) dec_t_kernel<1, 32><<<grid, DC_THREADS, smem, st>>>(tmQ, tmK, tmV, p); else dec_t_kernel<2, 32><<<grid, DC_THREADS, smem, st>>>(tmQ, tmK, tmV, p); }
+    else if (nch == 1) dec_split_kernel<1><<<grid, DC_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
+    else dec_split_kernel<2><<<grid, DC_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "dec_split_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
     launches->fetch_add(1);
