@@ -11,7 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # B200ATTN_LIB names another build of the same library (a profiling build, an older build to compare with)
 LIB_PATH = os.environ.get("B200ATTN_LIB") or os.path.join(_HERE, "lib", "libb200attn.so")
 
-F32, BF16 = 0, 1
+F32, BF16, F16 = 0, 1, 2
 PE_NONE, PE_ROPE_INTERLEAVED, PE_ROPE_HALF, PE_SINUSOIDAL, PE_ROPE_Q_ONLY, PE_ROPE_HALF_Q_ONLY = 0, 1, 2, 3, 4, 5
 FLAG_ASYNC, FLAG_FORCE_GENERIC, FLAG_FORCE_TWO_PASS, FLAG_PREFER_ONE_KERNEL = 1, 2, 4, 8
 OPT_SCORE_SCRATCH_MB, OPT_SPIN_LIMIT = 1, 2
@@ -103,6 +103,11 @@ def make_args(Q, K, V, out, B, H, Lq, Lk, D, dtype, pe=PE_NONE, rotary_dim=0, ro
                 cos_cache, sin_cache, stream, flags)
 
 
+def dtype_of(t):
+    import torch
+    return {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}[t.dtype]
+
+
 def check(status):
     if status != OK:
         raise B200AttnError(status, lib().b200attn_last_error().decode())
@@ -116,7 +121,7 @@ def forward(Q, K, V, out=None, pe=PE_NONE, rotary_dim=0, rope_base=0.0, cos_cach
     assert Q.is_cuda and K.is_cuda and V.is_cuda and Q.is_contiguous() and K.is_contiguous() and V.is_contiguous()
     B, H, Lq, D = Q.shape
     Lk = K.shape[2]
-    dtype = F32 if Q.dtype == torch.float32 else BF16
+    dtype = dtype_of(Q)
     if out is None:
         out = torch.empty_like(Q)
     if stream is None:
@@ -136,7 +141,7 @@ def args_for(Q, K, V, out, pe=PE_NONE, rotary_dim=0, rope_base=0.0, stream=None,
     if stream is None:
         stream = torch.cuda.current_stream(Q.device).cuda_stream
     return make_args(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), B, H, Lq, K.shape[2], D,
-                     F32 if Q.dtype == torch.float32 else BF16, pe, rotary_dim, rope_base, None, None, stream, flags)
+                     dtype_of(Q), pe, rotary_dim, rope_base, None, None, stream, flags)
 
 
 def kernel_times(enable, collect=False):
@@ -161,7 +166,7 @@ def forward_host(Q, K, V, out, pe=PE_NONE, rotary_dim=0, rope_base=0.0, flags=0)
     import torch
     B, H, Lq, D = Q.shape
     Lk = K.shape[2]
-    dtype = F32 if Q.dtype == torch.float32 else BF16
+    dtype = dtype_of(Q)
     a = make_args(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), B, H, Lq, Lk, D, dtype, pe, rotary_dim,
                   rope_base, None, None, None, flags)
     check(lib().b200attn_forward_host(C.byref(a)))

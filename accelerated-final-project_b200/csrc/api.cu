@@ -12,6 +12,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #include "../../include/b200attn.h"
@@ -93,8 +94,8 @@ struct DeviceCtx {
     unsigned *err_host_dev = nullptr;   // the same word as the device sees it
     unsigned *err_bits = nullptr;  // pinned landing place for the device word when err_host says there is something to read
     bool scratch_dirty = false;    // a failed fused launch may have left S / counters non-zero
-    bool attr_set[8] = {false, false, false, false, false, false, false, false};
-    size_t dyn_smem_max[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    bool attr_set[9] = {false, false, false, false, false, false, false, false, false};   // [kernel 0..2][fp32, bf16, fp16]
+    size_t dyn_smem_max[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
     void *stage[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // host-buffer entry point: two sets of Q,K,V,O chunk buffers
     size_t stage_bytes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     cudaStream_t host_streams[3] = {nullptr, nullptr, nullptr};   // copy-in, compute, copy-out
@@ -198,6 +199,8 @@ static size_t fused_smem_bytes(int ds) {
     return ((size_t)3 * SD_TILE * (ds + 4) + (size_t)SD_TILE * SD_PT_PITCH + ds / 2 + 4) * sizeof(float);
 }
 
+template <typename T> constexpr int type_slot() { return sizeof(T) == 4 ? 0 : std::is_same<T, __half>::value ? 2 : 1; }
+
 template <typename Kern>
 static int set_smem_attr(DeviceCtx &c, int slot, Kern kern) {
     if (!c.attr_set[slot]) {
@@ -269,7 +272,7 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
         }
     }
     if (fused) {
-        const int slot = sizeof(T) == 4 ? 0 : 1;
+        const int slot = type_slot<T>();
         int rc = set_smem_attr(c, slot, splitd_fused_kernel<T>);
         if (rc) return rc;
         if (smem > c.dyn_smem_max[slot]) fused = false;
@@ -322,9 +325,9 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
     if (chunk > 65535) chunk = 65535;
     int rc = ensure_scratch(c, (size_t)chunk * per_head, 0, st);
     if (rc) return rc;
-    rc = set_smem_attr(c, sizeof(T) == 4 ? 2 : 3, splitd_scores_kernel<T>);
+    rc = set_smem_attr(c, 3 + type_slot<T>(), splitd_scores_kernel<T>);
     if (rc) return rc;
-    rc = set_smem_attr(c, sizeof(T) == 4 ? 4 : 5, splitd_softmax_pv_kernel<T>);
+    rc = set_smem_attr(c, 6 + type_slot<T>(), splitd_softmax_pv_kernel<T>);
     if (rc) return rc;
     const size_t smem1 = ((size_t)2 * SD_TILE * (ds + 4) + ds / 2 + 4) * sizeof(float);
     const size_t smem2 = ((size_t)SD_TILE * (dv + 4) + (size_t)SD_TILE * SD_PT_PITCH + 2 * SD_TILE) * sizeof(float);
@@ -448,9 +451,9 @@ static int validate(const b200attn_args *a, int *rd_out, float *base_out) {
     if (a->batch_sz <= 0 || a->num_heads <= 0 || a->len_q <= 0 || a->len_k <= 0 || a->head_d <= 0)
         return fail(B200ATTN_ERR_INVALID_ARG, "batch_sz, num_heads, len_q, len_k, head_d must be positive (got %d,%d,%d,%d,%d)",
                     a->batch_sz, a->num_heads, a->len_q, a->len_k, a->head_d);
-    if (a->dtype != B200ATTN_F32 && a->dtype != B200ATTN_BF16) return fail(B200ATTN_ERR_INVALID_ARG, "unknown dtype %d", a->dtype);
+    if (a->dtype != B200ATTN_F32 && a->dtype != B200ATTN_BF16 && a->dtype != B200ATTN_F16) return fail(B200ATTN_ERR_INVALID_ARG, "unknown dtype %d", a->dtype);
     if (a->pe < B200ATTN_PE_NONE || a->pe > B200ATTN_PE_ROPE_HALF_Q_ONLY) return fail(B200ATTN_ERR_INVALID_ARG, "unknown pe kind %d", a->pe);
-    const size_t esz = a->dtype == B200ATTN_F32 ? 4 : 2;
+    const size_t esz = a->dtype == B200ATTN_F32 ? 4 : 2;   // bf16 and fp16 are both two bytes
     if (((uintptr_t)a->Q | (uintptr_t)a->K | (uintptr_t)a->V | (uintptr_t)a->out) & (esz - 1))
         return fail(B200ATTN_ERR_INVALID_ARG, "tensor pointers must be aligned to the element size");
     if (a->out == a->Q || a->out == a->K || a->out == a->V) return fail(B200ATTN_ERR_INVALID_ARG, "out must not alias an input");
@@ -520,7 +523,7 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
     // bf16 on the tensor cores: the two-kernel path (scores, then P V) takes every shape it supports;
     // the one-kernel cluster pipeline takes the rest of its own shapes (and all of them when the call
     // asks for it with B200ATTN_FLAG_PREFER_ONE_KERNEL: the two are measured against each other that way).
-    const bool tc_ok = a->dtype == B200ATTN_BF16 && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC);
+    const bool tc_ok = (a->dtype == B200ATTN_BF16 || a->dtype == B200ATTN_F16) && !(a->flags & B200ATTN_FLAG_FORCE_GENERIC);
     const bool wide_ok = tc_ok && tcw_supported(*a, rd), pair_ok = tc_ok && tc_bf16_supported(*a, rd);
     const bool use_pair = pair_ok && (!wide_ok || (a->flags & B200ATTN_FLAG_PREFER_ONE_KERNEL));
     if (use_pair) {
@@ -553,7 +556,8 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
         else if (rc != -1) return rc;
     }
     if (!done) {
-        rc = (a->dtype == B200ATTN_F32) ? run_splitd<float>(*c, *a, rd, base, st) : run_splitd<__nv_bfloat16>(*c, *a, rd, base, st);
+        rc = (a->dtype == B200ATTN_F32) ? run_splitd<float>(*c, *a, rd, base, st)
+           : (a->dtype == B200ATTN_F16) ? run_splitd<__half>(*c, *a, rd, base, st) : run_splitd<__nv_bfloat16>(*c, *a, rd, base, st);
         if (rc) return rc;
     }
     return check_kernel_errors(*c, st, !(a->flags & B200ATTN_FLAG_ASYNC));

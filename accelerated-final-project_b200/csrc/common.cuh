@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -92,6 +93,7 @@ __device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint3
 // ---- element conversion -----------------------------------------------------------------------
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
 
 template <typename T> struct OutCvt;
 template <> struct OutCvt<float> {
@@ -99,6 +101,9 @@ template <> struct OutCvt<float> {
 };
 template <> struct OutCvt<__nv_bfloat16> {
     static __device__ __forceinline__ __nv_bfloat16 one(float x) { return __float2bfloat16_rn(x); }
+};
+template <> struct OutCvt<__half> {
+    static __device__ __forceinline__ __half one(float x) { return __float2half_rn(x); }
 };
 
 __device__ __forceinline__ float warp_max(float v) {

@@ -41,6 +41,7 @@ struct DecParams {
     float scale_log2;          // log2(e) / sqrt(D)
     int table_kind;            // 0 none, 1 element-wise partner table (interleaved RoPE, sinusoidal), 2 rotate-half table
     int sinus, rotate_q, rotate_k;
+    int f16;                   // the tensors are fp16 (no encoding then), else bf16
     const __nv_bfloat16 *tab;  // [>= max(64, 128 * ceil(Lk / 128))][D]
     float *part_O;             // [BH][nsplit][64][D] unnormalised outputs of the splits
     float *part_ml;            // [BH][nsplit][64][2] their (max in log2 units, sum)
@@ -164,7 +165,7 @@ dec_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t id_s = umma_idesc_bf16(DC_MQ, DC_NK, 0, 0), id_o = umma_idesc_bf16(DC_MQ, D, 0, 1);
+            const uint32_t id_s = umma_idesc_16(DC_MQ, DC_NK, 0, 0, p.f16), id_o = umma_idesc_16(DC_MQ, D, 0, 1, p.f16);
             auto issue_scores = [&](int t) -> bool {
                 const int st = t & 1;
                 if (!mbar_wait(p.rotate_k ? &bars.k_ready[st] : &bars.k_full[st], (t >> 1) & 1, lim)) return false;
@@ -240,7 +241,7 @@ dec_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     const float e0 = (k0 < nvalid) ? fast_exp2(fmaf(__uint_as_float(r[2 * j]), p.scale_log2, -m_c)) : 0.0f;
                     const float e1 = (k0 + 1 < nvalid) ? fast_exp2(fmaf(__uint_as_float(r[2 * j + 1]), p.scale_log2, -m_c)) : 0.0f;
                     l_c += e0 + e1;
-                    w[j] = pack_bf16x2(e0, e1);
+                    w[j] = pack_16x2(e0, e1, p.f16 != 0);
                 }
                 if (lane < 16) {
 #pragma unroll
@@ -304,10 +305,10 @@ dec_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < D; j += 8) {
                     uint4 v;
-                    v.x = pack_bf16x2(o_run[j] * inv, o_run[j + 1] * inv);
-                    v.y = pack_bf16x2(o_run[j + 2] * inv, o_run[j + 3] * inv);
-                    v.z = pack_bf16x2(o_run[j + 4] * inv, o_run[j + 5] * inv);
-                    v.w = pack_bf16x2(o_run[j + 6] * inv, o_run[j + 7] * inv);
+                    v.x = pack_16x2(o_run[j] * inv, o_run[j + 1] * inv, p.f16 != 0);
+                    v.y = pack_16x2(o_run[j + 2] * inv, o_run[j + 3] * inv, p.f16 != 0);
+                    v.z = pack_16x2(o_run[j + 4] * inv, o_run[j + 5] * inv, p.f16 != 0);
+                    v.w = pack_16x2(o_run[j + 6] * inv, o_run[j + 7] * inv, p.f16 != 0);
                     *reinterpret_cast<uint4 *>(orow + j) = v;
                 }
             } else {
@@ -436,7 +437,7 @@ dec_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t id_s = umma_idesc_bf16(DC_NK, NQ, 0, 0), id_o = umma_idesc_bf16(D, NQ, 1, 0);
+            const uint32_t id_s = umma_idesc_16(DC_NK, NQ, 0, 0, p.f16), id_o = umma_idesc_16(D, NQ, 1, 0, p.f16);
             auto issue_scores = [&](int t) -> bool {
                 const int st = t & 1;
                 if (!mbar_wait(p.rotate_k ? &bars.k_ready[st] : &bars.k_full[st], (t >> 1) & 1, lim)) return false;
@@ -520,7 +521,7 @@ dec_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                 const float e = valid ? fast_exp2(sv[q] - mn) : 0.0f;
                 l_part[q] = fmaf(l_part[q], alpha[q], e);
                 // Pt as the K-major B operand [NQ rows x 128 keys]: row q, key j
-                *reinterpret_cast<__nv_bfloat16 *>(pbase + (q >> 3) * 1024 + (q & 7) * 128 + ((piece ^ (q & 7)) << 4)) = __float2bfloat16_rn(e);
+                *reinterpret_cast<uint16_t *>(pbase + (q >> 3) * 1024 + (q & 7) * 128 + ((piece ^ (q & 7)) << 4)) = pack_16(e, p.f16 != 0);
             }
             tc_fence_before();
             fence_proxy_async_smem();
@@ -572,7 +573,7 @@ dec_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                         if (q >= p.Lq) break;
                         const float l = (wsum[0][q] + wsum[1][q]) + (wsum[2][q] + wsum[3][q]);
                         if (p.nsplit == 1) {
-                            p.O[(bh * p.Lq + q) * (long long)D + drow] = __float2bfloat16_rn(o_run[q] / l);
+                            reinterpret_cast<uint16_t *>(p.O)[(bh * p.Lq + q) * (long long)D + drow] = pack_16(o_run[q] / l, p.f16 != 0);
                         } else {
                             p.part_O[((bh * p.nsplit + split) * DC_MQ + q) * (long long)D + drow] = o_run[q];
                             if (drow == 0) {
@@ -634,7 +635,7 @@ __global__ void dec_combine_kernel(const DecParams p) {
             o0 = fmaf(w, v.x, o0);
             o1 = fmaf(w, v.y, o1);
         }
-        *reinterpret_cast<uint32_t *>(p.O + (bh * p.Lq + i) * (long long)p.D + d) = pack_bf16x2(o0 * inv, o1 * inv);
+        *reinterpret_cast<uint32_t *>(p.O + (bh * p.Lq + i) * (long long)p.D + d) = pack_16x2(o0 * inv, o1 * inv, p.f16 != 0);
     }
 }
 
@@ -646,7 +647,7 @@ inline bool dec_set_smem(Kern kern, size_t optin) {
 }
 
 inline bool dec_supported(const b200attn_args &a, int rd) {
-    if (a.dtype != B200ATTN_BF16) return false;
+    if (a.dtype != B200ATTN_BF16 && !(a.dtype == B200ATTN_F16 && a.pe == B200ATTN_PE_NONE)) return false;   // the encodings are bf16 arithmetic
     if (a.head_d != 64 && a.head_d != 128) return false;
     if (a.len_q > DC_MQ || a.len_k <= 64) return false;   // short K runs on the split-head_d kernels
     if (a.cos_cache != nullptr && !pe_is_rope(a.pe)) return false;
@@ -700,6 +701,7 @@ inline int dec_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
     p.rotate_q = a.pe != B200ATTN_PE_NONE ? 1 : 0;
     p.rotate_k = pe_encodes_k(a.pe) ? 1 : 0;
     p.sinus = a.pe == B200ATTN_PE_SINUSOIDAL ? 1 : 0;
+    p.f16 = a.dtype == B200ATTN_F16 ? 1 : 0;
     p.table_kind = a.pe == B200ATTN_PE_NONE ? 0 : pe_pairs_halves(a.pe) ? 2 : 1;
     if (p.table_kind != 0) {
         const int Lt = total_chunks * DC_NK > DC_MQ ? total_chunks * DC_NK : DC_MQ;

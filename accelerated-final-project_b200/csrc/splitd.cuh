@@ -85,10 +85,10 @@ __device__ void load_slice(float *dst, int pitch, const T *src, int rows, int ro
                     x[1] = b.x; x[3] = b.y; x[5] = b.z; x[7] = b.w;
                 } else {
                     uint2 a = *reinterpret_cast<const uint2 *>(lo), b = *reinterpret_cast<const uint2 *>(hi);
-                    const __nv_bfloat16 *pa = reinterpret_cast<const __nv_bfloat16 *>(&a);
-                    const __nv_bfloat16 *pb = reinterpret_cast<const __nv_bfloat16 *>(&b);
+                    const T *pa = reinterpret_cast<const T *>(&a);
+                    const T *pb = reinterpret_cast<const T *>(&b);
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) { x[2 * t] = __bfloat162float(pa[t]); x[2 * t + 1] = __bfloat162float(pb[t]); }
+                    for (int t = 0; t < 4; ++t) { x[2 * t] = to_f32(pa[t]); x[2 * t + 1] = to_f32(pb[t]); }
                 }
             } else if ((!half || v >= rd) && n == 8 && base_aligned && (D % VEC == 0)) {
                 if constexpr (sizeof(T) == 4) {
@@ -97,9 +97,9 @@ __device__ void load_slice(float *dst, int pitch, const T *src, int rows, int ro
                     x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
                 } else {
                     uint4 a = *reinterpret_cast<const uint4 *>(rp + v);
-                    const __nv_bfloat16 *pa = reinterpret_cast<const __nv_bfloat16 *>(&a);
+                    const T *pa = reinterpret_cast<const T *>(&a);
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) x[t] = __bfloat162float(pa[t]);
+                    for (int t = 0; t < 8; ++t) x[t] = to_f32(pa[t]);
                 }
             } else {
                 for (int e = 0; e < n; ++e) x[e] = to_f32(rp[phys_col(v + e, pe, rd)]);
@@ -252,11 +252,8 @@ __device__ __forceinline__ void store_unit(T *O, int D, int nq, int w, int v0, i
             if constexpr (sizeof(T) == 4) {
                 *reinterpret_cast<float4 *>(op) = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
             } else {
-                __nv_bfloat162 a = __floats2bfloat162_rn(o[r][0], o[r][1]), b = __floats2bfloat162_rn(o[r][2], o[r][3]);
-                uint2 u;
-                u.x = *reinterpret_cast<uint32_t *>(&a);
-                u.y = *reinterpret_cast<uint32_t *>(&b);
-                *reinterpret_cast<uint2 *>(op) = u;
+                T h[4] = {OutCvt<T>::one(o[r][0]), OutCvt<T>::one(o[r][1]), OutCvt<T>::one(o[r][2]), OutCvt<T>::one(o[r][3])};
+                *reinterpret_cast<uint2 *>(op) = *reinterpret_cast<const uint2 *>(h);
             }
         } else {
             for (int e = 0; e < 4 && c + e < w; ++e) op[e] = OutCvt<T>::one(o[r][e]);

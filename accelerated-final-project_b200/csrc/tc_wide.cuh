@@ -49,6 +49,7 @@ struct TcwScoreParams {
     int mode;                  // 0: every tile, operands as given; 1: the encoding tile set; 2: all other tiles
     int pe;                    // mode 1: PE_ROPE_HALF, PE_ROPE_INTERLEAVED or PE_SINUSOIDAL
     int rotate_k;              // mode 1: 0 = only Q carries the encoding
+    int f16;                   // operands are fp16 (no encoding then), else bf16
     int tph;                   // tiles per head in this launch
     long long n_tiles;         // heads * tph
     float scale_log2;          // log2(e) / sqrt(D)
@@ -185,7 +186,7 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(TW_BM, TW_BN, 0, 0);
+            const uint32_t idesc = umma_idesc_16(TW_BM, TW_BN, 0, 0, p.f16);
             int it = 0;
             long long tc = 0;
             TWS_DECL;
@@ -505,7 +506,7 @@ tcw_scores256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(TW_BM, TW_BN, 0, 0);
+            const uint32_t idesc = umma_idesc_16(TW_BM, TW_BN, 0, 0, p.f16);
             int it = 0;
             long long tc = 0;
             for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x, ++tc) {
@@ -604,7 +605,8 @@ struct TcwPvParams {
     int nqt, nkt, nblk;        // Lq / 128, ceil(Lk / 256), Lk / 128
     long long n_units;         // heads * nqt * ndp
     const float *rowmax;       // as written by tcw_scores_kernel (the scores themselves come through the tensor map)
-    __nv_bfloat16 *O;          // [heads * Lq][D]
+    int f16;                   // V, P and the output are fp16, else bf16 (the stored scores are bf16 either way)
+    __nv_bfloat16 *O;          // [heads * Lq][D] (16-bit elements of the call's format)
     unsigned *err, *err_sys;
     unsigned spin_limit;
 };
@@ -730,7 +732,7 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                                 const int kg = vs * (TP_VS / 16) + kk;   // 16-key step within the block, 0..7
                                 const uint64_t da = umma_desc_k_sw128(smem_u32(p_smem + (size_t)pb * TC_P_BYTES + (kg >> 2) * (TW_BM * 128))) + 2 * (kg & 3);
                                 const uint64_t db = umma_desc_mn_sw128(smem_u32(v_smem + (size_t)s * v_stage_bytes + kk * 2048), TP_VS * 128);
-                                umma_bf16(tmem + vw * TP_VW, da, db, umma_idesc_bf16(TW_BM, N, 0, 1), (t | kg) != 0);
+                                umma_bf16(tmem + vw * TP_VW, da, db, umma_idesc_16(TW_BM, N, 0, 1, p.f16), (t | kg) != 0);
                             }
                             umma_commit(&bars.v_empty[s]);
                         }
@@ -801,7 +803,7 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                         const float e0 = fast_exp2(__uint_as_float(x[q] << 16) + off);
                         const float e1 = fast_exp2(__uint_as_float(x[q] & 0xffff0000u) + off);
                         sum += e0 + e1;
-                        o[q] = pack_bf16x2(e0, e1);
+                        o[q] = pack_16x2(e0, e1, p.f16 != 0);
                     }
                     if (i & 1) lB += sum; else lA += sum;
                     *pp = make_uint4(o[0], o[1], o[2], o[3]);
@@ -846,7 +848,7 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                         tmem_ld_wait();
 #pragma unroll
                         for (int q = 0; q < 16; ++q)
-                            wds[16 * hh + q] = pack_bf16x2(__uint_as_float(r[2 * q]) * inv, __uint_as_float(r[2 * q + 1]) * inv);
+                            wds[16 * hh + q] = pack_16x2(__uint_as_float(r[2 * q]) * inv, __uint_as_float(r[2 * q + 1]) * inv, p.f16 != 0);
                     }
                     store_rows_128B_transposed(row0 + cp * 128, (size_t)p.D * 2, wds, lane);
                 }
@@ -980,7 +982,7 @@ inline __nv_bfloat16 *tcw_half_table(TcwScratch &sc, int Lt, int D, float base, 
 }
 
 inline bool tcw_supported(const b200attn_args &a, int rd) {
-    if (a.dtype != B200ATTN_BF16) return false;
+    if (a.dtype != B200ATTN_BF16 && !(a.dtype == B200ATTN_F16 && a.pe == B200ATTN_PE_NONE)) return false;   // the encodings are bf16 arithmetic
     if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 8192) return false;
     if (a.len_q % TW_BM != 0 || a.len_k % TC_BN != 0) return false;
     if (a.len_k > 32 * TW_BN) return false;   // the offsets of a row's key tiles live one per lane
@@ -1066,6 +1068,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         TcwScoreParams sp{};
         sp.Lq = Lq; sp.Lk = Lk; sp.D = D; sp.nch = D / 64; sp.nqt = nqt; sp.nkt = nkt;
         sp.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+        sp.f16 = a.dtype == B200ATTN_F16 ? 1 : 0;
         sp.S = S; sp.rowmax = rowmax; sp.tab = tab; sp.q_store = qs; sp.k_store = ks;
         sp.pe = a.pe == B200ATTN_PE_ROPE_Q_ONLY ? (int)PE_ROPE_INTERLEAVED : a.pe == B200ATTN_PE_ROPE_HALF_Q_ONLY ? (int)PE_ROPE_HALF : a.pe;
         sp.rotate_k = rotate_k ? 1 : 0;
@@ -1108,6 +1111,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         TcwPvParams pp{};
         pp.Lq = Lq; pp.Lk = Lk; pp.D = D; pp.DW = DW; pp.ndp = ndp; pp.nqt = nqt; pp.nkt = nkt; pp.nblk = nblk;
         pp.n_units = nh * nqt * ndp;
+        pp.f16 = a.dtype == B200ATTN_F16 ? 1 : 0;
         pp.rowmax = rowmax; pp.O = (__nv_bfloat16 *)a.out + h0 * Lq * D;
         pp.err = err_dev; pp.err_sys = err_sys; pp.spin_limit = spin_limit;
         tcw_timer().begin(2, st);

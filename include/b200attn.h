@@ -105,7 +105,11 @@ enum b200attn_status {
     B200ATTN_ERR_TOO_LARGE = 5      /* a fixed-capacity entry point was given a problem beyond its limit */
 };
 
-enum b200attn_dtype { B200ATTN_F32 = 0, B200ATTN_BF16 = 1 };
+/* B200ATTN_F16 (IEEE half in and out, fp32 accumulation) has no launcher of its own in the reference's
+ * final/ tree; it covers what kernels/attention_kernel_fp16.cu:194 (attention_forward_fp16) does.  Without a
+ * positional encoding it runs on the tensor cores for the shapes the bf16 paths take; with one, on the
+ * CUDA-core kernels. */
+enum b200attn_dtype { B200ATTN_F32 = 0, B200ATTN_BF16 = 1, B200ATTN_F16 = 2 };
 
 /* Positional encoding applied to Q and K inside the load (no separate pass). */
 enum b200attn_pe {
