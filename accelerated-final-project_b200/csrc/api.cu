@@ -104,9 +104,10 @@ struct DeviceCtx {
     // tensor-core split-head_d path: double-buffered score scratch (see splitd_tc.cuh)
     float *sdtc_S = nullptr;
     unsigned *sdtc_cnt = nullptr;
-    int sdtc_cap = 0;              // heads per half
-    int sdtc_epoch = 0;            // half the next call sums into
-    int sdtc_prev_bh = 0;          // heads the last call left non-zero in the other half
+    unsigned *sdtc_gen = nullptr;
+    int sdtc_cap = 0;              // heads per buffer of the scratch ring
+    unsigned sdtc_seq = 0;         // calls so far: call n uses buffer n % ST_NBUF
+    unsigned sdtc_gen_expect[ST_NBUF] = {};   // heads the earlier users of each buffer will have cleared
     bool sdtc_attr = false;
     size_t sdtc_smem_max = 0;
     // the last enqueued call, when it was this kernel: a following call that is declared independent of it
@@ -185,9 +186,10 @@ static int ensure_scratch(DeviceCtx &c, size_t s_bytes, size_t n_counters, cudaS
         if (c.S) CU_TRY(cudaMemsetAsync(c.S, 0, c.S_bytes, st));
         if (c.counters) CU_TRY(cudaMemsetAsync(c.counters, 0, c.counters_n * sizeof(unsigned), st));
         if (c.sdtc_S) {
-            CU_TRY(cudaMemsetAsync(c.sdtc_S, 0, (size_t)2 * c.sdtc_cap * 4096 * sizeof(float), st));
-            CU_TRY(cudaMemsetAsync(c.sdtc_cnt, 0, (size_t)2 * c.sdtc_cap * sizeof(unsigned), st));
-            c.sdtc_prev_bh = 0;
+            CU_TRY(cudaMemsetAsync(c.sdtc_S, 0, (size_t)ST_NBUF * c.sdtc_cap * 4096 * sizeof(float), st));
+            CU_TRY(cudaMemsetAsync(c.sdtc_cnt, 0, (size_t)ST_NBUF * c.sdtc_cap * 2 * sizeof(unsigned), st));
+            CU_TRY(cudaMemsetAsync(c.sdtc_gen, 0, ST_NBUF * sizeof(unsigned), st));
+            for (int i = 0; i < ST_NBUF; ++i) c.sdtc_gen_expect[i] = 0;
         }
         CU_TRY(cudaMemsetAsync(c.err_dev, 0, sizeof(unsigned), st));
         c.scratch_dirty = false;
@@ -364,7 +366,7 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     const long long BH = (long long)a.batch_sz * a.num_heads;
     const int Lq = a.len_q, Lk = a.len_k, D = a.head_d;
     if (a.dtype != B200ATTN_F32 || a.pe != B200ATTN_PE_NONE || Lq > 64 || Lk > 64 || D % 4 != 0) return -1;
-    if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return -1;
+    if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V) & 15) != 0 || ((uintptr_t)a.out & 31) != 0) return -1;   // 32-byte output stores
     if (BH > c.sm_count || BH > 65535) return -1;
     const int natoms = (D + ST_ATOM - 1) / ST_ATOM;
     const int slots = (int)(c.sm_count / BH);
@@ -372,13 +374,19 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     if (apc > ST_MAX_ATOMS) return -1;
     const int nsplit = (natoms + apc - 1) / apc;
     // Overlap with the previous call: this call's inputs must not be that call's output.  (Two CTAs
-    // share an SM below half of its shared memory, i.e. with slices of up to 96 columns; the loads of
-    // this call then run under the tail of the previous one.  Wider slices still gain the launch latency.)
+    // share an SM up to half of its shared memory, i.e. with slices of up to 128 columns; the whole of this
+    // call then runs beside the previous one.  Wider slices still gain the launch latency.)
     const size_t in_q = (size_t)BH * Lq * D * 4, in_k = (size_t)BH * Lk * D * 4;
     auto hits_prev_out = [&](const void *ptr, size_t n) { return (uintptr_t)ptr < c.prev_out_hi && (uintptr_t)ptr + n > c.prev_out_lo; };
     const bool overlap = independent_of_prev && c.prev_sdtc && c.prev_stream == st && !c.scratch_dirty &&
                          !hits_prev_out(a.Q, in_q) && !hits_prev_out(a.K, in_k) && !hits_prev_out(a.V, in_k);
-    const size_t smem = sdtc_smem_bytes(apc);
+    // one ring stage instead of two where that brings the CTA to half of an SM's shared memory (128-column slices)
+    const int nlo = (overlap && apc == 4) ? 1 : ST_NLO;
+    const size_t smem = sdtc_smem_bytes(apc, nlo);
+    // tensor-memory columns: 64 for the scores; the output takes the slice width, twice that where V hi | V lo
+    // is one operand (slices of up to 128 columns)
+    const int o_cols = apc * ST_ATOM * (2 * apc * ST_ATOM <= 256 ? 2 : 1);
+    const int tmem_cols = o_cols <= 64 ? 64 : o_cols <= 128 ? 128 : 256;
     if (!c.sdtc_attr) {
         cudaFuncAttributes fa;
         CU_TRY(cudaFuncGetAttributes(&fa, sdtc_kernel));
@@ -389,8 +397,9 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     if (smem > c.sdtc_smem_max) return -1;
     if (c.sdtc_S == nullptr) {
         const int cap = c.sm_count;
-        CU_TRY(cudaMalloc(&c.sdtc_S, (size_t)2 * cap * 4096 * sizeof(float)));
-        CU_TRY(cudaMalloc(&c.sdtc_cnt, (size_t)2 * cap * sizeof(unsigned)));
+        CU_TRY(cudaMalloc(&c.sdtc_S, (size_t)ST_NBUF * cap * 4096 * sizeof(float)));
+        CU_TRY(cudaMalloc(&c.sdtc_cnt, (size_t)ST_NBUF * cap * 2 * sizeof(unsigned)));
+        CU_TRY(cudaMalloc(&c.sdtc_gen, ST_NBUF * sizeof(unsigned)));
         c.sdtc_cap = cap;
         c.scratch_dirty = true;   // cleared below, on this call's stream
     }
@@ -399,20 +408,21 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
         if (rc) return rc;
     }
     // (the four maps are copied before the next lookup can evict one: the cache is direct-mapped)
-    CUtensorMap tmQ, tmK, tmV, tmO;
+    CUtensorMap tmQ, tmK, tmV;
     const CUtensorMap *m;
     bool ok = (m = c.tmaps.get(a.Q, BH * Lq, D, Lq, CU_TENSOR_MAP_SWIZZLE_128B)) != nullptr;
     if (ok) { tmQ = *m; ok = (m = c.tmaps.get(a.K, BH * Lk, D, Lk, CU_TENSOR_MAP_SWIZZLE_128B)) != nullptr; }
     if (ok) { tmK = *m; ok = (m = c.tmaps.get(a.V, BH * Lk, D, Lk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) != nullptr; }
-    if (ok) { tmV = *m; ok = (m = c.tmaps.get(a.out, BH * Lq, D, Lq, CU_TENSOR_MAP_SWIZZLE_128B)) != nullptr; }
-    if (ok) tmO = *m;
+    if (ok) tmV = *m;
     if (!ok) return fail(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed for the split-head_d slices");
     SdtcParams p{};
     p.BH = BH; p.Lq = Lq; p.Lk = Lk; p.D = D;
     p.apc = apc; p.natoms = natoms; p.nsplit = nsplit;
-    p.epoch = c.sdtc_epoch; p.cap_bh = c.sdtc_cap; p.zero_bh = c.sdtc_prev_bh;
+    const int buf = (int)(c.sdtc_seq % ST_NBUF);
+    p.buf = buf; p.gen_expect = c.sdtc_gen_expect[buf]; p.cap_bh = c.sdtc_cap; p.tmem_cols = tmem_cols; p.nlo = nlo;
     p.scale = 1.0f / sqrtf((float)D);
-    p.S = c.sdtc_S; p.counters = c.sdtc_cnt;
+    p.O = (float *)a.out;
+    p.S = c.sdtc_S; p.counters = c.sdtc_cnt; p.gen = c.sdtc_gen;
     p.err = c.err_dev; p.err_sys = c.err_host_dev;
     p.spin_limit = spin_limit_from_env();
     p.wait_extra = g_test_wait_extra.load();
@@ -430,9 +440,9 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    CU_TRY(cudaLaunchKernelEx(&cfg, sdtc_kernel, tmQ, tmK, tmV, tmO, p));
-    c.sdtc_epoch ^= 1;
-    c.sdtc_prev_bh = (int)BH;
+    CU_TRY(cudaLaunchKernelEx(&cfg, sdtc_kernel, tmQ, tmK, tmV, p));
+    c.sdtc_seq += 1;
+    c.sdtc_gen_expect[buf] += (unsigned)BH;
     c.prev_sdtc = true;
     c.prev_stream = st;
     c.prev_out_lo = (uintptr_t)a.out;
@@ -922,7 +932,9 @@ void b200attn_release_workspace(void) {
         c.counters = nullptr; c.counters_n = 0;
         if (c.sdtc_S) cudaFree(c.sdtc_S);
         if (c.sdtc_cnt) cudaFree(c.sdtc_cnt);
-        c.sdtc_S = nullptr; c.sdtc_cnt = nullptr; c.sdtc_cap = 0; c.sdtc_epoch = 0; c.sdtc_prev_bh = 0;
+        if (c.sdtc_gen) cudaFree(c.sdtc_gen);
+        c.sdtc_S = nullptr; c.sdtc_cnt = nullptr; c.sdtc_gen = nullptr; c.sdtc_cap = 0; c.sdtc_seq = 0;
+        for (int i = 0; i < ST_NBUF; ++i) c.sdtc_gen_expect[i] = 0;
         for (int i = 0; i < 8; ++i) { if (c.stage[i]) cudaFree(c.stage[i]); c.stage[i] = nullptr; c.stage_bytes[i] = 0; }
         c.tc_tables.release();
         c.tcw.release();

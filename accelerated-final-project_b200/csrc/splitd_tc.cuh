@@ -23,11 +23,15 @@
 //             the wait is bounded all the same and reports an error instead of hanging.
 //   softmax   every slice CTA reads the 64 x 64 scores back, one warp per row (shuffle max / sum), and
 //             writes P as hi and lo in the K-major operand layout;
-//   output    O[:, slice] = Phi Vhi + Phi Vlo + Plo Vhi (N = slice width), read from tensor memory into
-//             a swizzled staging tile and written by TMA stores.
+//   output    O[:, slice] = Phi Vhi + Phi Vlo + Plo Vhi (N = slice width), read from tensor memory and
+//             written to global memory by the row's thread (128 bytes per row and atom).
 //
-// The scratch is double-buffered by call parity: a call sums into buffer `epoch` and clears the part
-// of buffer `1 - epoch` that the next call will use, so nothing has to be cleaned on the critical path.
+// Consecutive independent calls overlap on the GPU (programmatic dependent launch: a call's kernel starts
+// while the one before it is still running, and two to four CTAs share an SM when the slices are narrow).
+// The score scratch is therefore a ring of ST_NBUF buffers: call n sums into buffer n % ST_NBUF; the last
+// slice CTA of a head to have read the head's scores clears them (off the critical path, during P V) and
+// bumps the buffer's generation counter; a later call that gets the same buffer first checks (at its
+// start, long before it needs it) that the generation has reached what its predecessors must have left.
 #pragma once
 
 #include "tc_common.cuh"
@@ -40,8 +44,8 @@ constexpr int ST_ATOM = 32;            // fp32 columns in a 128-byte swizzled ro
 constexpr int ST_SLAB = 64 * 128;      // [64 rows x 128 B]
 constexpr int ST_CHUNK = 2 * ST_SLAB;  // one atom of Q and of K
 constexpr int ST_MAX_ATOMS = 8;        // widest slice: 256 columns (one MMA N; 24 KB per atom + the residual ring fit 227 KB)
-constexpr int ST_NLO = 2;              // residual ring depth
-constexpr int ST_TMEM_COLS = 256;
+constexpr int ST_NLO = 2;              // residual ring depth (one stage where that lets two CTAs share an SM)
+constexpr int ST_NBUF = 8;             // score-scratch ring
 
 struct SdtcParams {
     long long BH;
@@ -49,12 +53,16 @@ struct SdtcParams {
     int apc;                 // atoms per slice
     int natoms;              // ceil(D / 32)
     int nsplit;              // slices per head
-    int epoch;               // 0 / 1: which half of the scratch this call sums into
+    int buf;                 // which buffer of the scratch ring this call sums into
+    unsigned gen_expect;     // heads that earlier calls must have cleared in that buffer before it is used
+    int tmem_cols;           // tensor-memory columns to allocate (64, 128 or 256)
+    int nlo;                 // stages of the residual ring: 1 or 2
     float scale;
-    float *S;                // [2][cap_bh][64][64] partial-score sums; all zero outside the heads in use
-    unsigned *counters;      // [2][cap_bh] read-out warps (four per slice) that have added their scores
-    int cap_bh;              // heads each half of the scratch has room for
-    int zero_bh;             // heads the previous call on this device left non-zero in half 1 - epoch
+    float *O;                // [B*H*Lq][D]
+    float *S;                // [ST_NBUF][cap_bh][64][64] partial-score sums; all zero outside the heads in use
+    unsigned *counters;      // [ST_NBUF][cap_bh][2]: read-out warps (four per slice) that have added their scores; slices that have read the sum
+    unsigned *gen;           // [ST_NBUF] heads cleared so far, per buffer
+    int cap_bh;              // heads each buffer has room for
     unsigned *err, *err_sys;
     unsigned spin_limit;
     unsigned wait_extra;     // 0; a test makes the head wait for arrivals that never come
@@ -68,10 +76,21 @@ struct StBars {
     uint64_t full[ST_MAX_ATOMS];            // atom c of Q and K has landed
     uint64_t ready[ST_NLO], lo_free[ST_NLO];   // residual ring: split done / read by the MMAs
     uint64_t v_full, s_full, o_full;
+    uint64_t buf_ok;                        // the scratch buffer has been cleared by its previous users
 };
 
-// V slabs | Q,K atoms | residual ring (+ 1 KB to align the base)
-inline size_t sdtc_smem_bytes(int apc) { return (size_t)apc * (ST_SLAB + ST_CHUNK) + (size_t)ST_NLO * ST_CHUNK + 1024; }
+// The kernel's barriers and flags live in the dynamic allocation too (no static shared memory), in the
+// kilobyte that aligning the tiles to 1024 bytes leaves over: a slice of 128 columns with one ring stage is
+// then exactly half of an SM's shared memory.
+struct StShared {
+    StBars bars;
+    uint32_t tmem_slot;
+    unsigned s_fail;
+};
+static_assert(sizeof(StShared) <= 256, "the barriers have to fit the alignment slack");
+
+// V slabs | Q,K atoms | residual ring, + 1 KB (alignment of the tiles, barriers)
+inline size_t sdtc_smem_bytes(int apc, int nlo) { return (size_t)apc * (ST_SLAB + ST_CHUNK) + (size_t)nlo * ST_CHUNK + 1024; }
 
 // x -> (x with the low 13 mantissa bits cleared, the exact remainder)
 __device__ __forceinline__ void st_split4(const float4 x, float4 &hi, float4 &lo) {
@@ -105,14 +124,19 @@ __device__ __forceinline__ uint32_t st_swz(int row, int col) {
 
 __global__ void __launch_bounds__(ST_THREADS, 1)
 sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-            const __grid_constant__ CUtensorMap tmO, const SdtcParams p) {
-    extern __shared__ unsigned char st_smem_raw[];
+            const SdtcParams p) {
+    extern __shared__ __align__(256) unsigned char st_smem_raw[];
     if (threadIdx.x == 0) ST_STAMP(0);
-    __shared__ StBars bars;
-    __shared__ uint32_t tmem_slot;
-    __shared__ unsigned s_fail;
     const uint32_t raw_addr = smem_u32(st_smem_raw);
-    unsigned char *smem = st_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    const uint32_t slack = (1024u - (raw_addr & 1023u)) & 1023u;   // a multiple of 256
+    unsigned char *smem = st_smem_raw + slack;
+    const size_t tile_bytes = (size_t)p.apc * (ST_SLAB + ST_CHUNK) + (size_t)p.nlo * ST_CHUNK;
+    // the 1 KB beyond the tiles is split into `slack` bytes before them and the rest behind them: the
+    // barriers go where 256 bytes fit
+    StShared &sh = *reinterpret_cast<StShared *>(slack >= 256 ? st_smem_raw : smem + tile_bytes);
+    StBars &bars = sh.bars;
+    uint32_t &tmem_slot = sh.tmem_slot;
+    unsigned &s_fail = sh.s_fail;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slice = blockIdx.x;
     const long long bh = blockIdx.y;
@@ -126,19 +150,19 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 
     unsigned char *v_hi = smem;                                      // apc slabs [keys x 32 columns]
     unsigned char *qk = smem + (size_t)p.apc * ST_SLAB;              // apc atoms: Q [64 x 32] | K [64 x 32]
-    unsigned char *lo_ring = qk + (size_t)p.apc * ST_CHUNK;          // ST_NLO stages: Q lo | K lo
+    unsigned char *lo_ring = qk + (size_t)p.apc * ST_CHUNK;          // p.nlo stages: Q lo | K lo
     // once the score MMAs are done: V lo where the first Q, K atoms were (so that V hi | V lo is one
     // run of slabs when the slice is full), P behind it or in the residual ring, whichever has 32 KB
     unsigned char *v_lo = qk;
     unsigned char *p_hi = (p.apc >= 4) ? qk + (size_t)p.apc * ST_SLAB : lo_ring;   // two atoms of 32 keys
     unsigned char *p_lo = p_hi + 2 * ST_SLAB;
-    unsigned char *o_stage = v_hi;                                   // after the P V MMAs: output slabs
 
-    float *S_cur = p.S + ((size_t)p.epoch * p.cap_bh + bh) * 4096;
-    unsigned *cnt_cur = p.counters + (size_t)p.epoch * p.cap_bh + bh;
+    float *S_cur = p.S + ((size_t)p.buf * p.cap_bh + bh) * 4096;
+    unsigned *cnt_cur = p.counters + ((size_t)p.buf * p.cap_bh + bh) * 2;   // [0] arrivals, [1] readers
 
-    // one thread sets the barriers up and at once requests the whole slice: the loads are in flight
-    // while the other warps allocate tensor memory and meet at the barrier below
+    // one thread sets the barriers up and at once requests the whole slice, Q and K first and V behind them
+    // (a second issuing thread, or V requested alongside, measured no faster): the loads are in flight while
+    // the other warps allocate tensor memory and meet at the barrier below
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
         for (int i = 0; i < ST_MAX_ATOMS; ++i) mbar_init(&bars.full[i], 1);
@@ -146,6 +170,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         mbar_init(&bars.v_full, 1);
         mbar_init(&bars.s_full, 1);
         mbar_init(&bars.o_full, 1);
+        mbar_init(&bars.buf_ok, 1);
         s_fail = 0u;
         mbar_fence_init();
         for (int c = 0; c < nat; ++c) {
@@ -156,9 +181,8 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         }
         mbar_expect_tx(&bars.v_full, (uint32_t)nat * (uint32_t)Lk * 128u);
         for (int a = 0; a < nat; ++a) tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, atom_col(a), (int)(bh * Lk), &bars.v_full);
-        tma_prefetch_desc(&tmO);
     }
-    if (warp == 1) tmem_alloc(&tmem_slot, ST_TMEM_COLS);
+    if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -170,10 +194,21 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- the head's scores are complete when every read-out warp of every slice has arrived ----
-            grid_dependency_wait();
-            const unsigned want = 4u * (unsigned)p.nsplit + p.wait_extra;
+            // ---- the buffer of the scratch ring is clean once its earlier users have cleared their heads ----
             unsigned seen = 0;
+            for (unsigned it = 0; it < lim; ++it) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.gen + p.buf) : "memory");
+                if ((int)(seen - p.gen_expect) >= 0) break;
+                __nanosleep(100);
+            }
+            if ((int)(seen - p.gen_expect) < 0) {
+                report_kernel_error(p.err, p.err_sys, (unsigned)KERR_HEAD_BARRIER_TIMEOUT | (1u << 20));
+                *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
+            }
+            mbar_arrive(&bars.buf_ok);
+            // ---- the head's scores are complete when every read-out warp of every slice has arrived ----
+            const unsigned want = 4u * (unsigned)p.nsplit + p.wait_extra;
+            seen = 0;
             for (unsigned it = 0; it < lim; ++it) {
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt_cur) : "memory");
                 if (seen >= want) break;
@@ -190,8 +225,8 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             // ---- score MMAs ----
             const uint32_t id64 = umma_idesc_tf32(64, 64, 0, 0);
             for (int c = 0; c < nat; ++c) {
-                const int j = c % ST_NLO;
-                ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (c / ST_NLO) & 1, lim));
+                const int j = c % p.nlo;
+                ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (c / p.nlo) & 1, lim));
                 if (c == nat - 1) ST_STAMP(18);
                 tc_fence_after();
                 const uint32_t sa = smem_u32(qk + (size_t)c * ST_CHUNK), sl = smem_u32(lo_ring + (size_t)j * ST_CHUNK);
@@ -212,9 +247,9 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const int t = threadIdx.x - 64;   // 0..191
         // ---- hi / lo split of the landed Q and K atoms ----
         for (int c = 0; c < nat; ++c) {
-            const int j = c % ST_NLO;
+            const int j = c % p.nlo;
             ST_FAIL_AT(3, !mbar_wait(&bars.full[c], 0, lim));
-            ST_FAIL_AT(7, !mbar_wait(&bars.lo_free[j], ((c / ST_NLO) & 1) ^ 1, lim));
+            ST_FAIL_AT(7, !mbar_wait(&bars.lo_free[j], ((c / p.nlo) & 1) ^ 1, lim));
             if (t == 0 && c == 0) ST_STAMP(2);
             if (t == 0 && c == nat - 1) ST_STAMP(3);
             unsigned char *st = qk + (size_t)c * ST_CHUNK, *sl = lo_ring + (size_t)j * ST_CHUNK;
@@ -241,14 +276,14 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         if (!failed) {
             do {
                 ST_FAIL_AT(4, !mbar_wait(&bars.s_full, 0, lim));
+                if (warp >= 4) ST_FAIL_AT(8, !mbar_wait(&bars.buf_ok, 0, lim));   // (checked at the start of the kernel: long over)
             } while (false);
-            failed = __any_sync(0xffffffffu, failed);
+            failed = __any_sync(0xffffffffu, failed) || (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
         }
         // ---- read-out of the partial scores (warps 4-7: one tensor-memory lane quadrant each) ----
         if (warp >= 4 && !failed) {
             if (threadIdx.x == 128) ST_STAMP(4);
             tc_fence_after();
-            grid_dependency_wait();   // the scratch half summed into was cleared by the previous call
             const int q = warp & 3;
             const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
             const int row = 16 * q + lane;
@@ -289,18 +324,6 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 }
                 fence_proxy_async_smem();
             } while (false);
-        }
-        // ---- clear what the previous call summed into: the next call will use that half of the
-        // scratch.  The previous call has to be over first (it may still be running when this kernel
-        // was launched as its programmatic dependent). ----
-        {
-            grid_dependency_wait();
-            float4 *z = reinterpret_cast<float4 *>(p.S + (size_t)(1 - p.epoch) * p.cap_bh * 4096);
-            unsigned *zc = p.counters + (size_t)(1 - p.epoch) * p.cap_bh;
-            const long long cta = bh * p.nsplit + slice, ncta = p.BH * p.nsplit, nz = (long long)p.zero_bh * 1024;
-            for (long long i = cta * ST_SPLIT_THREADS + t; i < nz; i += ncta * ST_SPLIT_THREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (cta == 0)
-                for (int i = t; i < p.zero_bh; i += ST_SPLIT_THREADS) zc[i] = 0u;
         }
     }
     if (threadIdx.x == 64) ST_STAMP(9);
@@ -394,14 +417,32 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         umma_commit(&bars.o_full);
         ST_STAMP(22);
     }
+    // ---- while P V runs: this slice has read the head's scores; the last slice to say so clears them and
+    // the head's counters for the buffer's next user, then bumps the buffer's generation ----
+    if (warp == 2 && !failed) {
+        unsigned old = 0;
+        if (lane == 0) asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt_cur + 1) : "memory");
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == (unsigned)p.nsplit - 1u) {
+            float4 *z = reinterpret_cast<float4 *>(S_cur);
+#pragma unroll 4
+            for (int i = lane; i < 1024; i += 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (lane < 2) cnt_cur[lane] = 0u;
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.gen + p.buf) : "memory");
+        }
+    }
     if (!failed) {
         do {
             ST_FAIL_AT(6, !mbar_wait(&bars.o_full, 0, lim));
             if (threadIdx.x == 0) ST_STAMP(12);
             tc_fence_after();
-            // warp w reads lane quadrant w % 4 (rows 16 (w % 4) .. + 15 in its lanes 0-15), every second slab
+            // warp w reads lane quadrant w % 4 (rows 16 (w % 4) .. + 15 in its lanes 0-15), every second slab, and
+            // writes its rows' 128 bytes of that slab straight to global memory
             const int q = warp & 3, row = 16 * q + lane;
             const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
+            float *orow = p.O + (bh * Lq + row) * (long long)p.D;
             uint32_t r[32];
             for (int a = warp >> 2; a < nat; a += 2) {
                 tmem_ld32(ta + a * ST_ATOM, r);
@@ -414,33 +455,34 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 }
                 tmem_ld_wait();
                 ST_DBG(4, if (warp == 0 && a == 0 && lane < 2) { for (int j = 0; j < 32; ++j) p.dbg[704 + lane * 32 + j] = __uint_as_float(r[j]); });
-                if (lane < 16) {
-                    unsigned char *dst = o_stage + (size_t)a * ST_SLAB + (row >> 3) * 1024 + (row & 7) * 128;
+                const int col0 = atom_col(a);
+                if (col0 + ST_ATOM <= p.D && (p.D & 7) == 0) {
+                    // four neighbouring rows trade their 32-byte pieces, so that every store instruction writes whole
+                    // 128-byte lines (row-per-thread stores would touch 16 lines with 16 bytes each)
+                    store_rows_128B_transposed_if(reinterpret_cast<unsigned char *>(orow - (long long)(lane & 3) * p.D + col0), (size_t)p.D * 4, r, lane,
+                                                  lane < 16 ? Lq - (row & ~3) : 0);
+                } else if (lane < 16 && row < Lq) {   // the atom that crosses head_d (a multiple of 4: a 16-byte piece is inside or outside as a whole)
 #pragma unroll
                     for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4 *>(dst + ((c ^ (row & 7)) << 4)) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                        if (col0 + 4 * c < p.D)
+                            *reinterpret_cast<uint4 *>(orow + col0 + 4 * c) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
                 }
             }
-            fence_proxy_async_smem();
         } while (false);
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
     if (threadIdx.x == 0) ST_STAMP(13);
-    if (threadIdx.x == 0 && !failed) {
-        for (int a = 0; a < nat; ++a) tma_store_2d(&tmO, o_stage + (size_t)a * ST_SLAB, atom_col(a), (int)(bh * Lq));
-        tma_store_commit();
-        tma_store_wait_read();   // the writes themselves complete with the kernel
-        ST_STAMP(14);
-    }
+    failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
     if (failed && threadIdx.x == 0) {
         // never leave while this CTA's own bulk copies or MMAs may still be in flight
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
     }
+    // A kernel launched as the programmatic dependent of the previous call must not complete before it
+    // (the stream's order of completion is what later work in the stream relies on).
+    if (threadIdx.x == 0) grid_dependency_wait();
+    tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, ST_TMEM_COLS);
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem, (uint32_t)p.tmem_cols);
     if (threadIdx.x == 32) ST_STAMP(15);
 }
 

@@ -310,6 +310,31 @@ __device__ __forceinline__ void store_rows_128B_transposed(unsigned char *row0_p
                      make_uint4(w[8 * m + 4], w[8 * m + 5], w[8 * m + 6], w[8 * m + 7]));
 }
 
+// The same where only the first `rows_valid` rows of the lane's group of four exist (<= 0: none): the
+// trade is done by all lanes, the stores only for rows that exist.
+__device__ __forceinline__ void store_rows_128B_transposed_if(unsigned char *row0_ptr, size_t row_pitch, uint32_t (&w)[32], int lane, int rows_valid) {
+    const int j = lane & 3;
+#pragma unroll
+    for (int M = 2; M >= 1; M >>= 1) {
+        const bool up = (j & M) != 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (k & M) continue;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t send = up ? w[8 * k + e] : w[8 * (k | M) + e];
+                const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, M);
+                if (up) w[8 * k + e] = recv; else w[8 * (k | M) + e] = recv;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+        if (m < rows_valid)
+            st_global_v8(row0_ptr + (size_t)m * row_pitch + j * 32, make_uint4(w[8 * m], w[8 * m + 1], w[8 * m + 2], w[8 * m + 3]),
+                         make_uint4(w[8 * m + 4], w[8 * m + 5], w[8 * m + 6], w[8 * m + 7]));
+}
+
 // A bf16 row-major [rows][cols] matrix seen as [cols/64 groups][rows][64 columns], so that ONE request
 // fetches a box of `box_groups` 64-column groups x `box_rows` rows and lays it down as consecutive
 // [box_rows x 128 B] slabs with the 128-byte swizzle: the shared-memory layout of a K-major tile
