@@ -690,7 +690,7 @@ int b200attn_forward_many(const b200attn_args *args, int n) {
     if (args == nullptr || n < 0) return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_many: NULL args or negative n");
     for (int i = 0; i < n; ++i) {
         // the entries are independent problems by contract: entry i may overlap the tail of entry i - 1
-        int rc = forward_device(&args[i], i > 0);
+        int rc = forward_device(&args[i], i > 0 && !(args[i].flags & B200ATTN_FLAG_NO_OVERLAP));
         if (rc) return rc;
     }
     return B200ATTN_OK;

@@ -132,12 +132,12 @@ def make_inputs(pkg, torch, cfg, dev, seed):
     return Q, K, V, torch.empty_like(Q)
 
 
-def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None):
+def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None, flags=0):
     """Times `steps` forwards (cycling through `sets` of (Q,K,V,out)) with CUDA events on the
     stream the kernels are launched on; returns ms per step.  The steps are enqueued by one
     b200attn_forward_many call so that no interpreter time sits between launches."""
     n = len(sets)
-    mk = lambda i: pkg.args_for(*sets[i % n][:3], sets[i % n][3], pe=pe, flags=pkg.FLAG_ASYNC)
+    mk = lambda i: pkg.args_for(*sets[i % n][:3], sets[i % n][3], pe=pe, flags=pkg.FLAG_ASYNC | flags)
     if warmup:
         pkg.forward_many([mk(i) for i in range(warmup)])
     torch.cuda.synchronize()
@@ -157,24 +157,6 @@ def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None):
     if barrier:
         barrier()
     return e0.elapsed_time(e1) / steps
-
-
-def isolated_launch_us(pkg, torch, sets, pe, reps=60):
-    """Median device time of ONE launch with nothing queued behind or in front of it (CUDA events on the
-    launching stream, the device idle before each): the kernel's own duration plus its launch."""
-    ts = []
-    n = len(sets)
-    for i in range(reps):
-        Q, K, V, O = sets[i % n]
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
-        pkg.forward(Q, K, V, out=O, pe=pe, flags=pkg.FLAG_ASYNC)
-        e1.record()
-        torch.cuda.synchronize()
-        ts.append(e0.elapsed_time(e1) * 1e3)
-    ts.sort()
-    return ts[len(ts) // 2]
 
 
 def cpu_full(cfg, threads):
@@ -209,8 +191,8 @@ def cpu_full(cfg, threads):
 def fp32_sweep(pkg, torch, dev, pk, with_cpu=True):
     """The fp32 small-sequence configurations.  Per configuration: step time of back-to-back asynchronous
     launches through b200attn_forward_many, L2-cold (rotation through >= 512 MiB of distinct inputs) and
-    L2-warm (one set re-used); the duration of one isolated launch; a blocking call's host latency; the
-    HBM and compute rooflines; and the reference's CPU attention on the whole problem."""
+    L2-warm (one set re-used); the same launches without overlap between consecutive calls; a blocking
+    call's host latency; the HBM and compute rooflines; and the reference's CPU attention on the whole problem."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
     out = []
@@ -220,7 +202,7 @@ def fp32_sweep(pkg, torch, dev, pk, with_cpu=True):
         sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(nsets)]
         cold = min(time_steps(pkg, torch, sets, 0, nsets, nsets if r == 0 else 0) for r in range(3))
         warm = time_steps(pkg, torch, sets[:1], 0, 200, 20)
-        kern = isolated_launch_us(pkg, torch, sets, 0)
+        serial = min(time_steps(pkg, torch, sets, 0, nsets, 0, flags=pkg.FLAG_NO_OVERLAP) for r in range(2))
         Q, K, V, O = sets[0]
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -231,9 +213,8 @@ def fp32_sweep(pkg, torch, dev, pk, with_cpu=True):
         tfl = flops_of(cfg) / cold / 1e9
         row = {"config": cfg, "shape": [B, H, Lq, Lk, D], "path": pkg.last_path(), "cold_ms": round(cold, 5),
                "warm_ms": round(warm, 5), "blocking_call_ms": round(lat, 5),
-               "isolated_launch_us": round(kern, 2),
-               # step minus isolated launch: negative when consecutive independent launches overlap on the GPU
-               "step_minus_isolated_us": round(cold * 1e3 - kern, 2),
+               # the same launches with each one started only after the previous has completed: kernel + launch gap
+               "serial_step_us": round(serial * 1e3, 2), "overlap_gain_us": round((serial - cold) * 1e3, 2),
                "cold_gbs": round(nbytes / cold / 1e6, 1), "cold_tflops": round(tfl, 2),
                "cold_frac_of_hbm_peak": round(nbytes / cold / 1e6 / pk["hbm_gbs"], 4),
                "hbm_floor_us": round(nbytes / pk["hbm_gbs"] / 1e3, 2),
