@@ -362,7 +362,16 @@ static unsigned long long *g_sdtc_stamps = nullptr;
 // Slices are whole 32-column atoms; a head gets as many slices as the SM count allows.  Returns -1 when
 // the shape belongs to the CUDA-core kernels (an encoding, an odd head_d, more heads than SMs, a slice
 // wider than 256 columns).
-static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool independent_of_prev) {
+// tensor-memory columns of a CTA: 64 for the scores; the output (over them) takes the slice width, twice that
+// where V hi | V lo is one operand (slices of up to 128 columns, P V in one pass)
+static int sdtc_tmem_cols(int apc, int kc) {
+    const int o_cols = apc * ST_ATOM * ((2 * apc * ST_ATOM <= 256 && kc == 64) ? 2 : 1);
+    return o_cols <= 64 ? 64 : o_cols <= 128 ? 128 : 256;
+}
+
+// `independent_of_prev`: the caller declared this call independent of the one before it; `batched`: the call is
+// one of a batch of such calls (it, or the next one, may run beside its neighbour).
+static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool independent_of_prev, bool batched) {
     const long long BH = (long long)a.batch_sz * a.num_heads;
     const int Lq = a.len_q, Lk = a.len_k, D = a.head_d;
     if (a.dtype != B200ATTN_F32 || a.pe != B200ATTN_PE_NONE || Lq > 64 || Lk > 64 || D % 4 != 0) return -1;
@@ -370,7 +379,10 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     if (BH > c.sm_count || BH > 65535) return -1;
     const int natoms = (D + ST_ATOM - 1) / ST_ATOM;
     const int slots = (int)(c.sm_count / BH);
-    const int apc = (natoms + slots - 1) / slots;
+    int apc = (natoms + slots - 1) / slots;
+#ifdef B200ATTN_DEVTOOLS
+    if (const char *e = getenv("B200ATTN_SDTC_APC")) apc = atoi(e);
+#endif
     if (apc > ST_MAX_ATOMS) return -1;
     const int nsplit = (natoms + apc - 1) / apc;
     // Overlap with the previous call: this call's inputs must not be that call's output.  (Two CTAs
@@ -380,13 +392,40 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     auto hits_prev_out = [&](const void *ptr, size_t n) { return (uintptr_t)ptr < c.prev_out_hi && (uintptr_t)ptr + n > c.prev_out_lo; };
     const bool overlap = independent_of_prev && c.prev_sdtc && c.prev_stream == st && !c.scratch_dirty &&
                          !hits_prev_out(a.Q, in_q) && !hits_prev_out(a.K, in_k) && !hits_prev_out(a.V, in_k);
-    // one ring stage instead of two where that brings the CTA to half of an SM's shared memory (128-column slices)
-    const int nlo = (overlap && apc == 4) ? 1 : ST_NLO;
-    const size_t smem = sdtc_smem_bytes(apc, nlo);
-    // tensor-memory columns: 64 for the scores; the output takes the slice width, twice that where V hi | V lo
-    // is one operand (slices of up to 128 columns)
-    const int o_cols = apc * ST_ATOM * (2 * apc * ST_ATOM <= 256 ? 2 : 1);
-    const int tmem_cols = o_cols <= 64 ? 64 : o_cols <= 128 ? 128 : 256;
+    // Shared memory of a CTA.  A call on its own keeps its whole slice resident with a two-deep residual ring.
+    // A call of a batch takes the form that lets the most CTAs share an SM (its neighbours in the stream run
+    // beside it): fewer Q, K slots than atoms, one residual stage, P V in two passes - whatever it takes, as
+    // long as at least two slots remain; among equals the form with the most slots.
+    int nq = apc, nlo = ST_NLO, kc = 64;
+    if (batched || overlap) {
+        const size_t sm_bytes = (size_t)c.max_smem_optin + 1024;   // per SM; the system keeps 1 KB per CTA
+        int best = 0;
+        for (int q = apc; q >= (apc < 2 ? apc : 2); --q)
+            for (int l = ST_NLO; l >= 1; --l)
+                for (int k = 64; k >= 32; k -= 32) {
+                    if (!sdtc_pv_fits(apc, q, l, k)) continue;
+                    int n = (int)(sm_bytes / (sdtc_smem_bytes(apc, q, l) + 1024));
+                    const int by_tmem = 512 / sdtc_tmem_cols(apc, k);
+                    if (n > by_tmem) n = by_tmem;
+                    if (n > best) { best = n; nq = q; nlo = l; kc = k; }
+                }
+    }
+#ifdef B200ATTN_DEVTOOLS
+    if (const char *e = getenv("B200ATTN_SDTC_NQ")) nq = atoi(e);
+    if (const char *e = getenv("B200ATTN_SDTC_NLO")) nlo = atoi(e);
+    if (const char *e = getenv("B200ATTN_SDTC_KC")) kc = atoi(e);
+    if (nq < 1 || nq > apc || nlo < 1 || nlo > ST_NLO || (kc != 32 && kc != 64) || !sdtc_pv_fits(apc, nq, nlo, kc)) return -1;
+#endif
+    size_t smem = sdtc_smem_bytes(apc, nq, nlo);
+    const int tmem_cols = sdtc_tmem_cols(apc, kc);
+    // The CTAs that fit an SM by shared memory must also fit it by tensor memory (512 columns): a CTA that had to
+    // wait for columns held by CTAs that wait for its scores would never get them.  Ask for more shared memory
+    // where that is not so by itself.
+    {
+        const size_t sm_bytes = (size_t)c.max_smem_optin + 1024;
+        const size_t by_tmem = 512 / (size_t)tmem_cols;
+        if (sm_bytes / (smem + 1024) > by_tmem) smem = sm_bytes / (by_tmem + 1);
+    }
     if (!c.sdtc_attr) {
         cudaFuncAttributes fa;
         CU_TRY(cudaFuncGetAttributes(&fa, sdtc_kernel));
@@ -419,7 +458,7 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     p.BH = BH; p.Lq = Lq; p.Lk = Lk; p.D = D;
     p.apc = apc; p.natoms = natoms; p.nsplit = nsplit;
     const int buf = (int)(c.sdtc_seq % ST_NBUF);
-    p.buf = buf; p.gen_expect = c.sdtc_gen_expect[buf]; p.cap_bh = c.sdtc_cap; p.tmem_cols = tmem_cols; p.nlo = nlo;
+    p.buf = buf; p.gen_expect = c.sdtc_gen_expect[buf]; p.cap_bh = c.sdtc_cap; p.tmem_cols = tmem_cols; p.nlo = nlo; p.nq = nq; p.kc = kc;
     p.scale = 1.0f / sqrtf((float)D);
     p.O = (float *)a.out;
     p.S = c.sdtc_S; p.counters = c.sdtc_cnt; p.gen = c.sdtc_gen;
@@ -502,7 +541,7 @@ static int check_kernel_errors(DeviceCtx &c, cudaStream_t st, bool sync) {
     return report_kernel_errors(c, "kernel");
 }
 
-static int forward_device(const b200attn_args *a, bool independent_of_prev = false) {
+static int forward_device(const b200attn_args *a, bool independent_of_prev = false, bool batched = false) {
     int rd; float base;
     int rc = validate(a, &rd, &base);
     if (rc) return rc;
@@ -560,7 +599,7 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
     }
     if (!done && !(a->flags & (B200ATTN_FLAG_FORCE_GENERIC | B200ATTN_FLAG_FORCE_TWO_PASS))) {
         c->prev_sdtc = chain;
-        rc = run_sdtc(*c, *a, st, independent_of_prev);
+        rc = run_sdtc(*c, *a, st, independent_of_prev, batched);
         if (rc != B200ATTN_OK) c->prev_sdtc = false;
         if (rc == B200ATTN_OK) done = true;
         else if (rc != -1) return rc;
@@ -690,7 +729,9 @@ int b200attn_forward_many(const b200attn_args *args, int n) {
     if (args == nullptr || n < 0) return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_forward_many: NULL args or negative n");
     for (int i = 0; i < n; ++i) {
         // the entries are independent problems by contract: entry i may overlap the tail of entry i - 1
-        int rc = forward_device(&args[i], i > 0 && !(args[i].flags & B200ATTN_FLAG_NO_OVERLAP));
+        const bool beside_prev = i > 0 && !(args[i].flags & B200ATTN_FLAG_NO_OVERLAP);
+        const bool beside_next = i + 1 < n && !(args[i + 1].flags & B200ATTN_FLAG_NO_OVERLAP);
+        int rc = forward_device(&args[i], beside_prev, beside_prev || beside_next);
         if (rc) return rc;
     }
     return B200ATTN_OK;

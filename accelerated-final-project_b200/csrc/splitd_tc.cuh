@@ -10,10 +10,13 @@
 // reference kernel, final/attention.cu:120-142 and :169-181; the reference's own arithmetic is fp32
 // FMA, and the result here agrees with it to a few 1e-7.)
 //
-//   load      the whole slice is requested at once when the CTA starts (the bytes in flight per SM are
-//             what decides the HBM rate): Q and K as 32-column "atoms" (128 bytes per row, 128-byte
-//             swizzle: the K-major operand layout of the MMA), V as [keys x 32 columns] slabs with
-//             the 128-byte swizzle on 32-byte units, the MN-major operand layout of 32-bit elements.
+//   load      Q and K as 32-column "atoms" (128 bytes per row, 128-byte swizzle: the K-major operand
+//             layout of the MMA), V as [keys x 32 columns] slabs with the 128-byte swizzle on 32-byte
+//             units, the MN-major operand layout of 32-bit elements.  Either the whole slice is requested
+//             at once when the CTA starts (the bytes in flight per SM are what decides the HBM rate), or -
+//             the compact form, for calls that run beside their neighbours - V at once and the Q, K atoms
+//             through a ring of `nq` slots that the score MMAs hand back, so that a CTA of the widest slice
+//             takes less than half of an SM's shared memory and two calls share every SM.
 //   split     six warps rewrite each landed atom as hi (in place) and lo (into a two-deep ring);
 //   scores    one thread issues, per 8 columns, S[64 x 64] += Qhi Khi^T + Qhi Klo^T + Qlo Khi^T
 //             (M = 64: the accumulator row r sits in tensor-memory lane 32*(r/16) + r%16);
@@ -24,7 +27,9 @@
 //   softmax   every slice CTA reads the 64 x 64 scores back, one warp per row (shuffle max / sum), and
 //             writes P as hi and lo in the K-major operand layout;
 //   output    O[:, slice] = Phi Vhi + Phi Vlo + Plo Vhi (N = slice width), read from tensor memory and
-//             written to global memory by the row's thread (128 bytes per row and atom).
+//             written to global memory by the row's thread (128 bytes per row and atom).  V lo and P live
+//             where the Q, K atoms were; where that room is short the contraction runs in two halves of
+//             32 keys, V lo and P of the second half replacing those of the first.
 //
 // Consecutive independent calls overlap on the GPU (programmatic dependent launch: a call's kernel starts
 // while the one before it is still running, and two to four CTAs share an SM when the slices are narrow).
@@ -57,6 +62,8 @@ struct SdtcParams {
     unsigned gen_expect;     // heads that earlier calls must have cleared in that buffer before it is used
     int tmem_cols;           // tensor-memory columns to allocate (64, 128 or 256)
     int nlo;                 // stages of the residual ring: 1 or 2
+    int nq;                  // shared-memory slots for Q, K atoms: apc (all resident) or fewer (a ring)
+    int kc;                  // keys per pass of the P V contraction: 64 (one pass) or 32
     float scale;
     float *O;                // [B*H*Lq][D]
     float *S;                // [ST_NBUF][cap_bh][64][64] partial-score sums; all zero outside the heads in use
@@ -73,7 +80,8 @@ struct SdtcParams {
 };
 
 struct StBars {
-    uint64_t full[ST_MAX_ATOMS];            // atom c of Q and K has landed
+    uint64_t full[ST_MAX_ATOMS];            // slot c % nq: atom c of Q and K has landed
+    uint64_t qk_free[ST_MAX_ATOMS];         // slot c % nq: the MMAs of atom c have read it
     uint64_t ready[ST_NLO], lo_free[ST_NLO];   // residual ring: split done / read by the MMAs
     uint64_t v_full, s_full, o_full;
     uint64_t buf_ok;                        // the scratch buffer has been cleared by its previous users
@@ -89,8 +97,11 @@ struct StShared {
 };
 static_assert(sizeof(StShared) <= 256, "the barriers have to fit the alignment slack");
 
-// V slabs | Q,K atoms | residual ring, + 1 KB (alignment of the tiles, barriers)
-inline size_t sdtc_smem_bytes(int apc, int nlo) { return (size_t)apc * (ST_SLAB + ST_CHUNK) + (size_t)nlo * ST_CHUNK + 1024; }
+// V slabs | Q,K slots | residual ring, + 1 KB (alignment of the tiles, barriers)
+inline size_t sdtc_smem_bytes(int apc, int nq, int nlo) { return (size_t)apc * ST_SLAB + (size_t)(nq + nlo) * ST_CHUNK + 1024; }
+// What the P V contraction needs of the room the Q, K slots and the residual ring leave: V lo of a pass and
+// P hi, P lo of a pass.
+inline bool sdtc_pv_fits(int apc, int nq, int nlo, int kc) { return (size_t)apc * kc * 128 + (size_t)2 * (kc / 32) * ST_SLAB <= (size_t)(nq + nlo) * ST_CHUNK; }
 
 // x -> (x with the low 13 mantissa bits cleared, the exact remainder)
 __device__ __forceinline__ void st_split4(const float4 x, float4 &hi, float4 &lo) {
@@ -103,6 +114,22 @@ __device__ __forceinline__ void st_split4(const float4 x, float4 &hi, float4 &lo
 // byte offset of fp32 element (row, col) of a [64 rows x 32 columns] slab in the 128-byte swizzle
 __device__ __forceinline__ uint32_t st_swz(int row, int col) {
     return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 2) ^ (row & 7)) << 4)) + (col & 3) * 4);
+}
+
+// V hi in place and V lo (kc * 128 bytes per atom) for the key rows [k0, k0 + kc) of every atom, by the 192
+// threads of the split warps; key rows [Lk, kpad) enter the contraction and are written as zero
+__device__ __forceinline__ void st_split_v(unsigned char *v_hi, unsigned char *v_lo, int nat, int k0, int kc, int kpad, int Lk, int t) {
+    const int sh = kc == 64 ? 9 : 8;   // 16-byte pieces per atom and pass: kc * 8
+    for (int idx = t; idx < (nat << sh); idx += ST_SPLIT_THREADS) {
+        const int a = idx >> sh, i = idx & ((1 << sh) - 1), row = k0 + (i >> 3);
+        if (row < kpad) {
+            float4 *ph = reinterpret_cast<float4 *>(v_hi + (size_t)a * ST_SLAB + (size_t)k0 * 128 + (size_t)i * 16);
+            float4 hi = make_float4(0.f, 0.f, 0.f, 0.f), lo = hi;
+            if (row < Lk) st_split4(*ph, hi, lo);
+            *ph = hi;
+            *reinterpret_cast<float4 *>(v_lo + ((size_t)idx << 4)) = lo;   // a * kc * 128 + i * 16
+        }
+    }
 }
 
 #ifdef B200ATTN_DEVTOOLS
@@ -130,7 +157,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     const uint32_t raw_addr = smem_u32(st_smem_raw);
     const uint32_t slack = (1024u - (raw_addr & 1023u)) & 1023u;   // a multiple of 256
     unsigned char *smem = st_smem_raw + slack;
-    const size_t tile_bytes = (size_t)p.apc * (ST_SLAB + ST_CHUNK) + (size_t)p.nlo * ST_CHUNK;
+    const size_t tile_bytes = (size_t)p.apc * ST_SLAB + (size_t)(p.nq + p.nlo) * ST_CHUNK;
     // the 1 KB beyond the tiles is split into `slack` bytes before them and the rest behind them: the
     // barriers go where 256 bytes fit
     StShared &sh = *reinterpret_cast<StShared *>(slack >= 256 ? st_smem_raw : smem + tile_bytes);
@@ -149,13 +176,16 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     const uint32_t lim = p.spin_limit;
 
     unsigned char *v_hi = smem;                                      // apc slabs [keys x 32 columns]
-    unsigned char *qk = smem + (size_t)p.apc * ST_SLAB;              // apc atoms: Q [64 x 32] | K [64 x 32]
-    unsigned char *lo_ring = qk + (size_t)p.apc * ST_CHUNK;          // p.nlo stages: Q lo | K lo
-    // once the score MMAs are done: V lo where the first Q, K atoms were (so that V hi | V lo is one
-    // run of slabs when the slice is full), P behind it or in the residual ring, whichever has 32 KB
+    unsigned char *qk = smem + (size_t)p.apc * ST_SLAB;              // p.nq slots: Q [64 x 32] | K [64 x 32]
+    unsigned char *lo_ring = qk + (size_t)p.nq * ST_CHUNK;           // p.nlo stages: Q lo | K lo
+    // once the score MMAs are done: V lo of a pass (kc keys of every atom) where the first Q, K atoms were (so
+    // that V hi | V lo is one run of slabs when the slice is full and resident), P of a pass (kc / 32 atoms of
+    // 32 keys, hi and lo) at the end of the residual ring
+    const int kc = p.kc, pslabs = kc >> 5;
+    const uint32_t vlo_pitch = (uint32_t)kc * 128u;
     unsigned char *v_lo = qk;
-    unsigned char *p_hi = (p.apc >= 4) ? qk + (size_t)p.apc * ST_SLAB : lo_ring;   // two atoms of 32 keys
-    unsigned char *p_lo = p_hi + 2 * ST_SLAB;
+    unsigned char *p_hi = lo_ring + (size_t)p.nlo * ST_CHUNK - (size_t)2 * pslabs * ST_SLAB;
+    unsigned char *p_lo = p_hi + (size_t)pslabs * ST_SLAB;
 
     float *S_cur = p.S + ((size_t)p.buf * p.cap_bh + bh) * 4096;
     unsigned *cnt_cur = p.counters + ((size_t)p.buf * p.cap_bh + bh) * 2;   // [0] arrivals, [1] readers
@@ -165,7 +195,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     // the other warps allocate tensor memory and meet at the barrier below
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-        for (int i = 0; i < ST_MAX_ATOMS; ++i) mbar_init(&bars.full[i], 1);
+        for (int i = 0; i < ST_MAX_ATOMS; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.qk_free[i], 1); }
         for (int i = 0; i < ST_NLO; ++i) { mbar_init(&bars.ready[i], 6); mbar_init(&bars.lo_free[i], 1); }
         mbar_init(&bars.v_full, 1);
         mbar_init(&bars.s_full, 1);
@@ -173,7 +203,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         mbar_init(&bars.buf_ok, 1);
         s_fail = 0u;
         mbar_fence_init();
-        for (int c = 0; c < nat; ++c) {
+        for (int c = 0; c < nat && c < p.nq; ++c) {
             unsigned char *st = qk + (size_t)c * ST_CHUNK;
             mbar_expect_tx(&bars.full[c], (uint32_t)(Lq + Lk) * 128u);
             tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[c]);
@@ -206,6 +236,19 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
             }
             mbar_arrive(&bars.buf_ok);
+            // ---- the compact form: the atoms beyond the slots follow as the score MMAs hand slots back ----
+            for (int c = p.nq; c < nat; ++c) {
+                const int s = c % p.nq;
+                if (!mbar_wait(&bars.qk_free[s], ((c / p.nq) - 1) & 1, lim)) {
+                    report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 16));
+                    *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
+                    break;
+                }
+                unsigned char *st = qk + (size_t)s * ST_CHUNK;
+                mbar_expect_tx(&bars.full[s], (uint32_t)(Lq + Lk) * 128u);
+                tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[s]);
+                tma_load_2d(st + ST_SLAB, &tmK, atom_col(c), (int)(bh * Lk), &bars.full[s]);
+            }
             // ---- the head's scores are complete when every read-out warp of every slice has arrived ----
             const unsigned want = 4u * (unsigned)p.nsplit + p.wait_extra;
             seen = 0;
@@ -225,11 +268,11 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             // ---- score MMAs ----
             const uint32_t id64 = umma_idesc_tf32(64, 64, 0, 0);
             for (int c = 0; c < nat; ++c) {
-                const int j = c % p.nlo;
+                const int j = c % p.nlo, s = c % p.nq;
                 ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (c / p.nlo) & 1, lim));
                 if (c == nat - 1) ST_STAMP(18);
                 tc_fence_after();
-                const uint32_t sa = smem_u32(qk + (size_t)c * ST_CHUNK), sl = smem_u32(lo_ring + (size_t)j * ST_CHUNK);
+                const uint32_t sa = smem_u32(qk + (size_t)s * ST_CHUNK), sl = smem_u32(lo_ring + (size_t)j * ST_CHUNK);
                 const uint64_t dq_hi = umma_desc_k_sw128(sa), dk_hi = umma_desc_k_sw128(sa + ST_SLAB);
                 const uint64_t dq_lo = umma_desc_k_sw128(sl), dk_lo = umma_desc_k_sw128(sl + ST_SLAB);
 #pragma unroll
@@ -239,6 +282,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     umma_tf32(tmem, dq_lo + 2 * k, dk_hi + 2 * k, id64, 1u);
                 }
                 umma_commit(&bars.lo_free[j]);
+                if (c + p.nq < nat) umma_commit(&bars.qk_free[s]);
             }
             if (!failed) umma_commit(&bars.s_full);
             ST_STAMP(19);
@@ -247,12 +291,12 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const int t = threadIdx.x - 64;   // 0..191
         // ---- hi / lo split of the landed Q and K atoms ----
         for (int c = 0; c < nat; ++c) {
-            const int j = c % p.nlo;
-            ST_FAIL_AT(3, !mbar_wait(&bars.full[c], 0, lim));
+            const int j = c % p.nlo, s = c % p.nq;
+            ST_FAIL_AT(3, !mbar_wait(&bars.full[s], (c / p.nq) & 1, lim));
             ST_FAIL_AT(7, !mbar_wait(&bars.lo_free[j], ((c / p.nlo) & 1) ^ 1, lim));
             if (t == 0 && c == 0) ST_STAMP(2);
             if (t == 0 && c == nat - 1) ST_STAMP(3);
-            unsigned char *st = qk + (size_t)c * ST_CHUNK, *sl = lo_ring + (size_t)j * ST_CHUNK;
+            unsigned char *st = qk + (size_t)s * ST_CHUNK, *sl = lo_ring + (size_t)j * ST_CHUNK;
             for (int idx = t; idx < 1024; idx += ST_SPLIT_THREADS) {
                 const int part = idx >> 9, i = idx & 511;   // idx * 16 is the byte offset in both the atom pair and the ring stage
                 if ((i >> 3) < (part ? Lk : Lq)) {
@@ -307,21 +351,12 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             // release at gpu scope, cumulative over the warp's additions (ordered before it by the warp barrier)
             if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(cnt_cur) : "memory");
         }
-        // ---- hi / lo split of V; key rows [Lk, kpad) enter the contraction and must be zero ----
+        // ---- hi / lo split of V for the first pass of P V (all of V when there is one pass) ----
         if (!failed) {
             do {
                 ST_FAIL_AT(5, !mbar_wait(&bars.v_full, 0, lim));
                 if (t == 0) ST_STAMP(8);
-                for (int idx = t; idx < nat * 512; idx += ST_SPLIT_THREADS) {
-                    const int i = idx & 511, row = i >> 3;   // idx * 16 is the byte offset in the run of slabs
-                    if (row < kpad) {
-                        float4 *ph = reinterpret_cast<float4 *>(v_hi + (size_t)idx * 16);
-                        float4 hi = make_float4(0.f, 0.f, 0.f, 0.f), lo = hi;
-                        if (row < Lk) st_split4(*ph, hi, lo);
-                        *ph = hi;
-                        *reinterpret_cast<float4 *>(v_lo + (size_t)idx * 16) = lo;
-                    }
-                }
+                st_split_v(v_hi, v_lo, nat, 0, kc, kpad, Lk, t);
                 fence_proxy_async_smem();
             } while (false);
         }
@@ -331,12 +366,12 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     if (threadIdx.x == 0) ST_STAMP(10);
     failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
 
-    // ---- softmax of the head's scores: half a warp per row, four keys per lane (16-byte loads and
-    // stores); P written as hi / lo operand tiles ----
+    // ---- softmax of the head's scores: half a warp per row, four keys per lane (16-byte loads); the
+    // probabilities stay in registers until the pass of P V that takes their keys ----
+    constexpr int RPW = 4;   // row pairs per warp: warp w owns rows [8w, 8w + 8)
+    const int cg = lane & 15, r2 = lane >> 4;
+    float4 sv[RPW];
     if (!failed) {
-        constexpr int RPW = 4;   // row pairs per warp: warp w owns rows [8w, 8w + 8)
-        const int cg = lane & 15, r2 = lane >> 4;
-        float4 sv[RPW];
 #pragma unroll
         for (int k = 0; k < RPW; ++k) {
             const int i = 8 * warp + 2 * k + r2;
@@ -370,72 +405,91 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             for (int k = 0; k < RPW; ++k) tot[k] += __shfl_xor_sync(0xffffffffu, tot[k], o);
 #pragma unroll
         for (int k = 0; k < RPW; ++k) {
-            const int i = 8 * warp + 2 * k + r2;
-            if (i < Lq && 4 * cg < kpad) {
-                const float inv = __frcp_rn(tot[k]);
-                float4 hi, lo;
-                st_split4(make_float4(sv[k].x * inv, sv[k].y * inv, sv[k].z * inv, sv[k].w * inv), hi, lo);
-                const uint32_t off = (uint32_t)((cg >> 3) * ST_SLAB) + st_swz(i, 4 * (cg & 7));
-                *reinterpret_cast<float4 *>(p_hi + off) = hi;
-                *reinterpret_cast<float4 *>(p_lo + off) = lo;
-            }
+            const float inv = __frcp_rn(tot[k]);
+            sv[k].x *= inv; sv[k].y *= inv; sv[k].z *= inv; sv[k].w *= inv;
         }
-        if (threadIdx.x == 0) ST_STAMP(20);
-        fence_proxy_async_smem();
-        if (threadIdx.x == 0) ST_STAMP(21);
-        ST_DBG(2, if (warp == 0 && lane < 16) { p.dbg[384 + 4 * lane] = sv[0].x; });
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    ST_DBG(3, if (threadIdx.x < 64) { p.dbg[512 + threadIdx.x] = reinterpret_cast<float *>(p_hi)[threadIdx.x]; p.dbg[576 + threadIdx.x] = reinterpret_cast<float *>(v_hi)[threadIdx.x];
-                                      p.dbg[640 + threadIdx.x] = reinterpret_cast<float *>(v_lo)[threadIdx.x]; });
 
-    if (threadIdx.x == 0) ST_STAMP(11);
-    // ---- O[:, slice] = P V ----
-    // With a slice of at most 128 columns, V hi and V lo (contiguous slabs) are one B operand of
+    // ---- O[:, slice] = P V, in passes of kc keys ----
+    // With a resident slice of at most 128 columns, V hi and V lo (contiguous slabs) are one B operand of
     // N = 2 * width: P hi [V hi | V lo] and then columns [0, width) += P lo V hi, two MMAs per 8 keys
     // instead of three (an MMA of this size costs its issue latency, not its arithmetic).
-    const bool v_cat = (nat == p.apc) && (2 * nat * ST_ATOM <= 256);
-    if (warp == 1 && lane == 0 && !failed) {
-        const uint32_t idv = umma_idesc_tf32(64, nat * ST_ATOM, 0, 1), idv2 = umma_idesc_tf32(64, 2 * nat * ST_ATOM, 0, 1);
-        const int ksteps = kpad >> 3;
-        for (int kk = 0; kk < ksteps; ++kk) {
-            const uint64_t dp_hi = umma_desc_k_sw128(smem_u32(p_hi + (size_t)(kk >> 2) * ST_SLAB)) + 2 * (kk & 3);
-            const uint64_t dp_lo = umma_desc_k_sw128(smem_u32(p_lo + (size_t)(kk >> 2) * ST_SLAB)) + 2 * (kk & 3);
-            const uint64_t dv_hi = umma_desc_mn_sw128_32b(smem_u32(v_hi + (size_t)kk * 1024), ST_SLAB, 512);
-            const uint64_t dv_lo = umma_desc_mn_sw128_32b(smem_u32(v_lo + (size_t)kk * 1024), ST_SLAB, 512);
-            if (v_cat) {
-                umma_tf32(tmem, dp_hi, dv_hi, idv2, kk != 0);
-                umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
-            } else {
-                umma_tf32(tmem, dp_hi, dv_hi, idv, kk != 0);
-                umma_tf32(tmem, dp_hi, dv_lo, idv, 1u);
-                umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
-            }
+    const bool v_cat = (nat == p.apc) && (2 * nat * ST_ATOM <= 256) && kc == 64;
+    const int ksteps = kpad >> 3, kpc = kc >> 3;   // 8-key MMA steps in all and per pass
+    const int npass = (ksteps + kpc - 1) / kpc;
+    for (int h = 0; h < npass; ++h) {
+        if (h > 0 && !failed) {
+            // the MMAs of the previous pass have read their V lo and P: both are replaced
+            do { ST_FAIL_AT(9, !mbar_wait(&bars.o_full, (h - 1) & 1, lim)); } while (false);
+            if (!failed && warp >= 2) st_split_v(v_hi, v_lo, nat, h * kc, kc, kpad, Lk, (int)threadIdx.x - 64);
         }
-        umma_commit(&bars.o_full);
-        ST_STAMP(22);
-    }
-    // ---- while P V runs: this slice has read the head's scores; the last slice to say so clears them and
-    // the head's counters for the buffer's next user, then bumps the buffer's generation ----
-    if (warp == 2 && !failed) {
-        unsigned old = 0;
-        if (lane == 0) asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt_cur + 1) : "memory");
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old == (unsigned)p.nsplit - 1u) {
-            float4 *z = reinterpret_cast<float4 *>(S_cur);
+        if (!failed) {
+            // P of this pass as hi / lo operand tiles (K-major, 32 keys per 128-byte row)
+            const int ks = cg >> 3;                                  // which 32 keys this lane's four belong to
+            const bool mine = (pslabs == 2) ? true : (ks == h);
+            const uint32_t slab_off = (pslabs == 2) ? (uint32_t)ks * ST_SLAB : 0u;
+#pragma unroll
+            for (int k = 0; k < RPW; ++k) {
+                const int i = 8 * warp + 2 * k + r2;
+                if (mine && i < Lq && 4 * cg < kpad) {
+                    float4 hi, lo;
+                    st_split4(sv[k], hi, lo);
+                    const uint32_t off = slab_off + st_swz(i, 4 * (cg & 7));
+                    *reinterpret_cast<float4 *>(p_hi + off) = hi;
+                    *reinterpret_cast<float4 *>(p_lo + off) = lo;
+                }
+            }
+            if (threadIdx.x == 0) ST_STAMP(20);
+            fence_proxy_async_smem();
+            if (threadIdx.x == 0) ST_STAMP(21);
+        }
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+        failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
+        ST_DBG(3, if (h == 0 && threadIdx.x < 64) { p.dbg[512 + threadIdx.x] = reinterpret_cast<float *>(p_hi)[threadIdx.x]; p.dbg[576 + threadIdx.x] = reinterpret_cast<float *>(v_hi)[threadIdx.x];
+                                                    p.dbg[640 + threadIdx.x] = reinterpret_cast<float *>(v_lo)[threadIdx.x]; });
+        if (threadIdx.x == 0 && h == 0) ST_STAMP(11);
+        if (warp == 1 && lane == 0 && !failed) {
+            const uint32_t idv = umma_idesc_tf32(64, nat * ST_ATOM, 0, 1), idv2 = umma_idesc_tf32(64, 2 * nat * ST_ATOM, 0, 1);
+            for (int kk = h * kpc; kk < ksteps && kk < (h + 1) * kpc; ++kk) {
+                const int kl = kk - h * kpc;
+                const uint64_t dp_hi = umma_desc_k_sw128(smem_u32(p_hi + (size_t)(kl >> 2) * ST_SLAB)) + 2 * (kl & 3);
+                const uint64_t dp_lo = umma_desc_k_sw128(smem_u32(p_lo + (size_t)(kl >> 2) * ST_SLAB)) + 2 * (kl & 3);
+                const uint64_t dv_hi = umma_desc_mn_sw128_32b(smem_u32(v_hi + (size_t)kk * 1024), ST_SLAB, 512);
+                const uint64_t dv_lo = umma_desc_mn_sw128_32b(smem_u32(v_lo + (size_t)kl * 1024), vlo_pitch, 512);
+                if (v_cat) {
+                    umma_tf32(tmem, dp_hi, dv_hi, idv2, kk != 0);
+                    umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
+                } else {
+                    umma_tf32(tmem, dp_hi, dv_hi, idv, kk != 0);
+                    umma_tf32(tmem, dp_hi, dv_lo, idv, 1u);
+                    umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
+                }
+            }
+            umma_commit(&bars.o_full);
+            ST_STAMP(22);
+        }
+        // ---- while P V runs: this slice has read the head's scores; the last slice to say so clears them and
+        // the head's counters for the buffer's next user, then bumps the buffer's generation ----
+        if (h == 0 && warp == 2 && !failed) {
+            unsigned old = 0;
+            if (lane == 0) asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(cnt_cur + 1) : "memory");
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == (unsigned)p.nsplit - 1u) {
+                float4 *z = reinterpret_cast<float4 *>(S_cur);
 #pragma unroll 4
-            for (int i = lane; i < 1024; i += 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (lane < 2) cnt_cur[lane] = 0u;
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.gen + p.buf) : "memory");
+                for (int i = lane; i < 1024; i += 32) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (lane < 2) cnt_cur[lane] = 0u;
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.gen + p.buf) : "memory");
+            }
         }
     }
     if (!failed) {
         do {
-            ST_FAIL_AT(6, !mbar_wait(&bars.o_full, 0, lim));
+            ST_FAIL_AT(6, !mbar_wait(&bars.o_full, (npass - 1) & 1, lim));
             if (threadIdx.x == 0) ST_STAMP(12);
             tc_fence_after();
             // warp w reads lane quadrant w % 4 (rows 16 (w % 4) .. + 15 in its lanes 0-15), every second slab, and
