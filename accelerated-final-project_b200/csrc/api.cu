@@ -357,18 +357,12 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
 #ifdef B200ATTN_DEVTOOLS
 static float *g_sdtc_dbg = nullptr;
 static unsigned long long *g_sdtc_stamps = nullptr;
+static long long g_sdtc_stamp_calls = 0;   // with B200ATTN_SDTC_STAMP_STRIDE set: call n writes at n * stride
 #endif
 // ---- split-head_d path on the tensor cores (fp32, no positional encoding, len <= 64) ---------------
 // Slices are whole 32-column atoms; a head gets as many slices as the SM count allows.  Returns -1 when
 // the shape belongs to the CUDA-core kernels (an encoding, an odd head_d, more heads than SMs, a slice
 // wider than 256 columns).
-// tensor-memory columns of a CTA: 64 for the scores; the output (over them) takes the slice width, twice that
-// where V hi | V lo is one operand (slices of up to 128 columns, P V in one pass)
-static int sdtc_tmem_cols(int apc, int kc) {
-    const int o_cols = apc * ST_ATOM * ((2 * apc * ST_ATOM <= 256 && kc == 64) ? 2 : 1);
-    return o_cols <= 64 ? 64 : o_cols <= 128 ? 128 : 256;
-}
-
 // `independent_of_prev`: the caller declared this call independent of the one before it; `batched`: the call is
 // one of a batch of such calls (it, or the next one, may run beside its neighbour).
 static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool independent_of_prev, bool batched) {
@@ -392,37 +386,41 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     auto hits_prev_out = [&](const void *ptr, size_t n) { return (uintptr_t)ptr < c.prev_out_hi && (uintptr_t)ptr + n > c.prev_out_lo; };
     const bool overlap = independent_of_prev && c.prev_sdtc && c.prev_stream == st && !c.scratch_dirty &&
                          !hits_prev_out(a.Q, in_q) && !hits_prev_out(a.K, in_k) && !hits_prev_out(a.V, in_k);
-    // Shared memory of a CTA.  A call on its own keeps its whole slice resident with a two-deep residual ring.
-    // A call of a batch takes the form that lets the most CTAs share an SM (its neighbours in the stream run
-    // beside it): fewer Q, K slots than atoms, one residual stage, P V in two passes - whatever it takes, as
-    // long as at least two slots remain; among equals the form with the most slots.
-    int nq = apc, nlo = ST_NLO, kc = 64;
+    // Shared memory of a CTA: nq slots and nlo residual stages of 16 KB.  A call on its own takes a slot per atom
+    // and per pair of V slabs (everything is requested when the CTA starts) and does P V in one pass.  A call of a
+    // batch takes the form that lets the most CTAs share an SM - its neighbours in the stream run beside it -
+    // (at most three: the registers): fewer slots than atoms, one residual stage, P V in two passes; among
+    // equals the form with the most slots.
+    const int nb = sdtc_vblocks(apc), tmem_cols = 128 * nb;
+    const size_t sm_bytes = (size_t)c.max_smem_optin + 1024;   // per SM; the system keeps 1 KB per CTA
+    int nq = 0, nlo = ST_NLO, kc = 64;
     if (batched || overlap) {
-        const size_t sm_bytes = (size_t)c.max_smem_optin + 1024;   // per SM; the system keeps 1 KB per CTA
         int best = 0;
-        for (int q = apc; q >= (apc < 2 ? apc : 2); --q)
+        for (int q = apc + 2 * nb; q >= 2 * nb + 1; --q)
             for (int l = ST_NLO; l >= 1; --l)
                 for (int k = 64; k >= 32; k -= 32) {
-                    if (!sdtc_pv_fits(apc, q, l, k)) continue;
-                    int n = (int)(sm_bytes / (sdtc_smem_bytes(apc, q, l) + 1024));
-                    const int by_tmem = 512 / sdtc_tmem_cols(apc, k);
-                    if (n > by_tmem) n = by_tmem;
+                    if (!sdtc_layout_ok(apc, q, l, k)) continue;
+                    int n = (int)(sm_bytes / (sdtc_smem_bytes(q, l) + 1024));
+                    if (n > 512 / tmem_cols) n = 512 / tmem_cols;
+                    if (n > 3) n = 3;
                     if (n > best) { best = n; nq = q; nlo = l; kc = k; }
                 }
+    } else {
+        for (int q = apc + 2 * nb; q <= ST_MAX_SLOTS && nq == 0; ++q)
+            if (sdtc_layout_ok(apc, q, nlo, kc)) nq = q;
     }
 #ifdef B200ATTN_DEVTOOLS
     if (const char *e = getenv("B200ATTN_SDTC_NQ")) nq = atoi(e);
     if (const char *e = getenv("B200ATTN_SDTC_NLO")) nlo = atoi(e);
     if (const char *e = getenv("B200ATTN_SDTC_KC")) kc = atoi(e);
-    if (nq < 1 || nq > apc || nlo < 1 || nlo > ST_NLO || (kc != 32 && kc != 64) || !sdtc_pv_fits(apc, nq, nlo, kc)) return -1;
+    if (nlo < 1 || nlo > ST_NLO || (kc != 32 && kc != 64)) return -1;
 #endif
-    size_t smem = sdtc_smem_bytes(apc, nq, nlo);
-    const int tmem_cols = sdtc_tmem_cols(apc, kc);
+    if (nq == 0 || !sdtc_layout_ok(apc, nq, nlo, kc)) return -1;
+    size_t smem = sdtc_smem_bytes(nq, nlo);
     // The CTAs that fit an SM by shared memory must also fit it by tensor memory (512 columns): a CTA that had to
     // wait for columns held by CTAs that wait for its scores would never get them.  Ask for more shared memory
     // where that is not so by itself.
     {
-        const size_t sm_bytes = (size_t)c.max_smem_optin + 1024;
         const size_t by_tmem = 512 / (size_t)tmem_cols;
         if (sm_bytes / (smem + 1024) > by_tmem) smem = sm_bytes / (by_tmem + 1);
     }
@@ -468,6 +466,10 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
 #ifdef B200ATTN_DEVTOOLS
     p.dbg = g_sdtc_dbg;
     p.stamps = g_sdtc_stamps;
+    if (g_sdtc_stamps != nullptr) {
+        static const long long stride = getenv("B200ATTN_SDTC_STAMP_STRIDE") ? atoll(getenv("B200ATTN_SDTC_STAMP_STRIDE")) : 0;
+        p.stamps += (g_sdtc_stamp_calls++) * stride;
+    }
 #endif
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)nsplit, (unsigned)BH);
@@ -709,7 +711,7 @@ int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
 }
 
 void b200attn_debug_sdtc_dump(float *dev_buf) { g_sdtc_dbg = dev_buf; }
-void b200attn_debug_sdtc_stamps(unsigned long long *dev_buf) { g_sdtc_stamps = dev_buf; }
+void b200attn_debug_sdtc_stamps(unsigned long long *dev_buf) { g_sdtc_stamps = dev_buf; g_sdtc_stamp_calls = 0; }
 
 #ifdef B200ATTN_SD_PROFILE
 int b200attn_debug_sd_stamps(unsigned long long *out, int n) {

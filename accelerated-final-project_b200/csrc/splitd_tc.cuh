@@ -47,9 +47,10 @@ constexpr int ST_THREADS = 256;        // warp 0: TMA + arrival counter, warp 1:
 constexpr int ST_SPLIT_THREADS = 192;
 constexpr int ST_ATOM = 32;            // fp32 columns in a 128-byte swizzled row
 constexpr int ST_SLAB = 64 * 128;      // [64 rows x 128 B]
-constexpr int ST_CHUNK = 2 * ST_SLAB;  // one atom of Q and of K
-constexpr int ST_MAX_ATOMS = 8;        // widest slice: 256 columns (one MMA N; 24 KB per atom + the residual ring fit 227 KB)
-constexpr int ST_NLO = 2;              // residual ring depth (one stage where that lets two CTAs share an SM)
+constexpr int ST_CHUNK = 2 * ST_SLAB;  // a slot: one atom of Q and of K, or two slabs of V
+constexpr int ST_MAX_ATOMS = 8;        // widest slice: 256 columns (two blocks of 128 output columns)
+constexpr int ST_MAX_SLOTS = 12;       // atoms of the widest slice + its V slabs
+constexpr int ST_NLO = 2;              // residual ring depth (one stage in the compact forms)
 constexpr int ST_NBUF = 8;             // score-scratch ring
 
 struct SdtcParams {
@@ -60,9 +61,9 @@ struct SdtcParams {
     int nsplit;              // slices per head
     int buf;                 // which buffer of the scratch ring this call sums into
     unsigned gen_expect;     // heads that earlier calls must have cleared in that buffer before it is used
-    int tmem_cols;           // tensor-memory columns to allocate (64, 128 or 256)
+    int tmem_cols;           // tensor-memory columns to allocate (128 or 256)
     int nlo;                 // stages of the residual ring: 1 or 2
-    int nq;                  // shared-memory slots for Q, K atoms: apc (all resident) or fewer (a ring)
+    int nq;                  // shared-memory slots (16 KB): the last 2 * ceil(apc / 4) of them receive V
     int kc;                  // keys per pass of the P V contraction: 64 (one pass) or 32
     float scale;
     float *O;                // [B*H*Lq][D]
@@ -80,28 +81,35 @@ struct SdtcParams {
 };
 
 struct StBars {
-    uint64_t full[ST_MAX_ATOMS];            // slot c % nq: atom c of Q and K has landed
-    uint64_t qk_free[ST_MAX_ATOMS];         // slot c % nq: the MMAs of atom c have read it
+    uint64_t full[ST_MAX_SLOTS];            // slot c % nq: atom c of Q and K has landed
+    uint64_t qk_free[ST_MAX_SLOTS];         // slot c % nq: the MMAs of atom c have read it
     uint64_t ready[ST_NLO], lo_free[ST_NLO];   // residual ring: split done / read by the MMAs
     uint64_t v_full, s_full, o_full;
     uint64_t buf_ok;                        // the scratch buffer has been cleared by its previous users
 };
 
 // The kernel's barriers and flags live in the dynamic allocation too (no static shared memory), in the
-// kilobyte that aligning the tiles to 1024 bytes leaves over: a slice of 128 columns with one ring stage is
-// then exactly half of an SM's shared memory.
+// kilobyte that aligning the tiles to 1024 bytes leaves over.
 struct StShared {
     StBars bars;
     uint32_t tmem_slot;
     unsigned s_fail;
 };
-static_assert(sizeof(StShared) <= 256, "the barriers have to fit the alignment slack");
+static_assert(sizeof(StShared) <= 512, "the barriers have to fit the alignment slack");
 
-// V slabs | Q,K slots | residual ring, + 1 KB (alignment of the tiles, barriers)
-inline size_t sdtc_smem_bytes(int apc, int nq, int nlo) { return (size_t)apc * ST_SLAB + (size_t)(nq + nlo) * ST_CHUNK + 1024; }
-// What the P V contraction needs of the room the Q, K slots and the residual ring leave: V lo of a pass and
-// P hi, P lo of a pass.
-inline bool sdtc_pv_fits(int apc, int nq, int nlo, int kc) { return (size_t)apc * kc * 128 + (size_t)2 * (kc / 32) * ST_SLAB <= (size_t)(nq + nlo) * ST_CHUNK; }
+// Shared memory of a CTA: residual ring | slots, + 1 KB (alignment of the tiles, barriers).
+//   while the scores are computed   ring stages hold Q lo | K lo of the atom being multiplied; slot c % nq holds atom
+//                                   c of Q and K (hi in place);
+//   afterwards                      V (hi in place) sits in the last 2 * ceil(apc / 4) slots - requested as soon as
+//                                   the last atom that used a slot has been multiplied, at once for slots no atom
+//                                   ever uses; everything below them holds P of a pass and V lo of a pass.
+inline int sdtc_vblocks(int apc) { return (apc + 3) / 4; }
+inline size_t sdtc_smem_bytes(int nq, int nlo) { return (size_t)(nq + nlo) * ST_CHUNK + 1024; }
+// P [hi | lo] of a pass is kc / 32 slots, V lo of a pass the same per block of four atoms
+inline bool sdtc_layout_ok(int apc, int nq, int nlo, int kc) {
+    const int nb = sdtc_vblocks(apc);
+    return nq <= ST_MAX_SLOTS && nq >= 2 * nb + 1 && (1 + nb) * (kc / 32) <= nlo + nq - 2 * nb;
+}
 
 // x -> (x with the low 13 mantissa bits cleared, the exact remainder)
 __device__ __forceinline__ void st_split4(const float4 x, float4 &hi, float4 &lo) {
@@ -149,18 +157,18 @@ __device__ __forceinline__ void st_split_v(unsigned char *v_hi, unsigned char *v
         break;                                                                                       \
     }
 
-__global__ void __launch_bounds__(ST_THREADS, 1)
+__global__ void __launch_bounds__(ST_THREADS, 3)
 sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const SdtcParams p) {
     extern __shared__ __align__(256) unsigned char st_smem_raw[];
     if (threadIdx.x == 0) ST_STAMP(0);
     const uint32_t raw_addr = smem_u32(st_smem_raw);
-    const uint32_t slack = (1024u - (raw_addr & 1023u)) & 1023u;   // a multiple of 256
+    const uint32_t slack = (1024u - (raw_addr & 1023u)) & 1023u;   // 0, 256, 512 or 768
     unsigned char *smem = st_smem_raw + slack;
-    const size_t tile_bytes = (size_t)p.apc * ST_SLAB + (size_t)(p.nq + p.nlo) * ST_CHUNK;
+    const size_t tile_bytes = (size_t)(p.nq + p.nlo) * ST_CHUNK;
     // the 1 KB beyond the tiles is split into `slack` bytes before them and the rest behind them: the
-    // barriers go where 256 bytes fit
-    StShared &sh = *reinterpret_cast<StShared *>(slack >= 256 ? st_smem_raw : smem + tile_bytes);
+    // barriers go where 512 bytes fit
+    StShared &sh = *reinterpret_cast<StShared *>(slack >= 512 ? st_smem_raw : smem + tile_bytes);
     StBars &bars = sh.bars;
     uint32_t &tmem_slot = sh.tmem_slot;
     unsigned &s_fail = sh.s_fail;
@@ -174,28 +182,41 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     auto atom_col = [&](int c) { return (slice + c * p.nsplit) * ST_ATOM; };
     const int kpad = (Lk + 7) & ~7;              // keys covered by the P V contraction (8 per MMA)
     const uint32_t lim = p.spin_limit;
+    const int nq = p.nq, nblk = (p.apc + 3) >> 2;
+    const int vslot0 = nq - 2 * nblk;            // the slots from here on receive V, two slabs each
 
-    unsigned char *v_hi = smem;                                      // apc slabs [keys x 32 columns]
-    unsigned char *qk = smem + (size_t)p.apc * ST_SLAB;              // p.nq slots: Q [64 x 32] | K [64 x 32]
-    unsigned char *lo_ring = qk + (size_t)p.nq * ST_CHUNK;           // p.nlo stages: Q lo | K lo
-    // once the score MMAs are done: V lo of a pass (kc keys of every atom) where the first Q, K atoms were (so
-    // that V hi | V lo is one run of slabs when the slice is full and resident), P of a pass (kc / 32 atoms of
-    // 32 keys, hi and lo) at the end of the residual ring
+    unsigned char *lo_ring = smem;                                   // p.nlo stages: Q lo | K lo
+    unsigned char *slots = smem + (size_t)p.nlo * ST_CHUNK;          // nq slots: Q [64 x 32] | K [64 x 32]
+    unsigned char *v_hi = slots + (size_t)vslot0 * ST_CHUNK;         // afterwards: slab a = V[:, atom a] [keys x 32 columns]
+    // below V, once the score MMAs are done: P of a pass (per 32 keys: hi [64 x 32] | lo [64 x 32], one N = 128
+    // operand) and V lo of a pass (kc keys of every atom)
     const int kc = p.kc, pslabs = kc >> 5;
     const uint32_t vlo_pitch = (uint32_t)kc * 128u;
-    unsigned char *v_lo = qk;
-    unsigned char *p_hi = lo_ring + (size_t)p.nlo * ST_CHUNK - (size_t)2 * pslabs * ST_SLAB;
-    unsigned char *p_lo = p_hi + (size_t)pslabs * ST_SLAB;
+    unsigned char *p_buf = smem;
+    unsigned char *v_lo = smem + (size_t)pslabs * ST_CHUNK;
 
     float *S_cur = p.S + ((size_t)p.buf * p.cap_bh + bh) * 4096;
     unsigned *cnt_cur = p.counters + ((size_t)p.buf * p.cap_bh + bh) * 2;   // [0] arrivals, [1] readers
 
-    // one thread sets the barriers up and at once requests the whole slice, Q and K first and V behind them
-    // (a second issuing thread, or V requested alongside, measured no faster): the loads are in flight while
-    // the other warps allocate tensor memory and meet at the barrier below
+    // requests of thread 0
+    auto load_atom = [&](int c) {
+        const int s = c % nq;
+        unsigned char *st = slots + (size_t)s * ST_CHUNK;
+        mbar_expect_tx(&bars.full[s], (uint32_t)(Lq + Lk) * 128u);
+        tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[s]);
+        tma_load_2d(st + ST_SLAB, &tmK, atom_col(c), (int)(bh * Lk), &bars.full[s]);
+    };
+    auto load_v_slot = [&](int s) {   // the two slabs of V that live in slot s >= vslot0
+        for (int a = 2 * (s - vslot0); a < 2 * (s - vslot0) + 2 && a < nat; ++a)
+            tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, atom_col(a), (int)(bh * Lk), &bars.v_full);
+    };
+
+    // one thread sets the barriers up and at once requests what has room: the first nq atoms of Q and K, then the
+    // slabs of V whose slots no atom uses (a second issuing thread, or V requested alongside, measured no
+    // faster): the loads are in flight while the other warps allocate tensor memory and meet at the barrier below
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-        for (int i = 0; i < ST_MAX_ATOMS; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.qk_free[i], 1); }
+        for (int i = 0; i < ST_MAX_SLOTS; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.qk_free[i], 1); }
         for (int i = 0; i < ST_NLO; ++i) { mbar_init(&bars.ready[i], 6); mbar_init(&bars.lo_free[i], 1); }
         mbar_init(&bars.v_full, 1);
         mbar_init(&bars.s_full, 1);
@@ -203,14 +224,9 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         mbar_init(&bars.buf_ok, 1);
         s_fail = 0u;
         mbar_fence_init();
-        for (int c = 0; c < nat && c < p.nq; ++c) {
-            unsigned char *st = qk + (size_t)c * ST_CHUNK;
-            mbar_expect_tx(&bars.full[c], (uint32_t)(Lq + Lk) * 128u);
-            tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[c]);
-            tma_load_2d(st + ST_SLAB, &tmK, atom_col(c), (int)(bh * Lk), &bars.full[c]);
-        }
+        for (int c = 0; c < nat && c < nq; ++c) load_atom(c);
         mbar_expect_tx(&bars.v_full, (uint32_t)nat * (uint32_t)Lk * 128u);
-        for (int a = 0; a < nat; ++a) tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, atom_col(a), (int)(bh * Lk), &bars.v_full);
+        for (int s = (nat > vslot0 ? nat : vslot0); s < nq; ++s) load_v_slot(s);
     }
     if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
     tc_fence_before();
@@ -236,18 +252,18 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
             }
             mbar_arrive(&bars.buf_ok);
-            // ---- the compact form: the atoms beyond the slots follow as the score MMAs hand slots back ----
-            for (int c = p.nq; c < nat; ++c) {
-                const int s = c % p.nq;
-                if (!mbar_wait(&bars.qk_free[s], ((c / p.nq) - 1) & 1, lim)) {
+            // ---- as the score MMAs hand slots back: the atoms beyond the slots, then V into the slots whose last
+            // atom has been multiplied ----
+            for (int c = 0; c < nat; ++c) {
+                const int s = c % nq;
+                if (c + nq >= nat && s < vslot0) continue;   // nothing follows in this slot
+                if (!mbar_wait(&bars.qk_free[s], (c / nq) & 1, lim)) {
                     report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 16));
                     *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
                     break;
                 }
-                unsigned char *st = qk + (size_t)s * ST_CHUNK;
-                mbar_expect_tx(&bars.full[s], (uint32_t)(Lq + Lk) * 128u);
-                tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[s]);
-                tma_load_2d(st + ST_SLAB, &tmK, atom_col(c), (int)(bh * Lk), &bars.full[s]);
+                if (c + nq < nat) load_atom(c + nq);
+                else load_v_slot(s);
             }
             // ---- the head's scores are complete when every read-out warp of every slice has arrived ----
             const unsigned want = 4u * (unsigned)p.nsplit + p.wait_extra;
@@ -268,11 +284,11 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             // ---- score MMAs ----
             const uint32_t id64 = umma_idesc_tf32(64, 64, 0, 0);
             for (int c = 0; c < nat; ++c) {
-                const int j = c % p.nlo, s = c % p.nq;
+                const int j = c % p.nlo, s = c % nq;
                 ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (c / p.nlo) & 1, lim));
                 if (c == nat - 1) ST_STAMP(18);
                 tc_fence_after();
-                const uint32_t sa = smem_u32(qk + (size_t)s * ST_CHUNK), sl = smem_u32(lo_ring + (size_t)j * ST_CHUNK);
+                const uint32_t sa = smem_u32(slots + (size_t)s * ST_CHUNK), sl = smem_u32(lo_ring + (size_t)j * ST_CHUNK);
                 const uint64_t dq_hi = umma_desc_k_sw128(sa), dk_hi = umma_desc_k_sw128(sa + ST_SLAB);
                 const uint64_t dq_lo = umma_desc_k_sw128(sl), dk_lo = umma_desc_k_sw128(sl + ST_SLAB);
 #pragma unroll
@@ -282,7 +298,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     umma_tf32(tmem, dq_lo + 2 * k, dk_hi + 2 * k, id64, 1u);
                 }
                 umma_commit(&bars.lo_free[j]);
-                if (c + p.nq < nat) umma_commit(&bars.qk_free[s]);
+                umma_commit(&bars.qk_free[s]);
             }
             if (!failed) umma_commit(&bars.s_full);
             ST_STAMP(19);
@@ -291,12 +307,12 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         const int t = threadIdx.x - 64;   // 0..191
         // ---- hi / lo split of the landed Q and K atoms ----
         for (int c = 0; c < nat; ++c) {
-            const int j = c % p.nlo, s = c % p.nq;
-            ST_FAIL_AT(3, !mbar_wait(&bars.full[s], (c / p.nq) & 1, lim));
+            const int j = c % p.nlo, s = c % nq;
+            ST_FAIL_AT(3, !mbar_wait(&bars.full[s], (c / nq) & 1, lim));
             ST_FAIL_AT(7, !mbar_wait(&bars.lo_free[j], ((c / p.nlo) & 1) ^ 1, lim));
             if (t == 0 && c == 0) ST_STAMP(2);
             if (t == 0 && c == nat - 1) ST_STAMP(3);
-            unsigned char *st = qk + (size_t)s * ST_CHUNK, *sl = lo_ring + (size_t)j * ST_CHUNK;
+            unsigned char *st = slots + (size_t)s * ST_CHUNK, *sl = lo_ring + (size_t)j * ST_CHUNK;
             for (int idx = t; idx < 1024; idx += ST_SPLIT_THREADS) {
                 const int part = idx >> 9, i = idx & 511;   // idx * 16 is the byte offset in both the atom pair and the ring stage
                 if ((i >> 3) < (part ? Lk : Lq)) {
@@ -316,7 +332,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             if (lane == 0) mbar_arrive(&bars.ready[j]);
         }
         failed = __any_sync(0xffffffffu, failed);   // the collective tensor-memory loads below need whole warps
-        // ---- the score MMAs are done: the Q, K atoms may be overwritten (V lo, P) ----
+        // ---- the score MMAs are done: the residual ring and the slots below V may be overwritten (P, V lo) ----
         if (!failed) {
             do {
                 ST_FAIL_AT(4, !mbar_wait(&bars.s_full, 0, lim));
@@ -324,7 +340,8 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             } while (false);
             failed = __any_sync(0xffffffffu, failed) || (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
         }
-        // ---- read-out of the partial scores (warps 4-7: one tensor-memory lane quadrant each) ----
+        // ---- read-out of the partial scores (warps 4-7: one tensor-memory lane quadrant each; M = 64: row r is
+        // in lane 32 (r / 16) + r % 16) ----
         if (warp >= 4 && !failed) {
             if (threadIdx.x == 128) ST_STAMP(4);
             tc_fence_after();
@@ -410,24 +427,24 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         }
     }
 
-    // ---- O[:, slice] = P V, in passes of kc keys ----
-    // With a resident slice of at most 128 columns, V hi and V lo (contiguous slabs) are one B operand of
-    // N = 2 * width: P hi [V hi | V lo] and then columns [0, width) += P lo V hi, two MMAs per 8 keys
-    // instead of three (an MMA of this size costs its issue latency, not its arithmetic).
-    const bool v_cat = (nat == p.apc) && (2 * nat * ST_ATOM <= 256) && kc == 64;
+    // ---- O[:, slice]^T = V^T P^T in passes of kc keys: per block of 128 output columns (four atoms) and 8 keys,
+    // D[column][row | 64 + row] += Vhi^T [Phi | Plo]^T and += Vlo^T [Phi | Plo]^T - V is the M-major A operand
+    // (M = 128: a column per tensor-memory lane), P hi and P lo are one K-major B operand of N = 128, and the sum
+    // of a row's hi and lo halves is formed by the thread that stores it ----
     const int ksteps = kpad >> 3, kpc = kc >> 3;   // 8-key MMA steps in all and per pass
     const int npass = (ksteps + kpc - 1) / kpc;
     for (int h = 0; h < npass; ++h) {
         if (h > 0 && !failed) {
             // the MMAs of the previous pass have read their V lo and P: both are replaced
             do { ST_FAIL_AT(9, !mbar_wait(&bars.o_full, (h - 1) & 1, lim)); } while (false);
+            if (threadIdx.x == 64) ST_STAMP(23);
             if (!failed && warp >= 2) st_split_v(v_hi, v_lo, nat, h * kc, kc, kpad, Lk, (int)threadIdx.x - 64);
+            if (threadIdx.x == 64) ST_STAMP(24);
         }
         if (!failed) {
-            // P of this pass as hi / lo operand tiles (K-major, 32 keys per 128-byte row)
             const int ks = cg >> 3;                                  // which 32 keys this lane's four belong to
             const bool mine = (pslabs == 2) ? true : (ks == h);
-            const uint32_t slab_off = (pslabs == 2) ? (uint32_t)ks * ST_SLAB : 0u;
+            const uint32_t slab_off = (pslabs == 2) ? (uint32_t)ks * ST_CHUNK : 0u;
 #pragma unroll
             for (int k = 0; k < RPW; ++k) {
                 const int i = 8 * warp + 2 * k + r2;
@@ -435,40 +452,35 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                     float4 hi, lo;
                     st_split4(sv[k], hi, lo);
                     const uint32_t off = slab_off + st_swz(i, 4 * (cg & 7));
-                    *reinterpret_cast<float4 *>(p_hi + off) = hi;
-                    *reinterpret_cast<float4 *>(p_lo + off) = lo;
+                    *reinterpret_cast<float4 *>(p_buf + off) = hi;
+                    *reinterpret_cast<float4 *>(p_buf + ST_SLAB + off) = lo;
                 }
             }
-            if (threadIdx.x == 0) ST_STAMP(20);
+            if (threadIdx.x == 0) ST_STAMP(h == 0 ? 20 : 25);
             fence_proxy_async_smem();
-            if (threadIdx.x == 0) ST_STAMP(21);
+            if (threadIdx.x == 0) ST_STAMP(h == 0 ? 21 : 26);
         }
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
         failed = (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
-        ST_DBG(3, if (h == 0 && threadIdx.x < 64) { p.dbg[512 + threadIdx.x] = reinterpret_cast<float *>(p_hi)[threadIdx.x]; p.dbg[576 + threadIdx.x] = reinterpret_cast<float *>(v_hi)[threadIdx.x];
+        ST_DBG(3, if (h == 0 && threadIdx.x < 64) { p.dbg[512 + threadIdx.x] = reinterpret_cast<float *>(p_buf)[threadIdx.x]; p.dbg[576 + threadIdx.x] = reinterpret_cast<float *>(v_hi)[threadIdx.x];
                                                     p.dbg[640 + threadIdx.x] = reinterpret_cast<float *>(v_lo)[threadIdx.x]; });
-        if (threadIdx.x == 0 && h == 0) ST_STAMP(11);
+        if (threadIdx.x == 0) ST_STAMP(h == 0 ? 11 : 27);
         if (warp == 1 && lane == 0 && !failed) {
-            const uint32_t idv = umma_idesc_tf32(64, nat * ST_ATOM, 0, 1), idv2 = umma_idesc_tf32(64, 2 * nat * ST_ATOM, 0, 1);
+            const uint32_t idv = umma_idesc_tf32(128, 128, 1, 0);
             for (int kk = h * kpc; kk < ksteps && kk < (h + 1) * kpc; ++kk) {
                 const int kl = kk - h * kpc;
-                const uint64_t dp_hi = umma_desc_k_sw128(smem_u32(p_hi + (size_t)(kl >> 2) * ST_SLAB)) + 2 * (kl & 3);
-                const uint64_t dp_lo = umma_desc_k_sw128(smem_u32(p_lo + (size_t)(kl >> 2) * ST_SLAB)) + 2 * (kl & 3);
-                const uint64_t dv_hi = umma_desc_mn_sw128_32b(smem_u32(v_hi + (size_t)kk * 1024), ST_SLAB, 512);
-                const uint64_t dv_lo = umma_desc_mn_sw128_32b(smem_u32(v_lo + (size_t)kl * 1024), vlo_pitch, 512);
-                if (v_cat) {
-                    umma_tf32(tmem, dp_hi, dv_hi, idv2, kk != 0);
-                    umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
-                } else {
-                    umma_tf32(tmem, dp_hi, dv_hi, idv, kk != 0);
-                    umma_tf32(tmem, dp_hi, dv_lo, idv, 1u);
-                    umma_tf32(tmem, dp_lo, dv_hi, idv, 1u);
+                const uint64_t dp = umma_desc_k_sw128(smem_u32(p_buf + (size_t)(kl >> 2) * ST_CHUNK)) + 2 * (kl & 3);
+                for (int b = 0; b < nblk; ++b) {
+                    const uint64_t dv_hi = umma_desc_mn_sw128_32b(smem_u32(v_hi + (size_t)b * 4 * ST_SLAB + (size_t)kk * 1024), ST_SLAB, 512);
+                    const uint64_t dv_lo = umma_desc_mn_sw128_32b(smem_u32(v_lo + (size_t)b * 4 * vlo_pitch + (size_t)kl * 1024), vlo_pitch, 512);
+                    umma_tf32(tmem + b * 128, dv_hi, dp, idv, kk != 0);
+                    umma_tf32(tmem + b * 128, dv_lo, dp, idv, 1u);
                 }
             }
             umma_commit(&bars.o_full);
-            ST_STAMP(22);
+            ST_STAMP(h == 0 ? 22 : 28);
         }
         // ---- while P V runs: this slice has read the head's scores; the last slice to say so clears them and
         // the head's counters for the buffer's next user, then bumps the buffer's generation ----
@@ -492,34 +504,26 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             ST_FAIL_AT(6, !mbar_wait(&bars.o_full, (npass - 1) & 1, lim));
             if (threadIdx.x == 0) ST_STAMP(12);
             tc_fence_after();
-            // warp w reads lane quadrant w % 4 (rows 16 (w % 4) .. + 15 in its lanes 0-15), every second slab, and
-            // writes its rows' 128 bytes of that slab straight to global memory
-            const int q = warp & 3, row = 16 * q + lane;
-            const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
-            float *orow = p.O + (bh * Lq + row) * (long long)p.D;
-            uint32_t r[32];
-            for (int a = warp >> 2; a < nat; a += 2) {
-                tmem_ld32(ta + a * ST_ATOM, r);
-                if (v_cat) {
-                    uint32_t r2[32];
-                    tmem_ld32(ta + (nat + a) * ST_ATOM, r2);
+            // The thread of tensor-memory lane 32 q + l of block b holds output column l of atom 4 b + q: its row n
+            // is column n (P hi part) plus column 64 + n (P lo part).  A warp stores 128 contiguous bytes per row.
+            // One block: two warps per lane quadrant take 32 rows each; two blocks: a warp per block and quadrant.
+            const int q = warp & 3, b = (nblk == 2) ? (warp >> 2) : 0, a = 4 * b + q;
+            const int n_lo = (nblk == 2) ? 0 : 32 * (warp >> 2), n_hi = (nblk == 2) ? 64 : n_lo + 32;
+            const int col = atom_col(a) + lane;
+            if (a < nat) {
+                const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * 128u;
+                float *ocol = p.O + bh * Lq * (long long)p.D + col;
+                for (int n0 = n_lo; n0 < n_hi && n0 < Lq; n0 += 16) {
+                    uint32_t rh[16], rl[16];
+                    tmem_ld16(ta + n0, rh);
+                    tmem_ld16(ta + 64 + n0, rl);
                     tmem_ld_wait();
+                    ST_DBG(4, if (warp == 0 && n0 == 0 && lane < 2) { for (int j = 0; j < 16; ++j) p.dbg[704 + lane * 32 + j] = __uint_as_float(rh[j]) + __uint_as_float(rl[j]); });
+                    if (col < p.D) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-                }
-                tmem_ld_wait();
-                ST_DBG(4, if (warp == 0 && a == 0 && lane < 2) { for (int j = 0; j < 32; ++j) p.dbg[704 + lane * 32 + j] = __uint_as_float(r[j]); });
-                const int col0 = atom_col(a);
-                if (col0 + ST_ATOM <= p.D && (p.D & 7) == 0) {
-                    // four neighbouring rows trade their 32-byte pieces, so that every store instruction writes whole
-                    // 128-byte lines (row-per-thread stores would touch 16 lines with 16 bytes each)
-                    store_rows_128B_transposed_if(reinterpret_cast<unsigned char *>(orow - (long long)(lane & 3) * p.D + col0), (size_t)p.D * 4, r, lane,
-                                                  lane < 16 ? Lq - (row & ~3) : 0);
-                } else if (lane < 16 && row < Lq) {   // the atom that crosses head_d (a multiple of 4: a 16-byte piece is inside or outside as a whole)
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        if (col0 + 4 * c < p.D)
-                            *reinterpret_cast<uint4 *>(orow + col0 + 4 * c) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+                        for (int j = 0; j < 16; ++j)
+                            if (n0 + j < Lq) ocol[(long long)(n0 + j) * p.D] = __uint_as_float(rh[j]) + __uint_as_float(rl[j]);
+                    }
                 }
             }
         } while (false);
