@@ -386,37 +386,42 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     auto hits_prev_out = [&](const void *ptr, size_t n) { return (uintptr_t)ptr < c.prev_out_hi && (uintptr_t)ptr + n > c.prev_out_lo; };
     const bool overlap = independent_of_prev && c.prev_sdtc && c.prev_stream == st && !c.scratch_dirty &&
                          !hits_prev_out(a.Q, in_q) && !hits_prev_out(a.K, in_k) && !hits_prev_out(a.V, in_k);
-    // Shared memory of a CTA: nq slots and nlo residual stages of 16 KB.  A call on its own takes a slot per atom
-    // and per pair of V slabs (everything is requested when the CTA starts) and does P V in one pass.  A call of a
-    // batch takes the form that lets the most CTAs share an SM - its neighbours in the stream run beside it -
-    // (at most three: the registers): fewer slots than atoms, one residual stage, P V in two passes; among
-    // equals the form with the most slots.
+    // Shared memory of a CTA in units of 16 KB: nr landing slots, nst operand stages of two units, and V either in
+    // two units per block of its own (requested when the CTA starts) or over the stages.  A call on its own takes
+    // what an SM has: two stages, V on its own, a landing slot per atom as far as they fit, P V in one pass.  A
+    // call of a batch takes the form that lets the most CTAs share an SM - its neighbours in the stream run beside
+    // it - (at most three: the registers); among equals the form listed first below.
     const int nb = sdtc_vblocks(apc), tmem_cols = 128 * nb;
     const size_t sm_bytes = (size_t)c.max_smem_optin + 1024;   // per SM; the system keeps 1 KB per CTA
-    int nq = 0, nlo = ST_NLO, kc = 64;
+    int nr = 0, nst = ST_NST, v_own = 1, kc = 64;
     if (batched || overlap) {
         int best = 0;
-        for (int q = apc + 2 * nb; q >= 2 * nb + 1; --q)
-            for (int l = ST_NLO; l >= 1; --l)
-                for (int k = 64; k >= 32; k -= 32) {
-                    if (!sdtc_layout_ok(apc, q, l, k)) continue;
-                    int n = (int)(sm_bytes / (sdtc_smem_bytes(q, l) + 1024));
-                    if (n > 512 / tmem_cols) n = 512 / tmem_cols;
-                    if (n > 3) n = 3;
-                    if (n > best) { best = n; nq = q; nlo = l; kc = k; }
-                }
+        for (int s2 = ST_NST; s2 >= 1; --s2)
+            for (int vo = 1; vo >= 0; --vo)
+                for (int r = apc < ST_MAX_SLOTS ? apc : ST_MAX_SLOTS; r >= 1; --r)
+                    for (int k = 64; k >= 32; k -= 32) {
+                        if (!sdtc_layout_ok(apc, r, s2, vo, k)) continue;
+                        const size_t bytes = sdtc_smem_bytes(apc, r, s2, vo);
+                        if (bytes > (size_t)c.max_smem_optin) continue;
+                        int n = (int)(sm_bytes / (bytes + 1024));
+                        if (n > 512 / tmem_cols) n = 512 / tmem_cols;
+                        if (n > 3) n = 3;
+                        if (n > best) { best = n; nr = r; nst = s2; v_own = vo; kc = k; }
+                    }
     } else {
-        for (int q = apc + 2 * nb; q <= ST_MAX_SLOTS && nq == 0; ++q)
-            if (sdtc_layout_ok(apc, q, nlo, kc)) nq = q;
+        const int room = (int)(((size_t)c.max_smem_optin - 1024) / ST_CHUNK) - 2 * ST_NST - 2 * nb;   // units left for landing slots
+        nr = apc < room ? apc : room;
+        if (nr > ST_MAX_SLOTS) nr = ST_MAX_SLOTS;
     }
 #ifdef B200ATTN_DEVTOOLS
-    if (const char *e = getenv("B200ATTN_SDTC_NQ")) nq = atoi(e);
-    if (const char *e = getenv("B200ATTN_SDTC_NLO")) nlo = atoi(e);
+    if (const char *e = getenv("B200ATTN_SDTC_NR")) nr = atoi(e);
+    if (const char *e = getenv("B200ATTN_SDTC_NST")) nst = atoi(e);
+    if (const char *e = getenv("B200ATTN_SDTC_VOWN")) v_own = atoi(e);
     if (const char *e = getenv("B200ATTN_SDTC_KC")) kc = atoi(e);
-    if (nlo < 1 || nlo > ST_NLO || (kc != 32 && kc != 64)) return -1;
+    if (kc != 32 && kc != 64) return -1;
 #endif
-    if (nq == 0 || !sdtc_layout_ok(apc, nq, nlo, kc)) return -1;
-    size_t smem = sdtc_smem_bytes(nq, nlo);
+    if (nr < 1 || !sdtc_layout_ok(apc, nr, nst, v_own, kc)) return -1;
+    size_t smem = sdtc_smem_bytes(apc, nr, nst, v_own);
     // The CTAs that fit an SM by shared memory must also fit it by tensor memory (512 columns): a CTA that had to
     // wait for columns held by CTAs that wait for its scores would never get them.  Ask for more shared memory
     // where that is not so by itself.
@@ -456,7 +461,7 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     p.BH = BH; p.Lq = Lq; p.Lk = Lk; p.D = D;
     p.apc = apc; p.natoms = natoms; p.nsplit = nsplit;
     const int buf = (int)(c.sdtc_seq % ST_NBUF);
-    p.buf = buf; p.gen_expect = c.sdtc_gen_expect[buf]; p.cap_bh = c.sdtc_cap; p.tmem_cols = tmem_cols; p.nlo = nlo; p.nq = nq; p.kc = kc;
+    p.buf = buf; p.gen_expect = c.sdtc_gen_expect[buf]; p.cap_bh = c.sdtc_cap; p.tmem_cols = tmem_cols; p.nr = nr; p.nst = nst; p.v_own = v_own; p.kc = kc;
     p.scale = 1.0f / sqrtf((float)D);
     p.O = (float *)a.out;
     p.S = c.sdtc_S; p.counters = c.sdtc_cnt; p.gen = c.sdtc_gen;

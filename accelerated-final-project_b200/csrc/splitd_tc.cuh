@@ -5,34 +5,37 @@
 //
 // An fp32 value x is split into hi = x with the low 13 mantissa bits cleared (exactly representable
 // as tf32) and the residual lo = x - hi (exact in fp32, at most 13 significant bits, of which the
-// tensor core keeps 11).  A product a*b is taken as hi_a*hi_b + hi_a*lo_b + lo_a*hi_b with fp32
-// accumulation; the dropped term lo_a*lo_b is below 2^-22 |a b|.  (Replaces the scalar loops of the
-// reference kernel, final/attention.cu:120-142 and :169-181; the reference's own arithmetic is fp32
-// FMA, and the result here agrees with it to a few 1e-7.)
+// tensor core keeps 11).  A product a*b is taken as hi_a*hi_b + hi_a*lo_b + lo_a*hi_b (+ lo_a*lo_b, which is
+// below 2^-22 |a b| and comes for free) with fp32 accumulation.  (Replaces the scalar loops of the reference
+// kernel, final/attention.cu:120-142 and :169-181; the reference's own arithmetic is fp32 FMA, and the result
+// here agrees with it to a few 1e-7.)
 //
 //   load      Q and K as 32-column "atoms" (128 bytes per row, 128-byte swizzle: the K-major operand
-//             layout of the MMA), V as [keys x 32 columns] slabs with the 128-byte swizzle on 32-byte
-//             units, the MN-major operand layout of 32-bit elements.  Either the whole slice is requested
-//             at once when the CTA starts (the bytes in flight per SM are what decides the HBM rate), or -
-//             the compact form, for calls that run beside their neighbours - V at once and the Q, K atoms
-//             through a ring of `nq` slots that the score MMAs hand back, so that a CTA of the widest slice
-//             takes less than half of an SM's shared memory and two calls share every SM.
-//   split     six warps rewrite each landed atom as hi (in place) and lo (into a two-deep ring);
-//   scores    one thread issues, per 8 columns, S[64 x 64] += Qhi Khi^T + Qhi Klo^T + Qlo Khi^T
-//             (M = 64: the accumulator row r sits in tensor-memory lane 32*(r/16) + r%16);
+//             layout of the MMA) into landing slots, V as [keys x 32 columns] slabs with the 128-byte swizzle
+//             on 32-byte units, the M-major operand layout of 32-bit elements.  A call on its own requests its
+//             whole slice when the CTA starts (the bytes in flight per SM are what decides the HBM rate).  A
+//             call of a batch, which runs beside its neighbours in the stream, takes a compact form: fewer
+//             landing slots than atoms (a slot is requested again as soon as it has been split), and V lands
+//             over the slots and stages when the score MMAs are done, under the wait for the other slices - a
+//             CTA of the widest slice then takes half of an SM's shared memory, narrower ones a third.
+//   split     six warps write each landed atom as Q hi | Q lo | K hi | K lo into an operand stage;
+//   scores    one thread issues, per 8 columns, two MMAs of M = 64, N = 128 into one accumulator:
+//             Q hi [K hi; K lo]^T and Q lo [K hi; K lo]^T (M = 64: the accumulator row r sits in tensor-memory
+//             lane 32*(r/16) + r%16); a row's score is the sum of its two column halves;
 //   reduce    the partial scores of the slices of a head are summed in an L2-resident scratch with
 //             16-byte vector reductions; a per-head arrival counter tells when the sum is complete.
-//             The grid holds at most one CTA per SM, so all slices of a head are resident together;
-//             the wait is bounded all the same and reports an error instead of hanging.
-//   softmax   every slice CTA reads the 64 x 64 scores back, one warp per row (shuffle max / sum), and
-//             writes P as hi and lo in the K-major operand layout;
-//   output    O[:, slice] = Phi Vhi + Phi Vlo + Plo Vhi (N = slice width), read from tensor memory and
-//             written to global memory by the row's thread (128 bytes per row and atom).  V lo and P live
-//             where the Q, K atoms were; where that room is short the contraction runs in two halves of
-//             32 keys, V lo and P of the second half replacing those of the first.
+//             All CTAs of a call are resident together (the host sizes the grid and the shared memory for
+//             that); the wait is bounded all the same and reports an error instead of hanging.
+//   softmax   every slice CTA reads the 64 x 64 scores back, half a warp per row (shuffle max / sum);
+//   output    O[:, slice]^T = V^T P^T per block of 128 output columns: V hi and V lo in turn as the M-major
+//             A operand (M = 128: an output column per tensor-memory lane), [P hi | P lo] as one K-major B
+//             operand of N = 128; the thread of a column adds a row's hi and lo halves and a warp stores 128
+//             contiguous bytes of an output row.  P and V lo live where the atoms were; where that room is
+//             short the contraction runs in two passes of 32 keys, V lo and P of the second pass replacing
+//             those of the first.
 //
 // Consecutive independent calls overlap on the GPU (programmatic dependent launch: a call's kernel starts
-// while the one before it is still running, and two to four CTAs share an SM when the slices are narrow).
+// while the one before it is still running, and two or three CTAs share an SM).
 // The score scratch is therefore a ring of ST_NBUF buffers: call n sums into buffer n % ST_NBUF; the last
 // slice CTA of a head to have read the head's scores clears them (off the critical path, during P V) and
 // bumps the buffer's generation counter; a later call that gets the same buffer first checks (at its
@@ -47,10 +50,11 @@ constexpr int ST_THREADS = 256;        // warp 0: TMA + arrival counter, warp 1:
 constexpr int ST_SPLIT_THREADS = 192;
 constexpr int ST_ATOM = 32;            // fp32 columns in a 128-byte swizzled row
 constexpr int ST_SLAB = 64 * 128;      // [64 rows x 128 B]
-constexpr int ST_CHUNK = 2 * ST_SLAB;  // a slot: one atom of Q and of K, or two slabs of V
+constexpr int ST_CHUNK = 2 * ST_SLAB;  // the unit of the shared-memory layout: one atom of Q and of K as it lands, or two slabs of V
+constexpr int ST_STAGE = 2 * ST_CHUNK; // an atom as the score MMAs take it: Q hi | Q lo | K hi | K lo
 constexpr int ST_MAX_ATOMS = 8;        // widest slice: 256 columns (two blocks of 128 output columns)
-constexpr int ST_MAX_SLOTS = 12;       // atoms of the widest slice + its V slabs
-constexpr int ST_NLO = 2;              // residual ring depth (one stage in the compact forms)
+constexpr int ST_MAX_SLOTS = 8;        // landing slots
+constexpr int ST_NST = 2;              // operand stages (one in the most compact form)
 constexpr int ST_NBUF = 8;             // score-scratch ring
 
 struct SdtcParams {
@@ -62,8 +66,10 @@ struct SdtcParams {
     int buf;                 // which buffer of the scratch ring this call sums into
     unsigned gen_expect;     // heads that earlier calls must have cleared in that buffer before it is used
     int tmem_cols;           // tensor-memory columns to allocate (128 or 256)
-    int nlo;                 // stages of the residual ring: 1 or 2
-    int nq;                  // shared-memory slots (16 KB): the last 2 * ceil(apc / 4) of them receive V
+    int nr;                  // landing slots (16 KB each)
+    int nst;                 // operand stages (32 KB each): 1 or 2
+    int v_own;               // 1: V has shared memory of its own behind the stages and is requested at once;
+                             // 0: V lands over the stages once the score MMAs are done
     int kc;                  // keys per pass of the P V contraction: 64 (one pass) or 32
     float scale;
     float *O;                // [B*H*Lq][D]
@@ -81,9 +87,9 @@ struct SdtcParams {
 };
 
 struct StBars {
-    uint64_t full[ST_MAX_SLOTS];            // slot c % nq: atom c of Q and K has landed
-    uint64_t qk_free[ST_MAX_SLOTS];         // slot c % nq: the MMAs of atom c have read it
-    uint64_t ready[ST_NLO], lo_free[ST_NLO];   // residual ring: split done / read by the MMAs
+    uint64_t full[ST_MAX_SLOTS];            // slot c % nr: atom c of Q and K has landed
+    uint64_t raw_free[ST_MAX_SLOTS];        // slot c % nr: the split warps have read atom c
+    uint64_t ready[ST_NST], st_free[ST_NST];   // stage c % nst: operands written / read by the MMAs
     uint64_t v_full, s_full, o_full;
     uint64_t buf_ok;                        // the scratch buffer has been cleared by its previous users
 };
@@ -97,18 +103,21 @@ struct StShared {
 };
 static_assert(sizeof(StShared) <= 512, "the barriers have to fit the alignment slack");
 
-// Shared memory of a CTA: residual ring | slots, + 1 KB (alignment of the tiles, barriers).
-//   while the scores are computed   ring stages hold Q lo | K lo of the atom being multiplied; slot c % nq holds atom
-//                                   c of Q and K (hi in place);
-//   afterwards                      V (hi in place) sits in the last 2 * ceil(apc / 4) slots - requested as soon as
-//                                   the last atom that used a slot has been multiplied, at once for slots no atom
-//                                   ever uses; everything below them holds P of a pass and V lo of a pass.
+// Shared memory of a CTA in units of 16 KB: landing slots | operand stages | V (v_own), + 1 KB (alignment of the
+// tiles, barriers).
+//   while the scores are computed   TMA lands atom c of Q and K in slot c % nr; the split warps write it as
+//                                   Q hi | Q lo | K hi | K lo into stage c % nst (the slot is free again at once);
+//   afterwards                      V (hi in place) in the last 2 * ceil(apc / 4) units - its own, requested when the
+//                                   CTA starts, or the last of the stages and slots, requested when the last score
+//                                   MMA is done;
+//                                   everything below holds P of a pass and V lo of a pass.
 inline int sdtc_vblocks(int apc) { return (apc + 3) / 4; }
-inline size_t sdtc_smem_bytes(int nq, int nlo) { return (size_t)(nq + nlo) * ST_CHUNK + 1024; }
-// P [hi | lo] of a pass is kc / 32 slots, V lo of a pass the same per block of four atoms
-inline bool sdtc_layout_ok(int apc, int nq, int nlo, int kc) {
+inline int sdtc_units(int apc, int nr, int nst, int v_own) { return nr + 2 * nst + (v_own ? 2 * sdtc_vblocks(apc) : 0); }
+inline size_t sdtc_smem_bytes(int apc, int nr, int nst, int v_own) { return (size_t)sdtc_units(apc, nr, nst, v_own) * ST_CHUNK + 1024; }
+// P [hi | lo] of a pass is kc / 32 units, V lo of a pass the same per block of four atoms
+inline bool sdtc_layout_ok(int apc, int nr, int nst, int v_own, int kc) {
     const int nb = sdtc_vblocks(apc);
-    return nq <= ST_MAX_SLOTS && nq >= 2 * nb + 1 && (1 + nb) * (kc / 32) <= nlo + nq - 2 * nb;
+    return nr >= 1 && nr <= ST_MAX_SLOTS && nst >= 1 && nst <= ST_NST && (1 + nb) * (kc / 32) <= sdtc_units(apc, nr, nst, v_own) - 2 * nb;
 }
 
 // x -> (x with the low 13 mantissa bits cleared, the exact remainder)
@@ -140,6 +149,20 @@ __device__ __forceinline__ void st_split_v(unsigned char *v_hi, unsigned char *v
     }
 }
 
+// 4 x 4 transpose across the four lanes of a quad: on entry x[r] belongs to (this lane's column, row r); on exit
+// x[c] belongs to (column c of the quad, row = this lane's place in the quad)
+__device__ __forceinline__ void st_quad_transpose(float &x0, float &x1, float &x2, float &x3, int lane) {
+    const bool b0 = lane & 1, b1 = lane & 2;
+    float r = __shfl_xor_sync(0xffffffffu, b0 ? x0 : x1, 1);
+    if (b0) x0 = r; else x1 = r;
+    r = __shfl_xor_sync(0xffffffffu, b0 ? x2 : x3, 1);
+    if (b0) x2 = r; else x3 = r;
+    r = __shfl_xor_sync(0xffffffffu, b1 ? x0 : x2, 2);
+    if (b1) x0 = r; else x2 = r;
+    r = __shfl_xor_sync(0xffffffffu, b1 ? x1 : x3, 2);
+    if (b1) x1 = r; else x3 = r;
+}
+
 #ifdef B200ATTN_DEVTOOLS
 #define ST_DBG(slot, expr) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0) { expr; } } while (0)
 #define ST_STAMP(k) do { if (p.stamps) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
@@ -165,7 +188,9 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     const uint32_t raw_addr = smem_u32(st_smem_raw);
     const uint32_t slack = (1024u - (raw_addr & 1023u)) & 1023u;   // 0, 256, 512 or 768
     unsigned char *smem = st_smem_raw + slack;
-    const size_t tile_bytes = (size_t)(p.nq + p.nlo) * ST_CHUNK;
+    const int nr = p.nr, nst = p.nst, nblk = (p.apc + 3) >> 2;
+    const int units = nr + 2 * nst + (p.v_own ? 2 * nblk : 0);
+    const size_t tile_bytes = (size_t)units * ST_CHUNK;
     // the 1 KB beyond the tiles is split into `slack` bytes before them and the rest behind them: the
     // barriers go where 512 bytes fit
     StShared &sh = *reinterpret_cast<StShared *>(slack >= 512 ? st_smem_raw : smem + tile_bytes);
@@ -182,12 +207,10 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     auto atom_col = [&](int c) { return (slice + c * p.nsplit) * ST_ATOM; };
     const int kpad = (Lk + 7) & ~7;              // keys covered by the P V contraction (8 per MMA)
     const uint32_t lim = p.spin_limit;
-    const int nq = p.nq, nblk = (p.apc + 3) >> 2;
-    const int vslot0 = nq - 2 * nblk;            // the slots from here on receive V, two slabs each
 
-    unsigned char *lo_ring = smem;                                   // p.nlo stages: Q lo | K lo
-    unsigned char *slots = smem + (size_t)p.nlo * ST_CHUNK;          // nq slots: Q [64 x 32] | K [64 x 32]
-    unsigned char *v_hi = slots + (size_t)vslot0 * ST_CHUNK;         // afterwards: slab a = V[:, atom a] [keys x 32 columns]
+    unsigned char *raw = smem;                                       // nr landing slots: Q [64 x 32] | K [64 x 32]
+    unsigned char *stages = smem + (size_t)nr * ST_CHUNK;            // nst stages: Q hi | Q lo | K hi | K lo
+    unsigned char *v_hi = smem + (size_t)(units - 2 * nblk) * ST_CHUNK;   // afterwards: slab a = V[:, atom a] [keys x 32 columns]
     // below V, once the score MMAs are done: P of a pass (per 32 keys: hi [64 x 32] | lo [64 x 32], one N = 128
     // operand) and V lo of a pass (kc keys of every atom)
     const int kc = p.kc, pslabs = kc >> 5;
@@ -200,33 +223,32 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 
     // requests of thread 0
     auto load_atom = [&](int c) {
-        const int s = c % nq;
-        unsigned char *st = slots + (size_t)s * ST_CHUNK;
-        mbar_expect_tx(&bars.full[s], (uint32_t)(Lq + Lk) * 128u);
-        tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[s]);
-        tma_load_2d(st + ST_SLAB, &tmK, atom_col(c), (int)(bh * Lk), &bars.full[s]);
+        const int r = c % nr;
+        unsigned char *st = raw + (size_t)r * ST_CHUNK;
+        mbar_expect_tx(&bars.full[r], (uint32_t)(Lq + Lk) * 128u);
+        tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[r]);
+        tma_load_2d(st + ST_SLAB, &tmK, atom_col(c), (int)(bh * Lk), &bars.full[r]);
     };
-    auto load_v_slot = [&](int s) {   // the two slabs of V that live in slot s >= vslot0
-        for (int a = 2 * (s - vslot0); a < 2 * (s - vslot0) + 2 && a < nat; ++a)
-            tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, atom_col(a), (int)(bh * Lk), &bars.v_full);
+    auto load_v = [&]() {
+        for (int a = 0; a < nat; ++a) tma_load_2d(v_hi + (size_t)a * ST_SLAB, &tmV, atom_col(a), (int)(bh * Lk), &bars.v_full);
     };
 
-    // one thread sets the barriers up and at once requests what has room: the first nq atoms of Q and K, then the
-    // slabs of V whose slots no atom uses (a second issuing thread, or V requested alongside, measured no
-    // faster): the loads are in flight while the other warps allocate tensor memory and meet at the barrier below
+    // one thread sets the barriers up and at once requests what has room: the first nr atoms of Q and K, then V
+    // if it has room of its own (a second issuing thread, or V requested alongside, measured no faster): the
+    // loads are in flight while the other warps allocate tensor memory and meet at the barrier below
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-        for (int i = 0; i < ST_MAX_SLOTS; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.qk_free[i], 1); }
-        for (int i = 0; i < ST_NLO; ++i) { mbar_init(&bars.ready[i], 6); mbar_init(&bars.lo_free[i], 1); }
+        for (int i = 0; i < ST_MAX_SLOTS; ++i) { mbar_init(&bars.full[i], 1); mbar_init(&bars.raw_free[i], 6); }
+        for (int i = 0; i < ST_NST; ++i) { mbar_init(&bars.ready[i], 6); mbar_init(&bars.st_free[i], 1); }
         mbar_init(&bars.v_full, 1);
         mbar_init(&bars.s_full, 1);
         mbar_init(&bars.o_full, 1);
         mbar_init(&bars.buf_ok, 1);
         s_fail = 0u;
         mbar_fence_init();
-        for (int c = 0; c < nat && c < nq; ++c) load_atom(c);
+        for (int c = 0; c < nat && c < nr; ++c) load_atom(c);
         mbar_expect_tx(&bars.v_full, (uint32_t)nat * (uint32_t)Lk * 128u);
-        for (int s = (nat > vslot0 ? nat : vslot0); s < nq; ++s) load_v_slot(s);
+        if (p.v_own) load_v();
     }
     if (warp == 1) tmem_alloc(&tmem_slot, (uint32_t)p.tmem_cols);
     tc_fence_before();
@@ -252,18 +274,20 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
             }
             mbar_arrive(&bars.buf_ok);
-            // ---- as the score MMAs hand slots back: the atoms beyond the slots, then V into the slots whose last
-            // atom has been multiplied ----
-            for (int c = 0; c < nat; ++c) {
-                const int s = c % nq;
-                if (c + nq >= nat && s < vslot0) continue;   // nothing follows in this slot
-                if (!mbar_wait(&bars.qk_free[s], (c / nq) & 1, lim)) {
-                    report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 16));
-                    *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
-                    break;
-                }
-                if (c + nq < nat) load_atom(c + nq);
-                else load_v_slot(s);
+            // ---- the atoms beyond the landing slots follow as the split warps hand slots back; V lands over the
+            // stages once the last score MMA has read them ----
+            bool ok = true;
+            for (int c = nr; c < nat && ok; ++c) {
+                ok = mbar_wait(&bars.raw_free[c % nr], ((c / nr) - 1) & 1, lim);
+                if (ok) load_atom(c);
+            }
+            if (ok && !p.v_own) {
+                ok = mbar_wait(&bars.s_full, 0, lim);
+                if (ok) load_v();
+            }
+            if (!ok) {
+                report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 16));
+                *reinterpret_cast<volatile unsigned *>(&s_fail) = 1u;
             }
             // ---- the head's scores are complete when every read-out warp of every slice has arrived ----
             const unsigned want = 4u * (unsigned)p.nsplit + p.wait_extra;
@@ -281,58 +305,57 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- score MMAs ----
-            const uint32_t id64 = umma_idesc_tf32(64, 64, 0, 0);
+            // ---- score MMAs: per 8 columns two M = 64, N = 128 MMAs into one accumulator, Q hi [K hi; K lo]^T and
+            // Q lo [K hi; K lo]^T: a row's products with K hi in columns 0-63, with K lo in columns 64-127 ----
+            const uint32_t id = umma_idesc_tf32(64, 128, 0, 0);
             for (int c = 0; c < nat; ++c) {
-                const int j = c % p.nlo, s = c % nq;
-                ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (c / p.nlo) & 1, lim));
+                const int j = c % nst;
+                ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (c / nst) & 1, lim));
                 if (c == nat - 1) ST_STAMP(18);
                 tc_fence_after();
-                const uint32_t sa = smem_u32(slots + (size_t)s * ST_CHUNK), sl = smem_u32(lo_ring + (size_t)j * ST_CHUNK);
-                const uint64_t dq_hi = umma_desc_k_sw128(sa), dk_hi = umma_desc_k_sw128(sa + ST_SLAB);
-                const uint64_t dq_lo = umma_desc_k_sw128(sl), dk_lo = umma_desc_k_sw128(sl + ST_SLAB);
+                const uint32_t sa = smem_u32(stages + (size_t)j * ST_STAGE);
+                const uint64_t dq = umma_desc_k_sw128(sa), dk = umma_desc_k_sw128(sa + ST_CHUNK);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    umma_tf32(tmem, dq_hi + 2 * k, dk_hi + 2 * k, id64, (c | k) != 0);
-                    umma_tf32(tmem, dq_hi + 2 * k, dk_lo + 2 * k, id64, 1u);
-                    umma_tf32(tmem, dq_lo + 2 * k, dk_hi + 2 * k, id64, 1u);
+                    umma_tf32(tmem, dq + 2 * k, dk + 2 * k, id, (c | k) != 0);
+                    umma_tf32(tmem, dq + (ST_SLAB >> 4) + 2 * k, dk + 2 * k, id, 1u);
                 }
-                umma_commit(&bars.lo_free[j]);
-                umma_commit(&bars.qk_free[s]);
+                umma_commit(&bars.st_free[j]);
             }
             if (!failed) umma_commit(&bars.s_full);
             ST_STAMP(19);
         }
     } else {
         const int t = threadIdx.x - 64;   // 0..191
-        // ---- hi / lo split of the landed Q and K atoms ----
+        // ---- hi / lo split of the landed Q and K atoms into an operand stage ----
         for (int c = 0; c < nat; ++c) {
-            const int j = c % p.nlo, s = c % nq;
-            ST_FAIL_AT(3, !mbar_wait(&bars.full[s], (c / nq) & 1, lim));
-            ST_FAIL_AT(7, !mbar_wait(&bars.lo_free[j], ((c / p.nlo) & 1) ^ 1, lim));
+            const int r = c % nr, j = c % nst;
+            ST_FAIL_AT(3, !mbar_wait(&bars.full[r], (c / nr) & 1, lim));
+            ST_FAIL_AT(7, !mbar_wait(&bars.st_free[j], ((c / nst) & 1) ^ 1, lim));
             if (t == 0 && c == 0) ST_STAMP(2);
             if (t == 0 && c == nat - 1) ST_STAMP(3);
-            unsigned char *st = slots + (size_t)s * ST_CHUNK, *sl = lo_ring + (size_t)j * ST_CHUNK;
+            const unsigned char *src = raw + (size_t)r * ST_CHUNK;
+            unsigned char *dst = stages + (size_t)j * ST_STAGE;
             for (int idx = t; idx < 1024; idx += ST_SPLIT_THREADS) {
-                const int part = idx >> 9, i = idx & 511;   // idx * 16 is the byte offset in both the atom pair and the ring stage
+                const int part = idx >> 9, i = idx & 511;   // Q / K; 16-byte piece of the [64 x 128 B] slab
                 if ((i >> 3) < (part ? Lk : Lq)) {
-                    float4 *ph = reinterpret_cast<float4 *>(st + (size_t)idx * 16);
                     float4 hi, lo;
-                    st_split4(*ph, hi, lo);
-                    *ph = hi;
-                    *reinterpret_cast<float4 *>(sl + (size_t)idx * 16) = lo;
+                    st_split4(*reinterpret_cast<const float4 *>(src + (size_t)idx * 16), hi, lo);
+                    unsigned char *d = dst + (size_t)part * ST_CHUNK + (size_t)i * 16;
+                    *reinterpret_cast<float4 *>(d) = hi;
+                    *reinterpret_cast<float4 *>(d + ST_SLAB) = lo;
                 }
             }
             if (t == 0 && c == nat - 1) ST_STAMP(16);
-            ST_DBG(0, if (c == 0 && t < 64) { p.dbg[t] = reinterpret_cast<float *>(st)[t]; p.dbg[64 + t] = reinterpret_cast<float *>(sl)[t];
-                                              p.dbg[128 + t] = reinterpret_cast<float *>(st + ST_SLAB)[t]; p.dbg[192 + t] = reinterpret_cast<float *>(sl + ST_SLAB)[t]; });
+            ST_DBG(0, if (c == 0 && t < 64) { p.dbg[t] = reinterpret_cast<float *>(dst)[t]; p.dbg[64 + t] = reinterpret_cast<float *>(dst + ST_SLAB)[t];
+                                              p.dbg[128 + t] = reinterpret_cast<float *>(dst + ST_CHUNK)[t]; p.dbg[192 + t] = reinterpret_cast<float *>(dst + ST_CHUNK + ST_SLAB)[t]; });
             fence_proxy_async_smem();
             if (t == 0 && c == nat - 1) ST_STAMP(17);
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.ready[j]);
+            if (lane == 0) { mbar_arrive(&bars.ready[j]); mbar_arrive(&bars.raw_free[r]); }
         }
         failed = __any_sync(0xffffffffu, failed);   // the collective tensor-memory loads below need whole warps
-        // ---- the score MMAs are done: the residual ring and the slots below V may be overwritten (P, V lo) ----
+        // ---- the score MMAs are done: the landing slots and the stages may be overwritten ----
         if (!failed) {
             do {
                 ST_FAIL_AT(4, !mbar_wait(&bars.s_full, 0, lim));
@@ -341,7 +364,8 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             failed = __any_sync(0xffffffffu, failed) || (*reinterpret_cast<volatile unsigned *>(&s_fail) != 0u);
         }
         // ---- read-out of the partial scores (warps 4-7: one tensor-memory lane quadrant each; M = 64: row r is
-        // in lane 32 (r / 16) + r % 16) ----
+        // in lane 32 (r / 16) + r % 16): a thread adds its row's two column halves and then adds the sums to the
+        // head's scores in the scratch ----
         if (warp >= 4 && !failed) {
             if (threadIdx.x == 128) ST_STAMP(4);
             tc_fence_after();
@@ -349,17 +373,18 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16);
             const int row = 16 * q + lane;
             float *srow = S_cur + (size_t)row * 64;
-            uint32_t r0[32];
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                tmem_ld32(ta + hh * 32, r0);
+            for (int k = 0; k < 4; ++k) {
+                uint32_t r0[16], r1[16];
+                tmem_ld16(ta + 16 * k, r0);
+                tmem_ld16(ta + 64 + 16 * k, r1);
                 tmem_ld_wait();
-                ST_DBG(1, if (warp == 4 && hh == 0 && lane < 2) { for (int jj = 0; jj < 32; ++jj) p.dbg[256 + lane * 64 + jj] = __uint_as_float(r0[jj]); });
+                ST_DBG(1, if (warp == 4 && k == 0 && lane < 2) { for (int jj = 0; jj < 16; ++jj) p.dbg[256 + lane * 64 + jj] = __uint_as_float(r0[jj]); });
                 if (lane < 16 && row < Lq) {
 #pragma unroll
-                    for (int jj = 0; jj < 32; jj += 4)
-                        red_add_v4(srow + hh * 32 + jj, __uint_as_float(r0[jj]), __uint_as_float(r0[jj + 1]), __uint_as_float(r0[jj + 2]),
-                                   __uint_as_float(r0[jj + 3]));
+                    for (int jj = 0; jj < 16; jj += 4)
+                        red_add_v4(srow + 16 * k + jj, __uint_as_float(r0[jj]) + __uint_as_float(r1[jj]), __uint_as_float(r0[jj + 1]) + __uint_as_float(r1[jj + 1]),
+                                   __uint_as_float(r0[jj + 2]) + __uint_as_float(r1[jj + 2]), __uint_as_float(r0[jj + 3]) + __uint_as_float(r1[jj + 3]));
                 }
             }
             if (threadIdx.x == 128) ST_STAMP(5);
@@ -505,25 +530,35 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             if (threadIdx.x == 0) ST_STAMP(12);
             tc_fence_after();
             // The thread of tensor-memory lane 32 q + l of block b holds output column l of atom 4 b + q: its row n
-            // is column n (P hi part) plus column 64 + n (P lo part).  A warp stores 128 contiguous bytes per row.
-            // One block: two warps per lane quadrant take 32 rows each; two blocks: a warp per block and quadrant.
+            // is column n (P hi part) plus column 64 + n (P lo part).  The four lanes of a quad transpose 4 rows x 4
+            // columns among themselves, so that a lane stores 16 bytes and a store instruction writes four whole
+            // 128-byte lines.  One block: two warps per lane quadrant take 32 rows each; two blocks: a warp per
+            // block and quadrant.
             const int q = warp & 3, b = (nblk == 2) ? (warp >> 2) : 0, a = 4 * b + q;
             const int n_lo = (nblk == 2) ? 0 : 32 * (warp >> 2), n_hi = (nblk == 2) ? 64 : n_lo + 32;
-            const int col = atom_col(a) + lane;
             if (a < nat) {
                 const uint32_t ta = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)b * 128u;
-                float *ocol = p.O + bh * Lq * (long long)p.D + col;
+                const int col0 = atom_col(a) + (lane & ~3);   // head_d is a multiple of 4: the four columns are inside or outside together
+                float *obase = p.O + bh * Lq * (long long)p.D + col0;
                 for (int n0 = n_lo; n0 < n_hi && n0 < Lq; n0 += 16) {
                     uint32_t rh[16], rl[16];
                     tmem_ld16(ta + n0, rh);
                     tmem_ld16(ta + 64 + n0, rl);
                     tmem_ld_wait();
-                    ST_DBG(4, if (warp == 0 && n0 == 0 && lane < 2) { for (int j = 0; j < 16; ++j) p.dbg[704 + lane * 32 + j] = __uint_as_float(rh[j]) + __uint_as_float(rl[j]); });
-                    if (col < p.D) {
+                    if (threadIdx.x == 0 && n0 == 0) ST_STAMP(29);
+                    float v[16];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (n0 + j < Lq) ocol[(long long)(n0 + j) * p.D] = __uint_as_float(rh[j]) + __uint_as_float(rl[j]);
+                    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(rh[j]) + __uint_as_float(rl[j]);
+                    ST_DBG(4, if (warp == 0 && n0 == 0 && lane < 2) { for (int j = 0; j < 16; ++j) p.dbg[704 + lane * 32 + j] = v[j]; });
+#pragma unroll
+                    for (int t4 = 0; t4 < 4; ++t4) {
+                        st_quad_transpose(v[4 * t4], v[4 * t4 + 1], v[4 * t4 + 2], v[4 * t4 + 3], lane);
+                        const int row = n0 + 4 * t4 + (lane & 3);
+                        if (row < Lq && col0 < p.D)
+                            *reinterpret_cast<float4 *>(obase + (long long)row * p.D) = make_float4(v[4 * t4], v[4 * t4 + 1], v[4 * t4 + 2], v[4 * t4 + 3]);
                     }
+                    if (threadIdx.x == 0 && n0 == 0) ST_STAMP(30);
+                    if (threadIdx.x == 0 && n0 == 16) ST_STAMP(31);
                 }
             }
         } while (false);
