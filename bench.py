@@ -55,12 +55,12 @@ NCU_TRAFFIC_BYTES = {
     ("cfg4", "tc_wide"): 5.68e9,        # a 16-head capture (709.9 MB) x 8
     ("cfg3", "tc_bf16"): 514.8e6,       # 402.8 MB read + 112.0 MB written
     ("cfg5", "tc_bf16"): 8 * 2.0**30 + 2 * 2.0**30,   # scaled from the cfg 3 capture by input/output bytes plus the encoded-K scratch
-    ("cfg1", "splitd_tc"): 6.41e6 + 2.10e6,           # 6.41 MB read inside the kernel; the 2 MiB output leaves the L2 after it
-    ("cfg2c", "splitd_tc"): 25.28e6 + 8.39e6,         # 25.28 MB read; 8 MiB output
+    ("cfg1", "splitd_tc"): 6.42e6 + 2.10e6,           # 6.42 MB read inside the kernel; the 2 MiB output leaves the L2 after it
+    ("cfg2c", "splitd_tc"): 25.29e6 + 8.39e6,         # 25.29 MB read; 8 MiB output
     ("decode", "tc_decode"): 537.0e6 + 3.75e6,
 }
 # nominal fp32 FMA rate of the CUDA cores: 148 SMs x 128 lanes x 2 flops x 1.965 GHz (the fp32 path now
-# does its products on the tensor cores as three tf32 MMAs per product; the figure is reported as the
+# does its products on the tensor cores as tf32 MMAs on split operands; the figure is reported as the
 # "compute roof" the task statement asks for next to the HBM roof)
 FFMA_ROOF_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
