@@ -588,7 +588,7 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
     // few queries against many keys (decode, cross-attention): key splits on the tensor cores
-    if (!done && tc_ok && !wide_ok && dec_supported(*a, rd)) {
+    if (!done && tc_ok && dec_supported(*a, rd)) {
         rc = dec_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_decode"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());

@@ -75,6 +75,13 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *t
         "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *tmap, int x, int y, int z, int w, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -356,6 +363,19 @@ inline bool make_tmap_grouped(CUtensorMap *m, const void *base, long long rows, 
     cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_groups};
     cuuint32_t estr[3] = {1, 1, 1};
     return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The same for `heads` matrices of [rows][cols] one after the other, with the head as a fourth coordinate: rows
+// of a box beyond a head's last row read as zero instead of as the next head's rows.
+inline bool make_tmap_grouped_heads(CUtensorMap *m, const void *base, long long heads, long long rows, long long cols, int box_rows, int box_groups) {
+    PFN_tmapEncodeTiled enc = tmap_encode_fn();
+    if (!enc || cols % 64 != 0) return false;
+    cuuint64_t dims[4] = {64, (cuuint64_t)rows, (cuuint64_t)(cols / 64), (cuuint64_t)heads};
+    cuuint64_t strides[3] = {(cuuint64_t)cols * 2, 128, (cuuint64_t)rows * (cuuint64_t)cols * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_groups, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

@@ -27,8 +27,12 @@
 // every key tile once; a second launch computes all the other tiles from the encoded copies without
 // any transform.
 //
-// Shapes taken here: bf16, head_d % 64 == 0 (with an encoding: % 128; rotate-half: rotary_dim ==
-// head_d), len_q % 128 == 0, len_k % 128 == 0, len_k <= 8192.  Every wait is bounded.
+// Shapes taken here: bf16 (fp16 without an encoding), head_d % 64 == 0 (with an encoding: % 128; rotate-half:
+// rotary_dim == head_d), any len_q, len_k <= 8192 (not both <= 64).  Lengths that are not multiples of the
+// tiles: the operand tiles reach into the next head's rows (or read zeros behind the last head), whose
+// scores land in rows and columns of S that nobody uses - S keeps whole 128-blocks per head -; the
+// columns of keys that do not exist are written as -inf, V rows that do not exist read as zero (the head is a
+// coordinate of the V map), and output rows that do not exist are not stored.  Every wait is bounded.
 #pragma once
 
 #include "tc_bf16.cuh"
@@ -45,7 +49,8 @@ constexpr int TW_STAGE = TW_QCHUNK + TW_KCHUNK;
 
 struct TcwScoreParams {
     int Lq, Lk, D, nch;        // nch = D / 64
-    int nqt, nkt;              // Lq / 128, ceil(Lk / 256)
+    int Lqp, Lkp;              // Lq and Lk rounded up to multiples of 128: rows per head and row pitch of S
+    int nqt, nkt;              // ceil(Lq / 128), ceil(Lk / 256)
     int mode;                  // 0: every tile, operands as given; 1: the encoding tile set; 2: all other tiles
     int pe;                    // mode 1: PE_ROPE_HALF, PE_ROPE_INTERLEAVED or PE_SINUSOIDAL
     int rotate_k;              // mode 1: 0 = only Q carries the encoding
@@ -53,9 +58,9 @@ struct TcwScoreParams {
     int tph;                   // tiles per head in this launch
     long long n_tiles;         // heads * tph
     float scale_log2;          // log2(e) / sqrt(D)
-    __nv_bfloat16 *S;          // [heads * Lq][Lk]  scores, log2 units, relative to the tile's row maximum
-    float *rowmax;             // [heads * Lq][nkt] row maxima of the tiles, log2 units
-    const __nv_bfloat16 *tab;  // mode 1: [>= max(Lq, 256 * nkt)][D]; rotate-half: cos in columns [0, D/2), sin in [D/2, D);
+    __nv_bfloat16 *S;          // [heads * Lqp][Lkp]  scores, log2 units, relative to the tile's row maximum; -inf beyond Lk
+    float *rowmax;             // [heads * Lqp][nkt] row maxima of the tiles, log2 units
+    const __nv_bfloat16 *tab;  // mode 1: [>= max(Lqp, 256 * nkt)][D]; rotate-half: cos in columns [0, D/2), sin in [D/2, D);
                                // otherwise the layout of tc_build_pe_table (element-wise partner of the data)
     __nv_bfloat16 *q_store, *k_store;   // mode 1: rotated copies, [heads * Lq][D] and [heads * Lk][D]
     unsigned *err, *err_sys;
@@ -130,6 +135,67 @@ __device__ __forceinline__ uint4 tcw_ldg_here(const void *ptr) {
     uint4 v;
     asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
     return v;
+}
+
+// Epilogue of one accumulator row [<= 256 keys] of a score tile, by the row's thread: the maximum over the
+// tile's real keys, then the scores in log2 units relative to it as bf16, 64 keys (128 bytes) at a time with
+// neighbouring rows trading pieces so that the stores cover full lines.  Keys beyond the sequence (the tile's
+// columns >= valid) are written as -inf up to the end of the last 128-key block that holds a real key: they
+// weigh nothing in the P V kernel, which reads whole blocks.  `srow0` = the row's place in S minus
+// (lane & 3) rows.  Returns the maximum (log2 units).
+__device__ __forceinline__ float tcw_store_score_row(uint32_t ta, int valid, float scale_log2, unsigned char *srow0, size_t pitch_bytes, int lane) {
+    uint32_t r[32], wds[32];
+    const int nfull = valid >> 5, tail = valid & 31;
+    float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+    for (int c = 0; c < nfull; ++c) {
+        tmem_ld32(ta + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(r[j]));
+            mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
+        }
+    }
+    if (tail) {
+        tmem_ld32(ta + nfull * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            mx0 = fmaxf(mx0, j < tail ? __uint_as_float(r[j]) : -INFINITY);
+            mx1 = fmaxf(mx1, j + 1 < tail ? __uint_as_float(r[j + 1]) : -INFINITY);
+            mx2 = fmaxf(mx2, j + 2 < tail ? __uint_as_float(r[j + 2]) : -INFINITY);
+            mx3 = fmaxf(mx3, j + 3 < tail ? __uint_as_float(r[j + 3]) : -INFINITY);
+        }
+    }
+    const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+    const int npc = 2 * ((valid + 127) >> 7);   // 64-key pieces up to the end of the last block with a real key
+    for (int cp = 0; cp < npc; ++cp) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const int k0 = (2 * cp + hh) * 32;   // first key of this 32-column group (the same for the whole warp)
+            if (k0 >= valid) {
+#pragma unroll
+                for (int q = 0; q < 16; ++q) wds[16 * hh + q] = 0xFF80FF80u;   // (-inf, -inf)
+            } else {
+                tmem_ld32(ta + k0, r);
+                tmem_ld_wait();
+                if (k0 + 32 <= valid) {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        wds[16 * hh + q] = pack_bf16x2(fmaf(__uint_as_float(r[2 * q]), scale_log2, -mt), fmaf(__uint_as_float(r[2 * q + 1]), scale_log2, -mt));
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 16; ++q)
+                        wds[16 * hh + q] = pack_bf16x2(k0 + 2 * q < valid ? fmaf(__uint_as_float(r[2 * q]), scale_log2, -mt) : -INFINITY,
+                                                       k0 + 2 * q + 1 < valid ? fmaf(__uint_as_float(r[2 * q + 1]), scale_log2, -mt) : -INFINITY);
+                }
+            }
+        }
+        store_rows_128B_transposed(srow0 + cp * 128, pitch_bytes, wds, lane);
+    }
+    return mt;
 }
 
 __global__ void __launch_bounds__(TW_THREADS, 1)
@@ -217,7 +283,6 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // ---- epilogue: one thread per query row of the tile ----
         const int row = 32 * (warp & 3) + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
-        uint32_t r[32];
         long long tc = 0;
         for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x, ++tc) {
             const long long bh = tile / p.tph;
@@ -226,37 +291,12 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             const int ab = (int)(tc & 1);
             TW_FAIL_AT(3, !mbar_wait(&bars.acc_full[ab], (tc >> 1) & 1, lim));
             tc_fence_after();
-            const int ncc = min(TW_BN, p.Lk - kt * TW_BN) / 32;   // 32-column groups that hold real keys
             const uint32_t ta = lane_addr + ab * TW_BN;
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-            for (int c = 0; c < ncc; ++c) {
-                tmem_ld32(ta + c * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(r[j]));
-                    mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
-                    mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
-                }
-            }
-            const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
-            const long long grow = bh * p.Lq + (long long)qt * TW_BM + row;
+            const long long grow = bh * p.Lqp + (long long)qt * TW_BM + row;
+            __nv_bfloat16 *srow = p.S + grow * p.Lkp + (long long)kt * TW_BN;
+            const float mt = tcw_store_score_row(ta, min(TW_BN, p.Lk - kt * TW_BN), p.scale_log2,
+                                                 reinterpret_cast<unsigned char *>(srow - (long long)(lane & 3) * p.Lkp), (size_t)p.Lkp * 2, lane);
             p.rowmax[grow * p.nkt + kt] = mt;
-            __nv_bfloat16 *srow = p.S + grow * p.Lk + (long long)kt * TW_BN;
-            unsigned char *srow0 = reinterpret_cast<unsigned char *>(srow - (long long)(lane & 3) * p.Lk);
-            uint32_t wds[32];
-            for (int cp = 0; cp < ncc / 2; ++cp) {   // 64 keys = 128 bytes of the row at a time, stored as full lines
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    tmem_ld32(ta + cp * 64 + hh * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int q = 0; q < 16; ++q)
-                        wds[16 * hh + q] = pack_bf16x2(fmaf(__uint_as_float(r[2 * q]), p.scale_log2, -mt), fmaf(__uint_as_float(r[2 * q + 1]), p.scale_log2, -mt));
-                }
-                store_rows_128B_transposed(srow0 + cp * 128, (size_t)p.Lk * 2, wds, lane);
-            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.acc_empty[ab]);
@@ -361,7 +401,7 @@ tcw_scores_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     encode_piece(lo, hi, ta[i], tb[i]);
                     *reinterpret_cast<uint4 *>(lo_st + off) = lo;
                     *reinterpret_cast<uint4 *>(hi_st + off) = hi;
-                    if (cur.store_q) {
+                    if (cur.store_q && cur.qt * TW_BM + 32 * i + r0 < p.Lq) {
                         __nv_bfloat16 *g = p.q_store + (qrow0 + 32 * i + r0) * (long long)p.D + gcol;
                         *reinterpret_cast<uint4 *>(g) = lo;
                         *reinterpret_cast<uint4 *>(g + half) = hi;
@@ -541,7 +581,6 @@ tcw_scores256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int acc = warp >= 6 ? 1 : 0;
         const int row = 128 * acc + 32 * (warp & 3) + lane;
         const uint32_t ta = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + acc * TW_BN;
-        uint32_t r[32], wds[32];
         long long tc = 0;
         for (long long tile = blockIdx.x; tile < p.n_tiles && !failed; tile += gridDim.x, ++tc) {
             const long long bh = tile / p.tph;
@@ -549,35 +588,11 @@ tcw_scores256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             tcw_tile256_of(p.mode, (int)(tile - bh * p.tph), p.nkt, &qp, &kt);
             TW_FAIL_AT(20, !mbar_wait(&bars.acc_full[acc], tc & 1, lim));
             tc_fence_after();
-            const int ncc = min(TW_BN, p.Lk - kt * TW_BN) / 32;   // 32-column groups that hold real keys
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-            for (int c = 0; c < ncc; ++c) {
-                tmem_ld32(ta + c * 32, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(r[j]));
-                    mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
-                    mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
-                }
-            }
-            const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
-            const long long grow = bh * p.Lq + (long long)qp * 256 + row;
+            const long long grow = bh * p.Lqp + (long long)qp * 256 + row;
+            __nv_bfloat16 *srow = p.S + grow * p.Lkp + (long long)kt * TW_BN;
+            const float mt = tcw_store_score_row(ta, min(TW_BN, p.Lk - kt * TW_BN), p.scale_log2,
+                                                 reinterpret_cast<unsigned char *>(srow - (long long)(lane & 3) * p.Lkp), (size_t)p.Lkp * 2, lane);
             p.rowmax[grow * p.nkt + kt] = mt;
-            __nv_bfloat16 *srow = p.S + grow * p.Lk + (long long)kt * TW_BN;
-            unsigned char *srow0 = reinterpret_cast<unsigned char *>(srow - (long long)(lane & 3) * p.Lk);
-            for (int cp = 0; cp < ncc / 2; ++cp) {   // 64 keys = 128 bytes of the row at a time, stored as full lines
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    tmem_ld32(ta + cp * 64 + hh * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int q = 0; q < 16; ++q)
-                        wds[16 * hh + q] = pack_bf16x2(fmaf(__uint_as_float(r[2 * q]), p.scale_log2, -mt), fmaf(__uint_as_float(r[2 * q + 1]), p.scale_log2, -mt));
-                }
-                store_rows_128B_transposed(srow0 + cp * 128, (size_t)p.Lk * 2, wds, lane);
-            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.acc_empty[acc]);
@@ -602,7 +617,7 @@ constexpr int TP_NP = 4;   // score / P buffers (32 KB each)
 struct TcwPvParams {
     int Lq, Lk, D;
     int DW, ndp;               // output columns per unit (<= 512, a multiple of 64) and units per query tile
-    int nqt, nkt, nblk;        // Lq / 128, ceil(Lk / 256), Lk / 128
+    int nqt, nkt, nblk;        // ceil(Lq / 128), ceil(Lk / 256), ceil(Lk / 128): S has nqt * 128 rows per head, nblk * 128 columns
     long long n_units;         // heads * nqt * ndp
     const float *rowmax;       // as written by tcw_scores_kernel (the scores themselves come through the tensor map)
     int f16;                   // V, P and the output are fp16, else bf16 (the stored scores are bf16 either way)
@@ -679,8 +694,9 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                             // (ng < 4) are fetched too and never read
                             (void)ng;
                             mbar_expect_tx(&bars.v_full[s], (uint32_t)v_stage_bytes);
-                            tma_load_3d(v_smem + (size_t)s * v_stage_bytes, &tmV, 0, (int)(bh * p.Lk + t * TC_BN + vs * TP_VS),
-                                        (dp * DW + vw * TP_VW) / 64, &bars.v_full[s]);
+                            // (the head is a coordinate of its own: key rows beyond the sequence read as zero)
+                            tma_load_4d(v_smem + (size_t)s * v_stage_bytes, &tmV, 0, t * TC_BN + vs * TP_VS, (dp * DW + vw * TP_VW) / 64, (int)bh,
+                                        &bars.v_full[s]);
                         }
             }
             TWP_FLUSH(0, true);
@@ -761,9 +777,8 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                 oo[k] = m - warp_max(m);
             }
         };
-        auto grow0_of = [&](long long unit) {
-            const long long rest = unit / p.ndp;
-            return (rest / p.nqt) * p.Lq + (rest % p.nqt) * (long long)TW_BM + 8 * w;
+        auto grow0_of = [&](long long unit) {   // row of S and of the maxima: heads are nqt * 128 rows apart there
+            return (unit / p.ndp) * (long long)TW_BM + 8 * w;
         };
         float offs[8], offsn[8];
         for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x, ++ui) {
@@ -771,7 +786,7 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
             const long long rest = unit / p.ndp;
             const int qt = (int)(rest % p.nqt);
             const long long bh = rest / p.nqt;
-            const long long grow0 = bh * p.Lq + (long long)qt * TW_BM + 8 * w;
+            const long long grow0 = rest * (long long)TW_BM + 8 * w;
             // (the statistics of the unit were loaded while the previous unit was finishing)
             if (ui == 0) load_stats(grow0, offs);
             float lA = 0.0f, lB = 0.0f, offA = 0.0f, offB = 0.0f;
@@ -850,7 +865,7 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
                         for (int q = 0; q < 16; ++q)
                             wds[16 * hh + q] = pack_16x2(__uint_as_float(r[2 * q]) * inv, __uint_as_float(r[2 * q + 1]) * inv, p.f16 != 0);
                     }
-                    store_rows_128B_transposed(row0 + cp * 128, (size_t)p.D * 2, wds, lane);
+                    store_rows_128B_transposed_if(row0 + cp * 128, (size_t)p.D * 2, wds, lane, p.Lq - (qt * TW_BM + (row & ~3)));
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -984,7 +999,7 @@ inline __nv_bfloat16 *tcw_half_table(TcwScratch &sc, int Lt, int D, float base, 
 inline bool tcw_supported(const b200attn_args &a, int rd) {
     if (a.dtype != B200ATTN_BF16 && !(a.dtype == B200ATTN_F16 && a.pe == B200ATTN_PE_NONE)) return false;   // the encodings are bf16 arithmetic
     if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 8192) return false;
-    if (a.len_q % TW_BM != 0 || a.len_k % TC_BN != 0) return false;
+    if (a.len_q <= 64 && a.len_k <= 64) return false;   // short sequences: the split-head_d kernels
     if (a.len_k > 32 * TW_BN) return false;   // the offsets of a row's key tiles live one per lane
     if (a.cos_cache != nullptr && !pe_is_rope(a.pe)) return false;
     if (pe_pairs_halves(a.pe)) { if (a.head_d % 128 != 0 || rd != a.head_d) return false; }
@@ -992,7 +1007,7 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
     if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V | (uintptr_t)a.out) & 15) != 0) return false;
     if (((uintptr_t)a.out & 31) != 0) return false;   // the epilogue stores 32 bytes at a time
     const long long BH = (long long)a.batch_sz * a.num_heads;
-    if (BH * a.len_q >= (1ll << 31) || BH * (a.len_k + 256) >= (1ll << 31)) return false;
+    if (BH * (a.len_q + 128) >= (1ll << 31) || BH * (a.len_k + 256) >= (1ll << 31)) return false;
     return true;
 }
 
@@ -1008,7 +1023,9 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
     int ndp = 1;
     while (D % (64 * ndp) != 0 || D / ndp > 512) ++ndp;
     const int DW = D / ndp;
-    const int nqt = Lq / TW_BM, nkt = (Lk + TW_BN - 1) / TW_BN, nblk = Lk / TC_BN;
+    // any lengths: S and the maxima are kept with both lengths rounded up to whole 128-blocks
+    const int nqt = (Lq + TW_BM - 1) / TW_BM, nkt = (Lk + TW_BN - 1) / TW_BN, nblk = (Lk + TC_BN - 1) / TC_BN;
+    const int Lqp = nqt * TW_BM, Lkp = nblk * TC_BN;
     const size_t smem_s = (size_t)TW_NST * TW_STAGE + 1024;
     const size_t smem_p = (size_t)TP_NP * TC_P_BYTES + (size_t)TP_NV * TP_VS * TP_VW * 2 + 1024;
     static std::mutex attr_mu;
@@ -1033,18 +1050,18 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
     }
     // heads per pass: the score scratch of one pass stays below a cap (default 2 GiB)
     const size_t cap = score_scratch_cap;
-    const size_t s_head = (size_t)Lq * Lk * sizeof(__nv_bfloat16);
+    const size_t s_head = (size_t)Lqp * Lkp * sizeof(__nv_bfloat16);
     long long G = (long long)(cap / s_head);
     if (G < 1) G = 1;
     if (G > BH) G = BH;
     __nv_bfloat16 *S = (__nv_bfloat16 *)sc.get(0, (size_t)G * s_head);
-    float *rowmax = (float *)sc.get(1, (size_t)G * Lq * nkt * sizeof(float));
+    float *rowmax = (float *)sc.get(1, (size_t)G * Lqp * nkt * sizeof(float));
     __nv_bfloat16 *qs = nullptr, *ks = nullptr, *tab = nullptr;
     if (!S || !rowmax) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the score scratch"); return -1; }
     if (encoded) {
         qs = (__nv_bfloat16 *)sc.get(2, (size_t)G * Lq * D * 2);
         ks = (__nv_bfloat16 *)sc.get(3, (size_t)G * Lk * D * 2);
-        const int Lt = (Lq > nkt * TW_BN ? Lq : nkt * TW_BN);
+        const int Lt = (Lqp > nkt * TW_BN ? Lqp : nkt * TW_BN);
         if (!qs || !ks) { snprintf(t_tc_error, sizeof t_tc_error, "could not allocate the rotated-operand scratch"); return -1; }
         if (a.cos_cache != nullptr) {
             // the caller's angles: the table is rebuilt on every call (the caches may have changed)
@@ -1066,7 +1083,7 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
         const __nv_bfloat16 *Qg = (const __nv_bfloat16 *)a.Q + h0 * Lq * D, *Kg = (const __nv_bfloat16 *)a.K + h0 * Lk * D;
         const __nv_bfloat16 *Vg = (const __nv_bfloat16 *)a.V + h0 * Lk * D;
         TcwScoreParams sp{};
-        sp.Lq = Lq; sp.Lk = Lk; sp.D = D; sp.nch = D / 64; sp.nqt = nqt; sp.nkt = nkt;
+        sp.Lq = Lq; sp.Lk = Lk; sp.Lqp = Lqp; sp.Lkp = Lkp; sp.D = D; sp.nch = D / 64; sp.nqt = nqt; sp.nkt = nkt;
         sp.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
         sp.f16 = a.dtype == B200ATTN_F16 ? 1 : 0;
         sp.S = S; sp.rowmax = rowmax; sp.tab = tab; sp.q_store = qs; sp.k_store = ks;
@@ -1096,6 +1113,9 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
             launches->fetch_add(1);
             return B200ATTN_OK;
         };
+        CUtensorMap tmV, tmS;
+        const bool maps_ok = make_tmap_grouped_heads(&tmV, Vg, nh, Lk, D, TP_VS, TP_VW / 64) && make_tmap_grouped(&tmS, S, nh * Lqp, Lkp, TW_BM, 2);
+        if (!maps_ok) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return h0 == 0 ? -1 : B200ATTN_ERR_CUDA; }
         int rc;
         if (encoded) {
             const int nA = nqt > nkt ? nqt : nkt;
@@ -1105,9 +1125,6 @@ inline int tcw_run(const b200attn_args &a, int rd, float base, TcwScratch &sc, T
             rc = launch_scores(Qg, Kg, 0, nqt * nkt);
         }
         if (rc) return rc;
-        CUtensorMap tmV, tmS;
-        const bool maps_ok = make_tmap_grouped(&tmV, Vg, nh * Lk, D, TP_VS, TP_VW / 64) && make_tmap_grouped(&tmS, S, nh * Lq, Lk, TW_BM, 2);
-        if (!maps_ok) { snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed"); return B200ATTN_ERR_CUDA; }
         TcwPvParams pp{};
         pp.Lq = Lq; pp.Lk = Lk; pp.D = D; pp.DW = DW; pp.ndp = ndp; pp.nqt = nqt; pp.nkt = nkt; pp.nblk = nblk;
         pp.n_units = nh * nqt * ndp;
