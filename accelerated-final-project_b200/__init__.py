@@ -13,7 +13,7 @@ LIB_PATH = os.environ.get("B200ATTN_LIB") or os.path.join(_HERE, "lib", "libb200
 
 F32, BF16, F16 = 0, 1, 2
 PE_NONE, PE_ROPE_INTERLEAVED, PE_ROPE_HALF, PE_SINUSOIDAL, PE_ROPE_Q_ONLY, PE_ROPE_HALF_Q_ONLY = 0, 1, 2, 3, 4, 5
-FLAG_ASYNC, FLAG_FORCE_GENERIC, FLAG_FORCE_TWO_PASS, FLAG_PREFER_ONE_KERNEL, FLAG_NO_OVERLAP = 1, 2, 4, 8, 16
+FLAG_ASYNC, FLAG_FORCE_GENERIC, FLAG_FORCE_TWO_PASS, FLAG_PREFER_ONE_KERNEL, FLAG_NO_OVERLAP, FLAG_TWO_KERNELS = 1, 2, 4, 8, 16, 32
 OPT_SCORE_SCRATCH_MB, OPT_SPIN_LIMIT = 1, 2
 OK = 0
 

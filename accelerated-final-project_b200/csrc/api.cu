@@ -23,6 +23,7 @@
 #include "tc_bf16.cuh"
 #include "tc_wide.cuh"
 #include "dec.cuh"
+#include "tc_fa.cuh"
 
 namespace b200attn {
 
@@ -591,6 +592,12 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
     if (!done && tc_ok && dec_supported(*a, rd)) {
         rc = dec_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_decode"; done = true; }
+        else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
+    }
+    // narrow heads, many queries: one kernel, the scores stay in tensor memory
+    if (!done && tc_ok && !(a->flags & B200ATTN_FLAG_TWO_KERNELS) && fa_supported(*a)) {
+        rc = fa_run(*a, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        if (rc == B200ATTN_OK) { t_last_path = "tc_fused"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
     if (!done && wide_ok) {

@@ -1,0 +1,369 @@
+// bf16 / fp16 attention forward for narrow heads (head_d 64 or 128) as ONE kernel on the 5th-generation tensor
+// cores: the scores never leave the SM.  (At these widths the two-kernel path of tc_wide.cuh is bound by the
+// HBM round trip of its score scratch, whose bytes per FLOP grow as 1 / head_d.)  Same mathematics as the
+// reference's bf16 forward, kernels/attention_bf16_optimized_fused.cu:493-505: softmax(Q K^T / sqrt(d)) V with
+// fp32 scores, fp32 softmax statistics and fp32 accumulation.
+//
+// A CTA works on units of (head, 256 query rows) = two query tiles of 128 rows, persistently:
+//   warp 0        one thread requests tiles by TMA: the two Q tiles of the unit, then K_0, V_0, K_1, V_1, ...
+//                 (128 keys each) through a ring of stages;
+//   warp 1        one thread issues the MMAs.  Tensor memory holds, per query tile t, the score tile S_t
+//                 [128 x 128] fp32 and the output accumulator O_t [128 x head_d] fp32.  The order
+//                     S_0 = Q_0 K_0^T | S_1 = Q_1 K_j^T, O_0 += P_0 V_j, S_0 = Q_0 K_j+1^T, O_1 += P_1 V_j | ...
+//                 lets the softmax of one tile run under the MMAs of the other;
+//   warps 2-5     softmax and epilogue of query tile 0, one thread per query row: read the row of S_t from
+//   warps 6-9     tensor memory, online softmax with the running maximum in a register, write P (16-bit) back
+//                 to tensor memory OVER the first 64 columns of S_t - the P V product takes its A operand from
+//                 tensor memory, so P never touches shared memory.  The accumulator is only rescaled when a
+//                 row's maximum has grown by more than 2^8 since the reference maximum was set (the row sum
+//                 carries the same reference, so the result is exact; P stays far inside the 16-bit range):
+//                 after the first tiles that almost never happens.  At the end of a unit: O_t / row sum -> global.
+//
+// Sequence lengths of any size: the tensor maps have the head as a coordinate of their own, so that rows beyond a
+// sequence read as zero; the columns of keys that do not exist are set to -inf before the softmax; output rows
+// that do not exist are not stored.  Every wait is bounded; a wait that expires sets the error word.
+#pragma once
+
+#include "tc_bf16.cuh"
+
+namespace b200attn {
+
+constexpr int FA_THREADS = 320;
+constexpr int FA_BM = 128;          // query rows per tile (two tiles per unit)
+constexpr int FA_BN = 128;          // keys per tile
+constexpr int FA_MAX_STAGES = 8;
+constexpr float FA_RESCALE_LOG2 = 8.0f;   // the accumulator is rescaled when a row maximum grows by more than this (log2 units)
+
+struct FaParams {
+    int Lq, Lk, D;
+    int nqp;                   // pairs of query tiles per head: ceil(ceil(Lq / 128) / 2)
+    int nkt;                   // key tiles: ceil(Lk / 128)
+    int nst;                   // ring stages of [128 keys x head_d]
+    long long n_units;         // heads * nqp
+    float scale_log2;          // log2(e) / sqrt(head_d)
+    int f16;                   // the tensors are fp16, else bf16
+    __nv_bfloat16 *O;          // [heads * Lq][D] (16-bit elements of the call's format)
+    unsigned *err, *err_sys;
+    unsigned spin_limit;
+};
+
+struct FaBars {
+    uint64_t kv_full[FA_MAX_STAGES], kv_empty[FA_MAX_STAGES];
+    uint64_t q_full, q_empty;
+    uint64_t s_full[2];        // S_t has been computed
+    uint64_t p_full[2];        // P_t has been written (and O_t rescaled where needed)
+    uint64_t o_done[2];        // the P V MMAs of tile t issued so far have completed
+    uint64_t o_empty[2];       // the epilogue has read O_t
+};
+
+// D[tmem] (+)= A[tmem] * B[smem]: A [128 rows x 16] of 16-bit elements, a row per lane, two elements per 32-bit column
+__device__ __forceinline__ void umma_16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+#define FA_FAIL_AT(site, cond)                                                                      \
+    if (cond) {                                                                                     \
+        report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << (7 + (site))));  \
+        failed = true;                                                                              \
+        break;                                                                                      \
+    }
+
+template <bool F16>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+    extern __shared__ unsigned char fa_smem_raw[];
+    __shared__ FaBars bars;
+    __shared__ uint32_t tmem_slot;
+    const uint32_t raw_addr = smem_u32(fa_smem_raw);
+    unsigned char *smem = fa_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int D = p.D, nkt = p.nkt, nst = p.nst;
+    const int ng = D >> 6;                              // 64-column groups of a row
+    const uint32_t tile_bytes = (uint32_t)FA_BN * (uint32_t)D * 2u;   // a Q, K or V tile: [ng groups][128 rows][128 B]
+    unsigned char *q_smem = smem;                       // two Q tiles
+    unsigned char *ring = smem + 2 * (size_t)tile_bytes;
+    const uint32_t lim = p.spin_limit;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < FA_MAX_STAGES; ++i) { mbar_init(&bars.kv_full[i], 1); mbar_init(&bars.kv_empty[i], 1); }
+        mbar_init(&bars.q_full, 1);
+        mbar_init(&bars.q_empty, 1);
+        for (int t = 0; t < 2; ++t) { mbar_init(&bars.s_full[t], 1); mbar_init(&bars.p_full[t], 4); mbar_init(&bars.o_done[t], 1); mbar_init(&bars.o_empty[t], 4); }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;        // S_t: columns [128 t, 128 t + 128); O_t: [256 + 128 t, ...)
+    bool failed = false;
+    const bool skip = (*reinterpret_cast<volatile unsigned *>(p.err) != 0);   // an earlier kernel of the call failed
+
+    if (skip) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        if (lane == 0) {
+            long long it = 0;
+            int ui = 0;
+            for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x, ++ui) {
+                const int bh = (int)(unit / p.nqp), qp = (int)(unit % p.nqp);
+                FA_FAIL_AT(0, !mbar_wait(&bars.q_empty, (ui & 1) ^ 1, lim));
+                mbar_expect_tx(&bars.q_full, 2 * tile_bytes);
+                tma_load_4d(q_smem, &tmQ, 0, qp * 2 * FA_BM, 0, bh, &bars.q_full);
+                tma_load_4d(q_smem + tile_bytes, &tmQ, 0, qp * 2 * FA_BM + FA_BM, 0, bh, &bars.q_full);
+                for (int j = 0; j < 2 * nkt && !failed; ++j, ++it) {   // K_0, V_0, K_1, V_1, ...
+                    const int s = (int)(it % nst);
+                    FA_FAIL_AT(1, !mbar_wait(&bars.kv_empty[s], (uint32_t)((it / nst) & 1) ^ 1u, lim));
+                    mbar_expect_tx(&bars.kv_full[s], tile_bytes);
+                    tma_load_4d(ring + (size_t)s * tile_bytes, (j & 1) ? &tmV : &tmK, 0, (j >> 1) * FA_BN, 0, bh, &bars.kv_full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t id_qk = umma_idesc_16(FA_BM, FA_BN, 0, 0, F16 ? 1 : 0), id_pv = umma_idesc_16(FA_BM, D, 0, 1, F16 ? 1 : 0);
+            long long it = 0;      // ring position of this unit's K_0
+            long long sc = 0;      // tiles done so far per query tile: phase of s_full, p_full
+            int ui = 0;
+            bool ok = true;
+            auto kv_wait = [&](long long idx) {   // tile idx of the ring has landed
+                if (ok && !mbar_wait(&bars.kv_full[idx % nst], (uint32_t)((idx / nst) & 1), lim)) ok = false;
+                tc_fence_after();
+            };
+            auto qk = [&](int t, long long idx) {   // S_t = Q_t K^T
+                const uint32_t qa = smem_u32(q_smem + (size_t)t * tile_bytes), ka = smem_u32(ring + (size_t)(idx % nst) * tile_bytes);
+                for (int g = 0; g < ng; ++g) {
+                    const uint64_t dq = umma_desc_k_sw128(qa + g * (FA_BM * 128)), dk = umma_desc_k_sw128(ka + g * (FA_BN * 128));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma_bf16(tmem + t * 128, dq + 2 * k, dk + 2 * k, id_qk, (g | k) != 0);
+                }
+                umma_commit(&bars.s_full[t]);
+            };
+            auto pv = [&](int t, long long idx, bool acc) {   // O_t (+)= P_t V, P_t in the first 64 columns of S_t
+                const uint32_t va = smem_u32(ring + (size_t)(idx % nst) * tile_bytes);
+#pragma unroll
+                for (int kk = 0; kk < FA_BN / 16; ++kk)
+                    umma_16_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, umma_desc_mn_sw128(va + kk * 2048, FA_BN * 128), id_pv, (acc || kk != 0) ? 1u : 0u);
+                umma_commit(&bars.o_done[t]);
+            };
+            for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
+                if (!mbar_wait(&bars.q_full, (uint32_t)(ui & 1), lim)) { ok = false; break; }
+                tc_fence_after();
+                kv_wait(it);
+                if (!ok) break;
+                qk(0, it);
+                for (int j = 0; j < nkt && ok; ++j, ++sc) {
+                    const long long ik = it + 2 * j, iv = ik + 1;
+                    qk(1, ik);
+                    umma_commit(&bars.kv_empty[ik % nst]);
+                    if (j == nkt - 1) umma_commit(&bars.q_empty);   // the unit's last MMA that reads Q
+                    kv_wait(iv);
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        // the epilogue of the previous unit has read O_t
+                        if (j == 0 && !mbar_wait(&bars.o_empty[t], (uint32_t)(ui & 1) ^ 1u, lim)) { ok = false; break; }
+                        if (!mbar_wait(&bars.p_full[t], (uint32_t)(sc & 1), lim)) { ok = false; break; }
+                        tc_fence_after();
+                        pv(t, iv, j > 0);
+                        if (t == 0 && j + 1 < nkt) {
+                            kv_wait(ik + 2);
+                            if (!ok) break;
+                            qk(0, ik + 2);
+                        }
+                    }
+                    umma_commit(&bars.kv_empty[iv % nst]);
+                }
+                it += 2 * nkt;
+            }
+            if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 9)); failed = true; }
+        }
+    } else {
+        // ---- softmax and epilogue of query tile t; thread = query row (tensor-memory lane) ----
+        const int t = (warp - 2) >> 2, q = warp & 3;
+        const int row = 32 * q + lane;
+        const uint32_t ts = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)t * 128u;   // S_t / P_t of this row
+        const uint32_t to = tmem + ((uint32_t)(32 * q) << 16) + 256u + (uint32_t)t * 128u;
+        const float sl2 = p.scale_log2;
+        long long sc = 0;
+        float m_ref = 0.0f, l = 0.0f;
+        uint32_t r0[32], r1[32], r2[32], r3[32], w[32];
+        for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
+            const int bh = (int)(unit / p.nqp), qp = (int)(unit % p.nqp);
+            for (int j = 0; j < nkt; ++j, ++sc) {
+                FA_FAIL_AT(2, !mbar_wait(&bars.s_full[t], (uint32_t)(sc & 1), lim));
+                tc_fence_after();
+                const int valid = min(FA_BN, p.Lk - j * FA_BN);   // real keys in this tile
+                // ---- the row of S_t: all 128 scores in registers (four loads in flight) ----
+                tmem_ld32(ts, r0);
+                tmem_ld32(ts + 32, r1);
+                tmem_ld32(ts + 64, r2);
+                tmem_ld32(ts + 96, r3);
+                tmem_ld_wait();
+                if (valid < FA_BN) {   // (the same for every thread) keys that do not exist
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (i >= valid) r0[i] = 0xff800000u;
+                        if (32 + i >= valid) r1[i] = 0xff800000u;
+                        if (64 + i >= valid) r2[i] = 0xff800000u;
+                        if (96 + i >= valid) r3[i] = 0xff800000u;
+                    }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    mx0 = fmaxf(mx0, __uint_as_float(r0[i])); mx1 = fmaxf(mx1, __uint_as_float(r1[i]));
+                    mx2 = fmaxf(mx2, __uint_as_float(r2[i])); mx3 = fmaxf(mx3, __uint_as_float(r3[i]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+                if (j == 0) {
+                    m_ref = mx;
+                    l = 0.0f;
+                } else {
+                    // ---- rescale the accumulator where the maximum has outgrown its reference ----
+                    const bool need = mx > m_ref + FA_RESCALE_LOG2;
+                    if (__any_sync(0xffffffffu, need)) {
+                        FA_FAIL_AT(3, !mbar_wait(&bars.o_done[t], (uint32_t)((sc - 1) & 1), lim));   // the previous P V of this tile is done
+                        tc_fence_after();
+                        const float m_new = need ? mx : m_ref;
+                        const float f = fast_exp2(m_ref - m_new);
+                        for (int c = 0; c < (D >> 5); ++c) {
+                            tmem_ld32(to + 32 * c, w);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * f);
+                            tmem_st32(to + 32 * c, w);
+                        }
+                        tmem_st_wait();
+                        l *= f;
+                        m_ref = m_new;
+                    }
+                }
+                // ---- P = exp2(S * scale - reference), 64 keys at a time: 32 packed words over columns of S_t
+                // (masked keys: exp2(-inf) = 0) ----
+                float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(r0[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 1]), sl2, -m_ref));
+                    const float e2 = fast_exp2(fmaf(__uint_as_float(r1[2 * i]), sl2, -m_ref)), e3 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), sl2, -m_ref));
+                    sum0 += e0 + e1; sum1 += e2 + e3;
+                    w[i] = pack_16x2(e0, e1, F16);
+                    w[16 + i] = pack_16x2(e2, e3, F16);
+                }
+                tmem_st32(ts, w);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(r2[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r2[2 * i + 1]), sl2, -m_ref));
+                    const float e2 = fast_exp2(fmaf(__uint_as_float(r3[2 * i]), sl2, -m_ref)), e3 = fast_exp2(fmaf(__uint_as_float(r3[2 * i + 1]), sl2, -m_ref));
+                    sum0 += e0 + e1; sum1 += e2 + e3;
+                    r0[i] = pack_16x2(e0, e1, F16);
+                    r0[16 + i] = pack_16x2(e2, e3, F16);
+                }
+                tmem_st32(ts + 32, r0);
+                l += sum0 + sum1;
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.p_full[t]);
+            }
+            if (failed) break;
+            // ---- epilogue of the unit: O_t / row sum -> 16 bit -> global; lanes trade pieces so that the stores cover full lines ----
+            FA_FAIL_AT(4, !mbar_wait(&bars.o_done[t], (uint32_t)((sc - 1) & 1), lim));
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const int qrow0 = qp * 2 * FA_BM + t * FA_BM;   // first query row of the tile within its head
+            __nv_bfloat16 *orow = p.O + ((long long)bh * p.Lq + qrow0 + row) * (long long)D;
+            unsigned char *row0 = reinterpret_cast<unsigned char *>(orow - (long long)(lane & 3) * D);
+            for (int cp = 0; cp < ng; ++cp) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    tmem_ld32(to + cp * 64 + hh * 32, r0);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) w[16 * hh + i] = pack_16x2(__uint_as_float(r0[2 * i]) * inv, __uint_as_float(r0[2 * i + 1]) * inv, F16);
+                }
+                store_rows_128B_transposed_if(row0 + cp * 128, (size_t)D * 2, w, lane, p.Lq - (qrow0 + (row & ~3)));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.o_empty[t]);
+        }
+    }
+
+    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies and MMAs in flight drain
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+#undef FA_FAIL_AT
+
+// ---- host side ------------------------------------------------------------------------------------
+inline bool fa_supported(const b200attn_args &a) {
+    if (a.dtype != B200ATTN_BF16 && a.dtype != B200ATTN_F16) return false;
+    if (a.pe != B200ATTN_PE_NONE) return false;
+    if (a.head_d != 64 && a.head_d != 128) return false;
+    if (a.len_q <= 64) return false;   // few queries: the key-split kernels, or the split-head_d kernels
+    if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V) & 15) != 0 || ((uintptr_t)a.out & 31) != 0) return false;
+    const long long BH = (long long)a.batch_sz * a.num_heads;
+    if (BH >= (1ll << 31) || BH * ((a.len_q + 255) / 256) >= (1ll << 40)) return false;
+    return true;
+}
+
+// Returns B200ATTN_OK, -1 when the shape should run on another path (nothing has been launched then), or a
+// status with tc_bf16_error() set.
+inline int fa_run(const b200attn_args &a, unsigned *err_dev, unsigned *err_sys, int sm_count, unsigned spin_limit, cudaStream_t st,
+                  std::atomic<unsigned long long> *launches) {
+    const long long BH = (long long)a.batch_sz * a.num_heads;
+    const int D = a.head_d, Lq = a.len_q, Lk = a.len_k;
+    static std::mutex attr_mu;
+    static size_t smem_max[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> lk(attr_mu);
+        if (smem_max[dev & 63] == 0) {
+            cudaFuncAttributes fa;
+            cudaDeviceProp prop;
+            cudaGetDeviceProperties(&prop, dev);
+            const bool ok = cudaFuncGetAttributes(&fa, fa_kernel<false>) == cudaSuccess &&
+                            cudaFuncSetAttribute(fa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess &&
+                            cudaFuncSetAttribute(fa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
+            if (!ok) { (void)cudaGetLastError(); snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncSetAttribute(max dynamic shared memory) failed"); return B200ATTN_ERR_CUDA; }
+            smem_max[dev & 63] = prop.sharedMemPerBlockOptin - fa.sharedSizeBytes;
+        }
+    }
+    const size_t tile = (size_t)FA_BN * D * 2;
+    int nst = (int)((smem_max[dev & 63] - 1024 - 2 * tile) / tile);
+    if (nst > FA_MAX_STAGES) nst = FA_MAX_STAGES;
+    if (nst < 3) return -1;
+    CUtensorMap tmQ, tmK, tmV;
+    if (!make_tmap_grouped_heads(&tmQ, a.Q, BH, Lq, D, FA_BM, D / 64) || !make_tmap_grouped_heads(&tmK, a.K, BH, Lk, D, FA_BN, D / 64) ||
+        !make_tmap_grouped_heads(&tmV, a.V, BH, Lk, D, FA_BN, D / 64)) {
+        snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
+        return -1;
+    }
+    FaParams p{};
+    p.Lq = Lq; p.Lk = Lk; p.D = D;
+    p.nqp = ((Lq + FA_BM - 1) / FA_BM + 1) / 2;
+    p.nkt = (Lk + FA_BN - 1) / FA_BN;
+    p.nst = nst;
+    p.n_units = BH * p.nqp;
+    p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+    p.f16 = a.dtype == B200ATTN_F16 ? 1 : 0;
+    p.O = (__nv_bfloat16 *)a.out;
+    p.err = err_dev; p.err_sys = err_sys; p.spin_limit = spin_limit;
+    const unsigned grid = (unsigned)(p.n_units < sm_count ? p.n_units : sm_count);
+    if (p.f16) fa_kernel<true><<<grid, FA_THREADS, 2 * tile + (size_t)nst * tile + 1024, st>>>(tmQ, tmK, tmV, p);
+    else fa_kernel<false><<<grid, FA_THREADS, 2 * tile + (size_t)nst * tile + 1024, st>>>(tmQ, tmK, tmV, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "fa_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
+    launches->fetch_add(1);
+    return B200ATTN_OK;
+}
+
+}  // namespace b200attn

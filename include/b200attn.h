@@ -126,7 +126,8 @@ enum b200attn_flags {
     B200ATTN_FLAG_FORCE_GENERIC = 2,  /* use the CUDA-core split-head_d kernels even where a tensor-core kernel applies */
     B200ATTN_FLAG_FORCE_TWO_PASS = 4, /* split-head_d path: two launches instead of one fused launch */
     B200ATTN_FLAG_PREFER_ONE_KERNEL = 8, /* bf16: where both tensor-core paths take the shape, run the one-kernel cluster pipeline */
-    B200ATTN_FLAG_NO_OVERLAP = 16     /* b200attn_forward_many: start this entry only after the previous one has completed */
+    B200ATTN_FLAG_NO_OVERLAP = 16,    /* b200attn_forward_many: start this entry only after the previous one has completed */
+    B200ATTN_FLAG_TWO_KERNELS = 32    /* bf16 / fp16, head_d 64 or 128: run the two-kernel path where the one-kernel narrow-head path would run (the two are measured against each other that way) */
 };
 
 typedef struct b200attn_args {

@@ -1,0 +1,117 @@
+"""GPU parity of the one-kernel tensor-core path for narrow heads (head_d 64 or 128, bf16 / fp16, no encoding,
+more than 64 queries): scores and probabilities stay in tensor memory, online softmax with a lazily rescaled
+accumulator.  Oracle: fp32 CPU attention on the 16-bit-rounded inputs; tolerance max-abs 2e-2 (bf16)."""
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+from gpu_util import bf16_from_dev, bf16_problem, bf16_to_dev
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+SHAPES = [
+    (1, 1, 128, 128, 128),      # one tile of each
+    (1, 2, 256, 256, 128),      # one unit: two query tiles
+    (1, 2, 256, 384, 64),
+    (2, 3, 512, 1024, 128),     # several units per head, eight key tiles
+    (1, 150, 256, 256, 64),     # more units than SMs: CTAs take several
+    (1, 2, 384, 640, 128),      # an odd number of query tiles: the second tile of the last unit is empty
+    (2, 3, 200, 300, 128),      # ragged in both lengths
+    (1, 2, 129, 257, 64),
+    (1, 3, 700, 1000, 128),
+    (1, 1, 65, 4100, 128),      # 33 key tiles, the last with 4 keys
+    (1, 2, 300, 40, 64),        # fewer keys than a tile
+    (1, 1, 2048, 2048, 128),
+]
+
+
+def run(pkg, cuda, bits, **kw):
+    q, k, v = (bf16_to_dev(b, cuda) for b in bits)
+    return bf16_from_dev(pkg.forward(q, k, v, **kw))
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_fused_path_against_oracle(pkg, cuda, shape):
+    B, H, Lq, Lk, D = shape
+    bits, up = bf16_problem(B, H, Lq, Lk, D, 91, "normal")
+    want = ol.attention(*up)
+    got = run(pkg, cuda, bits)
+    assert pkg.last_path() == "tc_fused", pkg.last_path()
+    err = float(np.abs(got - want).max())
+    assert err <= TOL, (shape, err)
+    assert err <= 8e-3, (shape, err)   # observed 3e-4 ... 4e-3 (the rounding of P and of the result to bf16)
+
+
+def test_fused_path_agrees_with_the_two_kernel_path(pkg, cuda):
+    bits, up = bf16_problem(2, 4, 640, 896, 128, 92, "normal")
+    a = run(pkg, cuda, bits)
+    assert pkg.last_path() == "tc_fused"
+    b = run(pkg, cuda, bits, flags=pkg.FLAG_TWO_KERNELS)
+    assert pkg.last_path() == "tc_wide"
+    assert float(np.abs(a - b).max()) <= 8e-3
+
+
+def test_fused_path_with_peaked_rows_rescales_its_accumulator(pkg, cuda):
+    """Scores that keep growing along the keys (row maxima far apart from tile to tile) force the lazy rescale of
+    the accumulator again and again; scores that shrink leave the first reference maximum in place."""
+    B, H, Lq, Lk, D = 1, 2, 256, 1024, 128
+    rng = np.random.default_rng(93)
+    Q = rng.standard_normal((B, H, Lq, D)).astype(np.float32)
+    K = rng.standard_normal((B, H, Lk, D)).astype(np.float32)
+    V = rng.standard_normal((B, H, Lk, D)).astype(np.float32)
+    ramp = np.linspace(0.0, 12.0, Lk, dtype=np.float32)[None, :, None]     # key j is aligned with every query, more and more strongly
+    K[:, 0] = K[:, 0] * 0.2 + ramp * np.sign(Q[:, 0].mean(axis=1, keepdims=True))
+    K[:, 1] = K[:, 1] * 0.2 + ramp[:, ::-1] * np.sign(Q[:, 1].mean(axis=1, keepdims=True))
+    bits = tuple(ol.to_bf16_bits(x) for x in (Q, K, V))
+    up = tuple(ol.from_bf16_bits(b) for b in bits)
+    want = ol.attention(*up)
+    got = run(pkg, cuda, bits)
+    assert pkg.last_path() == "tc_fused"
+    assert float(np.abs(got - want).max()) <= TOL
+
+
+def test_fused_path_heads_do_not_see_their_neighbours(pkg, cuda):
+    B, H, Lq, Lk, D = 1, 3, 200, 300, 128
+    bits, up = bf16_problem(B, H, Lq, Lk, D, 94, "normal")
+    want = ol.attention(*up)
+    poisoned = [b.copy() for b in bits]
+    for b, pat in zip(poisoned, (0x7FC0, 0x7F80, 0xFF80)):   # NaN in Q, +inf in K, -inf in V of head 1
+        b[:, 1] = pat
+    got = run(pkg, cuda, poisoned)
+    assert pkg.last_path() == "tc_fused"
+    for h in (0, 2):
+        assert np.isfinite(got[:, h]).all(), h
+        assert float(np.abs(got[:, h] - want[:, h]).max()) <= 8e-3, h
+
+
+def test_fused_path_leaves_the_memory_behind_the_output_alone(pkg, cuda):
+    import torch
+    B, H, Lq, Lk, D = 1, 2, 130, 200, 64
+    bits, up = bf16_problem(B, H, Lq, Lk, D, 95, "normal")
+    q, k, v = (bf16_to_dev(b, cuda) for b in bits)
+    big = torch.full((B * H * Lq * D + 254 * D,), 7.0, dtype=torch.bfloat16, device=cuda)
+    out = big[: B * H * Lq * D].view(B, H, Lq, D)
+    pkg.forward(q, k, v, out=out)
+    assert pkg.last_path() == "tc_fused"
+    assert bool((big[B * H * Lq * D:] == 7.0).all())
+    assert float(np.abs(bf16_from_dev(out) - ol.attention(*up)).max()) <= 8e-3
+
+
+def test_fused_path_twice_in_a_row_same_result(pkg, cuda):
+    bits, up = bf16_problem(1, 4, 512, 768, 128, 96, "normal")
+    a = run(pkg, cuda, bits)
+    b = run(pkg, cuda, bits)
+    assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 256, 384, 128), (2, 2, 200, 300, 64)], ids=lambda s: "x".join(map(str, s)))
+def test_fused_path_fp16(pkg, cuda, shape):
+    import torch
+    B, H, Lq, Lk, D = shape
+    Q, K, V = ol.make_qkv(B, H, Lq, Lk, D, 97, "normal")
+    q, k, v = (torch.from_numpy(x).to(cuda).half() for x in (Q, K, V))
+    want = ol.attention(*(x.float().cpu().numpy() for x in (q, k, v)))
+    got = pkg.forward(q, k, v).float().cpu().numpy()
+    assert pkg.last_path() == "tc_fused"
+    assert float(np.abs(got - want).max()) <= 2e-3   # fp16 keeps three more bits than bf16

@@ -123,7 +123,7 @@ def test_ragged_lengths_on_the_tensor_cores(pkg, cuda, shape):
     B, H, Lq, Lk, D = shape
     bits, up = bf16_problem(B, H, Lq, Lk, D, 81, "normal")
     want = ol.attention(*up)
-    got = run(pkg, cuda, bits)
+    got = run(pkg, cuda, bits, flags=pkg.FLAG_TWO_KERNELS)   # (narrow heads would otherwise take the one-kernel path)
     assert pkg.last_path() == "tc_wide", pkg.last_path()
     err = float(np.abs(got - want).max())
     assert err <= 8e-3, (shape, err)
@@ -155,7 +155,7 @@ def test_ragged_heads_do_not_see_their_neighbours(pkg, cuda):
     poisoned = [b.copy() for b in bits]
     for b, pat in zip(poisoned, (0x7FC0, 0x7F80, 0xFF80)):   # NaN in Q, +inf in K, -inf in V
         b[:, 1] = pat
-    got = run(pkg, cuda, poisoned)
+    got = run(pkg, cuda, poisoned, flags=pkg.FLAG_TWO_KERNELS)
     assert pkg.last_path() == "tc_wide"
     for h in (0, 2):
         assert np.isfinite(got[:, h]).all(), h
@@ -170,7 +170,7 @@ def test_ragged_lengths_leave_the_memory_behind_the_output_alone(pkg, cuda):
     q, k, v = (bf16_to_dev(b, cuda) for b in bits)
     big = torch.full((B * H * Lq * D + 126 * D,), 7.0, dtype=torch.bfloat16, device=cuda)
     out = big[: B * H * Lq * D].view(B, H, Lq, D)
-    pkg.forward(q, k, v, out=out)
+    pkg.forward(q, k, v, out=out, flags=pkg.FLAG_TWO_KERNELS)
     assert pkg.last_path() == "tc_wide"
     assert bool((big[B * H * Lq * D:] == 7.0).all())
     assert float(np.abs(bf16_from_dev(out) - ol.attention(*up)).max()) <= 8e-3
