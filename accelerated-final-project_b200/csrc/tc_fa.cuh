@@ -132,11 +132,10 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
             long long sc = 0;      // tiles done so far per query tile: phase of s_full, p_full
             int ui = 0;
             bool ok = true;
-            auto kv_wait = [&](long long idx) {   // tile idx of the ring has landed
-                if (ok && !mbar_wait(&bars.kv_full[idx % nst], (uint32_t)((idx / nst) & 1), lim)) ok = false;
-                tc_fence_after();
-            };
-            auto qk = [&](int t, long long idx) {   // S_t = Q_t K^T
+            TC_PROF_DECL;
+            // tile idx of the ring has landed
+            auto kv_wait = [=](long long idx) { const bool r = mbar_wait(&bars.kv_full[idx % nst], (uint32_t)((idx / nst) & 1), lim); tc_fence_after(); return r; };
+            auto qk = [=](int t, long long idx) {   // S_t = Q_t K^T
                 const uint32_t qa = smem_u32(q_smem + (size_t)t * tile_bytes), ka = smem_u32(ring + (size_t)(idx % nst) * tile_bytes);
                 for (int g = 0; g < ng; ++g) {
                     const uint64_t dq = umma_desc_k_sw128(qa + g * (FA_BM * 128)), dk = umma_desc_k_sw128(ka + g * (FA_BN * 128));
@@ -145,7 +144,7 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                 }
                 umma_commit(&bars.s_full[t]);
             };
-            auto pv = [&](int t, long long idx, bool acc) {   // O_t (+)= P_t V, P_t in the first 64 columns of S_t
+            auto pv = [=](int t, long long idx, bool acc) {   // O_t (+)= P_t V, P_t in the first 64 columns of S_t
                 const uint32_t va = smem_u32(ring + (size_t)(idx % nst) * tile_bytes);
 #pragma unroll
                 for (int kk = 0; kk < FA_BN / 16; ++kk)
@@ -153,9 +152,9 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                 umma_commit(&bars.o_done[t]);
             };
             for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
-                if (!mbar_wait(&bars.q_full, (uint32_t)(ui & 1), lim)) { ok = false; break; }
+                ok = mbar_wait(&bars.q_full, (uint32_t)(ui & 1), lim);
                 tc_fence_after();
-                kv_wait(it);
+                ok = ok && kv_wait(it);
                 if (!ok) break;
                 qk(0, it);
                 for (int j = 0; j < nkt && ok; ++j, ++sc) {
@@ -163,15 +162,21 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                     qk(1, ik);
                     umma_commit(&bars.kv_empty[ik % nst]);
                     if (j == nkt - 1) umma_commit(&bars.q_empty);   // the unit's last MMA that reads Q
-                    kv_wait(iv);
+                    TC_PROF(2);
+                    ok = kv_wait(iv);
+                    TC_PROF(0);
                     for (int t = 0; t < 2 && ok; ++t) {
                         // the epilogue of the previous unit has read O_t
-                        if (j == 0 && !mbar_wait(&bars.o_empty[t], (uint32_t)(ui & 1) ^ 1u, lim)) { ok = false; break; }
-                        if (!mbar_wait(&bars.p_full[t], (uint32_t)(sc & 1), lim)) { ok = false; break; }
+                        if (j == 0) ok = mbar_wait(&bars.o_empty[t], (uint32_t)(ui & 1) ^ 1u, lim);
+                        ok = ok && mbar_wait(&bars.p_full[t], (uint32_t)(sc & 1), lim);
+                        if (!ok) break;
                         tc_fence_after();
+                        TC_PROF(1);
                         pv(t, iv, j > 0);
                         if (t == 0 && j + 1 < nkt) {
-                            kv_wait(ik + 2);
+                            TC_PROF(2);
+                            ok = kv_wait(ik + 2);
+                            TC_PROF(0);
                             if (!ok) break;
                             qk(0, ik + 2);
                         }
@@ -181,6 +186,7 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                 it += 2 * nkt;
             }
             if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 9)); failed = true; }
+            TC_PROF_FLUSH(8, true);
         }
     } else {
         // ---- softmax and epilogue of query tile t; thread = query row (tensor-memory lane) ----
@@ -192,11 +198,14 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         long long sc = 0;
         float m_ref = 0.0f, l = 0.0f;
         uint32_t r0[32], r1[32], r2[32], r3[32], w[32];
+        TC_PROF_DECL;
         for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
             const int bh = (int)(unit / p.nqp), qp = (int)(unit % p.nqp);
             for (int j = 0; j < nkt; ++j, ++sc) {
+                TC_PROF(4);
                 FA_FAIL_AT(2, !mbar_wait(&bars.s_full[t], (uint32_t)(sc & 1), lim));
                 tc_fence_after();
+                TC_PROF(0);
                 const int valid = min(FA_BN, p.Lk - j * FA_BN);   // real keys in this tile
                 // ---- the row of S_t: all 128 scores in registers (four loads in flight) ----
                 tmem_ld32(ts, r0);
@@ -204,7 +213,8 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                 tmem_ld32(ts + 64, r2);
                 tmem_ld32(ts + 96, r3);
                 tmem_ld_wait();
-                if (valid < FA_BN) {   // (the same for every thread) keys that do not exist
+                TC_PROF(1);
+                if (valid < FA_BN) {   // (the same for every thread) keys that do not exist: exp2(-inf) = 0
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         if (i >= valid) r0[i] = 0xff800000u;
@@ -243,28 +253,38 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                         m_ref = m_new;
                     }
                 }
-                // ---- P = exp2(S * scale - reference), 64 keys at a time: 32 packed words over columns of S_t
-                // (masked keys: exp2(-inf) = 0) ----
+                TC_PROF(2);
+                // ---- P = exp2(S * scale - reference), 64 keys at a time: 32 packed words, in place (word i replaces
+                // a score that has been used already) ----
                 float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float e0 = fast_exp2(fmaf(__uint_as_float(r0[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 1]), sl2, -m_ref));
-                    const float e2 = fast_exp2(fmaf(__uint_as_float(r1[2 * i]), sl2, -m_ref)), e3 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), sl2, -m_ref));
-                    sum0 += e0 + e1; sum1 += e2 + e3;
-                    w[i] = pack_16x2(e0, e1, F16);
-                    w[16 + i] = pack_16x2(e2, e3, F16);
+                    sum0 += e0; sum1 += e1;
+                    r0[i] = pack_16x2(e0, e1, F16);
                 }
-                tmem_st32(ts, w);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(r1[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), sl2, -m_ref));
+                    sum0 += e0; sum1 += e1;
+                    r0[16 + i] = pack_16x2(e0, e1, F16);
+                }
+                tmem_st32(ts, r0);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float e0 = fast_exp2(fmaf(__uint_as_float(r2[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r2[2 * i + 1]), sl2, -m_ref));
-                    const float e2 = fast_exp2(fmaf(__uint_as_float(r3[2 * i]), sl2, -m_ref)), e3 = fast_exp2(fmaf(__uint_as_float(r3[2 * i + 1]), sl2, -m_ref));
-                    sum0 += e0 + e1; sum1 += e2 + e3;
-                    r0[i] = pack_16x2(e0, e1, F16);
-                    r0[16 + i] = pack_16x2(e2, e3, F16);
+                    sum0 += e0; sum1 += e1;
+                    r2[i] = pack_16x2(e0, e1, F16);
                 }
-                tmem_st32(ts + 32, r0);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(r3[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r3[2 * i + 1]), sl2, -m_ref));
+                    sum0 += e0; sum1 += e1;
+                    r2[16 + i] = pack_16x2(e0, e1, F16);
+                }
+                tmem_st32(ts + 32, r2);
                 l += sum0 + sum1;
+                TC_PROF(3);
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -284,14 +304,16 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                     tmem_ld32(to + cp * 64 + hh * 32, r0);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) w[16 * hh + i] = pack_16x2(__uint_as_float(r0[2 * i]) * inv, __uint_as_float(r0[2 * i + 1]) * inv, F16);
+                    for (int i = 0; i < 16; ++i) r1[16 * hh + i] = pack_16x2(__uint_as_float(r0[2 * i]) * inv, __uint_as_float(r0[2 * i + 1]) * inv, F16);
                 }
-                store_rows_128B_transposed_if(row0 + cp * 128, (size_t)D * 2, w, lane, p.Lq - (qrow0 + (row & ~3)));
+                store_rows_128B_transposed_if(row0 + cp * 128, (size_t)D * 2, r1, lane, p.Lq - (qrow0 + (row & ~3)));
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.o_empty[t]);
+            TC_PROF(5);
         }
+        TC_PROF_FLUSH(16 + 8 * t, threadIdx.x == 64 || threadIdx.x == 192);
     }
 
     if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies and MMAs in flight drain

@@ -42,6 +42,9 @@ CONFIGS = {
     # the decode regime (few queries against a long key cache): K rotated beforehand (KV-cache use) / in the load
     "decode": ("bf16", "rope_half_q_only", 1, 32, 4, 32768, 128, "normal", "hbm"),
     "decode_rope": ("bf16", "rope_half", 1, 32, 4, 32768, 128, "normal", "hbm"),
+    # narrow heads (what most transformer models use): the one-kernel path
+    "narrow128": ("bf16", "none", 4, 16, 4096, 4096, 128, "normal", "tensor"),
+    "narrow64": ("bf16", "none", 4, 16, 4096, 4096, 64, "normal", "tensor"),
     # profiling-size variants of cfg4 and cfg5 (16 heads): small enough for a multi-pass ncu capture
     "cfg4p": ("bf16", "rope_half", 1, 16, 2048, 2048, 1024, "normal", "tensor"),
     "cfg5p": ("bf16", "sinusoidal", 1, 16, 4096, 4096, 512, "normal", "tensor"),
