@@ -594,11 +594,38 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
         if (rc == B200ATTN_OK) { t_last_path = "tc_decode"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
+    // A call with an encoding that runs on encoded copies of Q and K (the scratch of the two-kernel path's rotated
+    // operands): the narrow-head kernel below, and fp16 tensors on the two-kernel path (whose in-load encodings
+    // are bf16 arithmetic).
+    b200attn_args enc;
+    auto encode_copies = [&](b200attn_args *b) -> int {
+        const size_t BHs = (size_t)a->batch_sz * a->num_heads;
+        void *qc = c->tcw.get(2, BHs * a->len_q * a->head_d * 2);
+        void *kc = pe_encodes_k(a->pe) ? c->tcw.get(3, BHs * a->len_k * a->head_d * 2) : nullptr;
+        if (qc == nullptr || (pe_encodes_k(a->pe) && kc == nullptr)) return -1;
+        return a->dtype == B200ATTN_F16 ? fa_encode_copies<__half>(*a, rd, base, (__half *)qc, (__half *)kc, c->sm_count, st, &g_launches, b)
+                                        : fa_encode_copies<__nv_bfloat16>(*a, rd, base, (__nv_bfloat16 *)qc, (__nv_bfloat16 *)kc, c->sm_count, st, &g_launches, b);
+    };
     // narrow heads, many queries: one kernel, the scores stay in tensor memory
     if (!done && tc_ok && !(a->flags & B200ATTN_FLAG_TWO_KERNELS) && fa_supported(*a)) {
-        rc = fa_run(*a, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        const b200attn_args *use = a;
+        rc = B200ATTN_OK;
+        if (a->pe != B200ATTN_PE_NONE) { rc = encode_copies(&enc); use = &enc; }
+        if (rc == B200ATTN_OK) rc = fa_run(*use, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_fused"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
+    }
+    if (!done && tc_ok && !wide_ok && a->dtype == B200ATTN_F16 && a->pe != B200ATTN_PE_NONE) {
+        b200attn_args plain = *a;
+        plain.pe = B200ATTN_PE_NONE; plain.cos_cache = nullptr; plain.sin_cache = nullptr;
+        if (tcw_supported(plain, plain.head_d)) {
+            rc = encode_copies(&enc);
+            if (rc == B200ATTN_OK)
+                rc = tcw_run(enc, enc.head_d, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(),
+                             (size_t)g_score_scratch_mb.load() << 20, st, &g_launches);
+            if (rc == B200ATTN_OK) { t_last_path = "tc_wide"; done = true; }
+            else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
+        }
     }
     if (!done && wide_ok) {
         rc = tcw_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(),
@@ -927,7 +954,7 @@ int b200attn_rope_k(const void *X, void *X_rot, int batch_sz, int num_heads, int
                     int rotary_dim, float rope_base, int pos0, const float *cos_cache, const float *sin_cache, void *stream) {
     if (!X || !X_rot || batch_sz <= 0 || num_heads <= 0 || len <= 0 || head_d <= 0 || pos0 < 0)
         return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_rope_k: NULL pointer, non-positive size or negative position");
-    if (dtype != B200ATTN_F32 && dtype != B200ATTN_BF16) return fail(B200ATTN_ERR_INVALID_ARG, "unknown dtype %d", dtype);
+    if (dtype != B200ATTN_F32 && dtype != B200ATTN_BF16 && dtype != B200ATTN_F16) return fail(B200ATTN_ERR_INVALID_ARG, "unknown dtype %d", dtype);
     if (pairing != B200ATTN_PE_ROPE_INTERLEAVED && pairing != B200ATTN_PE_ROPE_HALF)
         return fail(B200ATTN_ERR_INVALID_ARG, "b200attn_rope_k: pairing must be B200ATTN_PE_ROPE_INTERLEAVED or B200ATTN_PE_ROPE_HALF");
     const int rd = rotary_dim == 0 ? head_d : rotary_dim;
@@ -946,7 +973,8 @@ int b200attn_rope_k(const void *X, void *X_rot, int batch_sz, int num_heads, int
     p.half = pairing == B200ATTN_PE_ROPE_HALF ? 1 : 0;
     p.pos0 = pos0; p.base = base; p.cos_cache = cos_cache; p.sin_cache = sin_cache;
     cudaError_t e = dtype == B200ATTN_F32 ? launch_rope_k<float>(p, c->sm_count, (cudaStream_t)stream)
-                                          : launch_rope_k<__nv_bfloat16>(p, c->sm_count, (cudaStream_t)stream);
+                    : dtype == B200ATTN_F16 ? launch_rope_k<__half>(p, c->sm_count, (cudaStream_t)stream)
+                                            : launch_rope_k<__nv_bfloat16>(p, c->sm_count, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(B200ATTN_ERR_CUDA, "CUDA error %d (%s) launching the rotation kernel", (int)e, cudaGetErrorString(e));
     g_launches.fetch_add(1);
     return B200ATTN_OK;

@@ -24,6 +24,8 @@ struct RopeKParams {
     int pos0;
     float base;
     const float *cos_cache, *sin_cache;   // optional [>= pos0 + L][rd], value of pair i at columns 2i and 2i+1
+    int sinus;                // 1: additive sinusoidal encoding instead of a rotation - x[2i] += sin, x[2i+1] += cos of
+                              // pos / 10000^(2i/D) (final/sinusoidal.cu:143-161); then rd = D, half = 0, base = 10000
 };
 
 template <typename T> struct RopeVec;
@@ -35,6 +37,22 @@ template <> struct RopeVec<float> {
     }
     static __device__ __forceinline__ void store(float *p, const float (&x)[4]) {
         *reinterpret_cast<float4 *>(p) = make_float4(x[0], x[1], x[2], x[3]);
+    }
+};
+template <> struct RopeVec<__half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __half *p, float (&x)[8]) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(p);
+        const __half *h = reinterpret_cast<const __half *>(&v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = __half2float(h[e]);
+    }
+    static __device__ __forceinline__ void store(__half *p, const float (&x)[8]) {
+        uint4 v;
+        __half2 *h = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
+        *reinterpret_cast<uint4 *>(p) = v;
     }
 };
 template <> struct RopeVec<__nv_bfloat16> {
@@ -107,7 +125,10 @@ __global__ void __launch_bounds__(256) rope_k_vec_kernel(const RopeKParams p) {
                 float x[N], y[N];
                 RopeVec<T>::load(X + bh * slab + row + d, x);
 #pragma unroll
-                for (int e = 0; e < N / 2; ++e) { y[2 * e] = x[2 * e] * c[e] - x[2 * e + 1] * s[e]; y[2 * e + 1] = x[2 * e] * s[e] + x[2 * e + 1] * c[e]; }
+                for (int e = 0; e < N / 2; ++e) {
+                    if (p.sinus) { y[2 * e] = x[2 * e] + s[e]; y[2 * e + 1] = x[2 * e + 1] + c[e]; }
+                    else { y[2 * e] = x[2 * e] * c[e] - x[2 * e + 1] * s[e]; y[2 * e + 1] = x[2 * e] * s[e] + x[2 * e + 1] * c[e]; }
+                }
                 RopeVec<T>::store(Y + bh * slab + row + d, y);
             }
         }
@@ -134,8 +155,8 @@ __global__ void __launch_bounds__(256) rope_k_scalar_kernel(const RopeKParams p)
             const int d0 = p.half ? it : 2 * it, d1 = p.half ? it + npair : 2 * it + 1;
             for (long long bh = 0; bh < p.BH; ++bh) {
                 const float a = to_f32(X[bh * slab + row + d0]), b = to_f32(X[bh * slab + row + d1]);
-                Y[bh * slab + row + d0] = OutCvt<T>::one(a * c - b * s);
-                Y[bh * slab + row + d1] = OutCvt<T>::one(a * s + b * c);
+                Y[bh * slab + row + d0] = OutCvt<T>::one(p.sinus ? a + s : a * c - b * s);
+                Y[bh * slab + row + d1] = OutCvt<T>::one(p.sinus ? b + c : a * s + b * c);
             }
         }
     }

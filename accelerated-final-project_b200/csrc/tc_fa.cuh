@@ -25,6 +25,7 @@
 #pragma once
 
 #include "tc_bf16.cuh"
+#include "rope_k.cuh"
 
 namespace b200attn {
 
@@ -327,7 +328,6 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 // ---- host side ------------------------------------------------------------------------------------
 inline bool fa_supported(const b200attn_args &a) {
     if (a.dtype != B200ATTN_BF16 && a.dtype != B200ATTN_F16) return false;
-    if (a.pe != B200ATTN_PE_NONE) return false;
     if (a.head_d != 64 && a.head_d != 128) return false;
     if (a.len_q <= 64) return false;   // few queries: the key-split kernels, or the split-head_d kernels
     if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V) & 15) != 0 || ((uintptr_t)a.out & 31) != 0) return false;
@@ -385,6 +385,44 @@ inline int fa_run(const b200attn_args &a, unsigned *err_dev, unsigned *err_sys, 
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "fa_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
     launches->fetch_add(1);
+    return B200ATTN_OK;
+}
+
+// Encoded copies for a call with a positional encoding: Q (and K, unless the caller keeps K encoded) is encoded once
+// into a scratch copy - fp32 arithmetic of the reference tables, one rounding to the 16-bit format - and `b` becomes
+// the same call on the copies without an encoding.  For the narrow heads of the kernel above, encoding K inside the
+// operand load would repeat the work once per 256 query rows, while the copy costs a few per cent of the attention
+// itself (0.27 GB of traffic against 0.65 ms of tensor-core work at B*H = 64, len 4096, head_d 128); the reference does
+// the same in attention_forward_separate_rope, final/rope.cu:1379-1416.  Also what gives fp16 tensors with an encoding
+// a tensor-core path at all (the in-load encodings of tc_wide.cuh are bf16 arithmetic).
+// `q_copy`, `k_copy`: device scratch of the sizes of Q, K.
+template <typename T>
+inline int fa_encode_copies(const b200attn_args &a, int rd, float base, T *q_copy, T *k_copy, int sm_count, cudaStream_t st,
+                            std::atomic<unsigned long long> *launches, b200attn_args *b) {
+    RopeKParams rp{};
+    rp.BH = (long long)a.batch_sz * a.num_heads;
+    rp.D = a.head_d;
+    rp.sinus = a.pe == B200ATTN_PE_SINUSOIDAL ? 1 : 0;
+    rp.rd = rp.sinus ? a.head_d : rd;
+    rp.half = pe_pairs_halves(a.pe) ? 1 : 0;
+    rp.pos0 = 0;
+    rp.base = rp.sinus ? 10000.0f : base;
+    rp.cos_cache = rp.sinus ? nullptr : a.cos_cache;
+    rp.sin_cache = rp.sinus ? nullptr : a.sin_cache;
+    rp.X = a.Q; rp.Y = q_copy; rp.L = a.len_q;
+    cudaError_t e = launch_rope_k<T>(rp, sm_count, st);
+    launches->fetch_add(1);
+    if (e == cudaSuccess && pe_encodes_k(a.pe)) {
+        rp.X = a.K; rp.Y = k_copy; rp.L = a.len_k;
+        e = launch_rope_k<T>(rp, sm_count, st);
+        launches->fetch_add(1);
+    }
+    if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "encoding kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
+    *b = a;
+    b->Q = q_copy;
+    if (pe_encodes_k(a.pe)) b->K = k_copy;
+    b->pe = B200ATTN_PE_NONE;
+    b->cos_cache = nullptr; b->sin_cache = nullptr;
     return B200ATTN_OK;
 }
 

@@ -184,8 +184,10 @@ const char *b200attn_last_error(void);
 /* Name of the kernel path the last successful b200attn_forward_ex on this thread used:
  * "splitd_tc" (fp32, short sequences, tensor cores with error-compensated tf32), "splitd_fused" and
  * "splitd_two_pass" (CUDA cores), "tc_wide" (bf16 on the tensor cores: score kernel, then P V kernel),
- * "tc_bf16" (bf16 on the tensor cores, one-kernel cluster pipeline) or "tc_decode" (bf16, up to 64 queries
- * against a long K/V: key splits on the tensor cores plus a combine kernel). */
+ * "tc_fused" (bf16 / fp16, head_d 64 or 128, more than 64 queries: one kernel, scores and probabilities in tensor
+ * memory; an encoding is applied to copies of Q and K first), "tc_bf16" (bf16 on the tensor cores, one-kernel
+ * cluster pipeline) or "tc_decode" (bf16, up to 64 queries against a long K/V: key splits on the tensor cores
+ * plus a combine kernel). */
 const char *b200attn_last_path(void);
 
 /* Number of kernel launches issued by this library in this process so far. */
@@ -197,7 +199,7 @@ void b200attn_release_workspace(void);
 /* Library version string. */
 const char *b200attn_version(void);
 
-/* "Rotate once and keep it": X_rot = RoPE(X) for a device tensor X [B,H,len,head_d] (fp32 or bf16), the
+/* "Rotate once and keep it": X_rot = RoPE(X) for a device tensor X [B,H,len,head_d] (fp32, bf16 or fp16), the
  * first rotary_dim columns rotated and the rest copied; row l of every (b,h) slice has position pos0 + l
  * (pos0 > 0 when keys are appended to a cache).  A KV-cache caller rotates K with this once and then calls
  * attention with a *_Q_ONLY encoding.  pairing is B200ATTN_PE_ROPE_INTERLEAVED or B200ATTN_PE_ROPE_HALF;

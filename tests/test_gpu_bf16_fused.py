@@ -115,3 +115,57 @@ def test_fused_path_fp16(pkg, cuda, shape):
     got = pkg.forward(q, k, v).float().cpu().numpy()
     assert pkg.last_path() == "tc_fused"
     assert float(np.abs(got - want).max()) <= 2e-3   # fp16 keeps three more bits than bf16
+
+
+PES = [ol.PE_ROPE_INTERLEAVED, ol.PE_ROPE_HALF, ol.PE_SINUSOIDAL, ol.PE_ROPE_Q_ONLY, ol.PE_ROPE_HALF_Q_ONLY]
+
+
+@pytest.mark.parametrize("pe", PES, ids=["rope_pairs", "rope_half", "sinusoidal", "rope_q_only", "rope_half_q_only"])
+@pytest.mark.parametrize("shape", [(1, 2, 256, 384, 128), (2, 2, 200, 300, 64), (1, 3, 129, 1000, 128)], ids=lambda s: "x".join(map(str, s)))
+def test_fused_path_with_encodings(pkg, cuda, pe, shape):
+    """With an encoding the narrow-head path works on encoded copies of Q and K (fp32 arithmetic, one rounding)."""
+    B, H, Lq, Lk, D = shape
+    bits, up = bf16_problem(B, H, Lq, Lk, D, 98, "normal")
+    q_only = pe in (ol.PE_ROPE_Q_ONLY, ol.PE_ROPE_HALF_Q_ONLY)
+    half = pe in (ol.PE_ROPE_HALF, ol.PE_ROPE_HALF_Q_ONLY)
+    if q_only:   # the caller keeps K rotated: give the library the rotated K, the oracle the plain one
+        kr = ol.from_bf16_bits(ol.to_bf16_bits(ol.apply_rope(up[1], half=half)))
+        want = ol.attention(ol.apply_rope(up[0], half=half), kr, up[2])
+        bits = (bits[0], ol.to_bf16_bits(kr), bits[2])
+    else:
+        want = ol.attention(*up, pe=pe)
+    got = run(pkg, cuda, bits, pe=pe)
+    assert pkg.last_path() == "tc_fused", pkg.last_path()
+    err = float(np.abs(got - want).max())
+    assert err <= TOL, (shape, pe, err)
+    assert err <= 1.2e-2, (shape, pe, err)
+
+
+def test_fused_path_partial_rotary_dim_and_caller_caches(pkg, cuda):
+    from gpu_util import to_dev
+    B, H, Lq, Lk, D, rd = 1, 2, 256, 512, 128, 64
+    bits, up = bf16_problem(B, H, Lq, Lk, D, 99, "normal")
+    for pe in (ol.PE_ROPE_INTERLEAVED, ol.PE_ROPE_HALF):
+        want = ol.attention(*up, pe=pe, rotary_dim=rd)
+        got = run(pkg, cuda, bits, pe=pe, rotary_dim=rd)
+        assert pkg.last_path() == "tc_fused"
+        assert float(np.abs(got - want).max()) <= 1.2e-2, pe
+    base = 500.0
+    c, s = ol.rope_cache(max(Lq, Lk), D, base)
+    want = ol.attention(*up, pe=ol.PE_ROPE_INTERLEAVED, base=base)
+    q, k, v = (bf16_to_dev(b, cuda) for b in bits)
+    got = bf16_from_dev(pkg.forward(q, k, v, pe=ol.PE_ROPE_INTERLEAVED, cos_cache=to_dev(c, cuda), sin_cache=to_dev(s, cuda)))
+    assert pkg.last_path() == "tc_fused"
+    assert float(np.abs(got - want).max()) <= 1.2e-2
+
+
+def test_fused_path_fp16_with_an_encoding(pkg, cuda):
+    import torch
+    B, H, Lq, Lk, D = 1, 2, 256, 384, 128
+    Q, K, V = ol.make_qkv(B, H, Lq, Lk, D, 100, "normal")
+    q, k, v = (torch.from_numpy(x).to(cuda).half() for x in (Q, K, V))
+    up = tuple(x.float().cpu().numpy() for x in (q, k, v))
+    for pe in (ol.PE_ROPE_HALF, ol.PE_SINUSOIDAL):
+        got = pkg.forward(q, k, v, pe=pe).float().cpu().numpy()
+        assert pkg.last_path() == "tc_fused"
+        assert float(np.abs(got - ol.attention(*up, pe=pe)).max()) <= 4e-3, pe

@@ -137,7 +137,7 @@ def test_ragged_lengths_with_encodings(pkg, cuda, pe, shape):
     B, H, Lq, Lk, D = shape
     bits, up = bf16_problem(B, H, Lq, Lk, D, 82, "normal")
     want = ol.attention(*up, pe=pe)
-    got = run(pkg, cuda, bits, pe=pe)
+    got = run(pkg, cuda, bits, pe=pe, flags=pkg.FLAG_TWO_KERNELS)   # (narrow heads would otherwise take the one-kernel path)
     assert pkg.last_path() == "tc_wide", pkg.last_path()
     err = float(np.abs(got - want).max())
     assert err <= TOL, (shape, pe, err)

@@ -45,11 +45,17 @@ def test_fp16_on_the_tensor_cores(pkg, cuda, shape):
     assert pkg.last_path() == ("tc_fused" if D in (64, 128) else "tc_wide")
     err = float(np.abs(got - ol.attention(*up)).max())
     assert err <= TOL, (shape, err)
-    # with an encoding the same shape runs on the CUDA cores (the tensor-core encodings are bf16 arithmetic)
-    if Lq * Lk * D <= 512 * 512 * 64 * 4:
-        got = run(pkg, cuda, h, pe=ol.PE_ROPE_HALF)
-        assert pkg.last_path().startswith("splitd")
-        assert float(np.abs(got - ol.attention(*up, pe=ol.PE_ROPE_HALF)).max()) <= TOL
+    # with an encoding: encoded fp16 copies of Q and K (fp32 arithmetic, one rounding), then the same kernels
+    for pe in (ol.PE_ROPE_HALF, ol.PE_SINUSOIDAL, ol.PE_ROPE_Q_ONLY):
+        want = ol.attention(*up, pe=pe)
+        if pe == ol.PE_ROPE_Q_ONLY:   # the caller keeps K rotated
+            kr = ol.apply_rope(up[1]).astype(np.float16)
+            want = ol.attention(ol.apply_rope(up[0]), kr.astype(np.float32), up[2])
+            got = run(pkg, cuda, (h[0], kr, h[2]), pe=pe)
+        else:
+            got = run(pkg, cuda, h, pe=pe)
+        assert pkg.last_path() == ("tc_fused" if D in (64, 128) else "tc_wide")
+        assert float(np.abs(got - want).max()) <= 4e-3, pe
 
 
 @pytest.mark.parametrize("shape", [(1, 16, 4, 4096, 128), (1, 4, 48, 2000, 64), (1, 32, 1, 8192, 128), (1, 3, 20, 777, 128)], ids=str)
