@@ -165,6 +165,25 @@ def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None, flags=0):
     return e0.elapsed_time(e1) / steps
 
 
+def narrow_sweep(pkg, torch, dev, pk):
+    """bf16 at the head widths most models use (64, 128), where the scores stay on the SM in one kernel: the default
+    path and, for comparison, the two-kernel path of the wide heads on the same inputs."""
+    out = []
+    for cfg in ("narrow128", "narrow64"):
+        _, _, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
+        sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(2)]
+        t = time_steps(pkg, torch, sets, 0, 20, 5)
+        path = pkg.last_path()
+        t2 = time_steps(pkg, torch, sets, 0, 10, 3, flags=pkg.FLAG_TWO_KERNELS)
+        fl = flops_of(cfg)
+        out.append({"config": cfg, "shape": [B, H, Lq, Lk, D], "path": path, "ms": round(t, 4), "tflops": round(fl / t / 1e9, 1),
+                    "frac_of_sustained_bf16_peak": round(fl / t / 1e9 / pk["bf16_tflops_sustained"], 4),
+                    "two_kernel_path_ms": round(t2, 4), "two_kernel_path_tflops": round(fl / t2 / 1e9, 1)})
+        del sets
+        torch.cuda.empty_cache()
+    return out
+
+
 def cpu_full(cfg, threads):
     """The reference's attention_cpu on the WHOLE problem of an fp32 configuration: with one thread exactly
     as written, or with the (b,h) slices fanned over `threads` host threads.  Returns seconds."""
@@ -576,6 +595,7 @@ def main():
         torch.cuda.empty_cache()
 
     if rank == 0 and world == 1 and not args.no_extras:
+        line["narrow_heads"] = narrow_sweep(pkg, torch, dev, pk)
         line["fp32_configs"] = fp32_sweep(pkg, torch, dev, pk)
         line["cpu_baseline_fp32"] = "per configuration in fp32_configs[].cpu_baseline: the reference's attention_cpu on the whole problem"
         cpu = CpuRef(cfg)

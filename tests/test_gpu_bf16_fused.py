@@ -169,3 +169,12 @@ def test_fused_path_fp16_with_an_encoding(pkg, cuda):
         got = pkg.forward(q, k, v, pe=pe).float().cpu().numpy()
         assert pkg.last_path() == "tc_fused"
         assert float(np.abs(got - ol.attention(*up, pe=pe)).max()) <= 4e-3, pe
+
+
+def test_fused_path_very_long_keys(pkg, cuda):
+    """No limit on len_k here (the two-kernel path stops at 8192 keys): 157 key tiles, the last with 32 keys."""
+    B, H, Lq, Lk, D = 1, 1, 128, 20000, 64
+    bits, up = bf16_problem(B, H, Lq, Lk, D, 101, "normal")
+    got = run(pkg, cuda, bits)
+    assert pkg.last_path() == "tc_fused"
+    assert float(np.abs(got - ol.attention(*up)).max()) <= 8e-3
