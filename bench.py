@@ -365,7 +365,7 @@ def torch_sdpa_arm(args):
     import torch
     import torch.nn.functional as F
     dev = torch.device("cuda:0")
-    names = [args.config] if args.config != "cfg5" or args.no_extras else ["cfg1", "cfg2a", "cfg2b", "cfg2c", "cfg2d", "cfg3", "cfg4", "cfg5"]
+    names = [args.config] if args.config != "cfg5" or args.no_extras else ["cfg1", "cfg2a", "cfg2b", "cfg2c", "cfg2d", "cfg3", "cfg4", "narrow128", "narrow64", "cfg5"]
     rows = []
     for cfg in names:
         dt, pe, B, H, Lq, Lk, D, dist, _ = CONFIGS[cfg]
