@@ -225,7 +225,7 @@ static std::atomic<unsigned> g_test_wait_extra{0}, g_test_spin_limit{0};
 static std::atomic<unsigned> g_spin_limit{1u << 21};
 static std::atomic<long long> g_score_scratch_mb{2048};
 
-static unsigned spin_limit_from_env() {
+static unsigned current_spin_limit() {
     if (unsigned t = g_test_spin_limit.load()) return t;
     return g_spin_limit.load();
 }
@@ -243,7 +243,7 @@ static int run_splitd(DeviceCtx &c, const b200attn_args &a, int rd, float base, 
     p.cos_cache = a.cos_cache; p.sin_cache = a.sin_cache;
     p.err = c.err_dev;
     p.err_sys = c.err_host_dev;
-    p.spin_limit = spin_limit_from_env();
+    p.spin_limit = current_spin_limit();
     p.wait_extra = g_test_wait_extra.load();
     const bool aligned16 = ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V) & 15) == 0);
     p.use_tma = (sizeof(T) == 4 && a.pe == B200ATTN_PE_NONE && D % 4 == 0 && aligned16) ? 1 : 0;
@@ -467,7 +467,7 @@ static int run_sdtc(DeviceCtx &c, const b200attn_args &a, cudaStream_t st, bool 
     p.O = (float *)a.out;
     p.S = c.sdtc_S; p.counters = c.sdtc_cnt; p.gen = c.sdtc_gen;
     p.err = c.err_dev; p.err_sys = c.err_host_dev;
-    p.spin_limit = spin_limit_from_env();
+    p.spin_limit = current_spin_limit();
     p.wait_extra = g_test_wait_extra.load();
 #ifdef B200ATTN_DEVTOOLS
     p.dbg = g_sdtc_dbg;
@@ -584,13 +584,13 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
     const bool wide_ok = tc_ok && tcw_supported(*a, rd), pair_ok = tc_ok && tc_bf16_supported(*a, rd);
     const bool use_pair = pair_ok && (!wide_ok || (a->flags & B200ATTN_FLAG_PREFER_ONE_KERNEL));
     if (use_pair) {
-        rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, current_spin_limit(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
     // few queries against many keys (decode, cross-attention): key splits on the tensor cores
     if (!done && tc_ok && dec_supported(*a, rd)) {
-        rc = dec_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        rc = dec_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, current_spin_limit(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_decode"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
@@ -611,7 +611,7 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
         const b200attn_args *use = a;
         rc = B200ATTN_OK;
         if (a->pe != B200ATTN_PE_NONE) { rc = encode_copies(&enc); use = &enc; }
-        if (rc == B200ATTN_OK) rc = fa_run(*use, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+        if (rc == B200ATTN_OK) rc = fa_run(*use, c->err_dev, c->err_host_dev, c->sm_count, current_spin_limit(), st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_fused"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
     }
@@ -621,19 +621,19 @@ static int forward_device(const b200attn_args *a, bool independent_of_prev = fal
         if (tcw_supported(plain, plain.head_d)) {
             rc = encode_copies(&enc);
             if (rc == B200ATTN_OK)
-                rc = tcw_run(enc, enc.head_d, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(),
+                rc = tcw_run(enc, enc.head_d, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, current_spin_limit(),
                              (size_t)g_score_scratch_mb.load() << 20, st, &g_launches);
             if (rc == B200ATTN_OK) { t_last_path = "tc_wide"; done = true; }
             else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
         }
     }
     if (!done && wide_ok) {
-        rc = tcw_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(),
+        rc = tcw_run(*a, rd, base, c->tcw, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, current_spin_limit(),
                      (size_t)g_score_scratch_mb.load() << 20, st, &g_launches);
         if (rc == B200ATTN_OK) { t_last_path = "tc_wide"; done = true; }
         else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
         else if (pair_ok && !use_pair) {   // no room for the score scratch: the one-kernel pipeline needs none
-            rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), st, &g_launches);
+            rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, current_spin_limit(), st, &g_launches);
             if (rc == B200ATTN_OK) { t_last_path = "tc_bf16"; done = true; }
             else if (rc != -1) return fail(rc, "%s", tc_bf16_error());
         }
@@ -744,7 +744,7 @@ int b200attn_debug_tc_scores(const b200attn_args *a, float *scores_dev) {
     if (rc) return rc;
     if (!tc_bf16_supported(*a, rd)) return fail(B200ATTN_ERR_INVALID_ARG, "shape not taken by the tensor-core kernel");
     std::lock_guard<std::mutex> lk(c->mu);
-    rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, spin_limit_from_env(), (cudaStream_t)a->stream, &g_launches, scores_dev);
+    rc = tc_bf16_run(*a, rd, base, c->tc_tables, c->err_dev, c->err_host_dev, c->sm_count, current_spin_limit(), (cudaStream_t)a->stream, &g_launches, scores_dev);
     if (rc) return fail(rc, "%s", tc_bf16_error());
     return check_kernel_errors(*c, (cudaStream_t)a->stream, true);
 }
