@@ -187,6 +187,30 @@ def narrow_sweep(pkg, torch, dev, pk):
     return out
 
 
+def bf16_sweep(pkg, torch, dev, pk, skip):
+    """The other bf16 benchmark configurations (cfg 3: no encoding; cfg 4: rotate-half RoPE, head_d 1024) and the
+    decode regime, one short measurement each, so that a default run reports them all."""
+    out = []
+    for cfg in ("cfg3", "cfg4", "decode"):
+        if cfg == skip:
+            continue
+        dt, pe_name, B, H, Lq, Lk, D, _, bound = CONFIGS[cfg]
+        sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(2)]
+        t = time_steps(pkg, torch, sets, PE[pe_name], 20, 5)
+        row = {"config": cfg, "shape": [B, H, Lq, Lk, D], "pe": pe_name, "path": pkg.last_path(), "ms": round(t, 4)}
+        if bound == "tensor":
+            row["tflops"] = round(flops_of(cfg) / t / 1e9, 1)
+            row["frac_of_sustained_bf16_peak"] = round(flops_of(cfg) / t / 1e9 / pk["bf16_tflops_sustained"], 4)
+        else:
+            row["gbs_algorithmic"] = round(bytes_of(cfg) / t / 1e6, 1)
+            row["frac_of_hbm_peak"] = round(bytes_of(cfg) / t / 1e6 / pk["hbm_gbs"], 4)
+        out.append(row)
+        del sets
+        pkg.lib().b200attn_release_workspace()
+        torch.cuda.empty_cache()
+    return out
+
+
 def cpu_full(cfg, threads):
     """The reference's attention_cpu on the WHOLE problem of an fp32 configuration: with one thread exactly
     as written, or with the (b,h) slices fanned over `threads` host threads.  Returns seconds."""
@@ -603,6 +627,7 @@ def main():
         torch.cuda.empty_cache()
 
     if rank == 0 and world == 1 and not args.no_extras:
+        line["bf16_configs"] = bf16_sweep(pkg, torch, dev, pk, cfg)
         line["narrow_heads"] = narrow_sweep(pkg, torch, dev, pk)
         line["fp32_configs"] = fp32_sweep(pkg, torch, dev, pk)
         line["cpu_baseline_fp32"] = "per configuration in fp32_configs[].cpu_baseline: the reference's attention_cpu on the whole problem"
