@@ -28,7 +28,7 @@
 // any transform.
 //
 // Shapes taken here: bf16 (fp16 without an encoding), head_d % 64 == 0 (with an encoding: % 128; rotate-half:
-// rotary_dim == head_d), any len_q, len_k <= 8192 (not both <= 64).  Lengths that are not multiples of the
+// rotary_dim == head_d), any len_q, len_k <= 65536 (not both <= 64).  Lengths that are not multiples of the
 // tiles: the operand tiles reach into the next head's rows (or read zeros behind the last head), whose
 // scores land in rows and columns of S that nobody uses - S keeps whole 128-blocks per head -; the
 // columns of keys that do not exist are written as -inf, V rows that do not exist read as zero (the head is a
@@ -764,23 +764,37 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
         // ---- softmax warps: warp w owns rows [8w, 8w+8) of every key block.  Eight lanes cover one
         // 128-byte row of a 64-key half (conflict-free 16-byte accesses), so a thread works on rows
         // 8w + lane/8 and 8w + 4 + lane/8, in both halves: four 16-byte pieces per block.  The offset
-        // (tile maximum - row maximum) of row 8w + k for key tile j is kept in lane j of offs[k]. ----
+        // (tile maximum - row maximum) of row 8w + k for key tile j is kept in lane j % 32 of offs[k], for the 32
+        // key tiles (8192 keys) the unit is working through; lane k of `tot` keeps the row maximum itself. ----
         const int w = warp - 2, rl = lane >> 3;
         int ui = 0;
         long long tg = 0;
         TWS_DECL;
-        // lane j keeps (tile maximum - row maximum) of key tile j for each of the warp's eight rows
-        auto load_stats = [&](long long g0, float (&oo)[8]) {
+        // lane j keeps (tile maximum - row maximum) of key tile j < 32 for each of the warp's eight rows
+        auto load_stats = [&](long long g0, float (&oo)[8], float &tt) {
+            tt = 0.0f;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
                 const float m = lane < p.nkt ? __ldg(p.rowmax + (g0 + k) * p.nkt + lane) : -INFINITY;
-                oo[k] = m - warp_max(m);
+                float mm = m;
+                for (int j = lane + 32; j < p.nkt; j += 32) mm = fmaxf(mm, __ldg(p.rowmax + (g0 + k) * p.nkt + j));   // more than 8192 keys
+                mm = warp_max(mm);
+                oo[k] = m - mm;
+                if (lane == k) tt = mm;
+            }
+        };
+        // the same for the next 32 key tiles, from tile kt0 on
+        auto next_stats = [&](long long g0, int kt0, float (&oo)[8], float tt) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float m = kt0 + lane < p.nkt ? __ldg(p.rowmax + (g0 + k) * p.nkt + kt0 + lane) : -INFINITY;
+                oo[k] = m - __shfl_sync(0xffffffffu, tt, k);
             }
         };
         auto grow0_of = [&](long long unit) {   // row of S and of the maxima: heads are nqt * 128 rows apart there
             return (unit / p.ndp) * (long long)TW_BM + 8 * w;
         };
-        float offs[8], offsn[8];
+        float offs[8], offsn[8], tot = 0.0f, totn = 0.0f;
         for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x, ++ui) {
             const int dp = (int)(unit % p.ndp);
             const long long rest = unit / p.ndp;
@@ -788,15 +802,16 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
             const long long bh = rest / p.nqt;
             const long long grow0 = rest * (long long)TW_BM + 8 * w;
             // (the statistics of the unit were loaded while the previous unit was finishing)
-            if (ui == 0) load_stats(grow0, offs);
+            if (ui == 0) load_stats(grow0, offs, tot);
             float lA = 0.0f, lB = 0.0f, offA = 0.0f, offB = 0.0f;
             for (int t = 0; t < nblk; ++t, ++tg) {
                 const int pb = (int)(tg % TP_NP);
                 if ((t & 1) == 0) {   // a new 256-key tile: fetch this thread's two offsets
                     const int kt = t >> 1;
+                    if (kt != 0 && (kt & 31) == 0) next_stats(grow0, kt, offs, tot);
                     float v[8];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) v[k] = __shfl_sync(0xffffffffu, offs[k], kt);
+                    for (int k = 0; k < 8; ++k) v[k] = __shfl_sync(0xffffffffu, offs[k], kt & 31);
                     offA = rl == 0 ? v[0] : rl == 1 ? v[1] : rl == 2 ? v[2] : v[3];
                     offB = rl == 0 ? v[4] : rl == 1 ? v[5] : rl == 2 ? v[6] : v[7];
                 }
@@ -831,7 +846,7 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
             }
             if (failed) break;
             const bool have_next = unit + gridDim.x < p.n_units;
-            if (have_next) load_stats(grow0_of(unit + gridDim.x), offsn);   // lands while this unit drains
+            if (have_next) load_stats(grow0_of(unit + gridDim.x), offsn, totn);   // lands while this unit drains
 #pragma unroll
             for (int o = 4; o > 0; o >>= 1) {
                 lA += __shfl_xor_sync(0xffffffffu, lA, o);
@@ -875,6 +890,7 @@ tcw_pv_kernel(const __grid_constant__ CUtensorMap tmV, const __grid_constant__ C
             if (have_next) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) offs[k] = offsn[k];
+                tot = totn;
             }
         }
         TWP_FLUSH(16, threadIdx.x == 64);
@@ -1000,7 +1016,7 @@ inline bool tcw_supported(const b200attn_args &a, int rd) {
     if (a.dtype != B200ATTN_BF16 && !(a.dtype == B200ATTN_F16 && a.pe == B200ATTN_PE_NONE)) return false;   // the encodings are bf16 arithmetic
     if (a.head_d % 64 != 0 || a.head_d < 64 || a.head_d > 8192) return false;
     if (a.len_q <= 64 && a.len_k <= 64) return false;   // short sequences: the split-head_d kernels
-    if (a.len_k > 32 * TW_BN) return false;   // the offsets of a row's key tiles live one per lane
+    if (a.len_k > 65536) return false;
     if (a.cos_cache != nullptr && !pe_is_rope(a.pe)) return false;
     if (pe_pairs_halves(a.pe)) { if (a.head_d % 128 != 0 || rd != a.head_d) return false; }
     else if (a.pe != B200ATTN_PE_NONE) { if (a.head_d % 128 != 0 || (a.pe != B200ATTN_PE_SINUSOIDAL && rd % 8 != 0)) return false; }

@@ -172,7 +172,7 @@ def test_fused_path_fp16_with_an_encoding(pkg, cuda):
 
 
 def test_fused_path_very_long_keys(pkg, cuda):
-    """No limit on len_k here (the two-kernel path stops at 8192 keys): 157 key tiles, the last with 32 keys."""
+    """157 key tiles, the last with 32 keys (the kernel has no limit on len_k)."""
     B, H, Lq, Lk, D = 1, 1, 128, 20000, 64
     bits, up = bf16_problem(B, H, Lq, Lk, D, 101, "normal")
     got = run(pkg, cuda, bits)

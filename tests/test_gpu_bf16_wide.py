@@ -174,3 +174,16 @@ def test_ragged_lengths_leave_the_memory_behind_the_output_alone(pkg, cuda):
     assert pkg.last_path() == "tc_wide"
     assert bool((big[B * H * Lq * D:] == 7.0).all())
     assert float(np.abs(bf16_from_dev(out) - ol.attention(*up)).max()) <= 8e-3
+
+
+@pytest.mark.parametrize("case", [((1, 1, 128, 10000, 256), ol.PE_NONE), ((1, 2, 200, 9000, 256), ol.PE_ROPE_HALF), ((1, 1, 130, 17000, 512), ol.PE_SINUSOIDAL)],
+                         ids=lambda c: "x".join(map(str, c[0])) + f"-pe{c[1]}")
+def test_more_than_8192_keys(pkg, cuda, case):
+    """The per-lane store of tile offsets holds 32 key tiles; longer sequences reload it every 8192 keys."""
+    (B, H, Lq, Lk, D), pe = case
+    bits, up = bf16_problem(B, H, Lq, Lk, D, 85, "normal")
+    want = ol.attention(*up, pe=pe)
+    got = run(pkg, cuda, bits, pe=pe)
+    assert pkg.last_path() == "tc_wide", pkg.last_path()
+    err = float(np.abs(got - want).max())
+    assert err <= (1.9e-2 if pe == ol.PE_SINUSOIDAL else 8e-3), (case, err)
