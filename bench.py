@@ -211,6 +211,35 @@ def bf16_sweep(pkg, torch, dev, pk, skip):
     return out
 
 
+def bind_to_gpu_numa_node(torch, dev_index):
+    """Pins this process to the CPUs of the NUMA node its GPU hangs off (read from sysfs), so that the pinned host
+    buffers allocated afterwards are node-local (first touch).  Returns what it found; does nothing where the
+    information is missing or the box has one node."""
+    info = {"gpu_numa_node": None, "numa_nodes": None, "bound": False}
+    try:
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        info["numa_nodes"] = len(nodes)
+        props = torch.cuda.get_device_properties(dev_index)
+        bus = "%04x:%02x:%02x.0" % (getattr(props, "pci_domain_id", 0), props.pci_bus_id, props.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        info["gpu_numa_node"] = node
+        if node < 0 or len(nodes) < 2:
+            return info
+        cpus = set()
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            info["bound"] = True
+    except (OSError, ValueError, AttributeError):
+        pass
+    return info
+
+
 def cpu_full(cfg, threads):
     """The reference's attention_cpu on the WHOLE problem of an fp32 configuration: with one thread exactly
     as written, or with the (b,h) slices fanned over `threads` host threads.  Returns seconds."""
@@ -556,7 +585,10 @@ def main():
 
     # ---- host -> device copy rate of this rank's PCIe link (pinned memory, one cudaMemcpyAsync per copy) ----
     h2d_gbs = None
+    numa = None
+    affinity0 = os.sched_getaffinity(0) if hasattr(os, "sched_getaffinity") else None
     if not args.no_extras:
+        numa = bind_to_gpu_numa_node(torch, dev.index or 0)   # the host buffers below are allocated node-local
         try:
             nb = 1 << 30
             hsrc = torch.empty(nb, dtype=torch.uint8).pin_memory()
@@ -609,7 +641,7 @@ def main():
             h2d_b, d2h_b = esz * B * H * D * (Lq + 2 * Lk), esz * B * H * D * Lq
             line["e2e"] = {"value": fl * world / (float(t[0].item()) * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": float(t[0].item()),
                            "steps": e2e_steps, "h2d_bytes_per_step": h2d_b, "d2h_bytes_per_step": d2h_b,
-                           "api": "b200attn_forward_host (pinned host buffers)"}
+                           "api": "b200attn_forward_host (pinned host buffers)", "numa": numa}
             tg = torch.tensor([h2d_gbs if h2d_gbs else 0.0], dtype=torch.float64, device=dev)
             if dist is not None:
                 dist.all_reduce(tg, op=dist.ReduceOp.MIN)
@@ -625,6 +657,8 @@ def main():
         del hq, hk, hv, ho
         pkg.lib().b200attn_release_workspace()
         torch.cuda.empty_cache()
+    if affinity0 is not None and numa and numa.get("bound"):
+        os.sched_setaffinity(0, affinity0)   # the CPU baseline below uses every host core again
 
     if rank == 0 and world == 1 and not args.no_extras:
         line["bf16_configs"] = bf16_sweep(pkg, torch, dev, pk, cfg)
