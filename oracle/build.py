@@ -16,7 +16,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("B200ATTN_REFERENCE_ROOT", "/root/reference")
+# the reference project's tree: B200ATTN_REFERENCE_ROOT, else a directory `reference` beside this repository
+REF_ROOT = os.environ.get("B200ATTN_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 ORACLE_SO = os.path.join(HERE, "_build", "liboracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libref_attn.so")
 

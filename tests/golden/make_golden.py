@@ -25,7 +25,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 import oracle_lib as ol  # noqa: E402
 
-REF = os.environ.get("B200ATTN_REFERENCE_ROOT", "/root/reference")
+# the reference project's tree: B200ATTN_REFERENCE_ROOT, else a directory `reference` beside this repository
+REF = os.environ.get("B200ATTN_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
 
 SDPA_SETS = [  # scripts/generate_pytorch_reference.py:87-94
     (1, 1, 4, 8, "tiny"), (1, 2, 8, 16, "small"), (1, 4, 64, 512, "hdim512"),
