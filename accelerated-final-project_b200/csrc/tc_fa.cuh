@@ -271,6 +271,18 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                     r0[16 + i] = pack_16x2(e0, e1, F16);
                 }
                 tmem_st32(ts, r0);
+                // (the second half of the row is fetched again rather than kept: 128 scores and the packing do not
+                // fit the registers a thread of this block may use)
+                tmem_ld32(ts + 64, r2);
+                tmem_ld32(ts + 96, r3);
+                tmem_ld_wait();
+                if (valid < FA_BN) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (64 + i >= valid) r2[i] = 0xff800000u;
+                        if (96 + i >= valid) r3[i] = 0xff800000u;
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const float e0 = fast_exp2(fmaf(__uint_as_float(r2[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r2[2 * i + 1]), sl2, -m_ref));
