@@ -335,12 +335,291 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     tc_fence_after();
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// head_d 256: the same idea with ONE query tile of 128 rows per unit.  The output accumulator [128 x 256] fp32 takes
+// half of the tensor memory; the other half holds two score buffers, so that S_j+1 = Q K_j+1^T is computed while the
+// softmax warps work on S_j:   S_0 | S_1, O += P_0 V_0, S_2, O += P_1 V_1, S_3, ...   K and V pass through the ring
+// in halves of 32 KB (K: 128 keys x 128 of the 256 columns; V: 64 keys x 256 columns) in exactly the order the MMA
+// thread consumes them.  One softmax warpgroup (a thread per row) serves both buffers: its row statistics are one
+// stream, and with 192 threads a thread may hold its 128 scores in registers.
+constexpr int FB_THREADS = 192;     // warp 0: TMA, warp 1: MMA, warps 2-5: softmax and epilogue
+constexpr int FB_D = 256;
+constexpr int FB_STAGE = 32768;
+
+template <bool F16>
+__global__ void __launch_bounds__(FB_THREADS, 1)
+fa256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+    extern __shared__ unsigned char fa_smem_raw[];
+    __shared__ FaBars bars;
+    __shared__ uint32_t tmem_slot;
+    const uint32_t raw_addr = smem_u32(fa_smem_raw);
+    unsigned char *smem = fa_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkt = p.nkt, nst = p.nst;
+    unsigned char *q_smem = smem;                       // [4 groups][128 rows][128 B]
+    unsigned char *ring = smem + 2 * FB_STAGE;
+    const uint32_t lim = p.spin_limit;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < FA_MAX_STAGES; ++i) { mbar_init(&bars.kv_full[i], 1); mbar_init(&bars.kv_empty[i], 1); }
+        mbar_init(&bars.q_full, 1);
+        mbar_init(&bars.q_empty, 1);
+        for (int t = 0; t < 2; ++t) { mbar_init(&bars.s_full[t], 1); mbar_init(&bars.p_full[t], 4); mbar_init(&bars.o_done[t], 1); mbar_init(&bars.o_empty[t], 4); }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;        // score buffer b: columns [128 b, 128 b + 128); O: [256, 512)
+    bool failed = false;
+    const bool skip = (*reinterpret_cast<volatile unsigned *>(p.err) != 0);
+
+    if (skip) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        if (lane == 0) {
+            long long it = 0;
+            int ui = 0;
+            auto load_k = [&](int bh, int j, bool &ok) {   // the two column halves of K tile j
+                for (int h = 0; h < 2 && ok; ++h, ++it) {
+                    const int s = (int)(it % nst);
+                    ok = mbar_wait(&bars.kv_empty[s], (uint32_t)((it / nst) & 1) ^ 1u, lim);
+                    if (!ok) break;
+                    mbar_expect_tx(&bars.kv_full[s], FB_STAGE);
+                    tma_load_4d(ring + (size_t)s * FB_STAGE, &tmK, 0, j * FA_BN, 2 * h, bh, &bars.kv_full[s]);
+                }
+            };
+            auto load_v = [&](int bh, int j, bool &ok) {   // the two key halves of V tile j
+                for (int h = 0; h < 2 && ok; ++h, ++it) {
+                    const int s = (int)(it % nst);
+                    ok = mbar_wait(&bars.kv_empty[s], (uint32_t)((it / nst) & 1) ^ 1u, lim);
+                    if (!ok) break;
+                    mbar_expect_tx(&bars.kv_full[s], FB_STAGE);
+                    tma_load_4d(ring + (size_t)s * FB_STAGE, &tmV, 0, j * FA_BN + 64 * h, 0, bh, &bars.kv_full[s]);
+                }
+            };
+            bool ok = true;
+            for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
+                const int bh = (int)(unit / p.nqp), qt = (int)(unit % p.nqp);
+                ok = mbar_wait(&bars.q_empty, (uint32_t)(ui & 1) ^ 1u, lim);
+                if (!ok) break;
+                mbar_expect_tx(&bars.q_full, 2 * FB_STAGE);
+                tma_load_4d(q_smem, &tmQ, 0, qt * FA_BM, 0, bh, &bars.q_full);
+                load_k(bh, 0, ok);                        // the order of the MMA thread: K_0 | K_1, V_0, K_2, V_1, ...
+                for (int j = 0; j < nkt && ok; ++j) {
+                    if (j + 1 < nkt) load_k(bh, j + 1, ok);
+                    if (ok) load_v(bh, j, ok);
+                }
+            }
+            if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 7)); failed = true; }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t id_qk = umma_idesc_16(FA_BM, FA_BN, 0, 0, F16 ? 1 : 0), id_pv = umma_idesc_16(FA_BM, FB_D, 0, 1, F16 ? 1 : 0);
+            long long it = 0, gt = 0;   // ring position; tiles issued so far (score buffer = tile & 1)
+            int ui = 0;
+            bool ok = true;
+            const uint32_t qa = smem_u32(q_smem);
+            auto qk = [&](long long g) {   // S_(g & 1) = Q K^T over the two column halves of the K tile
+                const int b = (int)(g & 1);
+                for (int h = 0; h < 2 && ok; ++h, ++it) {
+                    const int s = (int)(it % nst);
+                    ok = mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t ka = smem_u32(ring + (size_t)s * FB_STAGE);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        umma_bf16(tmem + b * 128, umma_desc_k_sw128(qa + (2 * h + (k >> 2)) * (FA_BM * 128)) + 2 * (k & 3),
+                                  umma_desc_k_sw128(ka + (k >> 2) * (FA_BN * 128)) + 2 * (k & 3), id_qk, (h | k) != 0);
+                    umma_commit(&bars.kv_empty[s]);
+                }
+                umma_commit(&bars.s_full[b]);
+            };
+            auto pv = [&](long long g, bool acc) {   // O (+)= P V over the two key halves of the V tile; P in the first 64 columns of the score buffer
+                const int b = (int)(g & 1);
+                for (int h = 0; h < 2 && ok; ++h, ++it) {
+                    const int s = (int)(it % nst);
+                    ok = mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t va = smem_u32(ring + (size_t)s * FB_STAGE);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_16_ts(tmem + 256, tmem + b * 128 + (4 * h + kk) * 8, umma_desc_mn_sw128(va + kk * 2048, 64 * 128), id_pv, (acc || h != 0 || kk != 0) ? 1u : 0u);
+                    umma_commit(&bars.kv_empty[s]);
+                }
+                umma_commit(&bars.o_done[b]);
+            };
+            for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
+                ok = mbar_wait(&bars.q_full, (uint32_t)(ui & 1), lim);
+                if (!ok) break;
+                tc_fence_after();
+                qk(gt);
+                for (int j = 0; j < nkt && ok; ++j) {
+                    if (j + 1 < nkt) qk(gt + j + 1);
+                    else umma_commit(&bars.q_empty);   // the unit's last score MMA has been issued
+                    if (!ok) break;
+                    if (j == 0) ok = mbar_wait(&bars.o_empty[0], (uint32_t)(ui & 1) ^ 1u, lim);   // the epilogue of the previous unit has read O
+                    const long long g = gt + j;
+                    ok = ok && mbar_wait(&bars.p_full[g & 1], (uint32_t)((g >> 1) & 1), lim);
+                    if (!ok) break;
+                    tc_fence_after();
+                    pv(g, j > 0);
+                }
+                gt += nkt;
+            }
+            if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 9)); failed = true; }
+        }
+    } else {
+        // ---- softmax and epilogue; thread = query row (tensor-memory lane) ----
+        const int q = warp & 3;
+        const int row = 32 * q + lane;
+        const uint32_t tl = tmem + ((uint32_t)(32 * q) << 16);
+        const uint32_t to = tl + 256u;
+        const float sl2 = p.scale_log2;
+        long long gt = 0;
+        float m_ref = 0.0f, l = 0.0f;
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        // The P V product of tile g arrives on o_done[g & 1].  The score MMA of tile g + 1 is issued before the P V MMA
+        // of tile g, so these warps can be a tile ahead of the products; a wait by parity can only tell the current
+        // phase of a barrier from the one before it, hence two barriers, each followed phase by phase: at the start
+        // of tile g the product of tile g - 2 is certainly done (the MMAs complete in the order they were issued) and
+        // is ticked off, which keeps every later wait within one phase of its barrier.
+        long long seen[2] = {0, 0};   // phases of o_done[b] seen complete
+        auto see_pv_done = [&](long long g) {   // true once the P V product of tile g (counted over the units) is done
+            const int b = (int)(g & 1);
+            while (seen[b] <= (g >> 1)) {
+                if (!mbar_wait(&bars.o_done[b], (uint32_t)(seen[b] & 1), lim)) return false;
+                ++seen[b];
+            }
+            return true;
+        };
+        for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
+            const int bh = (int)(unit / p.nqp), qt = (int)(unit % p.nqp);
+            for (int j = 0; j < nkt; ++j, ++gt) {
+                const uint32_t ts = tl + (uint32_t)(gt & 1) * 128u;
+                FA_FAIL_AT(2, !mbar_wait(&bars.s_full[gt & 1], (uint32_t)((gt >> 1) & 1), lim));
+                tc_fence_after();
+                const int valid = min(FA_BN, p.Lk - j * FA_BN);
+                if (gt >= 2) FA_FAIL_AT(5, !see_pv_done(gt - 2));   // (done long ago: ticked off)
+                tmem_ld32(ts, r0);
+                tmem_ld32(ts + 32, r1);
+                tmem_ld32(ts + 64, r2);
+                tmem_ld32(ts + 96, r3);
+                tmem_ld_wait();
+                if (valid < FA_BN) {   // (the same for every thread) keys that do not exist: exp2(-inf) = 0
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (i >= valid) r0[i] = 0xff800000u;
+                        if (32 + i >= valid) r1[i] = 0xff800000u;
+                        if (64 + i >= valid) r2[i] = 0xff800000u;
+                        if (96 + i >= valid) r3[i] = 0xff800000u;
+                    }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    mx0 = fmaxf(mx0, __uint_as_float(r0[i])); mx1 = fmaxf(mx1, __uint_as_float(r1[i]));
+                    mx2 = fmaxf(mx2, __uint_as_float(r2[i])); mx3 = fmaxf(mx3, __uint_as_float(r3[i]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+                if (j == 0) {
+                    m_ref = mx;
+                    l = 0.0f;
+                } else {
+                    const bool need = mx > m_ref + FA_RESCALE_LOG2;
+                    if (__any_sync(0xffffffffu, need)) {
+                        FA_FAIL_AT(3, !see_pv_done(gt - 1));   // the previous P V is done
+                        tc_fence_after();
+                        const float m_new = need ? mx : m_ref;
+                        const float f = fast_exp2(m_ref - m_new);
+                        uint32_t w[32];
+                        for (int c = 0; c < FB_D / 32; ++c) {
+                            tmem_ld32(to + 32 * c, w);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * f);
+                            tmem_st32(to + 32 * c, w);
+                        }
+                        tmem_st_wait();
+                        l *= f;
+                        m_ref = m_new;
+                    }
+                }
+                float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(r0[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 1]), sl2, -m_ref));
+                    sum0 += e0; sum1 += e1;
+                    r0[i] = pack_16x2(e0, e1, F16);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(r1[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), sl2, -m_ref));
+                    sum0 += e0; sum1 += e1;
+                    r0[16 + i] = pack_16x2(e0, e1, F16);
+                }
+                tmem_st32(ts, r0);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(r2[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r2[2 * i + 1]), sl2, -m_ref));
+                    sum0 += e0; sum1 += e1;
+                    r2[i] = pack_16x2(e0, e1, F16);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(r3[2 * i]), sl2, -m_ref)), e1 = fast_exp2(fmaf(__uint_as_float(r3[2 * i + 1]), sl2, -m_ref));
+                    sum0 += e0; sum1 += e1;
+                    r2[16 + i] = pack_16x2(e0, e1, F16);
+                }
+                tmem_st32(ts + 32, r2);
+                l += sum0 + sum1;
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.p_full[gt & 1]);
+            }
+            if (failed) break;
+            // ---- epilogue of the unit: O / row sum -> 16 bit -> global ----
+            if (gt >= 2) FA_FAIL_AT(4, !see_pv_done(gt - 2));
+            FA_FAIL_AT(4, !see_pv_done(gt - 1));
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const int qrow0 = qt * FA_BM;
+            __nv_bfloat16 *orow = p.O + ((long long)bh * p.Lq + qrow0 + row) * (long long)FB_D;
+            unsigned char *row0 = reinterpret_cast<unsigned char *>(orow - (long long)(lane & 3) * FB_D);
+            for (int cp = 0; cp < FB_D / 64; ++cp) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    tmem_ld32(to + cp * 64 + hh * 32, r0);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) r1[16 * hh + i] = pack_16x2(__uint_as_float(r0[2 * i]) * inv, __uint_as_float(r0[2 * i + 1]) * inv, F16);
+                }
+                store_rows_128B_transposed_if(row0 + cp * 128, (size_t)FB_D * 2, r1, lane, p.Lq - (qrow0 + (row & ~3)));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.o_empty[0]);
+        }
+    }
+
+    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
 #undef FA_FAIL_AT
 
 // ---- host side ------------------------------------------------------------------------------------
 inline bool fa_supported(const b200attn_args &a) {
     if (a.dtype != B200ATTN_BF16 && a.dtype != B200ATTN_F16) return false;
-    if (a.head_d != 64 && a.head_d != 128) return false;
+    if (a.head_d != 64 && a.head_d != 128 && a.head_d != 256) return false;
     if (a.len_q <= 64) return false;   // few queries: the key-split kernels, or the split-head_d kernels
     if ((((uintptr_t)a.Q | (uintptr_t)a.K | (uintptr_t)a.V) & 15) != 0 || ((uintptr_t)a.out & 31) != 0) return false;
     const long long BH = (long long)a.batch_sz * a.num_heads;
@@ -366,10 +645,42 @@ inline int fa_run(const b200attn_args &a, unsigned *err_dev, unsigned *err_sys, 
             cudaGetDeviceProperties(&prop, dev);
             const bool ok = cudaFuncGetAttributes(&fa, fa_kernel<false>) == cudaSuccess &&
                             cudaFuncSetAttribute(fa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess &&
-                            cudaFuncSetAttribute(fa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
+                            cudaFuncSetAttribute(fa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess &&
+                            cudaFuncSetAttribute(fa256_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess &&
+                            cudaFuncSetAttribute(fa256_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
             if (!ok) { (void)cudaGetLastError(); snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncSetAttribute(max dynamic shared memory) failed"); return B200ATTN_ERR_CUDA; }
             smem_max[dev & 63] = prop.sharedMemPerBlockOptin - fa.sharedSizeBytes;
         }
+    }
+    if (D == FB_D) {
+        // one query tile per unit, K and V through the ring in halves
+        int nst = (int)((smem_max[dev & 63] - 1024 - 2 * FB_STAGE) / FB_STAGE);
+        if (nst > FA_MAX_STAGES) nst = FA_MAX_STAGES;
+        if (nst < 5) return -1;
+        CUtensorMap tmQ, tmK, tmV;
+        if (!make_tmap_grouped_heads(&tmQ, a.Q, BH, Lq, D, FA_BM, 4) || !make_tmap_grouped_heads(&tmK, a.K, BH, Lk, D, FA_BN, 2) ||
+            !make_tmap_grouped_heads(&tmV, a.V, BH, Lk, D, 64, 4)) {
+            snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
+            return -1;
+        }
+        FaParams p{};
+        p.Lq = Lq; p.Lk = Lk; p.D = D;
+        p.nqp = (Lq + FA_BM - 1) / FA_BM;   // query tiles per head
+        p.nkt = (Lk + FA_BN - 1) / FA_BN;
+        p.nst = nst;
+        p.n_units = BH * p.nqp;
+        p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+        p.f16 = a.dtype == B200ATTN_F16 ? 1 : 0;
+        p.O = (__nv_bfloat16 *)a.out;
+        p.err = err_dev; p.err_sys = err_sys; p.spin_limit = spin_limit;
+        const unsigned grid = (unsigned)(p.n_units < sm_count ? p.n_units : sm_count);
+        const size_t smem = (size_t)(2 + nst) * FB_STAGE + 1024;
+        if (p.f16) fa256_kernel<true><<<grid, FB_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
+        else fa256_kernel<false><<<grid, FB_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "fa256_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
+        launches->fetch_add(1);
+        return B200ATTN_OK;
     }
     const size_t tile = (size_t)FA_BN * D * 2;
     int nst = (int)((smem_max[dev & 63] - 1024 - 2 * tile) / tile);

@@ -92,7 +92,7 @@ def test_benchmark_bf16_configs_sampled(pkg, cuda, cfg):
     for prefer_pair in ((False, True) if D <= 512 else (False,)):
         out = pkg.forward(Q, K, V, pe=pe, flags=pkg.FLAG_PREFER_ONE_KERNEL if prefer_pair else 0)
         torch.cuda.synchronize()
-        fused = pe == ol.PE_NONE and D in (64, 128)   # narrow heads without an encoding: the one-kernel path
+        fused = D in (64, 128, 256)   # the one-kernel path (with an encoding: on encoded copies of Q and K)
         assert pkg.last_path() == ("tc_bf16" if prefer_pair else "tc_fused" if fused else "tc_wide")
         o = out.view(B * H, L, D)
         for h, want in zip(heads, wants):

@@ -1,4 +1,4 @@
-"""GPU parity of the one-kernel tensor-core path for narrow heads (head_d 64 or 128, bf16 / fp16, no encoding,
+"""GPU parity of the one-kernel tensor-core path for narrow heads (head_d 64, 128 or 256, bf16 / fp16,
 more than 64 queries): scores and probabilities stay in tensor memory, online softmax with a lazily rescaled
 accumulator.  Oracle: fp32 CPU attention on the 16-bit-rounded inputs; tolerance max-abs 2e-2 (bf16)."""
 import numpy as np
@@ -23,6 +23,16 @@ SHAPES = [
     (1, 1, 65, 4100, 128),      # 33 key tiles, the last with 4 keys
     (1, 2, 300, 40, 64),        # fewer keys than a tile
     (1, 1, 2048, 2048, 128),
+    # head_d 256: one query tile per unit, two score buffers
+    (1, 1, 128, 128, 256),
+    (1, 2, 256, 256, 256),      # two full key tiles: the epilogue may be a tile ahead of the last P V product
+    (1, 2, 256, 384, 256),
+    (1, 150, 128, 128, 256),    # more units than SMs
+    (2, 3, 200, 300, 256),
+    (1, 3, 700, 1000, 256),
+    (1, 1, 65, 4100, 256),
+    (1, 2, 300, 40, 256),
+    (1, 160, 256, 640, 256),    # several units per CTA with an odd number of key tiles: the score buffers swap roles from unit to unit
 ]
 
 
@@ -105,7 +115,7 @@ def test_fused_path_twice_in_a_row_same_result(pkg, cuda):
     assert np.array_equal(a, b)
 
 
-@pytest.mark.parametrize("shape", [(1, 2, 256, 384, 128), (2, 2, 200, 300, 64)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("shape", [(1, 2, 256, 384, 128), (2, 2, 200, 300, 64), (1, 2, 256, 384, 256)], ids=lambda s: "x".join(map(str, s)))
 def test_fused_path_fp16(pkg, cuda, shape):
     import torch
     B, H, Lq, Lk, D = shape
@@ -121,7 +131,7 @@ PES = [ol.PE_ROPE_INTERLEAVED, ol.PE_ROPE_HALF, ol.PE_SINUSOIDAL, ol.PE_ROPE_Q_O
 
 
 @pytest.mark.parametrize("pe", PES, ids=["rope_pairs", "rope_half", "sinusoidal", "rope_q_only", "rope_half_q_only"])
-@pytest.mark.parametrize("shape", [(1, 2, 256, 384, 128), (2, 2, 200, 300, 64), (1, 3, 129, 1000, 128)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("shape", [(1, 2, 256, 384, 128), (2, 2, 200, 300, 64), (1, 3, 129, 1000, 128), (1, 2, 200, 300, 256)], ids=lambda s: "x".join(map(str, s)))
 def test_fused_path_with_encodings(pkg, cuda, pe, shape):
     """With an encoding the narrow-head path works on encoded copies of Q and K (fp32 arithmetic, one rounding)."""
     B, H, Lq, Lk, D = shape

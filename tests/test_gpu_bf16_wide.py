@@ -38,7 +38,7 @@ def test_wide_path_against_oracle(pkg, cuda, pe, shape):
     B, H, Lq, Lk, D = shape
     bits, up = bf16_problem(B, H, Lq, Lk, D, 71, "normal")
     want = ol.attention(*up, pe=pe)
-    got = run(pkg, cuda, bits, pe=pe)
+    got = run(pkg, cuda, bits, pe=pe, flags=pkg.FLAG_TWO_KERNELS)   # (head_d 256 would otherwise take the one-kernel path)
     if D > 512 or pe == ol.PE_ROPE_HALF:
         assert pkg.last_path() == "tc_wide"
     err = float(np.abs(got - want).max())
@@ -183,7 +183,7 @@ def test_more_than_8192_keys(pkg, cuda, case):
     (B, H, Lq, Lk, D), pe = case
     bits, up = bf16_problem(B, H, Lq, Lk, D, 85, "normal")
     want = ol.attention(*up, pe=pe)
-    got = run(pkg, cuda, bits, pe=pe)
+    got = run(pkg, cuda, bits, pe=pe, flags=pkg.FLAG_TWO_KERNELS)
     assert pkg.last_path() == "tc_wide", pkg.last_path()
     err = float(np.abs(got - want).max())
     assert err <= (1.9e-2 if pe == ol.PE_SINUSOIDAL else 8e-3), (case, err)

@@ -42,7 +42,7 @@ def test_fp16_on_the_tensor_cores(pkg, cuda, shape):
     B, H, Lq, Lk, D = shape
     h, up = problem(B, H, Lq, Lk, D, 102, "normal")
     got = run(pkg, cuda, h)
-    assert pkg.last_path() == ("tc_fused" if D in (64, 128) else "tc_wide")
+    assert pkg.last_path() == ("tc_fused" if D in (64, 128, 256) else "tc_wide")
     err = float(np.abs(got - ol.attention(*up)).max())
     assert err <= TOL, (shape, err)
     # with an encoding: encoded fp16 copies of Q and K (fp32 arithmetic, one rounding), then the same kernels
@@ -54,7 +54,7 @@ def test_fp16_on_the_tensor_cores(pkg, cuda, shape):
             got = run(pkg, cuda, (h[0], kr, h[2]), pe=pe)
         else:
             got = run(pkg, cuda, h, pe=pe)
-        assert pkg.last_path() == ("tc_fused" if D in (64, 128) else "tc_wide")
+        assert pkg.last_path() == ("tc_fused" if D in (64, 128, 256) else "tc_wide")
         assert float(np.abs(got - want).max()) <= 4e-3, pe
 
 
