@@ -45,6 +45,7 @@ CONFIGS = {
     # narrow heads (what most transformer models use): the one-kernel path
     "narrow128": ("bf16", "none", 4, 16, 4096, 4096, 128, "normal", "tensor"),
     "narrow64": ("bf16", "none", 4, 16, 4096, 4096, 64, "normal", "tensor"),
+    "narrow256": ("bf16", "none", 4, 16, 4096, 4096, 256, "normal", "tensor"),
     # profiling-size variants of cfg4 and cfg5 (16 heads): small enough for a multi-pass ncu capture
     "cfg4p": ("bf16", "rope_half", 1, 16, 2048, 2048, 1024, "normal", "tensor"),
     "cfg5p": ("bf16", "sinusoidal", 1, 16, 4096, 4096, 512, "normal", "tensor"),
@@ -169,10 +170,10 @@ def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None, flags=0, kerne
 
 
 def narrow_sweep(pkg, torch, dev, pk):
-    """bf16 at the head widths most models use (64, 128), where the scores stay on the SM in one kernel: the default
+    """bf16 at the head widths most models use (64, 128, 256), where the scores stay on the SM in one kernel: the default
     path and, for comparison, the two-kernel path of the wide heads on the same inputs."""
     out = []
-    for cfg in ("narrow128", "narrow64"):
+    for cfg in ("narrow256", "narrow128", "narrow64"):
         _, _, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
         sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(2)]
         t = time_steps(pkg, torch, sets, 0, 20, 5)
@@ -421,7 +422,7 @@ def torch_sdpa_arm(args):
     import torch
     import torch.nn.functional as F
     dev = torch.device("cuda:0")
-    names = [args.config] if args.config != "cfg5" or args.no_extras else ["cfg1", "cfg2a", "cfg2b", "cfg2c", "cfg2d", "cfg3", "cfg4", "narrow128", "narrow64", "cfg5"]
+    names = [args.config] if args.config != "cfg5" or args.no_extras else ["cfg1", "cfg2a", "cfg2b", "cfg2c", "cfg2d", "cfg3", "cfg4", "narrow256", "narrow128", "narrow64", "cfg5"]
     rows = []
     for cfg in names:
         dt, pe, B, H, Lq, Lk, D, dist, _ = CONFIGS[cfg]

@@ -127,7 +127,7 @@ enum b200attn_flags {
     B200ATTN_FLAG_FORCE_TWO_PASS = 4, /* split-head_d path: two launches instead of one fused launch */
     B200ATTN_FLAG_PREFER_ONE_KERNEL = 8, /* bf16: where both tensor-core paths take the shape, run the one-kernel cluster pipeline */
     B200ATTN_FLAG_NO_OVERLAP = 16,    /* b200attn_forward_many: start this entry only after the previous one has completed */
-    B200ATTN_FLAG_TWO_KERNELS = 32    /* bf16 / fp16, head_d 64 or 128: run the two-kernel path where the one-kernel narrow-head path would run (the two are measured against each other that way) */
+    B200ATTN_FLAG_TWO_KERNELS = 32    /* bf16 / fp16, head_d 64, 128 or 256: run the two-kernel path where the one-kernel narrow-head path would run (the two are measured against each other that way) */
 };
 
 typedef struct b200attn_args {
@@ -184,7 +184,7 @@ const char *b200attn_last_error(void);
 /* Name of the kernel path the last successful b200attn_forward_ex on this thread used:
  * "splitd_tc" (fp32, short sequences, tensor cores with error-compensated tf32), "splitd_fused" and
  * "splitd_two_pass" (CUDA cores), "tc_wide" (bf16 on the tensor cores: score kernel, then P V kernel),
- * "tc_fused" (bf16 / fp16, head_d 64 or 128, more than 64 queries: one kernel, scores and probabilities in tensor
+ * "tc_fused" (bf16 / fp16, head_d 64, 128 or 256, more than 64 queries: one kernel, scores and probabilities in tensor
  * memory; an encoding is applied to copies of Q and K first), "tc_bf16" (bf16 on the tensor cores, one-kernel
  * cluster pipeline) or "tc_decode" (bf16, up to 64 queries against a long K/V: key splits on the tensor cores
  * plus a combine kernel). */
