@@ -614,9 +614,299 @@ fa256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     tc_fence_after();
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// head_d 64 / 128, second layout: P through SHARED memory.  In fa_kernel P lies over its own score tile, so the next
+// score MMAs of a query tile must wait for the P V product, and a softmax warpgroup waits for both: per key tile the
+// chain is softmax -> P V -> Q K^T -> softmax.  Here a softmax thread takes the whole score row into registers and
+// says so (s_read); the score MMAs of the next key tile start then, under the softmax of this one.  P (16 bit) goes
+// to a shared-memory tile of its own in the K-major 128-byte-swizzle layout, in two halves of 64 keys (p_half,
+// p_full), so that the first half of P V runs under the second half of the softmax; P V takes both operands from
+// shared memory.  One issuing thread per query tile (warps 1 and 10), each following its tile's hand-offs in order:
+//     issuer t:  S_t = Q_t K_0^T | [s_read] S_t = Q_t K_j+1^T, [p_half] O_t += P_t[:, :64] V_j[:64], [p_full] O_t += P_t[:, 64:] V_j[64:] | ...
+struct Fa3Bars {
+    uint64_t kv_full[FA_MAX_STAGES], kv_empty[FA_MAX_STAGES];   // kv_empty: one arrival per issuer
+    uint64_t q_full, q_empty;                                   // q_empty: one arrival per issuer
+    uint64_t s_full[2], s_read[2];      // per query tile: scores are there / are in the softmax threads' registers
+    uint64_t p_half[2], p_full[2];      // the first / second 64 keys of P are in shared memory
+    uint64_t pa_done[2], o_done[2];     // the MMAs over the first half / all of P have completed
+    uint64_t o_empty[2];
+};
+constexpr int F3_THREADS = 352;
+constexpr int F3_MMA1_WARP = 10;
+constexpr uint32_t F3_P_BYTES = 128u * 128u * 2u;   // a P tile: [2 groups of 64 keys][128 rows][128 B]
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+template <bool F16>
+__global__ void __launch_bounds__(F3_THREADS, 1)
+fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const FaParams p) {
+    extern __shared__ unsigned char fa_smem_raw[];
+    __shared__ Fa3Bars bars;
+    __shared__ uint32_t tmem_slot;
+    const uint32_t raw_addr = smem_u32(fa_smem_raw);
+    unsigned char *smem = fa_smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int D = p.D, nkt = p.nkt, nst = p.nst;
+    const int ng = D >> 6;
+    const uint32_t tile_bytes = (uint32_t)FA_BN * (uint32_t)D * 2u;   // a Q, K or V tile: [ng groups][128 rows][128 B]
+    unsigned char *q_smem = smem;                                      // two Q tiles
+    unsigned char *p_smem = smem + 2 * (size_t)tile_bytes;             // two P tiles
+    unsigned char *ring = p_smem + 2 * (size_t)F3_P_BYTES;
+    const uint32_t lim = p.spin_limit;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < FA_MAX_STAGES; ++i) { mbar_init(&bars.kv_full[i], 1); mbar_init(&bars.kv_empty[i], 2); }
+        mbar_init(&bars.q_full, 1);
+        mbar_init(&bars.q_empty, 2);
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&bars.s_full[t], 1); mbar_init(&bars.s_read[t], 4);
+            mbar_init(&bars.p_half[t], 4); mbar_init(&bars.p_full[t], 4);
+            mbar_init(&bars.pa_done[t], 1); mbar_init(&bars.o_done[t], 1);
+            mbar_init(&bars.o_empty[t], 4);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;        // S_t: columns [128 t, 128 t + 128); O_t: [256 + 128 t, ...)
+    bool failed = false;
+    const bool skip = (*reinterpret_cast<volatile unsigned *>(p.err) != 0);   // an earlier kernel of the call failed
+
+    if (skip) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        if (lane == 0) {
+            long long it = 0;
+            int ui = 0;
+            bool ok = true;
+            auto load_kv = [&](const CUtensorMap *tm, int bh, int j) {
+                const int s = (int)(it % nst);
+                ok = ok && mbar_wait(&bars.kv_empty[s], (uint32_t)((it / nst) & 1) ^ 1u, lim);
+                if (!ok) return;
+                mbar_expect_tx(&bars.kv_full[s], tile_bytes);
+                tma_load_4d(ring + (size_t)s * tile_bytes, tm, 0, j * FA_BN, 0, bh, &bars.kv_full[s]);
+                ++it;
+            };
+            for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
+                const int bh = (int)(unit / p.nqp), qp = (int)(unit % p.nqp);
+                ok = mbar_wait(&bars.q_empty, (uint32_t)(ui & 1) ^ 1u, lim);
+                if (!ok) break;
+                mbar_expect_tx(&bars.q_full, 2 * tile_bytes);
+                tma_load_4d(q_smem, &tmQ, 0, qp * 2 * FA_BM, 0, bh, &bars.q_full);
+                tma_load_4d(q_smem + tile_bytes, &tmQ, 0, qp * 2 * FA_BM + FA_BM, 0, bh, &bars.q_full);
+                load_kv(&tmK, bh, 0);                     // the order of the issuers: K_0 | K_1, V_0 | K_2, V_1 | ...
+                for (int j = 0; j < nkt && ok; ++j) {
+                    if (j + 1 < nkt) load_kv(&tmK, bh, j + 1);
+                    load_kv(&tmV, bh, j);
+                }
+            }
+            if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 7)); failed = true; }
+        }
+    } else if (warp == 1 || warp == F3_MMA1_WARP) {
+        if (lane == 0) {
+            const int t = warp == 1 ? 0 : 1;
+            const uint32_t id_qk = umma_idesc_16(FA_BM, FA_BN, 0, 0, F16 ? 1 : 0), id_pv = umma_idesc_16(FA_BM, D, 0, 1, F16 ? 1 : 0);
+            const uint32_t qa = smem_u32(q_smem + (size_t)t * tile_bytes), pa = smem_u32(p_smem + (size_t)t * F3_P_BYTES);
+            const uint32_t t_s = tmem + t * 128, t_o = tmem + 256 + t * 128;
+            long long it = 0;      // ring position
+            long long sc = 0;      // key tiles done so far: phase of the hand-offs with the softmax warps
+            int ui = 0;
+            bool ok = true;
+            auto qk = [&](bool last) {   // S_t = Q_t K^T with the K tile at the ring position; then this issuer is done with the tile
+                const int s = (int)(it % nst);
+                ok = ok && mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);
+                if (!ok) return;
+                tc_fence_after();
+                const uint32_t ka = smem_u32(ring + (size_t)s * tile_bytes);
+                for (int g = 0; g < ng; ++g) {
+                    const uint64_t dq = umma_desc_k_sw128(qa + g * (FA_BM * 128)), dk = umma_desc_k_sw128(ka + g * (FA_BN * 128));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) umma_bf16(t_s, dq + 2 * k, dk + 2 * k, id_qk, (g | k) != 0);
+                }
+                umma_commit(&bars.s_full[t]);
+                umma_commit(&bars.kv_empty[s]);
+                if (last) umma_commit(&bars.q_empty);   // this issuer's last MMA of the unit that reads Q
+                ++it;
+            };
+            for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
+                ok = mbar_wait(&bars.q_full, (uint32_t)(ui & 1), lim);
+                if (!ok) break;
+                tc_fence_after();
+                qk(nkt == 1);   // (S_t is free: the wait for p_full of the previous unit's last tile came after its s_read)
+                for (int j = 0; j < nkt && ok; ++j, ++sc) {
+                    if (j + 1 < nkt) {
+                        ok = mbar_wait(&bars.s_read[t], (uint32_t)(sc & 1), lim);   // the scores of tile j are in registers
+                        if (!ok) break;
+                        tc_fence_after();
+                        qk(j + 2 == nkt);
+                        if (!ok) break;
+                    }
+                    const int s = (int)(it % nst);
+                    ok = mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);   // V_j
+                    if (ok && j == 0) ok = mbar_wait(&bars.o_empty[t], (uint32_t)(ui & 1) ^ 1u, lim);   // the epilogue of the previous unit has read O_t
+                    const uint32_t va = smem_u32(ring + (size_t)s * tile_bytes);
+#pragma unroll
+                    for (int h = 0; h < 2 && ok; ++h) {
+                        ok = mbar_wait(h == 0 ? &bars.p_half[t] : &bars.p_full[t], (uint32_t)(sc & 1), lim);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint64_t dp = umma_desc_k_sw128(pa + h * (FA_BM * 128));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma_bf16(t_o, dp + 2 * k, umma_desc_mn_sw128(va + (4 * h + k) * 2048, FA_BN * 128), id_pv, (j > 0 || h != 0 || k != 0) ? 1u : 0u);
+                        umma_commit(h == 0 ? &bars.pa_done[t] : &bars.o_done[t]);
+                    }
+                    if (!ok) break;
+                    umma_commit(&bars.kv_empty[s]);
+                    ++it;
+                }
+            }
+            if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 9)); failed = true; }
+        }
+    } else {
+        // ---- softmax and epilogue of query tile t; thread = query row (tensor-memory lane) ----
+        const int t = (warp - 2) >> 2, q = warp & 3;
+        const int row = 32 * q + lane;
+        const uint32_t ts = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)t * 128u;   // S_t of this row
+        const uint32_t to = tmem + ((uint32_t)(32 * q) << 16) + 256u + (uint32_t)t * 128u;
+        const uint32_t prow = smem_u32(p_smem + (size_t)t * F3_P_BYTES) + (uint32_t)row * 128u;   // this row of P_t, first group of 64 keys
+        const uint32_t sw = (uint32_t)(row & 7);
+        const float sl2 = p.scale_log2;
+        long long sc = 0;
+        float m_ref = 0.0f, l = 0.0f;
+        uint32_t r0[32], r1[32], r2[32], r3[32];
+        for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
+            const int bh = (int)(unit / p.nqp), qp = (int)(unit % p.nqp);
+            for (int j = 0; j < nkt; ++j, ++sc) {
+                FA_FAIL_AT(2, !mbar_wait(&bars.s_full[t], (uint32_t)(sc & 1), lim));
+                tc_fence_after();
+                const int valid = min(FA_BN, p.Lk - j * FA_BN);   // real keys in this tile
+                tmem_ld32(ts, r0);
+                tmem_ld32(ts + 32, r1);
+                tmem_ld32(ts + 64, r2);
+                tmem_ld32(ts + 96, r3);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.s_read[t]);   // S_t may be overwritten
+                if (valid < FA_BN) {   // (the same for every thread) keys that do not exist: exp2(-inf) = 0
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (i >= valid) r0[i] = 0xff800000u;
+                        if (32 + i >= valid) r1[i] = 0xff800000u;
+                        if (64 + i >= valid) r2[i] = 0xff800000u;
+                        if (96 + i >= valid) r3[i] = 0xff800000u;
+                    }
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    mx0 = fmaxf(mx0, __uint_as_float(r0[i])); mx1 = fmaxf(mx1, __uint_as_float(r1[i]));
+                    mx2 = fmaxf(mx2, __uint_as_float(r2[i])); mx3 = fmaxf(mx3, __uint_as_float(r3[i]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+                if (j == 0) {
+                    m_ref = mx;
+                    l = 0.0f;
+                } else {
+                    // ---- rescale the accumulator where the maximum has outgrown its reference (rare) ----
+                    const bool need = mx > m_ref + FA_RESCALE_LOG2;
+                    if (__any_sync(0xffffffffu, need)) {
+                        FA_FAIL_AT(3, !mbar_wait(&bars.o_done[t], (uint32_t)((sc - 1) & 1), lim));   // the previous P V of this tile is done
+                        tc_fence_after();
+                        const float m_new = need ? mx : m_ref;
+                        const float f = fast_exp2(m_ref - m_new);
+                        uint32_t w[16];
+                        for (int c = 0; c < (D >> 4); ++c) {
+                            tmem_ld16(to + 16 * c, w);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) * f);
+                            tmem_st16(to + 16 * c, w);
+                        }
+                        tmem_st_wait();
+                        l *= f;
+                        m_ref = m_new;
+                    }
+                }
+                // ---- P = exp2(S * scale - reference) -> 16 bit -> this row of the shared-memory tile, 8 keys (16 bytes) at a time ----
+                float sum0 = 0.0f, sum1 = 0.0f;
+                auto half = [&](const uint32_t (&a)[32], const uint32_t (&b)[32], uint32_t base) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int e = 8 * (c & 3) + 2 * i;
+                            const float x0 = __uint_as_float(c < 4 ? a[e] : b[e]), x1 = __uint_as_float(c < 4 ? a[e + 1] : b[e + 1]);
+                            const float e0 = fast_exp2(fmaf(x0, sl2, -m_ref)), e1 = fast_exp2(fmaf(x1, sl2, -m_ref));
+                            sum0 += e0; sum1 += e1;
+                            pk[i] = pack_16x2(e0, e1, F16);
+                        }
+                        st_shared_v4(base + ((((uint32_t)c) ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+                    }
+                };
+                if (sc > 0) FA_FAIL_AT(5, !mbar_wait(&bars.pa_done[t], (uint32_t)((sc - 1) & 1), lim));   // the MMAs have read the first half of P
+                half(r0, r1, prow);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.p_half[t]);
+                if (sc > 0) FA_FAIL_AT(6, !mbar_wait(&bars.o_done[t], (uint32_t)((sc - 1) & 1), lim));    // ... and the second
+                half(r2, r3, prow + FA_BM * 128);
+                l += sum0 + sum1;
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.p_full[t]);
+            }
+            if (failed) break;
+            // ---- epilogue of the unit: O_t / row sum -> 16 bit -> global; lanes trade pieces so that the stores cover full lines ----
+            FA_FAIL_AT(4, !mbar_wait(&bars.o_done[t], (uint32_t)((sc - 1) & 1), lim));
+            tc_fence_after();
+            const float inv = 1.0f / l;
+            const int qrow0 = qp * 2 * FA_BM + t * FA_BM;   // first query row of the tile within its head
+            __nv_bfloat16 *orow = p.O + ((long long)bh * p.Lq + qrow0 + row) * (long long)D;
+            unsigned char *row0 = reinterpret_cast<unsigned char *>(orow - (long long)(lane & 3) * D);
+            for (int cp = 0; cp < ng; ++cp) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    tmem_ld32(to + cp * 64 + hh * 32, r0);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) r1[16 * hh + i] = pack_16x2(__uint_as_float(r0[2 * i]) * inv, __uint_as_float(r0[2 * i + 1]) * inv, F16);
+                }
+                store_rows_128B_transposed_if(row0 + cp * 128, (size_t)D * 2, r1, lane, p.Lq - (qrow0 + (row & ~3)));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.o_empty[t]);
+        }
+    }
+
+    if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies and MMAs in flight drain
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
 #undef FA_FAIL_AT
 
 // ---- host side ------------------------------------------------------------------------------------
+// (development: which of the two layouts for head_d 64 / 128 runs)
+inline bool fa_use_layout2() {
+#ifdef B200ATTN_DEVTOOLS
+    static const bool v = getenv("B200ATTN_FA_LAYOUT1") == nullptr;
+    return v;
+#else
+    return true;
+#endif
+}
+
 inline bool fa_supported(const b200attn_args &a) {
     if (a.dtype != B200ATTN_BF16 && a.dtype != B200ATTN_F16) return false;
     if (a.head_d != 64 && a.head_d != 128 && a.head_d != 256) return false;
@@ -640,16 +930,23 @@ inline int fa_run(const b200attn_args &a, unsigned *err_dev, unsigned *err_sys, 
     {
         std::lock_guard<std::mutex> lk(attr_mu);
         if (smem_max[dev & 63] == 0) {
-            cudaFuncAttributes fa;
+            cudaFuncAttributes fa, fb, fc;
             cudaDeviceProp prop;
             cudaGetDeviceProperties(&prop, dev);
-            const bool ok = cudaFuncGetAttributes(&fa, fa_kernel<false>) == cudaSuccess &&
-                            cudaFuncSetAttribute(fa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess &&
-                            cudaFuncSetAttribute(fa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess &&
-                            cudaFuncSetAttribute(fa256_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess &&
-                            cudaFuncSetAttribute(fa256_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(prop.sharedMemPerBlockOptin - fa.sharedSizeBytes)) == cudaSuccess;
+            // one limit for the kernels of this file: the opt-in maximum less the largest static allocation among them
+            bool ok = cudaFuncGetAttributes(&fa, fa_kernel<false>) == cudaSuccess && cudaFuncGetAttributes(&fb, fa256_kernel<false>) == cudaSuccess &&
+                      cudaFuncGetAttributes(&fc, fa3_kernel<false>) == cudaSuccess;
+            size_t stat = 0;
+            if (ok) { stat = fa.sharedSizeBytes; if (fb.sharedSizeBytes > stat) stat = fb.sharedSizeBytes; if (fc.sharedSizeBytes > stat) stat = fc.sharedSizeBytes; }
+            const int dyn = ok ? (int)(prop.sharedMemPerBlockOptin - stat) : 0;
+            ok = ok && cudaFuncSetAttribute(fa_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
+                 cudaFuncSetAttribute(fa_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
+                 cudaFuncSetAttribute(fa256_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
+                 cudaFuncSetAttribute(fa256_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
+                 cudaFuncSetAttribute(fa3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess &&
+                 cudaFuncSetAttribute(fa3_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess;
             if (!ok) { (void)cudaGetLastError(); snprintf(t_tc_error, sizeof t_tc_error, "cudaFuncSetAttribute(max dynamic shared memory) failed"); return B200ATTN_ERR_CUDA; }
-            smem_max[dev & 63] = prop.sharedMemPerBlockOptin - fa.sharedSizeBytes;
+            smem_max[dev & 63] = (size_t)dyn;
         }
     }
     if (D == FB_D) {
@@ -679,6 +976,36 @@ inline int fa_run(const b200attn_args &a, unsigned *err_dev, unsigned *err_sys, 
         else fa256_kernel<false><<<grid, FB_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "fa256_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
+        launches->fetch_add(1);
+        return B200ATTN_OK;
+    }
+    if (fa_use_layout2()) {
+        const size_t tb = (size_t)FA_BN * D * 2;
+        int nst3 = (int)((smem_max[dev & 63] - 1024 - 2 * tb - 2 * (size_t)F3_P_BYTES) / tb);
+        if (nst3 > FA_MAX_STAGES) nst3 = FA_MAX_STAGES;
+        if (nst3 < 3) return -1;
+        CUtensorMap tmQ, tmK, tmV;
+        if (!make_tmap_grouped_heads(&tmQ, a.Q, BH, Lq, D, FA_BM, D / 64) || !make_tmap_grouped_heads(&tmK, a.K, BH, Lk, D, FA_BN, D / 64) ||
+            !make_tmap_grouped_heads(&tmV, a.V, BH, Lk, D, FA_BN, D / 64)) {
+            snprintf(t_tc_error, sizeof t_tc_error, "cuTensorMapEncodeTiled failed");
+            return -1;
+        }
+        FaParams p{};
+        p.Lq = Lq; p.Lk = Lk; p.D = D;
+        p.nqp = ((Lq + FA_BM - 1) / FA_BM + 1) / 2;
+        p.nkt = (Lk + FA_BN - 1) / FA_BN;
+        p.nst = nst3;
+        p.n_units = BH * p.nqp;
+        p.scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+        p.f16 = a.dtype == B200ATTN_F16 ? 1 : 0;
+        p.O = (__nv_bfloat16 *)a.out;
+        p.err = err_dev; p.err_sys = err_sys; p.spin_limit = spin_limit;
+        const unsigned grid = (unsigned)(p.n_units < sm_count ? p.n_units : sm_count);
+        const size_t smem = 2 * tb + 2 * (size_t)F3_P_BYTES + (size_t)nst3 * tb + 1024;
+        if (p.f16) fa3_kernel<true><<<grid, F3_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
+        else fa3_kernel<false><<<grid, F3_THREADS, smem, st>>>(tmQ, tmK, tmV, p);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { snprintf(t_tc_error, sizeof t_tc_error, "fa3_kernel launch failed: %s", cudaGetErrorString(e)); return B200ATTN_ERR_CUDA; }
         launches->fetch_add(1);
         return B200ATTN_OK;
     }
