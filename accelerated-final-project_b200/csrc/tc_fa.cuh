@@ -622,7 +622,7 @@ fa256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 // says so (s_read); the score MMAs of the next key tile start then, under the softmax of this one.  P (16 bit) goes
 // to a shared-memory tile of its own in the K-major 128-byte-swizzle layout, in two halves of 64 keys (p_half,
 // p_full), so that the first half of P V runs under the second half of the softmax; P V takes both operands from
-// shared memory.  One issuing thread per query tile (warps 1 and 10), each following its tile's hand-offs in order:
+// shared memory.  One issuing thread per query tile (warps 1 and 2), each following its tile's hand-offs in order:
 //     issuer t:  S_t = Q_t K_0^T | [s_read] S_t = Q_t K_j+1^T, [p_half] O_t += P_t[:, :64] V_j[:64], [p_full] O_t += P_t[:, 64:] V_j[64:] | ...
 struct Fa3Bars {
     uint64_t kv_full[FA_MAX_STAGES], kv_empty[FA_MAX_STAGES];   // kv_empty: one arrival per issuer
@@ -632,8 +632,8 @@ struct Fa3Bars {
     uint64_t pa_done[2], o_done[2];     // the MMAs over the first half / all of P have completed
     uint64_t o_empty[2];
 };
-constexpr int F3_THREADS = 352;
-constexpr int F3_MMA1_WARP = 10;
+constexpr int F3_THREADS = 384;      // warpgroup 0: warp 0 loads, warps 1 and 2 issue the MMAs of query tile 0 / 1 (warp 3 idles); warpgroups 1, 2: softmax of tile 0 / 1
+constexpr int F3_REGS_SMALL = 80, F3_REGS_LARGE = 208;   // registers per thread after the hand-over: 128 * 80 + 256 * 208 <= 384 * 168
 constexpr uint32_t F3_P_BYTES = 128u * 128u * 2u;   // a P tile: [2 groups of 64 keys][128 rows][128 B]
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -678,16 +678,23 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     bool failed = false;
     const bool skip = (*reinterpret_cast<volatile unsigned *>(p.err) != 0);   // an earlier kernel of the call failed
 
+    // the softmax threads hold a whole score row: they take over registers that the loading and issuing warps do not need
+    // (each branch opens with its setmaxnreg, so that the compiler budgets the branch accordingly)
     if (skip) {
         // fall through to the common exit
-    } else if (warp == 0) {
+    } else if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(F3_REGS_SMALL));
+      if (warp == 0) {
         if (lane == 0) {
             long long it = 0;
             int ui = 0;
             bool ok = true;
+            TC_PROF_DECL;
             auto load_kv = [&](const CUtensorMap *tm, int bh, int j) {
                 const int s = (int)(it % nst);
+                TC_PROF(1);
                 ok = ok && mbar_wait(&bars.kv_empty[s], (uint32_t)((it / nst) & 1) ^ 1u, lim);
+                TC_PROF(0);
                 if (!ok) return;
                 mbar_expect_tx(&bars.kv_full[s], tile_bytes);
                 tma_load_4d(ring + (size_t)s * tile_bytes, tm, 0, j * FA_BN, 0, bh, &bars.kv_full[s]);
@@ -707,10 +714,11 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 }
             }
             if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 7)); failed = true; }
+            TC_PROF_FLUSH(8, true);
         }
-    } else if (warp == 1 || warp == F3_MMA1_WARP) {
+      } else if (warp < 3) {
         if (lane == 0) {
-            const int t = warp == 1 ? 0 : 1;
+            const int t = warp - 1;
             const uint32_t id_qk = umma_idesc_16(FA_BM, FA_BN, 0, 0, F16 ? 1 : 0), id_pv = umma_idesc_16(FA_BM, D, 0, 1, F16 ? 1 : 0);
             const uint32_t qa = smem_u32(q_smem + (size_t)t * tile_bytes), pa = smem_u32(p_smem + (size_t)t * F3_P_BYTES);
             const uint32_t t_s = tmem + t * 128, t_o = tmem + 256 + t * 128;
@@ -718,11 +726,13 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             long long sc = 0;      // key tiles done so far: phase of the hand-offs with the softmax warps
             int ui = 0;
             bool ok = true;
+            TC_PROF_DECL;
             auto qk = [&](bool last) {   // S_t = Q_t K^T with the K tile at the ring position; then this issuer is done with the tile
                 const int s = (int)(it % nst);
                 ok = ok && mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);
                 if (!ok) return;
                 tc_fence_after();
+                TC_PROF(1);
                 const uint32_t ka = smem_u32(ring + (size_t)s * tile_bytes);
                 for (int g = 0; g < ng; ++g) {
                     const uint64_t dq = umma_desc_k_sw128(qa + g * (FA_BM * 128)), dk = umma_desc_k_sw128(ka + g * (FA_BN * 128));
@@ -733,6 +743,7 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 umma_commit(&bars.kv_empty[s]);
                 if (last) umma_commit(&bars.q_empty);   // this issuer's last MMA of the unit that reads Q
                 ++it;
+                TC_PROF(2);
             };
             for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
                 ok = mbar_wait(&bars.q_full, (uint32_t)(ui & 1), lim);
@@ -741,8 +752,10 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 qk(nkt == 1);   // (S_t is free: the wait for p_full of the previous unit's last tile came after its s_read)
                 for (int j = 0; j < nkt && ok; ++j, ++sc) {
                     if (j + 1 < nkt) {
+                        TC_PROF(7);
                         ok = mbar_wait(&bars.s_read[t], (uint32_t)(sc & 1), lim);   // the scores of tile j are in registers
                         if (!ok) break;
+                        TC_PROF(0);
                         tc_fence_after();
                         qk(j + 2 == nkt);
                         if (!ok) break;
@@ -750,17 +763,20 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     const int s = (int)(it % nst);
                     ok = mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);   // V_j
                     if (ok && j == 0) ok = mbar_wait(&bars.o_empty[t], (uint32_t)(ui & 1) ^ 1u, lim);   // the epilogue of the previous unit has read O_t
+                    TC_PROF(3);
                     const uint32_t va = smem_u32(ring + (size_t)s * tile_bytes);
 #pragma unroll
                     for (int h = 0; h < 2 && ok; ++h) {
                         ok = mbar_wait(h == 0 ? &bars.p_half[t] : &bars.p_full[t], (uint32_t)(sc & 1), lim);
                         if (!ok) break;
                         tc_fence_after();
+                        TC_PROF(4 + h);
                         const uint64_t dp = umma_desc_k_sw128(pa + h * (FA_BM * 128));
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             umma_bf16(t_o, dp + 2 * k, umma_desc_mn_sw128(va + (4 * h + k) * 2048, FA_BN * 128), id_pv, (j > 0 || h != 0 || k != 0) ? 1u : 0u);
                         umma_commit(h == 0 ? &bars.pa_done[t] : &bars.o_done[t]);
+                        TC_PROF(6);
                     }
                     if (!ok) break;
                     umma_commit(&bars.kv_empty[s]);
@@ -768,10 +784,13 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 }
             }
             if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 9)); failed = true; }
+            TC_PROF_FLUSH(8 * t, t == 0);
         }
+      }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(F3_REGS_LARGE));
         // ---- softmax and epilogue of query tile t; thread = query row (tensor-memory lane) ----
-        const int t = (warp - 2) >> 2, q = warp & 3;
+        const int t = (warp - 4) >> 2, q = warp & 3;
         const int row = 32 * q + lane;
         const uint32_t ts = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)t * 128u;   // S_t of this row
         const uint32_t to = tmem + ((uint32_t)(32 * q) << 16) + 256u + (uint32_t)t * 128u;
@@ -781,11 +800,14 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         long long sc = 0;
         float m_ref = 0.0f, l = 0.0f;
         uint32_t r0[32], r1[32], r2[32], r3[32];
+        TC_PROF_DECL;
         for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
             const int bh = (int)(unit / p.nqp), qp = (int)(unit % p.nqp);
             for (int j = 0; j < nkt; ++j, ++sc) {
+                TC_PROF(6);
                 FA_FAIL_AT(2, !mbar_wait(&bars.s_full[t], (uint32_t)(sc & 1), lim));
                 tc_fence_after();
+                TC_PROF(0);
                 const int valid = min(FA_BN, p.Lk - j * FA_BN);   // real keys in this tile
                 tmem_ld32(ts, r0);
                 tmem_ld32(ts + 32, r1);
@@ -795,6 +817,7 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.s_read[t]);   // S_t may be overwritten
+                TC_PROF(1);
                 if (valid < FA_BN) {   // (the same for every thread) keys that do not exist: exp2(-inf) = 0
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
@@ -836,6 +859,7 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     }
                 }
                 // ---- P = exp2(S * scale - reference) -> 16 bit -> this row of the shared-memory tile, 8 keys (16 bytes) at a time ----
+                TC_PROF(2);
                 float sum0 = 0.0f, sum1 = 0.0f;
                 auto half = [&](const uint32_t (&a)[32], const uint32_t (&b)[32], uint32_t base) {
 #pragma unroll
@@ -853,16 +877,20 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     }
                 };
                 if (sc > 0) FA_FAIL_AT(5, !mbar_wait(&bars.pa_done[t], (uint32_t)((sc - 1) & 1), lim));   // the MMAs have read the first half of P
+                TC_PROF(7);
                 half(r0, r1, prow);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.p_half[t]);
+                TC_PROF(3);
                 if (sc > 0) FA_FAIL_AT(6, !mbar_wait(&bars.o_done[t], (uint32_t)((sc - 1) & 1), lim));    // ... and the second
+                TC_PROF(7);
                 half(r2, r3, prow + FA_BM * 128);
                 l += sum0 + sum1;
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.p_full[t]);
+                TC_PROF(4);
             }
             if (failed) break;
             // ---- epilogue of the unit: O_t / row sum -> 16 bit -> global; lanes trade pieces so that the stores cover full lines ----
@@ -885,7 +913,9 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.o_empty[t]);
+            TC_PROF(5);
         }
+        TC_PROF_FLUSH(16 + 8 * t, (threadIdx.x & 127) == 64);
     }
 
     if (failed) for (int i = 0; i < 2000; ++i) __nanosleep(1000);   // let copies and MMAs in flight drain
