@@ -381,24 +381,25 @@ fa256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         // fall through to the common exit
     } else if (warp == 0) {
         if (lane == 0) {
-            long long it = 0;
+            int s = 0;            // ring stage and the parity of its use (kept by hand: a division here costs the thread hundreds of clocks)
+            uint32_t ph = 0;
             int ui = 0;
             auto load_k = [&](int bh, int j, bool &ok) {   // the two column halves of K tile j
-                for (int h = 0; h < 2 && ok; ++h, ++it) {
-                    const int s = (int)(it % nst);
-                    ok = mbar_wait(&bars.kv_empty[s], (uint32_t)((it / nst) & 1) ^ 1u, lim);
+                for (int h = 0; h < 2 && ok; ++h) {
+                    ok = mbar_wait(&bars.kv_empty[s], ph ^ 1u, lim);
                     if (!ok) break;
                     mbar_expect_tx(&bars.kv_full[s], FB_STAGE);
                     tma_load_4d(ring + (size_t)s * FB_STAGE, &tmK, 0, j * FA_BN, 2 * h, bh, &bars.kv_full[s]);
+                    if (++s == nst) { s = 0; ph ^= 1u; }
                 }
             };
             auto load_v = [&](int bh, int j, bool &ok) {   // the two key halves of V tile j
-                for (int h = 0; h < 2 && ok; ++h, ++it) {
-                    const int s = (int)(it % nst);
-                    ok = mbar_wait(&bars.kv_empty[s], (uint32_t)((it / nst) & 1) ^ 1u, lim);
+                for (int h = 0; h < 2 && ok; ++h) {
+                    ok = mbar_wait(&bars.kv_empty[s], ph ^ 1u, lim);
                     if (!ok) break;
                     mbar_expect_tx(&bars.kv_full[s], FB_STAGE);
                     tma_load_4d(ring + (size_t)s * FB_STAGE, &tmV, 0, j * FA_BN + 64 * h, 0, bh, &bars.kv_full[s]);
+                    if (++s == nst) { s = 0; ph ^= 1u; }
                 }
             };
             bool ok = true;
@@ -419,15 +420,16 @@ fa256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t id_qk = umma_idesc_16(FA_BM, FA_BN, 0, 0, F16 ? 1 : 0), id_pv = umma_idesc_16(FA_BM, FB_D, 0, 1, F16 ? 1 : 0);
-            long long it = 0, gt = 0;   // ring position; tiles issued so far (score buffer = tile & 1)
+            int s = 0;                  // ring stage and the parity of its use
+            uint32_t ph = 0;
+            long long gt = 0;           // tiles issued so far (score buffer = tile & 1)
             int ui = 0;
             bool ok = true;
             const uint32_t qa = smem_u32(q_smem);
             auto qk = [&](long long g) {   // S_(g & 1) = Q K^T over the two column halves of the K tile
                 const int b = (int)(g & 1);
-                for (int h = 0; h < 2 && ok; ++h, ++it) {
-                    const int s = (int)(it % nst);
-                    ok = mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);
+                for (int h = 0; h < 2 && ok; ++h) {
+                    ok = mbar_wait(&bars.kv_full[s], ph, lim);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t ka = smem_u32(ring + (size_t)s * FB_STAGE);
@@ -436,14 +438,14 @@ fa256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                         umma_bf16(tmem + b * 128, umma_desc_k_sw128(qa + (2 * h + (k >> 2)) * (FA_BM * 128)) + 2 * (k & 3),
                                   umma_desc_k_sw128(ka + (k >> 2) * (FA_BN * 128)) + 2 * (k & 3), id_qk, (h | k) != 0);
                     umma_commit(&bars.kv_empty[s]);
+                    if (++s == nst) { s = 0; ph ^= 1u; }
                 }
                 umma_commit(&bars.s_full[b]);
             };
             auto pv = [&](long long g, bool acc) {   // O (+)= P V over the two key halves of the V tile; P in the first 64 columns of the score buffer
                 const int b = (int)(g & 1);
-                for (int h = 0; h < 2 && ok; ++h, ++it) {
-                    const int s = (int)(it % nst);
-                    ok = mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);
+                for (int h = 0; h < 2 && ok; ++h) {
+                    ok = mbar_wait(&bars.kv_full[s], ph, lim);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t va = smem_u32(ring + (size_t)s * FB_STAGE);
@@ -451,6 +453,7 @@ fa256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
                     for (int kk = 0; kk < 4; ++kk)
                         umma_16_ts(tmem + 256, tmem + b * 128 + (4 * h + kk) * 8, umma_desc_mn_sw128(va + kk * 2048, 64 * 128), id_pv, (acc || h != 0 || kk != 0) ? 1u : 0u);
                     umma_commit(&bars.kv_empty[s]);
+                    if (++s == nst) { s = 0; ph ^= 1u; }
                 }
                 umma_commit(&bars.o_done[b]);
             };
@@ -686,19 +689,19 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(F3_REGS_SMALL));
       if (warp == 0) {
         if (lane == 0) {
-            long long it = 0;
+            int s = 0;            // ring stage and the parity of its use (kept by hand: a division here costs the thread hundreds of clocks)
+            uint32_t ph = 0;
             int ui = 0;
             bool ok = true;
             TC_PROF_DECL;
             auto load_kv = [&](const CUtensorMap *tm, int bh, int j) {
-                const int s = (int)(it % nst);
                 TC_PROF(1);
-                ok = ok && mbar_wait(&bars.kv_empty[s], (uint32_t)((it / nst) & 1) ^ 1u, lim);
+                ok = ok && mbar_wait(&bars.kv_empty[s], ph ^ 1u, lim);
                 TC_PROF(0);
                 if (!ok) return;
                 mbar_expect_tx(&bars.kv_full[s], tile_bytes);
                 tma_load_4d(ring + (size_t)s * tile_bytes, tm, 0, j * FA_BN, 0, bh, &bars.kv_full[s]);
-                ++it;
+                if (++s == nst) { s = 0; ph ^= 1u; }
             };
             for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
                 const int bh = (int)(unit / p.nqp), qp = (int)(unit % p.nqp);
@@ -722,14 +725,14 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             const uint32_t id_qk = umma_idesc_16(FA_BM, FA_BN, 0, 0, F16 ? 1 : 0), id_pv = umma_idesc_16(FA_BM, D, 0, 1, F16 ? 1 : 0);
             const uint32_t qa = smem_u32(q_smem + (size_t)t * tile_bytes), pa = smem_u32(p_smem + (size_t)t * F3_P_BYTES);
             const uint32_t t_s = tmem + t * 128, t_o = tmem + 256 + t * 128;
-            long long it = 0;      // ring position
-            long long sc = 0;      // key tiles done so far: phase of the hand-offs with the softmax warps
+            int s = 0;             // ring stage and the parity of its use
+            uint32_t ph = 0;
+            uint32_t sc = 0;       // key tiles done so far: phase of the hand-offs with the softmax warps
             int ui = 0;
             bool ok = true;
             TC_PROF_DECL;
             auto qk = [&](bool last) {   // S_t = Q_t K^T with the K tile at the ring position; then this issuer is done with the tile
-                const int s = (int)(it % nst);
-                ok = ok && mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);
+                ok = ok && mbar_wait(&bars.kv_full[s], ph, lim);
                 if (!ok) return;
                 tc_fence_after();
                 TC_PROF(1);
@@ -742,7 +745,7 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 umma_commit(&bars.s_full[t]);
                 umma_commit(&bars.kv_empty[s]);
                 if (last) umma_commit(&bars.q_empty);   // this issuer's last MMA of the unit that reads Q
-                ++it;
+                if (++s == nst) { s = 0; ph ^= 1u; }
                 TC_PROF(2);
             };
             for (long long unit = blockIdx.x; unit < p.n_units && ok; unit += gridDim.x, ++ui) {
@@ -753,21 +756,20 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 for (int j = 0; j < nkt && ok; ++j, ++sc) {
                     if (j + 1 < nkt) {
                         TC_PROF(7);
-                        ok = mbar_wait(&bars.s_read[t], (uint32_t)(sc & 1), lim);   // the scores of tile j are in registers
+                        ok = mbar_wait(&bars.s_read[t], sc & 1u, lim);   // the scores of tile j are in registers
                         if (!ok) break;
                         TC_PROF(0);
                         tc_fence_after();
                         qk(j + 2 == nkt);
                         if (!ok) break;
                     }
-                    const int s = (int)(it % nst);
-                    ok = mbar_wait(&bars.kv_full[s], (uint32_t)((it / nst) & 1), lim);   // V_j
+                    ok = mbar_wait(&bars.kv_full[s], ph, lim);   // V_j
                     if (ok && j == 0) ok = mbar_wait(&bars.o_empty[t], (uint32_t)(ui & 1) ^ 1u, lim);   // the epilogue of the previous unit has read O_t
                     TC_PROF(3);
                     const uint32_t va = smem_u32(ring + (size_t)s * tile_bytes);
 #pragma unroll
                     for (int h = 0; h < 2 && ok; ++h) {
-                        ok = mbar_wait(h == 0 ? &bars.p_half[t] : &bars.p_full[t], (uint32_t)(sc & 1), lim);
+                        ok = mbar_wait(h == 0 ? &bars.p_half[t] : &bars.p_full[t], sc & 1u, lim);
                         if (!ok) break;
                         tc_fence_after();
                         TC_PROF(4 + h);
@@ -780,7 +782,7 @@ fa3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     }
                     if (!ok) break;
                     umma_commit(&bars.kv_empty[s]);
-                    ++it;
+                    if (++s == nst) { s = 0; ph ^= 1u; }
                 }
             }
             if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 9)); failed = true; }
