@@ -62,8 +62,8 @@ NCU_TRAFFIC_BYTES = {
     ("cfg1", "splitd_tc"): 6.42e6 + 2.10e6,           # 6.42 MB read inside the kernel; the 2 MiB output leaves the L2 after it
     ("cfg2c", "splitd_tc"): 25.29e6 + 8.39e6,         # 25.29 MB read; 8 MiB output
     ("decode", "tc_decode"): 537.0e6 + 3.75e6,
-    ("narrow128", "tc_fused"): 201.5e6 + 47.2e6,      # (part of the 67 MB output is still in L2 when the kernel ends)
-    ("narrow256", "tc_fused"): 403.3e6 + 113.5e6,
+    ("narrow128", "tc_fused"): 201.7e6 + 44.5e6,      # (part of the 67 MB output is still in L2 when the kernel ends)
+    ("narrow256", "tc_fused"): 403.1e6 + 112.5e6,
 }
 # nominal fp32 FMA rate of the CUDA cores: 148 SMs x 128 lanes x 2 flops x 1.965 GHz (the fp32 path now
 # does its products on the tensor cores as tf32 MMAs on split operands; the figure is reported as the
