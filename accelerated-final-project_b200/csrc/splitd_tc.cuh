@@ -222,8 +222,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     unsigned *cnt_cur = p.counters + ((size_t)p.buf * p.cap_bh + bh) * 2;   // [0] arrivals, [1] readers
 
     // requests of thread 0
-    auto load_atom = [&](int c) {
-        const int r = c % nr;
+    auto load_atom = [&](int c, int r) {   // atom c into landing slot r = c % nr
         unsigned char *st = raw + (size_t)r * ST_CHUNK;
         mbar_expect_tx(&bars.full[r], (uint32_t)(Lq + Lk) * 128u);
         tma_load_2d(st, &tmQ, atom_col(c), (int)(bh * Lq), &bars.full[r]);
@@ -246,7 +245,7 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         mbar_init(&bars.buf_ok, 1);
         s_fail = 0u;
         mbar_fence_init();
-        for (int c = 0; c < nat && c < nr; ++c) load_atom(c);
+        for (int c = 0; c < nat && c < nr; ++c) load_atom(c, c);
         mbar_expect_tx(&bars.v_full, (uint32_t)nat * (uint32_t)Lk * 128u);
         if (p.v_own) load_v();
     }
@@ -277,9 +276,11 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             // ---- the atoms beyond the landing slots follow as the split warps hand slots back; V lands over the
             // stages once the last score MMA has read them ----
             bool ok = true;
-            for (int c = nr; c < nat && ok; ++c) {
-                ok = mbar_wait(&bars.raw_free[c % nr], ((c / nr) - 1) & 1, lim);
-                if (ok) load_atom(c);
+            // (slot and parity are counted along: a division by the run-time slot count costs a lone thread ~100 clocks)
+            for (int c = nr, r = 0, par = 0; c < nat && ok; ++c) {
+                ok = mbar_wait(&bars.raw_free[r], (uint32_t)par, lim);
+                if (ok) load_atom(c, r);
+                if (++r == nr) { r = 0; par ^= 1; }
             }
             if (ok && !p.v_own) {
                 ok = mbar_wait(&bars.s_full, 0, lim);
@@ -308,9 +309,8 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             // ---- score MMAs: per 8 columns two M = 64, N = 128 MMAs into one accumulator, Q hi [K hi; K lo]^T and
             // Q lo [K hi; K lo]^T: a row's products with K hi in columns 0-63, with K lo in columns 64-127 ----
             const uint32_t id = umma_idesc_tf32(64, 128, 0, 0);
-            for (int c = 0; c < nat; ++c) {
-                const int j = c % nst;
-                ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (c / nst) & 1, lim));
+            for (int c = 0, j = 0, jph = 0; c < nat; ++c, jph ^= (j + 1 == nst), j = (j + 1 == nst) ? 0 : j + 1) {
+                ST_FAIL_AT(2, !mbar_wait(&bars.ready[j], (uint32_t)jph, lim));
                 if (c == nat - 1) ST_STAMP(18);
                 tc_fence_after();
                 const uint32_t sa = smem_u32(stages + (size_t)j * ST_STAGE);
@@ -328,10 +328,10 @@ sdtc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     } else {
         const int t = threadIdx.x - 64;   // 0..191
         // ---- hi / lo split of the landed Q and K atoms into an operand stage ----
-        for (int c = 0; c < nat; ++c) {
-            const int r = c % nr, j = c % nst;
-            ST_FAIL_AT(3, !mbar_wait(&bars.full[r], (c / nr) & 1, lim));
-            ST_FAIL_AT(7, !mbar_wait(&bars.st_free[j], ((c / nst) & 1) ^ 1, lim));
+        for (int c = 0, r = 0, rph = 0, j = 0, jph = 0; c < nat;
+             ++c, rph ^= (r + 1 == nr), r = (r + 1 == nr) ? 0 : r + 1, jph ^= (j + 1 == nst), j = (j + 1 == nst) ? 0 : j + 1) {
+            ST_FAIL_AT(3, !mbar_wait(&bars.full[r], (uint32_t)rph, lim));
+            ST_FAIL_AT(7, !mbar_wait(&bars.st_free[j], (uint32_t)jph ^ 1u, lim));
             if (t == 0 && c == 0) ST_STAMP(2);
             if (t == 0 && c == nat - 1) ST_STAMP(3);
             const unsigned char *src = raw + (size_t)r * ST_CHUNK;
