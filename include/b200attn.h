@@ -184,7 +184,7 @@ const char *b200attn_last_error(void);
 /* Name of the kernel path the last successful b200attn_forward_ex on this thread used:
  * "splitd_tc" (fp32, short sequences, tensor cores with error-compensated tf32), "splitd_fused" and
  * "splitd_two_pass" (CUDA cores), "tc_wide" (bf16 on the tensor cores: score kernel, then P V kernel),
- * "tc_fused" (bf16 / fp16, head_d 64, 128 or 256, more than 64 queries: one kernel, scores and probabilities in tensor
+ * "tc_fused" (bf16 / fp16, head_d 64, 128 or 256, more than 64 queries: one kernel, scores in tensor
  * memory; an encoding is applied to copies of Q and K first), "tc_bf16" (bf16 on the tensor cores, one-kernel
  * cluster pipeline) or "tc_decode" (bf16, up to 64 queries against a long K/V: key splits on the tensor cores
  * plus a combine kernel). */
