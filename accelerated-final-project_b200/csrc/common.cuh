@@ -72,8 +72,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {   // one look, never suspends
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: returns false when `limit` polls went by without the phase completing.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit) {
+    if (mbar_test_wait(bar, parity)) return true;   // often the phase is long complete: try_wait costs ~80 clocks more even then
     for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (it > 64) __nanosleep(32);
