@@ -98,7 +98,7 @@ struct FaPairBars {
     uint64_t q_full, q_empty;                                   // q_empty: one arrival per issuer
     uint64_t s_full[2], s_read[2];      // per query tile: scores are there / are in the softmax threads' registers
     uint64_t p_half[2], p_full[2];      // the first / second 64 keys of P are in shared memory
-    uint64_t pa_done[2], o_done[2];     // the MMAs over the first half / all of P have completed
+    uint64_t o_done[2];                 // the MMAs over P (both halves) have completed
     uint64_t o_empty[2];
 };
 constexpr int FA_THREADS = 384;      // warpgroup 0: warp 0 loads, warps 1 and 2 issue the MMAs of query tile 0 / 1 (warp 3 idles); warpgroups 1, 2: softmax of tile 0 / 1
@@ -133,7 +133,7 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         for (int t = 0; t < 2; ++t) {
             mbar_init(&bars.s_full[t], 1); mbar_init(&bars.s_read[t], 4);
             mbar_init(&bars.p_half[t], 4); mbar_init(&bars.p_full[t], 4);
-            mbar_init(&bars.pa_done[t], 1); mbar_init(&bars.o_done[t], 1);
+            mbar_init(&bars.o_done[t], 1);
             mbar_init(&bars.o_empty[t], 4);
         }
         mbar_fence_init();
@@ -243,7 +243,7 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             umma_bf16(t_o, dp + 2 * k, umma_desc_mn_sw128(va + (4 * h + k) * 2048, FA_BN * 128), id_pv, (j > 0 || h != 0 || k != 0) ? 1u : 0u);
-                        umma_commit(h == 0 ? &bars.pa_done[t] : &bars.o_done[t]);
+                        if (h == 1) umma_commit(&bars.o_done[t]);
                         TC_PROF(6);
                     }
                     if (!ok) break;
@@ -344,14 +344,15 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                         st_shared_v4(base + ((((uint32_t)c) ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
                     }
                 };
-                if (sc > 0) FA_FAIL_AT(5, !mbar_wait(&bars.pa_done[t], (uint32_t)((sc - 1) & 1), lim));   // the MMAs have read the first half of P
+                // the MMAs of the previous key tile have read P (its second half was handed over ~800 clocks ago: one wait
+                // here, instead of one per half, is rarely a real wait and saves the cost of the second)
+                if (sc > 0) FA_FAIL_AT(5, !mbar_wait(&bars.o_done[t], (uint32_t)((sc - 1) & 1), lim));
                 TC_PROF(7);
                 half(r0, r1, prow);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.p_half[t]);
                 TC_PROF(3);
-                if (sc > 0) FA_FAIL_AT(6, !mbar_wait(&bars.o_done[t], (uint32_t)((sc - 1) & 1), lim));    // ... and the second
                 TC_PROF(7);
                 half(r2, r3, prow + FA_BM * 128);
                 l += sum0 + sum1;
