@@ -67,39 +67,80 @@ inline size_t dec_smem_bytes(int nch) { return (size_t)nch * DC_QSLAB + (size_t)
     }
 
 // Encodes `rows` x (64 * nch) bf16 laid out as nch slabs [rows x 128 B] with the 128-byte swizzle, in place;
-// row r has position pos0 + r.  128 threads.
-__device__ __forceinline__ void dec_encode_tile(unsigned char *tile, int rows, int slab_bytes, int nch, int D, int pos0, int table_kind, bool sinus,
-                                                const __nv_bfloat16 *tab, int tid) {
+// row r has position pos0 + r.  128 threads.  The table values of eight pieces are requested before the first is
+// used: with one fetch at a time a K chunk cost its transform warps eight L2 round trips in a row, more than the
+// chunk's share of the HBM time.
+// `landed` is called once, after the first eight fetches have been issued and before the tile is touched: the wait
+// for the tile's TMA load goes there, so that the table values travel while the tile does.  Returns what it returned.
+template <class Landed>
+__device__ __forceinline__ bool dec_encode_tile(unsigned char *tile, int rows, int slab_bytes, int nch, int D, int pos0, int table_kind, bool sinus,
+                                                const __nv_bfloat16 *tab, int tid, Landed landed) {
     const int per_slab = rows * 8;   // 16-byte pieces per slab
+    constexpr int U = 8;
+    bool waited = false;
     if (table_kind == 2) {
-        const int half_slabs = nch >> 1;
-        for (int o = tid; o < half_slabs * per_slab; o += 128) {
-            const int c = o / per_slab, w = o - c * per_slab, r = w >> 3, q = (w & 7) ^ (r & 7);
-            uint4 *plo = reinterpret_cast<uint4 *>(tile + (size_t)c * slab_bytes + (size_t)w * 16);
-            uint4 *phi = reinterpret_cast<uint4 *>(tile + (size_t)(c + half_slabs) * slab_bytes + (size_t)w * 16);
-            const __nv_bfloat16 *tp = tab + (long long)(pos0 + r) * D + c * 64 + q * 8;
-            const uint4 tc = tcw_ldg_here(tp), ts = tcw_ldg_here(tp + (D >> 1));
-            uint4 lo = *plo, hi = *phi;
-            tcw_rotate(lo.x, hi.x, tc.x, ts.x);
-            tcw_rotate(lo.y, hi.y, tc.y, ts.y);
-            tcw_rotate(lo.z, hi.z, tc.z, ts.z);
-            tcw_rotate(lo.w, hi.w, tc.w, ts.w);
-            *plo = lo;
-            *phi = hi;
+        const int half_slabs = nch >> 1, total = half_slabs * per_slab;
+        for (int o0 = tid; o0 < total; o0 += 128 * U) {
+            uint4 tc[U], ts[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int o = o0 + 128 * u;
+                if (o < total) {
+                    const int c = o / per_slab, w = o - c * per_slab, r = w >> 3, q = (w & 7) ^ (r & 7);
+                    const __nv_bfloat16 *tp = tab + (long long)(pos0 + r) * D + c * 64 + q * 8;
+                    tc[u] = tcw_ldg_here(tp);
+                    ts[u] = tcw_ldg_here(tp + (D >> 1));
+                }
+            }
+            if (!waited) { if (!landed()) return false; waited = true; }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int o = o0 + 128 * u;
+                if (o < total) {
+                    const int c = o / per_slab, w = o - c * per_slab;
+                    uint4 *plo = reinterpret_cast<uint4 *>(tile + (size_t)c * slab_bytes + (size_t)w * 16);
+                    uint4 *phi = reinterpret_cast<uint4 *>(tile + (size_t)(c + half_slabs) * slab_bytes + (size_t)w * 16);
+                    uint4 lo = *plo, hi = *phi;
+                    tcw_rotate(lo.x, hi.x, tc[u].x, ts[u].x);
+                    tcw_rotate(lo.y, hi.y, tc[u].y, ts[u].y);
+                    tcw_rotate(lo.z, hi.z, tc[u].z, ts[u].z);
+                    tcw_rotate(lo.w, hi.w, tc[u].w, ts[u].w);
+                    *plo = lo;
+                    *phi = hi;
+                }
+            }
         }
     } else {
-        for (int o = tid; o < nch * per_slab; o += 128) {
-            const int c = o / per_slab, w = o - c * per_slab, r = w >> 3, q = (w & 7) ^ (r & 7);
-            uint4 *px = reinterpret_cast<uint4 *>(tile + (size_t)c * slab_bytes + (size_t)w * 16);
-            const uint4 t = tcw_ldg_here(tab + (long long)(pos0 + r) * D + c * 64 + q * 8);
-            uint4 v = *px;
-            v.x = tc_pe_pair(v.x, t.x, sinus);
-            v.y = tc_pe_pair(v.y, t.y, sinus);
-            v.z = tc_pe_pair(v.z, t.z, sinus);
-            v.w = tc_pe_pair(v.w, t.w, sinus);
-            *px = v;
+        const int total = nch * per_slab;
+        for (int o0 = tid; o0 < total; o0 += 128 * U) {
+            uint4 t[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int o = o0 + 128 * u;
+                if (o < total) {
+                    const int c = o / per_slab, w = o - c * per_slab, r = w >> 3, q = (w & 7) ^ (r & 7);
+                    t[u] = tcw_ldg_here(tab + (long long)(pos0 + r) * D + c * 64 + q * 8);
+                }
+            }
+            if (!waited) { if (!landed()) return false; waited = true; }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int o = o0 + 128 * u;
+                if (o < total) {
+                    const int c = o / per_slab, w = o - c * per_slab;
+                    uint4 *px = reinterpret_cast<uint4 *>(tile + (size_t)c * slab_bytes + (size_t)w * 16);
+                    uint4 v = *px;
+                    v.x = tc_pe_pair(v.x, t[u].x, sinus);
+                    v.y = tc_pe_pair(v.y, t[u].y, sinus);
+                    v.z = tc_pe_pair(v.z, t[u].z, sinus);
+                    v.w = tc_pe_pair(v.w, t[u].w, sinus);
+                    *px = v;
+                }
+            }
         }
     }
+    if (!waited) return landed();   // (an empty tile)
+    return true;
 }
 
 template <int NCH>   // head_d / 64
@@ -325,8 +366,8 @@ dec_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int tid = threadIdx.x - 6 * 32;
         do {
             if (p.rotate_q) {
-                DC_FAIL_AT(10, !mbar_wait(&bars.q_full, 0, lim));
-                dec_encode_tile(q_smem, DC_MQ, DC_QSLAB, nch, D, 0, p.table_kind, p.sinus != 0, p.tab, tid);
+                DC_FAIL_AT(10, !dec_encode_tile(q_smem, DC_MQ, DC_QSLAB, nch, D, 0, p.table_kind, p.sinus != 0, p.tab, tid,
+                                                [&]() { return mbar_wait(&bars.q_full, 0, lim); }));
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.q_ready);
@@ -334,8 +375,8 @@ dec_split_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (p.rotate_k) {
                 for (int t = 0; t < n; ++t) {
                     const int st = t & 1;
-                    DC_FAIL_AT(11, !mbar_wait(&bars.k_full[st], (t >> 1) & 1, lim));
-                    dec_encode_tile(k_smem + (size_t)st * kv_stage, DC_NK, DC_KSLAB, nch, D, (c0 + t) * DC_NK, p.table_kind, p.sinus != 0, p.tab, tid);
+                    DC_FAIL_AT(11, !dec_encode_tile(k_smem + (size_t)st * kv_stage, DC_NK, DC_KSLAB, nch, D, (c0 + t) * DC_NK, p.table_kind, p.sinus != 0, p.tab, tid,
+                                                    [&]() { return mbar_wait(&bars.k_full[st], (t >> 1) & 1, lim); }));
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.k_ready[st]);
@@ -590,8 +631,8 @@ dec_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const int tid = threadIdx.x - 6 * 32;
         do {
             if (p.rotate_q) {
-                DC_FAIL_AT(10, !mbar_wait(&bars.q_full, 0, lim));
-                dec_encode_tile(q_smem, DC_MQ, DC_QSLAB, nch, D, 0, p.table_kind, p.sinus != 0, p.tab, tid);
+                DC_FAIL_AT(10, !dec_encode_tile(q_smem, DC_MQ, DC_QSLAB, nch, D, 0, p.table_kind, p.sinus != 0, p.tab, tid,
+                                                [&]() { return mbar_wait(&bars.q_full, 0, lim); }));
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars.q_ready);
@@ -599,8 +640,8 @@ dec_t_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
             if (p.rotate_k) {
                 for (int t = 0; t < n; ++t) {
                     const int st = t & 1;
-                    DC_FAIL_AT(11, !mbar_wait(&bars.k_full[st], (t >> 1) & 1, lim));
-                    dec_encode_tile(k_smem + (size_t)st * kv_stage, DC_NK, DC_KSLAB, nch, D, (c0 + t) * DC_NK, p.table_kind, p.sinus != 0, p.tab, tid);
+                    DC_FAIL_AT(11, !dec_encode_tile(k_smem + (size_t)st * kv_stage, DC_NK, DC_KSLAB, nch, D, (c0 + t) * DC_NK, p.table_kind, p.sinus != 0, p.tab, tid,
+                                                    [&]() { return mbar_wait(&bars.k_full[st], (t >> 1) & 1, lim); }));
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.k_ready[st]);
