@@ -194,7 +194,7 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
             int s = 0;             // ring stage and the parity of its use
             uint32_t ph = 0;
             uint32_t sc = 0;       // key tiles done so far: phase of the hand-offs with the softmax warps
-            int ui = 0;
+            int ui = 0, lu = 0;    // units; units in which this query tile has rows (phase of o_empty)
             bool ok = true;
             TC_PROF_DECL;
             auto qk = [&](bool last) {   // S_t = Q_t K^T with the K tile at the ring position; then this issuer is done with the tile
@@ -218,6 +218,18 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                 ok = mbar_wait(&bars.q_full, (uint32_t)(ui & 1), lim);
                 if (!ok) break;
                 tc_fence_after();
+                if (((int)(unit % p.nqp) * 2 + t) * FA_BM >= p.Lq) {
+                    // the query tile lies beyond the sequence (an odd number of query tiles): nothing to compute, but the
+                    // ring and the Q buffer are handed back in step with the other issuer - one arrival per landed tile
+                    mbar_arrive(&bars.q_empty);
+                    for (int i = 0; i < 2 * nkt && ok; ++i) {
+                        ok = mbar_wait(&bars.kv_full[s], ph, lim);
+                        if (!ok) break;
+                        mbar_arrive(&bars.kv_empty[s]);
+                        if (++s == nst) { s = 0; ph ^= 1u; }
+                    }
+                    continue;
+                }
                 qk(nkt == 1);   // (S_t is free: the wait for p_full of the previous unit's last tile came after its s_read)
                 for (int j = 0; j < nkt && ok; ++j, ++sc) {
                     if (j + 1 < nkt) {
@@ -230,7 +242,7 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                         if (!ok) break;
                     }
                     ok = mbar_wait(&bars.kv_full[s], ph, lim);   // V_j
-                    if (ok && j == 0) ok = mbar_wait(&bars.o_empty[t], (uint32_t)(ui & 1) ^ 1u, lim);   // the epilogue of the previous unit has read O_t
+                    if (ok && j == 0) ok = mbar_wait(&bars.o_empty[t], (uint32_t)(lu & 1) ^ 1u, lim);   // the epilogue of the previous unit has read O_t
                     TC_PROF(3);
                     const uint32_t va = smem_u32(ring + (size_t)s * tile_bytes);
 #pragma unroll
@@ -250,6 +262,7 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
                     umma_commit(&bars.kv_empty[s]);
                     if (++s == nst) { s = 0; ph ^= 1u; }
                 }
+                ++lu;
             }
             if (!ok) { report_kernel_error(p.err, p.err_sys, (unsigned)KERR_MBAR_TIMEOUT | (1u << 9)); failed = true; }
             TC_PROF_FLUSH(8 * t, t == 0);
@@ -271,6 +284,7 @@ fa_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         TC_PROF_DECL;
         for (long long unit = blockIdx.x; unit < p.n_units && !failed; unit += gridDim.x) {
             const int bh = (int)(unit / p.nqp), qp = (int)(unit % p.nqp);
+            if ((qp * 2 + t) * FA_BM >= p.Lq) continue;   // this query tile lies beyond the sequence: its issuer skips it too
             for (int j = 0; j < nkt; ++j, ++sc) {
                 TC_PROF(6);
                 FA_FAIL_AT(2, !mbar_wait(&bars.s_full[t], (uint32_t)(sc & 1), lim));

@@ -17,6 +17,8 @@ SHAPES = [
     (2, 3, 512, 1024, 128),     # several units per head, eight key tiles
     (1, 150, 256, 256, 64),     # more units than SMs: CTAs take several
     (1, 2, 384, 640, 128),      # an odd number of query tiles: the second tile of the last unit is empty
+    (1, 200, 384, 384, 128),    # ... with more units than SMs: a CTA meets empty and full second tiles in turn
+    (2, 160, 128, 256, 64),     # ... every unit with an empty second tile
     (2, 3, 200, 300, 128),      # ragged in both lengths
     (1, 2, 129, 257, 64),
     (1, 3, 700, 1000, 128),
