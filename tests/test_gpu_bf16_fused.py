@@ -1,6 +1,6 @@
 """GPU parity of the one-kernel tensor-core path for narrow heads (head_d 64, 128 or 256, bf16 / fp16,
-more than 64 queries): scores and probabilities stay in tensor memory, online softmax with a lazily rescaled
-accumulator.  Oracle: fp32 CPU attention on the 16-bit-rounded inputs; tolerance max-abs 2e-2 (bf16)."""
+more than 64 queries): scores and the output accumulator stay in tensor memory, online softmax with a lazily
+rescaled accumulator.  Oracle: fp32 CPU attention on the 16-bit-rounded inputs; tolerance max-abs 2e-2 (bf16)."""
 import numpy as np
 import pytest
 
