@@ -192,9 +192,10 @@ def narrow_sweep(pkg, torch, dev, pk):
 
 def bf16_sweep(pkg, torch, dev, pk, skip):
     """The other bf16 benchmark configurations (cfg 3: no encoding; cfg 4: rotate-half RoPE, head_d 1024) and the
-    decode regime, one short measurement each, so that a default run reports them all."""
+    decode regime (K rotated beforehand, and rotated in the load), one short measurement each, so that a default run
+    reports them all."""
     out = []
-    for cfg in ("cfg3", "cfg4", "decode"):
+    for cfg in ("cfg3", "cfg4", "decode", "decode_rope"):
         if cfg == skip:
             continue
         dt, pe_name, B, H, Lq, Lk, D, _, bound = CONFIGS[cfg]
