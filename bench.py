@@ -171,6 +171,18 @@ def time_steps(pkg, torch, sets, pe, steps, warmup, barrier=None, flags=0, kerne
     return e0.elapsed_time(e1) / steps
 
 
+SETTLE_S = 3.0   # idle time before each side measurement of a default run
+
+
+def settle(torch):
+    """The side measurements follow the long, power-capped steps of the main configuration; the board's power
+    controller averages over seconds, so a short configuration measured right after them runs at the clocks the
+    main one left behind (decode: 0.57 of the HBM peak against 0.72 on its own).  A few idle seconds put each side
+    measurement in the state a run of that configuration alone starts from; the rows carry `settle_s`."""
+    torch.cuda.synchronize()
+    time.sleep(SETTLE_S)
+
+
 def narrow_sweep(pkg, torch, dev, pk):
     """bf16 at the head widths most models use (64, 128, 256), where the scores stay on the SM in one kernel: the default
     path and, for comparison, the two-kernel path of the wide heads on the same inputs."""
@@ -178,13 +190,14 @@ def narrow_sweep(pkg, torch, dev, pk):
     for cfg in ("narrow256", "narrow128", "narrow64"):
         _, _, B, H, Lq, Lk, D, _, _ = CONFIGS[cfg]
         sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(2)]
+        settle(torch)
         t = time_steps(pkg, torch, sets, 0, 20, 5)
         path = pkg.last_path()
         t2 = time_steps(pkg, torch, sets, 0, 10, 3, flags=pkg.FLAG_TWO_KERNELS)
         fl = flops_of(cfg)
         out.append({"config": cfg, "shape": [B, H, Lq, Lk, D], "path": path, "ms": round(t, 4), "tflops": round(fl / t / 1e9, 1),
                     "frac_of_sustained_bf16_peak": round(fl / t / 1e9 / pk["bf16_tflops_sustained"], 4),
-                    "two_kernel_path_ms": round(t2, 4), "two_kernel_path_tflops": round(fl / t2 / 1e9, 1)})
+                    "two_kernel_path_ms": round(t2, 4), "two_kernel_path_tflops": round(fl / t2 / 1e9, 1), "settle_s": SETTLE_S})
         del sets
         torch.cuda.empty_cache()
     return out
@@ -200,8 +213,9 @@ def bf16_sweep(pkg, torch, dev, pk, skip):
             continue
         dt, pe_name, B, H, Lq, Lk, D, _, bound = CONFIGS[cfg]
         sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(2)]
+        settle(torch)
         t = time_steps(pkg, torch, sets, PE[pe_name], 20, 5)
-        row = {"config": cfg, "shape": [B, H, Lq, Lk, D], "pe": pe_name, "path": pkg.last_path(), "ms": round(t, 4)}
+        row = {"config": cfg, "shape": [B, H, Lq, Lk, D], "pe": pe_name, "path": pkg.last_path(), "ms": round(t, 4), "settle_s": SETTLE_S}
         if bound == "tensor":
             row["tflops"] = round(flops_of(cfg) / t / 1e9, 1)
             row["frac_of_sustained_bf16_peak"] = round(flops_of(cfg) / t / 1e9 / pk["bf16_tflops_sustained"], 4)
