@@ -299,6 +299,7 @@ def fp32_sweep(pkg, torch, dev, pk, with_cpu=True):
         nbytes = bytes_of(cfg)
         nsets = max(2, min(256, (512 << 20) // nbytes))
         sets = [make_inputs(pkg, torch, cfg, dev, 42 + i) for i in range(nsets)]
+        settle(torch)
         cold = min(time_steps(pkg, torch, sets, 0, nsets, nsets if r == 0 else 0) for r in range(3))
         warm = time_steps(pkg, torch, sets[:1], 0, 200, 20)
         serial = min(time_steps(pkg, torch, sets, 0, nsets, 0, flags=pkg.FLAG_NO_OVERLAP) for r in range(2))
@@ -318,7 +319,7 @@ def fp32_sweep(pkg, torch, dev, pk, with_cpu=True):
                "cold_frac_of_hbm_peak": round(nbytes / cold / 1e6 / pk["hbm_gbs"], 4),
                "hbm_floor_us": round(nbytes / pk["hbm_gbs"] / 1e3, 2),
                "frac_of_fp32_compute_roof": round(tfl / FFMA_ROOF_TFLOPS, 4), "fp32_compute_roof_tflops": round(FFMA_ROOF_TFLOPS, 1),
-               "rotation_sets": nsets}
+               "rotation_sets": nsets, "settle_s": SETTLE_S}
         if with_cpu:
             one = cpu_full(cfg, 1)
             fan = cpu_full(cfg, B * H)
