@@ -93,6 +93,7 @@ __device__ __forceinline__ void umma_16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 //   ... with a quarter / half of the exponentials as a cubic on the FMA pipe instead of ex2      1060 / 940
 //   ... with a P buffer of 64 keys only (second half held in registers) and a fourth K / V stage         960
 //   ... with ring stage and parity kept incrementally (a 64-bit division cost each wait ~400 clocks)    1150
+//   ... with a non-suspending look before every barrier wait, and one wait per key tile for the P buffer   1200 - 1230
 struct FaPairBars {
     uint64_t kv_full[FA_MAX_STAGES], kv_empty[FA_MAX_STAGES];   // kv_empty: one arrival per issuer
     uint64_t q_full, q_empty;                                   // q_empty: one arrival per issuer
